@@ -1,0 +1,153 @@
+/*
+ * b200nn - C ABI of the B200 (sm_100a) neural-network evaluation backend for lc0.
+ *
+ * This is the boundary an lc0 backend plug-in binds: everything above it (the
+ * `lczero::Network` / `NetworkComputation` classes registered with
+ * REGISTER_NETWORK, or a Python/ctypes harness) is host glue; everything below
+ * it is hand-written CUDA.  Plain pointers and sizes only; no C++ or torch types.
+ *
+ * Every function returns B200_OK (0) or an error code; `b200_last_error()`
+ * returns a thread-local description of the last failure.  Nothing here falls
+ * back to a CPU implementation: without a usable CUDA device the create call fails.
+ */
+#ifndef B200NN_H_
+#define B200NN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  B200_OK = 0,
+  B200_ERR_INVALID = 1,     /* bad argument, unknown key, inconsistent weight sizes */
+  B200_ERR_CUDA = 2,        /* a CUDA runtime/driver call failed */
+  B200_ERR_UNSUPPORTED = 3, /* network format the backend does not implement */
+  B200_ERR_NOMEM = 4,
+  B200_ERR_TIMEOUT = 5      /* a bounded device-side wait gave up (kernel status word) */
+};
+
+/* Arithmetic/storage type of activations and matrices on the device. */
+enum { B200_PREC_FP32 = 0, B200_PREC_FP16 = 1, B200_PREC_BF16 = 2 };
+
+#define B200_INPUT_PLANES 112  /* lczero::kInputPlanes, src/neural/network.h:38 */
+#define B200_POLICY_SIZE 1858  /* policy vector length, src/neural/backends/blas/network_blas.cc:130 */
+
+typedef struct b200_builder b200_builder;
+typedef struct b200_net b200_net;
+typedef struct b200_comp b200_comp;
+
+const char* b200_last_error(void);
+
+/* ---- Network description -------------------------------------------------------------
+ * Replaces the `WeightsFile` + `MultiHeadWeights` hand-over of the reference's backend
+ * constructors (src/neural/backends/blas/network_blas.cc:983-1072,
+ * src/neural/network_legacy.h:178-229): the host flattens the decoded weights into named
+ * fp32 tensors ("encoder.3.mha.q_w", "policy.ip2_pol_w", "residual.0.se.w1", ...; dense
+ * weights [out][in] row-major, conv weights [Cout][Cin][3][3], batch norm already folded)
+ * and integer attributes:
+ *   network, policy, value, moves_left, input_embedding, input_format, output_format
+ *       -- pblczero::NetworkFormat enum values (proto/net.proto:275-367)
+ *   default_activation, smolgen_activation, ffn_activation
+ *       -- resolved lczero::ActivationFunction values (src/neural/tables/activation_function.h)
+ *   headcount, pol_headcount
+ */
+int b200_builder_create(b200_builder** out);
+int b200_builder_set_int(b200_builder* b, const char* key, long long value);
+int b200_builder_add_tensor(b200_builder* b, const char* name, const float* data, size_t count);
+void b200_builder_destroy(b200_builder* b);
+
+/* ---- Network (lczero::Network, src/neural/network.h:116-126) ----------------------------
+ * b200_net_create uploads and re-lays-out the weights on device `gpu` and allocates
+ * `slots` evaluation workspaces of `max_batch` positions each (no allocation happens
+ * during evaluation).  Options mirror the reference CUDA backend's `gpu` / `max_batch`
+ * keys (src/neural/backends/cuda/network_cuda.cc:210-254). */
+typedef struct b200_net_options {
+  int gpu;        /* CUDA device ordinal */
+  int max_batch;  /* largest batch one computation may hold */
+  int precision;  /* B200_PREC_* */
+  int slots;      /* concurrent computations (>= 1) */
+  int mlh;        /* 0 disables the moves-left head like the reference's mlh=false */
+  int flags;      /* B200_FLAG_* */
+} b200_net_options;
+
+enum {
+  B200_FLAG_NO_TENSOR_CORES = 1 /* force the plain FMA matrix kernels in fp16/bf16 mode */
+};
+
+typedef struct b200_net_info {
+  int input_format, output_format, moves_left_format; /* NetworkCapabilities, network.h:85-113 */
+  int wdl;            /* 1: q = W - L and d = D; 0: q = tanh(value), d = 0 */
+  int has_mlh;        /* GetMVal returns 0 when 0 */
+  int attention_body; /* 1 for NETWORK_ATTENTIONBODY_* */
+  int embedding, encoder_layers, heads, dff, filters, residual_blocks;
+  int max_batch, precision, sm_count;
+  long long weight_bytes, workspace_bytes;
+  double flops_per_position;      /* all matrix products, 2 * MACs */
+  double gemm_flops_per_position; /* encoder QKV / out-projection / FFN products only */
+} b200_net_info;
+
+int b200_net_create(const b200_builder* b, const b200_net_options* opt, b200_net** out);
+int b200_net_get_info(const b200_net* net, b200_net_info* info);
+void b200_net_destroy(b200_net* net);
+
+/* ---- Computation (lczero::NetworkComputation, src/neural/network.h:56-71) -----------------
+ * create -> add_input x n -> compute -> read results -> destroy; the heavy buffers are
+ * pooled in the network like the reference does (network_cuda.cc:1066-1083). */
+int b200_comp_create(b200_net* net, b200_comp** out);                       /* NewComputation */
+int b200_comp_add_input(b200_comp* c, const uint64_t* masks, const float* values); /* AddInput: 112 + 112 */
+int b200_comp_add_inputs(b200_comp* c, const uint64_t* masks, const float* values, int n);
+int b200_comp_compute(b200_comp* c);                                        /* ComputeBlocking */
+int b200_comp_batch_size(const b200_comp* c);                               /* GetBatchSize */
+float b200_comp_q(const b200_comp* c, int sample);                          /* GetQVal */
+float b200_comp_d(const b200_comp* c, int sample);                          /* GetDVal */
+float b200_comp_m(const b200_comp* c, int sample);                          /* GetMVal */
+float b200_comp_p(const b200_comp* c, int sample, int move_id);             /* GetPVal: raw logit */
+const float* b200_comp_policy(const b200_comp* c, int sample);              /* 1858 raw logits */
+void b200_comp_destroy(b200_comp* c);
+
+/* ---- Whole-batch entry points ----------------------------------------------------------------
+ * b200_net_eval_host: one call = add n inputs, compute, copy results out.  Host pointers;
+ *   H2D and D2H copies are part of the call.  policy [n][1858], q/d/m [n]; any may be NULL.
+ * b200_net_eval_device: inputs and outputs already in device memory of the net's GPU
+ *   (masks [n][112] u64, values [n][112] f32, policy [n][1858] f32, qdm [n][3] f32 as q,d,m);
+ *   enqueues on the slot's stream and synchronises before returning.
+ * b200_net_enqueue_device / b200_net_sync: the same without the final synchronisation, so a
+ *   caller can time many evaluations with events on b200_net_stream(). */
+int b200_net_eval_host(b200_net* net, const uint64_t* masks, const float* values, int n,
+                       float* policy, float* q, float* d, float* m);
+int b200_net_eval_device(b200_net* net, const void* d_masks, const void* d_values, int n,
+                         void* d_policy, void* d_qdm);
+int b200_net_enqueue_device(b200_net* net, const void* d_masks, const void* d_values, int n,
+                            void* d_policy, void* d_qdm);
+int b200_net_sync(b200_net* net);
+void* b200_net_stream(b200_net* net); /* cudaStream_t of slot 0 */
+
+/* Number of kernels this library launched on behalf of `net` since creation. */
+long long b200_net_launch_count(const b200_net* net);
+/* Device status word written by kernels whose bounded waits gave up (0 = none). */
+int b200_net_device_status(b200_net* net);
+
+/* ---- Stand-alone operators (unit-test and profiling surface of the same kernels) --------------
+ * All pointers are device pointers on the current device; `stream` is a cudaStream_t or NULL.
+ * b200_op_expand_planes: 112 (mask,value) pairs per position -> dense [n][112][64] values of
+ *   `precision` type (BlasComputation::EncodePlanes, network_blas.cc:973-981).
+ * b200_op_gemm: C[M][N] = act(A[M][K] . W[N][K]^T + bias) in the given precision, using the
+ *   tcgen05 tensor-core kernel when use_tc != 0 (fp16/bf16 only) else the FMA kernel
+ *   (FullyConnectedLayer::Forward1D, fully_connected_layer.cc:50-106).
+ * b200_op_layer_norm: out = LN(alpha * x + skip) * gamma + beta over rows of width C
+ *   (LayerNorm2DWithSkipConnection, backends/blas/encoder.h:29-78). */
+int b200_op_expand_planes(const void* d_masks, const void* d_values, int n, void* d_out,
+                          int precision, void* stream);
+int b200_op_gemm(const void* A, const void* W, const float* bias, void* C, int M, int N, int K,
+                 int activation, int precision, int use_tc, void* stream);
+int b200_op_layer_norm(void* out, const void* x, const void* skip, const float* gamma,
+                       const float* beta, int rows, int C, float alpha, float eps, int precision,
+                       void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200NN_H_ */

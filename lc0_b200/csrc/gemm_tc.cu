@@ -1,0 +1,458 @@
+// Tensor-core GEMM for sm_100a: C[M][N] = epilogue(A[M][K] . W[N][K]^T), 16-bit inputs, fp32 accumulation.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor 2D loads (no multicast) of a 128x64 A tile and a
+//               BNx64 W tile per k-block into a ring of 128B-swizzled shared-memory stages
+//   warp 1      MMA issuer: tcgen05.mma.cta_group::1.kind::f16, 128xBNx16 per instruction, accumulating in
+//               tensor memory (TMEM); two accumulators so the epilogue of tile i overlaps the MMAs of i+1
+//   warps 2..5  epilogue: tcgen05.ld TMEM -> registers, scale + bias + activation (+ alpha * v + skip),
+//               convert and store
+// Synchronisation is by mbarriers (full/empty per stage, full/empty per accumulator).  Every wait is
+// bounded by wall-clock time; a wait that gives up raises a status word and all roles leave the kernel.
+//
+// It computes what the reference obtains from cuBLAS for every dense layer
+// (cublasXgemm call sites, src/neural/backends/cuda/layers.cc:1587-1605) fused with the bias/activation
+// kernels that follow them there (addBiasBatched / addVectors, backends/cuda/common_kernels.cu:47-309).
+#include <cuda.h>
+
+#include <atomic>
+#include <mutex>
+#include <unordered_map>
+
+#include "kernels.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 16-bit elements = one 128-byte swizzle row
+constexpr int kThreads = 192;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this or another role timed out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63) == 0) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = code;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with the 128-byte
+// swizzle (what a TMA box of 64 16-bit elements x R rows with CU_TENSOR_MAP_SWIZZLE_128B produces):
+// start address >> 4 in bits [0,14), stride between 8-row groups (1024 B) >> 4 in bits [32,46),
+// descriptor version 1 in bits [46,48), layout type 2 (SWIZZLE_128B) in bits [61,64).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+template <typename T> struct FmtCode;
+template <> struct FmtCode<__half> { static constexpr uint32_t v = 0; };
+template <> struct FmtCode<__nv_bfloat16> { static constexpr uint32_t v = 1; };
+
+// Instruction descriptor of tcgen05.mma.kind::f16: D format fp32 (bits 4-5 = 1), A/B format (bits 7-9,
+// 10-12: 0 = f16, 1 = bf16), both operands K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+template <typename T, int BN>
+__device__ __forceinline__ constexpr uint32_t make_idesc() {
+  return (1u << 4) | (FmtCode<T>::v << 7) | (FmtCode<T>::v << 10) | ((uint32_t)(BN >> 3) << 17) |
+         ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int BN> struct TileCfg {
+  static constexpr int kStageBytes = (BM + BN) * BK * 2;
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct TcParams {
+  const float* bias;
+  void* C;
+  long long ldc;
+  const void* skip;
+  long long ldskip;
+  int M, N, K;
+  int act;
+  float scale, alpha;
+  int out_f32;
+  int* status;
+};
+
+template <typename T, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+               const TcParams p) {
+  using Cfg = TileCfg<BN>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bar_mem = smem + S * Cfg::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_mem);       // [S]
+  uint64_t* empty_bar = full_bar + S;                               // [S]
+  uint64_t* tfull_bar = empty_bar + S;                              // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;                             // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
+  const int tiles = m_tiles * n_tiles;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(smem_u32(&full_bar[i]), 1);
+      mbar_init(smem_u32(&empty_bar[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&tfull_bar[i]), 1);
+      mbar_init(smem_u32(&tempty_bar[i]), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)Cfg::kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        const int m0 = (t / n_tiles) * BM, n0 = (t % n_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, 1)) { ok = false; break; }
+          const uint32_t fb = smem_u32(&full_bar[s]);
+          mbar_expect_tx(fb, Cfg::kStageBytes);
+          const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
+          tma_load_2d(sa, &tmap_a, kb * BK, m0, fb);
+          tma_load_2d(sa + BM * BK * 2, &tmap_w, kb * BK, n0, fb);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc<T, BN>();
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++tile_it) {
+        const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
+        if (!mbar_wait(smem_u32(&tempty_bar[acc]), aph ^ 1, abort_flag, 2)) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, 3)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
+          const uint64_t adesc = make_smem_desc(sa);
+          const uint64_t bdesc = make_smem_desc(sa + BM * BK * 2);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // advancing 16 elements (32 bytes) along K inside the swizzle row = +2 in the address field
+            tcgen05_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(smem_u32(&empty_bar[s]));  // frees the stage once the MMAs have read it
+        }
+        if (ok) tcgen05_commit(smem_u32(&tfull_bar[acc]));
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
+    const T* skip = reinterpret_cast<const T*>(p.skip);
+    uint32_t tile_it = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
+      const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
+      const int m0 = (t / n_tiles) * BM, n0 = (t % n_tiles) * BN;
+      if (!mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4)) break;
+      tcgen05_fence_after();
+      const int m = m0 + quarter * 32 + lane;
+      const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(trow + c0, r);
+        tmem_ld_wait();
+        const int nb = n0 + c0;
+        if (m < p.M && nb < p.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = nb + j;
+            float x = __uint_as_float(r[j]) * p.scale;
+            if (p.bias && n < p.N) x += __ldg(p.bias + n);
+            v[j] = activate<true>(x, p.act);
+          }
+          if (skip) {
+            const T* srow = skip + (long long)m * p.ldskip + nb;
+            if (nb + 32 <= p.N && (p.ldskip & 7) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                const uint4 u = *reinterpret_cast<const uint4*>(srow + j);
+                const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[j + i] = p.alpha * v[j + i] + to_f(e[i]);
+              }
+            } else {
+              for (int j = 0; j < 32 && nb + j < p.N; ++j) v[j] = p.alpha * v[j] + to_f(srow[j]);
+            }
+          }
+          if (p.out_f32) {
+            float* crow = reinterpret_cast<float*>(p.C) + (long long)m * p.ldc + nb;
+            if (nb + 32 <= p.N && (p.ldc & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(crow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+              for (int j = 0; j < 32 && nb + j < p.N; ++j) crow[j] = v[j];
+            }
+          } else {
+            T* crow = reinterpret_cast<T*>(p.C) + (long long)m * p.ldc + nb;
+            if (nb + 32 <= p.N && (p.ldc & 7) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                __align__(16) T o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = from_f<T>(v[j + i]);
+                *reinterpret_cast<uint4*>(crow + j) = *reinterpret_cast<const uint4*>(o);
+              }
+            } else {
+              for (int j = 0; j < 32 && nb + j < p.N; ++j) crow[j] = from_f<T>(v[j]);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+    }
+  }
+
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // Give copies that may still be in flight time to land before the CTA's shared memory is released.
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, 100 + *abort_flag);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)Cfg::kTmemCols)
+                 : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::mutex g_mutex;
+
+struct MapKey {
+  const void* ptr; long long ld; int rows, cols, box_rows, prec;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && ld == o.ld && rows == o.rows && cols == o.cols && box_rows == o.box_rows && prec == o.prec;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.ptr);
+    h = h * 1000003u ^ std::hash<long long>()(k.ld);
+    h = h * 1000003u ^ (size_t)k.rows;
+    h = h * 1000003u ^ (size_t)k.cols;
+    h = h * 1000003u ^ (size_t)(k.box_rows * 4 + k.prec);
+    return h;
+  }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+// 2D map over a row-major [rows][cols] 16-bit matrix with leading dimension ld; box = 64 columns x box_rows.
+cudaError_t get_map(const void* ptr, long long ld, int rows, int cols, int box_rows, int prec, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_encode) return cudaErrorNotReady;
+  MapKey key{ptr, ld, rows, cols, box_rows, prec};
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return cudaSuccess;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = g_encode(&m, prec == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                        const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
+    return cudaErrorInvalidValue;
+  }
+  if (g_maps.size() > 4096) g_maps.clear();
+  g_maps.emplace(key, m);
+  *out = m;
+  return cudaSuccess;
+}
+
+template <typename T, int BN>
+cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream_t s) {
+  using Cfg = TileCfg<BN>;
+  // The opt-in to large dynamic shared memory is per device.
+  static std::atomic<unsigned long long> attr_mask{0};
+  int dev = 0;
+  cudaError_t de = cudaGetDevice(&dev);
+  if (de != cudaSuccess) return de;
+  if (!(attr_mask.load() >> (dev & 63) & 1ull)) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_mask.fetch_or(1ull << (dev & 63));
+  }
+  CUtensorMap ma, mw;
+  const int prec = TypeTag<T>::prec;
+  cudaError_t e = get_map(g.A, g.lda, g.M, g.K, BM, prec, &ma);
+  if (e != cudaSuccess) return e;
+  e = get_map(g.W, g.ldw, g.N, g.K, BN, prec, &mw);
+  if (e != cudaSuccess) return e;
+  TcParams p;
+  p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.skip = g.skip; p.ldskip = g.ldskip;
+  p.M = g.M; p.N = g.N; p.K = g.K; p.act = g.act; p.scale = g.scale; p.alpha = g.alpha;
+  p.out_f32 = g.out_f32 ? 1 : 0; p.status = status;
+  const int tiles = ceil_div(g.M, BM) * ceil_div(g.N, BN);
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  gemm_tc_kernel<T, BN><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t gemm_tc_init() {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_encode) return cudaSuccess;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess) return e;
+  if (qres != cudaDriverEntryPointSuccess || !fn) return cudaErrorNotSupported;
+  g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  return cudaSuccess;
+}
+
+bool gemm_tc_supported(const GemmParams& p) {
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  return p.batch == 1 && p.M >= 1 && p.N >= 8 && p.K >= 8 && (p.K % 8) == 0 && (p.lda % 8) == 0 &&
+         (p.ldw % 8) == 0 && al16(p.A) && al16(p.W);
+}
+
+template <typename T>
+cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaStream_t s) {
+  if (p.M <= 0 || p.N <= 0) return cudaSuccess;
+  if (!gemm_tc_supported(p)) return cudaErrorInvalidValue;
+  // Wide tiles amortise the A-tile loads; narrow problems take the smallest tile that covers N.
+  if (p.N > 128) return launch_bn<T, 256>(p, status, sm_count, s);
+  if (p.N > 64) return launch_bn<T, 128>(p, status, sm_count, s);
+  return launch_bn<T, 64>(p, status, sm_count, s);
+}
+
+template cudaError_t launch_gemm_tc<__half>(const GemmParams&, int*, int, cudaStream_t);
+template cudaError_t launch_gemm_tc<__nv_bfloat16>(const GemmParams&, int*, int, cudaStream_t);
+
+}  // namespace b200

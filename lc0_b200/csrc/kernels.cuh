@@ -1,0 +1,89 @@
+// Launchers of the hand-written kernels (one explicit instantiation per storage type).
+#pragma once
+#include "common.cuh"
+
+namespace b200 {
+
+struct GemmParams {
+  // C[b][M][N] = epilogue(scale * A[b][M][K] . W[b][N][K]^T)
+  // epilogue(v): v += bias[n]; v = act(v); if (skip) v = alpha * v + skip[m][n]
+  const void* A = nullptr; long long lda = 0, strideA = 0;
+  const void* W = nullptr; long long ldw = 0, strideW = 0;
+  const float* bias = nullptr;
+  void* C = nullptr; long long ldc = 0, strideC = 0;
+  const void* skip = nullptr; long long ldskip = 0;
+  int M = 0, N = 0, K = 0, batch = 1;
+  int act = ACT_NONE;
+  float scale = 1.0f, alpha = 1.0f;
+  bool out_f32 = false;  // C holds float even when the storage type is 16-bit
+};
+
+template <typename T> cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t s);
+// tcgen05 / TMEM / TMA kernel (gemm_tc.cu); T is __half or __nv_bfloat16, batch must be 1.
+// `status` is a device int the kernel sets non-zero when a bounded wait gives up.
+template <typename T> cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaStream_t s);
+bool gemm_tc_supported(const GemmParams& p);
+cudaError_t gemm_tc_init();  // resolves the driver entry point used to encode TMA descriptors
+
+template <typename T>
+cudaError_t launch_expand_planes(const uint64_t* masks, const float* values, int n, T* out, cudaStream_t s);
+// tokens[n*64][cin]: columns 0..111 expanded planes (NHWC), columns 112.. positional encoding taken
+// from pe_static [64][pe_ch] (fp32 table) or pe_dense [n][64][pe_ch] (T), zero padded to cin.
+template <typename T>
+cudaError_t launch_expand_tokens(const uint64_t* masks, const float* values, int n, const float* pe_static,
+                                 const T* pe_dense, int pe_ch, int cin, T* out, cudaStream_t s);
+// pre[n][64*12]: first 12 planes, square-major (input of the PE_DENSE preprocessing layer).
+template <typename T>
+cudaError_t launch_expand_pre12(const uint64_t* masks, const float* values, int n, T* out, cudaStream_t s);
+
+// out = LN(alpha * x + skip) * gamma + beta, then optional gating out * mult[r%64][c] + add[r%64][c].
+template <typename T>
+cudaError_t launch_layer_norm(T* out, const T* x, const T* skip, const float* gamma, const float* beta,
+                              const float* gate_mult, const float* gate_add, int rows, int C, float alpha,
+                              float eps, cudaStream_t s);
+template <typename T>
+cudaError_t launch_gate(T* x, const float* gate_mult, const float* gate_add, int rows, int C, cudaStream_t s);
+
+// 64-token multi-head attention: per (sample, head) softmax(scale * Q K^T + bias) V.
+// q/k/v point into one row-major activation with leading dimension ld; head h uses columns h*d...
+// bias: [n][heads][64][64] or nullptr.
+template <typename T>
+cudaError_t launch_attention(const T* q, const T* k, const T* v, long long ld, const T* bias, T* out,
+                             long long ldo, int n, int heads, int depth, float scale, cudaStream_t s);
+
+// Attention policy: promotion logits + gather to 1858 (network_blas.cc:873-914).
+// logits: fp32 [n][64*64] (already scaled), kp: [n*64][dm] keys, w4: fp32 [4][dm].
+template <typename T>
+cudaError_t launch_policy_attn_gather(const float* logits, const T* kp, const float* w4, int dm,
+                                      const short* src_slot, int n, float* policy, cudaStream_t s);
+// Generic gather for conv policy: policy[n][j] = raw[n][src[j]] (raw row stride ld), T -> fp32.
+template <typename T>
+cudaError_t launch_policy_gather(const T* raw, long long ld, const short* src_slot, int n, float* policy,
+                                 cudaStream_t s);
+template <typename T>
+cudaError_t launch_copy_to_f32(const T* src, long long ld, int rows, int cols, float* dst, cudaStream_t s);
+
+// Final tiny layers of the value / moves-left heads, one warp per sample:
+// mode 0: 3 logits -> softmax -> (q = w - l, d); mode 1: 1 output -> tanh -> q, d = 0;
+// mode 2: 1 output -> relu -> m.  h: [n][k]; w: fp32 [outs][k]; b: fp32 [outs]; qdm: [n][3].
+template <typename T>
+cudaError_t launch_head_final(const T* h, int k, const float* w, const float* b, int mode, int n,
+                              float* qdm, cudaStream_t s);
+
+// ---- residual tower (NHWC activations [n*64][C]) ----
+// 3x3 same-padded convolution as an implicit GEMM; w: [9][Cout][Cin] (tap-major).
+template <typename T>
+cudaError_t launch_conv3x3(const T* x, int cin, const T* w, const float* bias, T* y, int cout, int n,
+                           int act, cudaStream_t s);
+// Squeeze-excitation + skip + activation (se_unit.cc:31-91) on NHWC: y = act(sig(z0)*x + skip + z1 + sig(z0)*b).
+template <typename T>
+cudaError_t launch_se(const T* x, const float* conv_bias, const T* skip, const float* w1, const float* b1,
+                      const float* w2, const float* b2, T* y, int C, int se_k, int n, int act, cudaStream_t s);
+template <typename T>
+cudaError_t launch_bias_skip_act(const T* x, const float* bias, const T* skip, T* y, int C, int rows, int act,
+                                 cudaStream_t s);
+// NHWC [n][64][C] -> channel-major flatten [n][C*64] (what the reference's FC layers after a 1x1 conv see).
+template <typename T>
+cudaError_t launch_nhwc_to_nchw(const T* x, T* y, int C, int n, cudaStream_t s);
+
+}  // namespace b200

@@ -1,0 +1,1193 @@
+// Host side of the backend: network construction from named tensors, the evaluation schedule
+// (which kernel runs on which buffer), computation objects, and the C ABI of include/b200nn.h.
+//
+// The schedule restates BlasComputation::ComputeBlocking / ForwardEncoderLayer
+// (src/neural/backends/blas/network_blas.cc:271-971) as a sequence of CUDA kernel launches on one stream
+// per workspace slot.  Activations are token-major ([position*64 + square][channels]) for both attention
+// and residual bodies, so every dense layer and every 1x1 convolution is a plain row-major GEMM.
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <condition_variable>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/b200nn.h"
+#include "kernels.cuh"
+
+namespace b200 {
+
+static thread_local std::string g_last_error;
+void set_error(const std::string& msg) { g_last_error = msg; }
+int cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
+  set_error(std::string("CUDA error: ") + cudaGetErrorString(e) + " in " + what + " (" + file + ":" +
+            std::to_string(line) + ")");
+  return B200_ERR_CUDA;
+}
+
+struct Fail {
+  int code;
+  std::string msg;
+};
+#define CK(call)                                                                   \
+  do {                                                                             \
+    cudaError_t e__ = (call);                                                      \
+    if (e__ != cudaSuccess)                                                        \
+      throw Fail{B200_ERR_CUDA, std::string("CUDA error: ") + cudaGetErrorString(e__) + " in " #call + \
+                                    " (" __FILE__ ":" + std::to_string(__LINE__) + ")"};            \
+  } while (0)
+
+// NetworkFormat enum values (proto/net.proto:275-367).
+enum { NET_CLASSICAL_HF = 3, NET_SE_HF = 4, NET_ATTN_HF = 6, NET_ATTN_MHF = 7 };
+enum { POLICY_CLASSICAL = 1, POLICY_CONVOLUTION = 2, POLICY_ATTENTION = 3 };
+enum { VALUE_CLASSICAL = 1, VALUE_WDL = 2 };
+enum { EMB_NONE = 0, EMB_PE_MAP = 1, EMB_PE_DENSE = 2 };
+
+// ---- policy tables, generated from chess geometry (reference arrays: neural/encoder.cc:339,
+// neural/tables/attention_policy_map.h:24 and :386, neural/tables/policy_map.h:24) ----------------
+struct Tables {
+  std::vector<short> attn_src;   // [1858] slot in the 64*64 + 8*24 attention-policy vector
+  std::vector<short> conv_src;   // [1858] plane*64 + square of the convolutional policy output
+  std::vector<float> pos_enc;    // [64][64]
+};
+static bool reachable(int a, int b) {
+  if (a == b) return false;
+  const int dx = b % 8 - a % 8, dy = b / 8 - a / 8;
+  if (dx == 0 || dy == 0 || std::abs(dx) == std::abs(dy)) return true;
+  return (std::abs(dx) == 1 && std::abs(dy) == 2) || (std::abs(dx) == 2 && std::abs(dy) == 1);
+}
+static const Tables& tables() {
+  static const Tables t = [] {
+    Tables t;
+    // Policy index of a plain move from a to b, and of promotion (file f -> file g, piece i in q,r,b).
+    std::vector<int> plain(64 * 64, -1);
+    int idx = 0;
+    for (int a = 0; a < 64; ++a)
+      for (int b = 0; b < 64; ++b)
+        if (reachable(a, b)) plain[a * 64 + b] = idx++;
+    int promo[8][8][3];
+    for (int f = 0; f < 8; ++f)
+      for (int g = 0; g < 8; ++g)
+        for (int i = 0; i < 3; ++i) promo[f][g][i] = -1;
+    for (int f = 0; f < 8; ++f)
+      for (int g = f - 1; g <= f + 1; ++g)
+        if (g >= 0 && g < 8)
+          for (int i = 0; i < 3; ++i) promo[f][g][i] = idx++;
+    t.attn_src.assign(1858, 0);
+    for (int a = 0; a < 64; ++a)
+      for (int b = 0; b < 64; ++b)
+        if (plain[a * 64 + b] >= 0) t.attn_src[plain[a * 64 + b]] = short(a * 64 + b);
+    for (int f = 0; f < 8; ++f)
+      for (int g = 0; g < 8; ++g)
+        for (int i = 0; i < 3; ++i)
+          if (promo[f][g][i] >= 0) t.attn_src[promo[f][g][i]] = short(4096 + 24 * f + 3 * g + i);
+    // Convolutional policy planes: 8 directions x 7 distances, 8 knight jumps, 3 directions x (r, b, q).
+    static const int qd[8][2] = {{0, 1}, {1, 1}, {1, 0}, {1, -1}, {0, -1}, {-1, -1}, {-1, 0}, {-1, 1}};
+    static const int kn[8][2] = {{1, 2}, {2, 1}, {2, -1}, {1, -2}, {-1, -2}, {-2, -1}, {-2, 1}, {-1, 2}};
+    t.conv_src.assign(1858, 0);
+    for (int sq = 0; sq < 64; ++sq) {
+      const int x = sq % 8, y = sq / 8;
+      for (int d = 0; d < 8; ++d)
+        for (int dist = 1; dist < 8; ++dist) {
+          const int tx = x + qd[d][0] * dist, ty = y + qd[d][1] * dist;
+          if (tx >= 0 && tx < 8 && ty >= 0 && ty < 8)
+            t.conv_src[plain[sq * 64 + ty * 8 + tx]] = short((d * 7 + dist - 1) * 64 + sq);
+        }
+      for (int k = 0; k < 8; ++k) {
+        const int tx = x + kn[k][0], ty = y + kn[k][1];
+        if (tx >= 0 && tx < 8 && ty >= 0 && ty < 8)
+          t.conv_src[plain[sq * 64 + ty * 8 + tx]] = short((56 + k) * 64 + sq);
+      }
+      if (y == 6)
+        for (int d = 0; d < 3; ++d) {
+          const int tx = x + d - 1;
+          if (tx < 0 || tx >= 8) continue;
+          static const int piece_of_plane[3] = {1, 2, 0};  // planes are ordered r, b, q; indices q, r, b
+          for (int i = 0; i < 3; ++i)
+            t.conv_src[promo[x][tx][piece_of_plane[i]]] = short((64 + 3 * d + i) * 64 + sq);
+        }
+    }
+    t.pos_enc.assign(64 * 64, 0.f);
+    for (int a = 0; a < 64; ++a)
+      for (int b = 0; b < 64; ++b) t.pos_enc[a * 64 + b] = a == b ? -1.f : (reachable(a, b) ? 1.f : 0.f);
+    return t;
+  }();
+  return t;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+struct b200_builder {
+  std::map<std::string, std::vector<float>> tensors;
+  std::map<std::string, long long> ints;
+};
+
+namespace b200 {
+
+// ---- device memory bookkeeping --------------------------------------------------------------------
+struct DeviceAllocs {
+  std::vector<void*> ptrs;
+  long long bytes = 0;
+  void* alloc(size_t n) {
+    void* p = nullptr;
+    if (n == 0) n = 16;
+    CK(cudaMalloc(&p, n));
+    ptrs.push_back(p);
+    bytes += (long long)n;
+    return p;
+  }
+  void release() {
+    for (void* p : ptrs) cudaFree(p);
+    ptrs.clear();
+  }
+};
+
+template <typename T> static T host_cast(float v);
+template <> float host_cast<float>(float v) { return v; }
+template <> __half host_cast<__half>(float v) {
+  return __float2half_rn(std::min(std::max(v, -65504.f), 65504.f));
+}
+template <> __nv_bfloat16 host_cast<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T> struct Dense {
+  T* w = nullptr;        // [out][in]
+  float* b = nullptr;    // [out] or nullptr
+  int out = 0, in = 0;
+};
+
+template <typename T> struct EncoderW {
+  Dense<T> qkv, proj, ffn1, ffn2;
+  float *ln1g = nullptr, *ln1b = nullptr, *ln2g = nullptr, *ln2b = nullptr;
+  bool smolgen = false;
+  Dense<T> sg_compress, sg_d1, sg_d2;
+  float *sg_ln1g = nullptr, *sg_ln1b = nullptr, *sg_ln2g = nullptr, *sg_ln2b = nullptr;
+};
+
+template <typename T> struct ConvW {
+  T* w = nullptr;  // [9][Cout][Cin]
+  float* b = nullptr;
+  int cout = 0, cin = 0;
+};
+
+template <typename T> struct ResidualW {
+  ConvW<T> c1, c2;
+  bool se = false;
+  float *se_w1 = nullptr, *se_b1 = nullptr, *se_w2 = nullptr, *se_b2 = nullptr;
+  int se_k = 0;
+};
+
+struct NetBase {
+  virtual ~NetBase() {}
+  b200_net_info info{};
+  b200_net_options opt{};
+  std::atomic<long long> launches{0};
+  virtual int eval_device(int slot, const void* d_masks, const void* d_values, int n, void* d_policy,
+                          void* d_qdm, bool sync) = 0;
+  virtual int eval_staged(int slot, const uint64_t* masks, const float* values, int n) = 0;
+  virtual cudaStream_t stream(int slot) = 0;
+  virtual int device_status() = 0;
+  // pinned host staging of a slot
+  virtual uint64_t* h_masks(int slot) = 0;
+  virtual float* h_values(int slot) = 0;
+  virtual float* h_policy(int slot) = 0;
+  virtual float* h_qdm(int slot) = 0;
+  // slot pool
+  std::mutex mu;
+  std::condition_variable cv;
+  std::vector<int> free_slots;
+  int acquire() {
+    std::unique_lock<std::mutex> l(mu);
+    cv.wait(l, [&] { return !free_slots.empty(); });
+    int s = free_slots.back();
+    free_slots.pop_back();
+    return s;
+  }
+  void release(int s) {
+    {
+      std::lock_guard<std::mutex> l(mu);
+      free_slots.push_back(s);
+    }
+    cv.notify_one();
+  }
+};
+
+template <typename T>
+struct Net : NetBase {
+  DeviceAllocs walloc, salloc;
+  int sm_count = 148;
+  bool use_tc = false;
+  int* d_status = nullptr;
+
+  // format
+  int network = 0, policy_fmt = 0, value_fmt = 0, emb_fmt = 0;
+  int act_default = ACT_RELU, act_smolgen = ACT_SWISH, act_ffn = ACT_RELU_2;
+  bool attn_body = false, wdl = false, mlh = false;
+
+  // attention body
+  int E = 0, H = 0, cin = 0, pe_ch = 0, layers = 0, emb_dff = 0, max_dff = 0;
+  int sg_hc = 0, sg_hid = 0, sg_gen = 0;  // sg_gen = heads * per-head generator width
+  float alpha = 1.f, ln_eps = 1e-6f;
+  Dense<T> emb_pre, emb, emb_ffn1, emb_ffn2, smolgen_w;
+  float *emb_lng = nullptr, *emb_lnb = nullptr, *emb_ffn_lng = nullptr, *emb_ffn_lnb = nullptr;
+  float *gate_mult = nullptr, *gate_add = nullptr, *pos_enc = nullptr;
+  std::vector<EncoderW<T>> enc;
+
+  // residual body
+  int C = 0;
+  ConvW<T> conv_in;
+  std::vector<ResidualW<T>> res;
+
+  // heads
+  Dense<T> pol_emb, pol_q, pol_k, pol_fc;  // attention policy (emb, wq, wk) / classical FC
+  float* pol_w4 = nullptr;
+  int pol_dm = 0;
+  ConvW<T> pol_conv1, pol_conv2;
+  Dense<T> pol_c1x1;
+  short *d_attn_src = nullptr, *d_conv_src = nullptr;
+  int pol_planes = 0;
+  Dense<T> val_emb, val_fc1, mov_emb, mov_fc1;
+  float *val_w2 = nullptr, *val_b2 = nullptr, *mov_w2 = nullptr, *mov_b2 = nullptr;
+
+  struct Slot {
+    cudaStream_t stream = nullptr;
+    uint64_t *d_masks = nullptr, *h_masks = nullptr;
+    float *d_values = nullptr, *h_values = nullptr;
+    float *d_policy = nullptr, *h_policy = nullptr, *d_qdm = nullptr, *h_qdm = nullptr;
+    T *tokens = nullptr, *pre = nullptr, *pe = nullptr;
+    T *x = nullptr, *x1 = nullptr, *y = nullptr, *qkv = nullptr, *att = nullptr, *ffn = nullptr;
+    T *sg_c = nullptr, *sg_h1 = nullptr, *sg_h2 = nullptr, *sg_bias = nullptr;
+    T *pemb = nullptr, *pq = nullptr, *pk = nullptr, *praw = nullptr;
+    float* logits = nullptr;
+    T *vtok = nullptr, *vhid = nullptr, *mtok = nullptr, *mhid = nullptr;
+  };
+  std::vector<Slot> slots;
+
+  ~Net() override {
+    for (auto& s : slots) {
+      if (s.stream) cudaStreamDestroy(s.stream);
+      if (s.h_masks) cudaFreeHost(s.h_masks);
+      if (s.h_values) cudaFreeHost(s.h_values);
+      if (s.h_policy) cudaFreeHost(s.h_policy);
+      if (s.h_qdm) cudaFreeHost(s.h_qdm);
+    }
+    walloc.release();
+    salloc.release();
+  }
+
+  // ---- weight upload helpers ----
+  const b200_builder* bld = nullptr;
+  const std::vector<float>* find(const std::string& name) const {
+    auto it = bld->tensors.find(name);
+    return it == bld->tensors.end() ? nullptr : &it->second;
+  }
+  const std::vector<float>& need(const std::string& name, size_t count = 0) const {
+    const std::vector<float>* v = find(name);
+    if (!v || v->empty()) throw Fail{B200_ERR_INVALID, "weights: missing tensor '" + name + "'"};
+    if (count && v->size() != count)
+      throw Fail{B200_ERR_INVALID, "weights: tensor '" + name + "' has " + std::to_string(v->size()) +
+                                       " values, expected " + std::to_string(count)};
+    return *v;
+  }
+  size_t size_of(const std::string& name) const {
+    const std::vector<float>* v = find(name);
+    return v ? v->size() : 0;
+  }
+  float* up_f32(const std::vector<float>& v) {
+    float* d = (float*)walloc.alloc(v.size() * sizeof(float));
+    CK(cudaMemcpy(d, v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice));
+    return d;
+  }
+  float* up_f32(const std::string& name, size_t count) { return up_f32(need(name, count)); }
+  T* up_T(const std::vector<float>& v) {
+    std::vector<T> h(v.size());
+    for (size_t i = 0; i < v.size(); ++i) h[i] = host_cast<T>(v[i]);
+    T* d = (T*)walloc.alloc(h.size() * sizeof(T));
+    CK(cudaMemcpy(d, h.data(), h.size() * sizeof(T), cudaMemcpyHostToDevice));
+    return d;
+  }
+  Dense<T> dense(const std::string& wname, const std::string& bname, int out, int in) {
+    Dense<T> d;
+    d.out = out;
+    d.in = in;
+    d.w = up_T(need(wname, (size_t)out * in));
+    if (!bname.empty()) d.b = up_f32(bname, out);
+    return d;
+  }
+  // FC that consumes a channel-major flatten [c*64 + sq] in the file; our activations are square-major.
+  Dense<T> dense_chw(const std::string& wname, const std::string& bname, int out, int planes) {
+    const std::vector<float>& w = need(wname, (size_t)out * planes * 64);
+    std::vector<float> p(w.size());
+    for (int o = 0; o < out; ++o)
+      for (int c = 0; c < planes; ++c)
+        for (int sq = 0; sq < 64; ++sq)
+          p[(size_t)o * planes * 64 + sq * planes + c] = w[(size_t)o * planes * 64 + c * 64 + sq];
+    Dense<T> d;
+    d.out = out;
+    d.in = planes * 64;
+    d.w = up_T(p);
+    if (!bname.empty()) d.b = up_f32(bname, out);
+    return d;
+  }
+  ConvW<T> conv3(const std::string& prefix, int cout, int cin_) {
+    const std::vector<float>& w = need(prefix + ".weights", (size_t)cout * cin_ * 9);
+    std::vector<float> p(w.size());
+    for (int o = 0; o < cout; ++o)
+      for (int c = 0; c < cin_; ++c)
+        for (int t = 0; t < 9; ++t) p[((size_t)t * cout + o) * cin_ + c] = w[((size_t)o * cin_ + c) * 9 + t];
+    ConvW<T> cw;
+    cw.cout = cout;
+    cw.cin = cin_;
+    cw.w = up_T(p);
+    cw.b = up_f32(prefix + ".biases", cout);
+    return cw;
+  }
+  Dense<T> conv1(const std::string& prefix, int cout, int cin_) {
+    return dense(prefix + ".weights", prefix + ".biases", cout, cin_);
+  }
+  void add_flops(double rows_per_pos, const Dense<T>& d, bool encoder_gemm = false) {
+    const double f = 2.0 * rows_per_pos * d.out * d.in;
+    info.flops_per_position += f;
+    if (encoder_gemm) info.gemm_flops_per_position += f;
+  }
+
+  long long geti(const std::string& k, long long def = 0) const {
+    auto it = bld->ints.find(k);
+    return it == bld->ints.end() ? def : it->second;
+  }
+
+  EncoderW<T> load_encoder(const std::string& p, int emb, int heads) {
+    EncoderW<T> e;
+    const int dm = (int)size_of(p + ".mha.q_b");
+    if (dm <= 0 || dm % heads) throw Fail{B200_ERR_INVALID, "weights: bad attention width in " + p};
+    if (dm != emb) throw Fail{B200_ERR_UNSUPPORTED, "attention width different from the embedding is not supported"};
+    std::vector<float> w, b;
+    for (const char* n : {"q", "k", "v"}) {
+      const auto& ww = need(p + ".mha." + n + "_w", (size_t)dm * emb);
+      const auto& bb = need(p + ".mha." + n + "_b", dm);
+      w.insert(w.end(), ww.begin(), ww.end());
+      b.insert(b.end(), bb.begin(), bb.end());
+    }
+    e.qkv.out = 3 * dm;
+    e.qkv.in = emb;
+    e.qkv.w = up_T(w);
+    e.qkv.b = up_f32(b);
+    e.proj = dense(p + ".mha.dense_w", p + ".mha.dense_b", emb, dm);
+    const int dff = (int)size_of(p + ".ffn.dense1_b");
+    e.ffn1 = dense(p + ".ffn.dense1_w", p + ".ffn.dense1_b", dff, emb);
+    e.ffn2 = dense(p + ".ffn.dense2_w", p + ".ffn.dense2_b", emb, dff);
+    e.ln1g = up_f32(p + ".ln1_gammas", emb);
+    e.ln1b = up_f32(p + ".ln1_betas", emb);
+    e.ln2g = up_f32(p + ".ln2_gammas", emb);
+    e.ln2b = up_f32(p + ".ln2_betas", emb);
+    add_flops(64, e.qkv, true);
+    add_flops(64, e.proj, true);
+    add_flops(64, e.ffn1, true);
+    add_flops(64, e.ffn2, true);
+    info.flops_per_position += 2.0 * 2.0 * heads * 64 * 64 * (dm / heads);
+    if (size_of(p + ".mha.smolgen.compress")) {
+      e.smolgen = true;
+      const int hc = (int)size_of(p + ".mha.smolgen.compress") / emb;
+      const int hid = (int)size_of(p + ".mha.smolgen.dense1_b");
+      const int gen = (int)size_of(p + ".mha.smolgen.dense2_b");
+      e.sg_compress = dense(p + ".mha.smolgen.compress", "", hc, emb);
+      e.sg_d1 = dense(p + ".mha.smolgen.dense1_w", p + ".mha.smolgen.dense1_b", hid, 64 * hc);
+      e.sg_d2 = dense(p + ".mha.smolgen.dense2_w", p + ".mha.smolgen.dense2_b", gen, hid);
+      e.sg_ln1g = up_f32(p + ".mha.smolgen.ln1_gammas", hid);
+      e.sg_ln1b = up_f32(p + ".mha.smolgen.ln1_betas", hid);
+      e.sg_ln2g = up_f32(p + ".mha.smolgen.ln2_gammas", gen);
+      e.sg_ln2b = up_f32(p + ".mha.smolgen.ln2_betas", gen);
+      if (gen % heads) throw Fail{B200_ERR_INVALID, "weights: smolgen width not divisible by heads"};
+      if (sg_hc == 0) { sg_hc = hc; sg_hid = hid; sg_gen = gen; }
+      if (hc != sg_hc || hid != sg_hid || gen != sg_gen)
+        throw Fail{B200_ERR_UNSUPPORTED, "smolgen sizes differ between layers"};
+      add_flops(64, e.sg_compress);
+      add_flops(1, e.sg_d1);
+      add_flops(1, e.sg_d2);
+      info.flops_per_position += 2.0 * heads * (gen / heads) * 4096;
+    }
+    return e;
+  }
+
+  void build(const b200_builder* b, const b200_net_options& o) {
+    bld = b;
+    opt = o;
+    network = (int)geti("network");
+    policy_fmt = (int)geti("policy");
+    value_fmt = (int)geti("value");
+    emb_fmt = (int)geti("input_embedding");
+    act_default = (int)geti("default_activation", ACT_RELU);
+    act_smolgen = (int)geti("smolgen_activation", act_default);
+    act_ffn = (int)geti("ffn_activation", act_default);
+    if (network != NET_CLASSICAL_HF && network != NET_SE_HF && network != NET_ATTN_HF && network != NET_ATTN_MHF)
+      throw Fail{B200_ERR_UNSUPPORTED, "Network format " + std::to_string(network) + " is not supported by the b200 backend."};
+    if (policy_fmt < POLICY_CLASSICAL || policy_fmt > POLICY_ATTENTION)
+      throw Fail{B200_ERR_UNSUPPORTED, "Policy format " + std::to_string(policy_fmt) + " is not supported by the b200 backend."};
+    if (value_fmt != VALUE_CLASSICAL && value_fmt != VALUE_WDL)
+      throw Fail{B200_ERR_UNSUPPORTED, "Value format " + std::to_string(value_fmt) + " is not supported by the b200 backend."};
+    if (geti("moves_left") != 0 && geti("moves_left") != 1)
+      throw Fail{B200_ERR_UNSUPPORTED, "Moves left head format is not supported by the b200 backend."};
+    for (int a : {act_default, act_smolgen, act_ffn})
+      if (a < ACT_MISH || a > ACT_RELU_2) throw Fail{B200_ERR_UNSUPPORTED, "unsupported activation function"};
+    attn_body = network == NET_ATTN_HF || network == NET_ATTN_MHF;
+    wdl = value_fmt == VALUE_WDL;
+    mlh = geti("moves_left") == 1 && opt.mlh != 0;
+    for (auto& kv : b->tensors)
+      if (kv.first.find("pol_encoder") != std::string::npos)
+        throw Fail{B200_ERR_UNSUPPORTED, "policy-head encoder layers are not supported by the b200 backend"};
+
+    CK(cudaSetDevice(opt.gpu));
+    cudaDeviceProp prop;
+    CK(cudaGetDeviceProperties(&prop, opt.gpu));
+    sm_count = prop.multiProcessorCount;
+    use_tc = sizeof(T) == 2 && !(opt.flags & B200_FLAG_NO_TENSOR_CORES);
+    if (use_tc) {
+      if (prop.major != 10)
+        throw Fail{B200_ERR_UNSUPPORTED, "the tensor-core path needs an sm_100 device, found sm_" +
+                                             std::to_string(prop.major) + std::to_string(prop.minor)};
+      CK(gemm_tc_init());
+    }
+    d_status = (int*)walloc.alloc(sizeof(int));
+    CK(cudaMemset(d_status, 0, sizeof(int)));
+
+    const Tables& tb = tables();
+    d_attn_src = (short*)walloc.alloc(1858 * sizeof(short));
+    CK(cudaMemcpy(d_attn_src, tb.attn_src.data(), 1858 * sizeof(short), cudaMemcpyHostToDevice));
+
+    // ---- residual tower ----
+    int res_blocks = 0;
+    while (size_of("residual." + std::to_string(res_blocks) + ".conv1.weights")) ++res_blocks;
+    if (res_blocks > 0 || !attn_body) {
+      C = (int)size_of("input.biases");
+      if (C <= 0) throw Fail{B200_ERR_INVALID, "weights: missing input convolution"};
+      conv_in = conv3("input", C, 112);
+      info.flops_per_position += 2.0 * 64 * 9 * 112 * C;
+      for (int i = 0; i < res_blocks; ++i) {
+        const std::string p = "residual." + std::to_string(i);
+        ResidualW<T> r;
+        r.c1 = conv3(p + ".conv1", C, C);
+        r.c2 = conv3(p + ".conv2", C, C);
+        info.flops_per_position += 2.0 * 2.0 * 64 * 9 * C * C;
+        if (size_of(p + ".se.w1")) {
+          r.se = true;
+          r.se_k = (int)size_of(p + ".se.b1");
+          r.se_w1 = up_f32(p + ".se.w1", (size_t)r.se_k * C);
+          r.se_b1 = up_f32(p + ".se.b1", r.se_k);
+          r.se_w2 = up_f32(p + ".se.w2", (size_t)2 * C * r.se_k);
+          r.se_b2 = up_f32(p + ".se.b2", 2 * C);
+        }
+        res.push_back(r);
+      }
+    }
+    const int body_ch = attn_body ? (int)size_of("ip_emb_b") : C;
+
+    // ---- attention body ----
+    if (attn_body) {
+      E = (int)size_of("ip_emb_b");
+      H = (int)geti("headcount");
+      if (E <= 0 || H <= 0 || E % H) throw Fail{B200_ERR_INVALID, "weights: bad embedding size / head count"};
+      if (E % 8) throw Fail{B200_ERR_UNSUPPORTED, "embedding size must be a multiple of 8"};
+      int in_ch;
+      if (res_blocks == 0) {
+        if (emb_fmt == EMB_PE_DENSE) {
+          pe_ch = (int)size_of("ip_emb_preproc_b") / 64;
+          emb_pre = dense("ip_emb_preproc_w", "ip_emb_preproc_b", 64 * pe_ch, 64 * 12);
+          add_flops(1, emb_pre);
+        } else {
+          pe_ch = 64;
+          pos_enc = up_f32(tb.pos_enc);
+        }
+        in_ch = 112 + pe_ch;
+      } else {
+        in_ch = C;
+      }
+      cin = (in_ch + 7) / 8 * 8;
+      {  // embedding weight, columns zero padded to cin
+        const std::vector<float>& w = need("ip_emb_w", (size_t)E * in_ch);
+        std::vector<float> p((size_t)E * cin, 0.f);
+        for (int o = 0; o < E; ++o) std::copy(&w[(size_t)o * in_ch], &w[(size_t)o * in_ch] + in_ch, &p[(size_t)o * cin]);
+        emb.out = E;
+        emb.in = cin;
+        emb.w = up_T(p);
+        emb.b = up_f32("ip_emb_b", E);
+        add_flops(64, emb);
+      }
+      if (emb_fmt == EMB_PE_DENSE) {
+        emb_lng = up_f32("ip_emb_ln_gammas", E);
+        emb_lnb = up_f32("ip_emb_ln_betas", E);
+      }
+      if (size_of("ip_mult_gate") && size_of("ip_add_gate")) {
+        const auto& m = need("ip_mult_gate", (size_t)E * 64);
+        const auto& a = need("ip_add_gate", (size_t)E * 64);
+        std::vector<float> mt((size_t)64 * E), at((size_t)64 * E);
+        for (int c = 0; c < E; ++c)
+          for (int sq = 0; sq < 64; ++sq) {
+            mt[(size_t)sq * E + c] = m[(size_t)c * 64 + sq];
+            at[(size_t)sq * E + c] = a[(size_t)c * 64 + sq];
+          }
+        gate_mult = up_f32(mt);
+        gate_add = up_f32(at);
+      }
+      while (size_of("encoder." + std::to_string(layers) + ".mha.q_w")) ++layers;
+      alpha = (float)std::pow(2.0 * layers, -0.25);
+      ln_eps = emb_fmt == EMB_PE_DENSE ? 1e-3f : 1e-6f;
+      if (emb_fmt == EMB_PE_DENSE) {
+        emb_dff = (int)size_of("ip_emb_ffn.dense1_b");
+        emb_ffn1 = dense("ip_emb_ffn.dense1_w", "ip_emb_ffn.dense1_b", emb_dff, E);
+        emb_ffn2 = dense("ip_emb_ffn.dense2_w", "ip_emb_ffn.dense2_b", E, emb_dff);
+        emb_ffn_lng = up_f32("ip_emb_ffn_ln_gammas", E);
+        emb_ffn_lnb = up_f32("ip_emb_ffn_ln_betas", E);
+        add_flops(64, emb_ffn1);
+        add_flops(64, emb_ffn2);
+      }
+      max_dff = emb_dff;
+      for (int i = 0; i < layers; ++i) {
+        enc.push_back(load_encoder("encoder." + std::to_string(i), E, H));
+        max_dff = std::max(max_dff, enc.back().ffn1.out);
+      }
+      if (sg_gen) smolgen_w = dense("smolgen_w", "", 4096, sg_gen / H);
+    }
+
+    // ---- policy head ----
+    if (policy_fmt == POLICY_ATTENTION) {
+      const int pe = (int)size_of("policy.ip_pol_b");
+      pol_dm = (int)size_of("policy.ip2_pol_b");
+      pol_emb = dense("policy.ip_pol_w", "policy.ip_pol_b", pe, body_ch);
+      pol_q = dense("policy.ip2_pol_w", "policy.ip2_pol_b", pol_dm, pe);
+      pol_k = dense("policy.ip3_pol_w", "policy.ip3_pol_b", pol_dm, pe);
+      pol_w4 = up_f32("policy.ip4_pol_w", (size_t)4 * pol_dm);
+      add_flops(64, pol_emb);
+      add_flops(64, pol_q);
+      add_flops(64, pol_k);
+      info.flops_per_position += 2.0 * 64 * 64 * pol_dm;
+    } else if (policy_fmt == POLICY_CONVOLUTION) {
+      if (attn_body) throw Fail{B200_ERR_UNSUPPORTED, "convolutional policy with an attention body is not supported"};
+      pol_planes = (int)size_of("policy.policy.biases");
+      if (pol_planes < 73) throw Fail{B200_ERR_INVALID, "weights: convolutional policy needs at least 73 planes"};
+      pol_conv1 = conv3("policy.policy1", C, C);
+      pol_conv2 = conv3("policy.policy", pol_planes, C);
+      info.flops_per_position += 2.0 * 64 * 9 * C * (C + pol_planes);
+      std::vector<short> src(1858);
+      for (int j = 0; j < 1858; ++j) {
+        const int plane = tb.conv_src[j] / 64, sq = tb.conv_src[j] % 64;
+        src[j] = short(sq * pol_planes + plane);
+      }
+      d_conv_src = (short*)walloc.alloc(1858 * sizeof(short));
+      CK(cudaMemcpy(d_conv_src, src.data(), 1858 * sizeof(short), cudaMemcpyHostToDevice));
+    } else {
+      if (attn_body) throw Fail{B200_ERR_UNSUPPORTED, "classical policy with an attention body is not supported"};
+      pol_planes = (int)size_of("policy.policy.biases");
+      pol_c1x1 = conv1("policy.policy", pol_planes, C);
+      pol_fc = dense_chw("policy.ip_pol_w", "policy.ip_pol_b", 1858, pol_planes);
+      add_flops(64, pol_c1x1);
+      add_flops(1, pol_fc);
+    }
+
+    // ---- value head ----
+    {
+      const int vh = (int)size_of("value.ip1_val_b");
+      int vp;
+      if (attn_body) {
+        vp = (int)size_of("value.ip_val_b");
+        val_emb = dense("value.ip_val_w", "value.ip_val_b", vp, E);
+        val_fc1 = dense("value.ip1_val_w", "value.ip1_val_b", vh, vp * 64);
+      } else {
+        vp = (int)size_of("value.value.biases");
+        val_emb = conv1("value.value", vp, C);
+        val_fc1 = dense_chw("value.ip1_val_w", "value.ip1_val_b", vh, vp);
+      }
+      const int outs = wdl ? 3 : 1;
+      val_w2 = up_f32("value.ip2_val_w", (size_t)outs * vh);
+      val_b2 = up_f32("value.ip2_val_b", outs);
+      add_flops(64, val_emb);
+      add_flops(1, val_fc1);
+    }
+    // ---- moves-left head ----
+    if (mlh) {
+      const int mh = (int)size_of("ip1_mov_b");
+      int mp;
+      if (attn_body) {
+        mp = (int)size_of("ip_mov_b");
+        mov_emb = dense("ip_mov_w", "ip_mov_b", mp, E);
+        mov_fc1 = dense("ip1_mov_w", "ip1_mov_b", mh, mp * 64);
+      } else {
+        mp = (int)size_of("moves_left.biases");
+        mov_emb = conv1("moves_left", mp, C);
+        mov_fc1 = dense_chw("ip1_mov_w", "ip1_mov_b", mh, mp);
+      }
+      mov_w2 = up_f32("ip2_mov_w", mh);
+      mov_b2 = up_f32("ip2_mov_b", 1);
+      add_flops(64, mov_emb);
+      add_flops(1, mov_fc1);
+    }
+
+    alloc_slots();
+
+    info.input_format = (int)geti("input_format");
+    info.output_format = (int)geti("output_format");
+    info.moves_left_format = (int)geti("moves_left");
+    info.wdl = wdl;
+    info.has_mlh = mlh;
+    info.attention_body = attn_body;
+    info.embedding = E;
+    info.encoder_layers = layers;
+    info.heads = H;
+    info.dff = enc.empty() ? 0 : enc[0].ffn1.out;
+    info.filters = C;
+    info.residual_blocks = (int)res.size();
+    info.max_batch = opt.max_batch;
+    info.precision = opt.precision;
+    info.sm_count = sm_count;
+    info.weight_bytes = walloc.bytes;
+    info.workspace_bytes = salloc.bytes;
+    bld = nullptr;
+  }
+
+  void alloc_slots() {
+    const size_t nb = (size_t)opt.max_batch, R = nb * 64;
+    slots.resize(opt.slots);
+    auto A = [&](size_t elems) { return (T*)salloc.alloc(elems * sizeof(T)); };
+    for (int si = 0; si < opt.slots; ++si) {
+      Slot& s = slots[si];
+      CK(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+      s.d_masks = (uint64_t*)salloc.alloc(nb * 112 * 8);
+      s.d_values = (float*)salloc.alloc(nb * 112 * 4);
+      s.d_policy = (float*)salloc.alloc(nb * 1858 * 4);
+      s.d_qdm = (float*)salloc.alloc(nb * 3 * 4);
+      CK(cudaMallocHost(&s.h_masks, nb * 112 * 8));
+      CK(cudaMallocHost(&s.h_values, nb * 112 * 4));
+      CK(cudaMallocHost(&s.h_policy, nb * 1858 * 4));
+      CK(cudaMallocHost(&s.h_qdm, nb * 3 * 4));
+      const int body_ch = attn_body ? E : C;
+      if (!res.empty() || !attn_body) {
+        s.tokens = A(R * 112);
+        s.x = A(R * C);
+        s.x1 = A(R * C);
+        s.y = A(R * C);
+      }
+      if (attn_body) {
+        if (res.empty()) s.tokens = A(R * cin);
+        if (emb_fmt == EMB_PE_DENSE && res.empty()) {
+          s.pre = A(nb * 768);
+          s.pe = A(nb * 64 * pe_ch);
+        }
+        if (!s.x || E > C) {
+          s.x = A(R * E);
+          s.x1 = A(R * E);
+          s.y = A(R * E);
+        }
+        s.qkv = A(R * 3 * E);
+        s.att = A(R * E);
+        s.ffn = A(R * std::max(max_dff, 8));
+        if (sg_gen) {
+          s.sg_c = A(R * sg_hc);
+          s.sg_h1 = A(nb * sg_hid);
+          s.sg_h2 = A(nb * sg_gen);
+          s.sg_bias = A(nb * H * 4096);
+        }
+      }
+      if (policy_fmt == POLICY_ATTENTION) {
+        s.pemb = A(R * pol_emb.out);
+        s.pq = A(R * pol_dm);
+        s.pk = A(R * pol_dm);
+        s.logits = (float*)salloc.alloc(nb * 4096 * 4);
+      } else if (policy_fmt == POLICY_CONVOLUTION) {
+        s.praw = A(R * pol_planes);
+      } else {
+        s.praw = A(R * pol_planes);
+      }
+      (void)body_ch;
+      s.vtok = A(R * val_emb.out);
+      s.vhid = A(nb * val_fc1.out);
+      if (mlh) {
+        s.mtok = A(R * mov_emb.out);
+        s.mhid = A(nb * mov_fc1.out);
+      }
+      free_slots.push_back(si);
+    }
+  }
+
+  // ---- launch helpers ----
+  void gemm(cudaStream_t st, const T* A, long long lda, const Dense<T>& d, T* Cout, long long ldc, int M, int act,
+            const T* skip = nullptr, long long ldskip = 0, float alpha_ = 1.f, bool out_f32 = false,
+            void* cf32 = nullptr) {
+    GemmParams p;
+    p.A = A; p.lda = lda; p.W = d.w; p.ldw = d.in; p.bias = d.b;
+    p.C = out_f32 ? cf32 : (void*)Cout; p.ldc = ldc; p.M = M; p.N = d.out; p.K = d.in; p.act = act;
+    p.skip = skip; p.ldskip = ldskip; p.alpha = alpha_; p.out_f32 = out_f32;
+    run_gemm(st, p);
+  }
+  void run_gemm(cudaStream_t st, const GemmParams& p) {
+    launches++;
+    if constexpr (sizeof(T) == 2) {
+      if (use_tc && p.M >= 64 && gemm_tc_supported(p)) {
+        CK(launch_gemm_tc<T>(p, d_status, sm_count, st));
+        return;
+      }
+    }
+    CK(launch_gemm_simt<T>(p, st));
+  }
+  void ln(cudaStream_t st, T* out, const T* x, const T* skip, const float* g, const float* b, int rows, int Cc,
+          float a, float eps, const float* gm = nullptr, const float* ga = nullptr) {
+    launches++;
+    CK(launch_layer_norm<T>(out, x, skip, g, b, gm, ga, rows, Cc, a, eps, st));
+  }
+
+  void encoder_layer(Slot& s, const EncoderW<T>& e, int n, T*& x, T*& x1) {
+    cudaStream_t st = s.stream;
+    const int R = n * 64;
+    const int depth = E / H;
+    const T* bias = nullptr;
+    if (e.smolgen) {  // network_blas.cc:300-339
+      gemm(st, x, E, e.sg_compress, s.sg_c, sg_hc, R, ACT_NONE);
+      gemm(st, s.sg_c, 64 * sg_hc, e.sg_d1, s.sg_h1, sg_hid, n, act_smolgen);
+      ln(st, s.sg_h1, s.sg_h1, nullptr, e.sg_ln1g, e.sg_ln1b, n, sg_hid, 1.f, 1e-3f);
+      gemm(st, s.sg_h1, sg_hid, e.sg_d2, s.sg_h2, sg_gen, n, act_smolgen);
+      ln(st, s.sg_h2, s.sg_h2, nullptr, e.sg_ln2g, e.sg_ln2b, n, sg_gen, 1.f, 1e-3f);
+      gemm(st, s.sg_h2, sg_gen / H, smolgen_w, s.sg_bias, 4096, n * H, ACT_NONE);
+      bias = s.sg_bias;
+    }
+    gemm(st, x, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE);  // :341-350, :408-412
+    launches++;
+    CK(launch_attention<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
+                           1.0f / sqrtf((float)depth), st));  // :352-439
+    gemm(st, s.att, E, e.proj, s.y, E, R, ACT_NONE);           // :441-445
+    ln(st, x1, s.y, x, e.ln1g, e.ln1b, R, E, alpha, ln_eps);   // :447-452
+    gemm(st, x1, E, e.ffn1, s.ffn, e.ffn1.out, R, act_ffn);    // :454-458
+    gemm(st, s.ffn, e.ffn1.out, e.ffn2, s.y, E, R, ACT_NONE);  // :460-463
+    ln(st, x, s.y, x1, e.ln2g, e.ln2b, R, E, alpha, ln_eps);   // :465-470
+  }
+
+  void forward(Slot& s, const uint64_t* d_masks, const float* d_values, int n, float* d_policy, float* d_qdm) {
+    cudaStream_t st = s.stream;
+    const int R = n * 64;
+    T* flow = nullptr;  // output of the body, [R][body_ch]
+    int body_ch = 0;
+    CK(cudaMemsetAsync(d_qdm, 0, (size_t)n * 3 * sizeof(float), st));
+    if (!res.empty() || !attn_body) {  // network_blas.cc:564-601
+      launches++;
+      CK(launch_expand_tokens<T>(d_masks, d_values, n, nullptr, (const T*)nullptr, 0, 112, s.tokens, st));
+      launches++;
+      CK(launch_conv3x3<T>(s.tokens, 112, conv_in.w, conv_in.b, s.x, C, n, act_default, st));
+      T *cur = s.x, *tmp = s.x1, *tmp2 = s.y;
+      for (const auto& r : res) {
+        launches++;
+        CK(launch_conv3x3<T>(cur, C, r.c1.w, r.c1.b, tmp, C, n, act_default, st));
+        launches++;
+        CK(launch_conv3x3<T>(tmp, C, r.c2.w, nullptr, tmp2, C, n, ACT_NONE, st));
+        launches++;
+        if (r.se) {
+          CK(launch_se<T>(tmp2, r.c2.b, cur, r.se_w1, r.se_b1, r.se_w2, r.se_b2, tmp, C, r.se_k, n, act_default, st));
+        } else {
+          CK(launch_bias_skip_act<T>(tmp2, r.c2.b, cur, tmp, C, R, act_default, st));
+        }
+        std::swap(cur, tmp);
+      }
+      flow = cur;
+      body_ch = C;
+      if (attn_body) throw Fail{B200_ERR_UNSUPPORTED, "attention body on top of a residual tower is not supported"};
+    }
+    if (attn_body) {  // network_blas.cc:603-721
+      if (emb_fmt == EMB_PE_DENSE) {
+        launches++;
+        CK(launch_expand_pre12<T>(d_masks, d_values, n, s.pre, st));
+        gemm(st, s.pre, 768, emb_pre, s.pe, 64 * pe_ch, n, ACT_NONE);
+        launches++;
+        CK(launch_expand_tokens<T>(d_masks, d_values, n, nullptr, s.pe, pe_ch, cin, s.tokens, st));
+      } else {
+        launches++;
+        CK(launch_expand_tokens<T>(d_masks, d_values, n, pos_enc, (const T*)nullptr, pe_ch, cin, s.tokens, st));
+      }
+      T *x = s.x, *x1 = s.x1;
+      gemm(st, s.tokens, cin, emb, x, E, R, act_default);
+      if (emb_fmt == EMB_PE_DENSE) {
+        ln(st, x, x, nullptr, emb_lng, emb_lnb, R, E, 1.f, 1e-3f, gate_mult, gate_add);
+        gemm(st, x, E, emb_ffn1, s.ffn, emb_dff, R, act_ffn);
+        gemm(st, s.ffn, emb_dff, emb_ffn2, s.y, E, R, ACT_NONE);
+        ln(st, x1, s.y, x, emb_ffn_lng, emb_ffn_lnb, R, E, alpha, 1e-3f);
+        std::swap(x, x1);
+      } else if (gate_mult) {
+        launches++;
+        CK(launch_gate<T>(x, gate_mult, gate_add, R, E, st));
+      }
+      for (const auto& e : enc) encoder_layer(s, e, n, x, x1);
+      flow = x;
+      body_ch = E;
+    }
+
+    // ---- value head (network_blas.cc:725-772) ----
+    gemm(st, flow, body_ch, val_emb, s.vtok, val_emb.out, R, act_default);
+    gemm(st, s.vtok, 64 * val_emb.out, val_fc1, s.vhid, val_fc1.out, n, act_default);
+    launches++;
+    CK(launch_head_final<T>(s.vhid, val_fc1.out, val_w2, val_b2, wdl ? 0 : 1, n, d_qdm, st));
+    // ---- moves-left head (:775-803) ----
+    if (mlh) {
+      gemm(st, flow, body_ch, mov_emb, s.mtok, mov_emb.out, R, act_default);
+      gemm(st, s.mtok, 64 * mov_emb.out, mov_fc1, s.mhid, mov_fc1.out, n, act_default);
+      launches++;
+      CK(launch_head_final<T>(s.mhid, mov_fc1.out, mov_w2, mov_b2, 2, n, d_qdm, st));
+    }
+    // ---- policy head (:806-968) ----
+    if (policy_fmt == POLICY_ATTENTION) {
+      gemm(st, flow, body_ch, pol_emb, s.pemb, pol_emb.out, R, attn_body ? act_default : ACT_SELU);
+      gemm(st, s.pemb, pol_emb.out, pol_q, s.pq, pol_dm, R, ACT_NONE);
+      gemm(st, s.pemb, pol_emb.out, pol_k, s.pk, pol_dm, R, ACT_NONE);
+      GemmParams p;  // per-position Q.K^T, scaled
+      p.A = s.pq; p.lda = pol_dm; p.strideA = 64LL * pol_dm;
+      p.W = s.pk; p.ldw = pol_dm; p.strideW = 64LL * pol_dm;
+      p.C = s.logits; p.ldc = 64; p.strideC = 4096; p.out_f32 = true;
+      p.M = 64; p.N = 64; p.K = pol_dm; p.batch = n; p.scale = 1.0f / sqrtf((float)pol_dm);
+      launches++;
+      CK(launch_gemm_simt<T>(p, st));
+      launches++;
+      CK(launch_policy_attn_gather<T>(s.logits, s.pk, pol_w4, pol_dm, d_attn_src, n, d_policy, st));
+    } else if (policy_fmt == POLICY_CONVOLUTION) {
+      launches++;
+      T* t1 = s.y;  // free: the tower ping-pongs between x and x1
+      CK(launch_conv3x3<T>(flow, C, pol_conv1.w, pol_conv1.b, t1, C, n, act_default, st));
+      launches++;
+      CK(launch_conv3x3<T>(t1, C, pol_conv2.w, pol_conv2.b, s.praw, pol_planes, n, ACT_NONE, st));
+      launches++;
+      CK(launch_policy_gather<T>(s.praw, 64LL * pol_planes, d_conv_src, n, d_policy, st));
+    } else {
+      gemm(st, flow, C, pol_c1x1, s.praw, pol_planes, R, act_default);
+      gemm(st, s.praw, 64 * pol_planes, pol_fc, nullptr, 1858, n, ACT_NONE, nullptr, 0, 1.f, true, d_policy);
+    }
+  }
+
+  int eval_device(int slot, const void* d_masks, const void* d_values, int n, void* d_policy, void* d_qdm,
+                  bool sync) override {
+    Slot& s = slots[slot];
+    forward(s, (const uint64_t*)d_masks, (const float*)d_values, n, (float*)d_policy, (float*)d_qdm);
+    if (sync) CK(cudaStreamSynchronize(s.stream));
+    return B200_OK;
+  }
+  int eval_staged(int slot, const uint64_t* masks, const float* values, int n) override {
+    Slot& s = slots[slot];
+    if (masks != s.h_masks) memcpy(s.h_masks, masks, (size_t)n * 112 * 8);
+    if (values != s.h_values) memcpy(s.h_values, values, (size_t)n * 112 * 4);
+    CK(cudaMemcpyAsync(s.d_masks, s.h_masks, (size_t)n * 112 * 8, cudaMemcpyHostToDevice, s.stream));
+    CK(cudaMemcpyAsync(s.d_values, s.h_values, (size_t)n * 112 * 4, cudaMemcpyHostToDevice, s.stream));
+    forward(s, s.d_masks, s.d_values, n, s.d_policy, s.d_qdm);
+    CK(cudaMemcpyAsync(s.h_policy, s.d_policy, (size_t)n * 1858 * 4, cudaMemcpyDeviceToHost, s.stream));
+    CK(cudaMemcpyAsync(s.h_qdm, s.d_qdm, (size_t)n * 3 * 4, cudaMemcpyDeviceToHost, s.stream));
+    CK(cudaStreamSynchronize(s.stream));
+    return B200_OK;
+  }
+  cudaStream_t stream(int slot) override { return slots[slot].stream; }
+  int device_status() override {
+    int v = 0;
+    cudaMemcpy(&v, d_status, sizeof(int), cudaMemcpyDeviceToHost);
+    return v;
+  }
+  uint64_t* h_masks(int slot) override { return slots[slot].h_masks; }
+  float* h_values(int slot) override { return slots[slot].h_values; }
+  float* h_policy(int slot) override { return slots[slot].h_policy; }
+  float* h_qdm(int slot) override { return slots[slot].h_qdm; }
+};
+
+}  // namespace b200
+
+struct b200_net {
+  std::unique_ptr<NetBase> impl;
+};
+
+// A computation owns host copies of its inputs and, after compute, of its outputs; the device
+// workspace slot is held only while computing.
+struct b200_comp {
+  b200_net* net;
+  std::vector<uint64_t> masks;
+  std::vector<float> values;
+  std::vector<float> policy, qdm;
+  int n = 0;
+  bool computed = false;
+};
+
+template <typename F>
+static int guarded(F&& f) {
+  try {
+    return f();
+  } catch (const Fail& e) {
+    set_error(e.msg);
+    return e.code;
+  } catch (const std::bad_alloc&) {
+    set_error("out of host memory");
+    return B200_ERR_NOMEM;
+  } catch (const std::exception& e) {
+    set_error(e.what());
+    return B200_ERR_INVALID;
+  }
+}
+
+template <typename F32, typename F16, typename BF16>
+static int by_precision(int precision, F32&& f32, F16&& f16, BF16&& bf16) {
+  if (precision == B200_PREC_FP32) return f32();
+  if (precision == B200_PREC_FP16) return f16();
+  if (precision == B200_PREC_BF16) return bf16();
+  set_error("unknown precision");
+  return B200_ERR_INVALID;
+}
+
+extern "C" {
+
+const char* b200_last_error(void) { return g_last_error.c_str(); }
+
+int b200_builder_create(b200_builder** out) {
+  if (!out) return B200_ERR_INVALID;
+  *out = new b200_builder();
+  return B200_OK;
+}
+int b200_builder_set_int(b200_builder* b, const char* key, long long value) {
+  if (!b || !key) return B200_ERR_INVALID;
+  b->ints[key] = value;
+  return B200_OK;
+}
+int b200_builder_add_tensor(b200_builder* b, const char* name, const float* data, size_t count) {
+  if (!b || !name || (!data && count)) {
+    set_error("b200_builder_add_tensor: null argument");
+    return B200_ERR_INVALID;
+  }
+  return guarded([&] {
+    b->tensors[name].assign(data, data + count);
+    return B200_OK;
+  });
+}
+void b200_builder_destroy(b200_builder* b) { delete b; }
+
+int b200_net_create(const b200_builder* b, const b200_net_options* opt, b200_net** out) {
+  if (!b || !opt || !out) {
+    set_error("b200_net_create: null argument");
+    return B200_ERR_INVALID;
+  }
+  *out = nullptr;
+  return guarded([&] {
+    b200_net_options o = *opt;
+    if (o.max_batch <= 0) o.max_batch = 1024;
+    if (o.slots <= 0) o.slots = 1;
+    if (o.max_batch > 65536) throw Fail{B200_ERR_INVALID, "max_batch too large (limit 65536)"};
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0)
+      throw Fail{B200_ERR_CUDA, std::string("no usable CUDA device: ") + cudaGetErrorString(e)};
+    if (o.gpu < 0 || o.gpu >= ndev)
+      throw Fail{B200_ERR_INVALID, "Invalid GPU Id: " + std::to_string(o.gpu)};
+    std::unique_ptr<NetBase> impl;
+    if (o.precision == B200_PREC_FP32) {
+      auto n = std::make_unique<Net<float>>();
+      n->build(b, o);
+      impl = std::move(n);
+    } else if (o.precision == B200_PREC_FP16) {
+      auto n = std::make_unique<Net<__half>>();
+      n->build(b, o);
+      impl = std::move(n);
+    } else if (o.precision == B200_PREC_BF16) {
+      auto n = std::make_unique<Net<__nv_bfloat16>>();
+      n->build(b, o);
+      impl = std::move(n);
+    } else {
+      throw Fail{B200_ERR_INVALID, "unknown precision " + std::to_string(o.precision)};
+    }
+    *out = new b200_net{std::move(impl)};
+    return B200_OK;
+  });
+}
+int b200_net_get_info(const b200_net* net, b200_net_info* info) {
+  if (!net || !info) return B200_ERR_INVALID;
+  *info = net->impl->info;
+  return B200_OK;
+}
+void b200_net_destroy(b200_net* net) {
+  if (!net) return;
+  cudaSetDevice(net->impl->opt.gpu);
+  delete net;
+}
+
+int b200_comp_create(b200_net* net, b200_comp** out) {
+  if (!net || !out) return B200_ERR_INVALID;
+  return guarded([&] {
+    *out = new b200_comp();
+    (*out)->net = net;
+    return B200_OK;
+  });
+}
+int b200_comp_add_inputs(b200_comp* c, const uint64_t* masks, const float* values, int n) {
+  if (!c || !masks || !values || n < 0) return B200_ERR_INVALID;
+  return guarded([&] {
+    if (c->n + n > c->net->impl->opt.max_batch)
+      throw Fail{B200_ERR_INVALID, "computation exceeds max_batch=" + std::to_string(c->net->impl->opt.max_batch)};
+    c->masks.insert(c->masks.end(), masks, masks + (size_t)n * 112);
+    c->values.insert(c->values.end(), values, values + (size_t)n * 112);
+    c->n += n;
+    return B200_OK;
+  });
+}
+int b200_comp_add_input(b200_comp* c, const uint64_t* masks, const float* values) {
+  return b200_comp_add_inputs(c, masks, values, 1);
+}
+int b200_comp_compute(b200_comp* c) {
+  if (!c) return B200_ERR_INVALID;
+  return guarded([&] {
+    NetBase* nb = c->net->impl.get();
+    c->policy.resize((size_t)c->n * 1858);
+    c->qdm.resize((size_t)c->n * 3);
+    c->computed = true;
+    if (c->n == 0) return (int)B200_OK;
+    CK(cudaSetDevice(nb->opt.gpu));
+    const int slot = nb->acquire();
+    int rc;
+    try {
+      rc = nb->eval_staged(slot, c->masks.data(), c->values.data(), c->n);
+      if (rc == B200_OK) {
+        memcpy(c->policy.data(), nb->h_policy(slot), c->policy.size() * 4);
+        memcpy(c->qdm.data(), nb->h_qdm(slot), c->qdm.size() * 4);
+      }
+    } catch (...) {
+      nb->release(slot);
+      throw;
+    }
+    nb->release(slot);
+    return rc;
+  });
+}
+int b200_comp_batch_size(const b200_comp* c) { return c ? c->n : 0; }
+float b200_comp_q(const b200_comp* c, int s) { return c->qdm[(size_t)s * 3 + 0]; }
+float b200_comp_d(const b200_comp* c, int s) { return c->qdm[(size_t)s * 3 + 1]; }
+float b200_comp_m(const b200_comp* c, int s) { return c->qdm[(size_t)s * 3 + 2]; }
+float b200_comp_p(const b200_comp* c, int s, int move_id) { return c->policy[(size_t)s * 1858 + move_id]; }
+const float* b200_comp_policy(const b200_comp* c, int s) { return c->policy.data() + (size_t)s * 1858; }
+void b200_comp_destroy(b200_comp* c) { delete c; }
+
+int b200_net_eval_host(b200_net* net, const uint64_t* masks, const float* values, int n, float* policy,
+                       float* q, float* d, float* m) {
+  if (!net || n < 0 || (n > 0 && (!masks || !values))) return B200_ERR_INVALID;
+  return guarded([&] {
+    NetBase* nb = net->impl.get();
+    if (n > nb->opt.max_batch)
+      throw Fail{B200_ERR_INVALID, "batch " + std::to_string(n) + " exceeds max_batch=" + std::to_string(nb->opt.max_batch)};
+    if (n == 0) return (int)B200_OK;
+    CK(cudaSetDevice(nb->opt.gpu));
+    const int slot = nb->acquire();
+    int rc;
+    try {
+      rc = nb->eval_staged(slot, masks, values, n);
+      if (rc == B200_OK) {
+        if (policy) memcpy(policy, nb->h_policy(slot), (size_t)n * 1858 * 4);
+        const float* qdm = nb->h_qdm(slot);
+        for (int i = 0; i < n; ++i) {
+          if (q) q[i] = qdm[i * 3];
+          if (d) d[i] = qdm[i * 3 + 1];
+          if (m) m[i] = qdm[i * 3 + 2];
+        }
+      }
+    } catch (...) {
+      nb->release(slot);
+      throw;
+    }
+    nb->release(slot);
+    return rc;
+  });
+}
+
+static int eval_dev(b200_net* net, const void* d_masks, const void* d_values, int n, void* d_policy, void* d_qdm,
+                    bool sync) {
+  if (!net || n < 0 || (n > 0 && (!d_masks || !d_values || !d_policy || !d_qdm))) return B200_ERR_INVALID;
+  return guarded([&] {
+    NetBase* nb = net->impl.get();
+    if (n > nb->opt.max_batch)
+      throw Fail{B200_ERR_INVALID, "batch " + std::to_string(n) + " exceeds max_batch=" + std::to_string(nb->opt.max_batch)};
+    if (n == 0) return (int)B200_OK;
+    CK(cudaSetDevice(nb->opt.gpu));
+    return nb->eval_device(0, d_masks, d_values, n, d_policy, d_qdm, sync);
+  });
+}
+int b200_net_eval_device(b200_net* net, const void* d_masks, const void* d_values, int n, void* d_policy,
+                         void* d_qdm) {
+  return eval_dev(net, d_masks, d_values, n, d_policy, d_qdm, true);
+}
+int b200_net_enqueue_device(b200_net* net, const void* d_masks, const void* d_values, int n, void* d_policy,
+                            void* d_qdm) {
+  return eval_dev(net, d_masks, d_values, n, d_policy, d_qdm, false);
+}
+int b200_net_sync(b200_net* net) {
+  if (!net) return B200_ERR_INVALID;
+  return guarded([&] {
+    CK(cudaSetDevice(net->impl->opt.gpu));
+    CK(cudaStreamSynchronize(net->impl->stream(0)));
+    return B200_OK;
+  });
+}
+void* b200_net_stream(b200_net* net) { return net ? (void*)net->impl->stream(0) : nullptr; }
+long long b200_net_launch_count(const b200_net* net) { return net ? net->impl->launches.load() : 0; }
+int b200_net_device_status(b200_net* net) { return net ? net->impl->device_status() : 0; }
+
+// ---- stand-alone operators ----------------------------------------------------------------------
+int b200_op_expand_planes(const void* d_masks, const void* d_values, int n, void* d_out, int precision,
+                          void* stream) {
+  auto run = [&](auto tag) -> int {
+    using T = decltype(tag);
+    B200_CUDA(launch_expand_planes<T>((const uint64_t*)d_masks, (const float*)d_values, n, (T*)d_out,
+                                      (cudaStream_t)stream));
+    return B200_OK;
+  };
+  return by_precision(precision, [&] { return run(float()); }, [&] { return run(__half()); },
+                      [&] { return run(__nv_bfloat16()); });
+}
+
+int b200_op_gemm(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int activation,
+                 int precision, int use_tc, void* stream) {
+  GemmParams p;
+  p.A = A; p.lda = K; p.W = W; p.ldw = K; p.bias = bias; p.C = C; p.ldc = N;
+  p.M = M; p.N = N; p.K = K; p.act = activation;
+  if (use_tc) {
+    if (precision == B200_PREC_FP32 || !gemm_tc_supported(p)) {
+      set_error("b200_op_gemm: shape or precision not supported by the tensor-core kernel");
+      return B200_ERR_UNSUPPORTED;
+    }
+    B200_CUDA(gemm_tc_init());
+    int dev = 0, sms = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    static int* status = nullptr;  // one status word per process for the stand-alone operator
+    if (!status) {
+      B200_CUDA(cudaMalloc(&status, sizeof(int)));
+      B200_CUDA(cudaMemset(status, 0, sizeof(int)));
+    }
+    if (precision == B200_PREC_FP16) B200_CUDA(launch_gemm_tc<__half>(p, status, sms, (cudaStream_t)stream));
+    else B200_CUDA(launch_gemm_tc<__nv_bfloat16>(p, status, sms, (cudaStream_t)stream));
+    B200_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    int st = 0;
+    B200_CUDA(cudaMemcpy(&st, status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (st) {
+      cudaMemset(status, 0, sizeof(int));
+      set_error("tensor-core GEMM: a bounded device-side wait gave up, status " + std::to_string(st));
+      return B200_ERR_TIMEOUT;
+    }
+    return B200_OK;
+  }
+  auto run = [&](auto tag) -> int {
+    using T = decltype(tag);
+    B200_CUDA(launch_gemm_simt<T>(p, (cudaStream_t)stream));
+    return B200_OK;
+  };
+  return by_precision(precision, [&] { return run(float()); }, [&] { return run(__half()); },
+                      [&] { return run(__nv_bfloat16()); });
+}
+
+int b200_op_layer_norm(void* out, const void* x, const void* skip, const float* gamma, const float* beta, int rows,
+                       int C, float alpha, float eps, int precision, void* stream) {
+  auto run = [&](auto tag) -> int {
+    using T = decltype(tag);
+    B200_CUDA(launch_layer_norm<T>((T*)out, (const T*)x, (const T*)skip, gamma, beta, nullptr, nullptr, rows, C,
+                                   alpha, eps, (cudaStream_t)stream));
+    return B200_OK;
+  };
+  return by_precision(precision, [&] { return run(float()); }, [&] { return run(__half()); },
+                      [&] { return run(__nv_bfloat16()); });
+}
+
+}  // extern "C"

@@ -1,0 +1,216 @@
+"""Host-side mirror of lc0's backend plug-in interface over the C ABI.
+
+`Network` / `NetworkComputation` follow lczero::Network / lczero::NetworkComputation
+(src/neural/network.h:56-126): same method names (snake_case of AddInput, ComputeBlocking,
+GetBatchSize, GetQVal, GetDVal, GetMVal, GetPVal), same argument meaning, and the
+error behaviour of the reference's backends (unknown head names, unsupported formats, bad
+GPU ids and unknown options raise).  `create_network` plays the role of the factory lambda
+registered by REGISTER_NETWORK (src/neural/factory.h:111-142): weights file + option
+string in, network out.
+"""
+import ctypes
+
+import numpy as np
+
+from . import _lib, netproto, weights as _weights
+
+_KNOWN_OPTIONS = {"gpu", "max_batch", "precision", "slots", "mlh", "policy_head", "value_head",
+                  "tensor_cores"}
+
+
+def parse_options(opts):
+    """Parse a `key=value,key=value` backend-options string (the flat subset of
+    lc0's OptionsDict syntax, src/utils/optionsdict.cc:238-279). Unknown keys raise,
+    like OptionsDict::CheckAllOptionsRead (src/utils/optionsdict.cc:331-341)."""
+    if isinstance(opts, dict):
+        d = dict(opts)
+    else:
+        d = {}
+        for part in filter(None, (p.strip() for p in (opts or "").split(","))):
+            if "=" not in part:
+                raise ValueError("Bad backend option '%s' (expected key=value)" % part)
+            k, v = part.split("=", 1)
+            d[k.strip()] = v.strip()
+    for k in d:
+        if k not in _KNOWN_OPTIONS:
+            raise ValueError("Unknown backend option: %s" % k)
+    return d
+
+
+def _as_bool(v):
+    return str(v).lower() not in ("0", "false", "no", "off")
+
+
+class NetworkComputation:
+    """One batch: add_input x n, compute_blocking, then read results (single use)."""
+
+    def __init__(self, network):
+        self._lib = _lib.load()
+        self._net = network
+        h = ctypes.c_void_p()
+        _lib.check(self._lib.b200_comp_create(network._handle, ctypes.byref(h)))
+        self._h = h
+
+    def add_input(self, masks, values):
+        """AddInput: 112 plane masks (uint64) and 112 plane values (float32)."""
+        m = np.ascontiguousarray(masks, np.uint64).reshape(-1)
+        v = np.ascontiguousarray(values, np.float32).reshape(-1)
+        if m.size != 112 or v.size != 112:
+            raise ValueError("add_input expects 112 masks and 112 values")
+        _lib.check(self._lib.b200_comp_add_input(self._h, m.ctypes.data, v.ctypes.data))
+
+    def add_inputs(self, masks, values):
+        m = np.ascontiguousarray(masks, np.uint64).reshape(-1, 112)
+        v = np.ascontiguousarray(values, np.float32).reshape(-1, 112)
+        if m.shape != v.shape:
+            raise ValueError("masks and values must describe the same number of positions")
+        _lib.check(self._lib.b200_comp_add_inputs(self._h, m.ctypes.data, v.ctypes.data, m.shape[0]))
+
+    def compute_blocking(self):
+        _lib.check(self._lib.b200_comp_compute(self._h))
+
+    def get_batch_size(self):
+        return self._lib.b200_comp_batch_size(self._h)
+
+    def _chk(self, sample):
+        if not 0 <= sample < self.get_batch_size():
+            raise IndexError("sample %d out of range" % sample)
+
+    def get_q_val(self, sample):
+        self._chk(sample)
+        return self._lib.b200_comp_q(self._h, sample)
+
+    def get_d_val(self, sample):
+        self._chk(sample)
+        return self._lib.b200_comp_d(self._h, sample)
+
+    def get_m_val(self, sample):
+        self._chk(sample)
+        return self._lib.b200_comp_m(self._h, sample)
+
+    def get_p_val(self, sample, move_id):
+        self._chk(sample)
+        if not 0 <= move_id < _lib.POLICY_SIZE:
+            raise IndexError("move id %d out of range" % move_id)
+        return self._lib.b200_comp_p(self._h, sample, move_id)
+
+    def policy(self, sample):
+        """All 1858 raw logits of one sample (a copy)."""
+        self._chk(sample)
+        p = self._lib.b200_comp_policy(self._h, sample)
+        return np.ctypeslib.as_array(p, shape=(_lib.POLICY_SIZE,)).copy()
+
+    def close(self):
+        if self._h:
+            self._lib.b200_comp_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Network:
+    """lczero::Network over b200_net."""
+
+    def __init__(self, net, options=None):
+        opts = parse_options(options)
+        lib = _lib.load()
+        self._lib = lib
+        self._handle = None
+        prec = str(opts.get("precision", "fp16")).lower()
+        if prec not in _lib.PRECISIONS:
+            raise ValueError("Unknown precision '%s'" % prec)
+        meta, tensors = _weights.flatten(net, policy_head=opts.get("policy_head", "vanilla"),
+                                         value_head=opts.get("value_head", "winner"))
+        b = ctypes.c_void_p()
+        _lib.check(lib.b200_builder_create(ctypes.byref(b)))
+        try:
+            for k, v in meta.items():
+                _lib.check(lib.b200_builder_set_int(b, k.encode(), int(v)))
+            for name, arr in tensors.items():
+                a = np.ascontiguousarray(arr, np.float32)
+                _lib.check(lib.b200_builder_add_tensor(b, name.encode(), a.ctypes.data, a.size))
+            o = _lib.NetOptions(gpu=int(opts.get("gpu", 0)), max_batch=int(opts.get("max_batch", 1024)),
+                                precision=_lib.PRECISIONS[prec], slots=int(opts.get("slots", 1)),
+                                mlh=1 if _as_bool(opts.get("mlh", True)) else 0,
+                                flags=0 if _as_bool(opts.get("tensor_cores", True)) else _lib.FLAG_NO_TENSOR_CORES)
+            h = ctypes.c_void_p()
+            _lib.check(lib.b200_net_create(b, ctypes.byref(o), ctypes.byref(h)))
+            self._handle = h
+        finally:
+            lib.b200_builder_destroy(b)
+        self.info = _lib.NetInfo()
+        _lib.check(lib.b200_net_get_info(self._handle, ctypes.byref(self.info)))
+        self.precision = prec
+
+    # -- lczero::Network --
+    def get_capabilities(self):
+        return {"input_format": self.info.input_format, "output_format": self.info.output_format,
+                "moves_left": self.info.moves_left_format if self.info.has_mlh else 0}
+
+    def new_computation(self):
+        return NetworkComputation(self)
+
+    def get_threads(self):
+        return 1
+
+    def is_cpu(self):
+        return False
+
+    def get_mini_batch_size(self):
+        return 2 * self.info.sm_count
+
+    def get_preferred_batch_step(self):
+        return 1
+
+    # -- whole-batch helpers --
+    def evaluate(self, masks, values):
+        """Evaluate host arrays in one call; returns dict(policy, q, d, m)."""
+        m = np.ascontiguousarray(masks, np.uint64).reshape(-1, 112)
+        v = np.ascontiguousarray(values, np.float32).reshape(-1, 112)
+        n = m.shape[0]
+        out = dict(policy=np.empty((n, 1858), np.float32), q=np.empty(n, np.float32),
+                   d=np.empty(n, np.float32), m=np.empty(n, np.float32))
+        _lib.check(self._lib.b200_net_eval_host(self._handle, m.ctypes.data, v.ctypes.data, n,
+                                                out["policy"].ctypes.data, out["q"].ctypes.data,
+                                                out["d"].ctypes.data, out["m"].ctypes.data))
+        return out
+
+    def enqueue_device(self, d_masks, d_values, n, d_policy, d_qdm):
+        _lib.check(self._lib.b200_net_enqueue_device(self._handle, d_masks, d_values, n, d_policy, d_qdm))
+
+    def sync(self):
+        _lib.check(self._lib.b200_net_sync(self._handle))
+
+    def stream(self):
+        return self._lib.b200_net_stream(self._handle)
+
+    def launch_count(self):
+        return self._lib.b200_net_launch_count(self._handle)
+
+    def device_status(self):
+        return self._lib.b200_net_device_status(self._handle)
+
+    def close(self):
+        if self._handle:
+            self._lib.b200_net_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def create_network(weights_path_or_net, options=None):
+    """Factory: a weights file path (or parsed Net dict) plus options -> Network."""
+    if weights_path_or_net is None:
+        raise ValueError("The b200 backend requires a network file.")
+    net = weights_path_or_net
+    if not isinstance(net, dict):
+        net = netproto.load_net(net)
+    return Network(net, options)
