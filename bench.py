@@ -1,0 +1,318 @@
+#!/usr/bin/env python
+"""Benchmark of the lc0 NN-evaluation hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--precision fp16|bf16|fp32]
+    python bench.py --impl reference ...      # the reference's own CPU (blas) backend on the host cores
+
+One step = one evaluation of a batch of `--batch` positions (default 1024) per GPU with the seeded
+BT4-class network (15 encoder layers, embedding 1024, 32 heads, dff 1536, smolgen) -- the configuration
+the headline metric is quoted on.  Data are synthetic: seeded random-init weights and seeded random
+legal playouts (tests/golden/positions_fmt2_*.npz).  With N > 1 (launched by torch.distributed.run, one
+rank per GPU) every rank evaluates its own batch with replicated weights; there is no collective on the
+data path, only a barrier and a max-reduction of the measured time.
+
+`value` is timed with CUDA events on the evaluation stream with inputs resident in device memory; `e2e`
+is timed through the NetworkComputation-style API with host buffers (H2D + D2H inside the timed region).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "nn_evals_per_sec"
+UNIT = "evals/s"
+NET = "cfg4"
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(tflops_sustained=p["bf16_tflops_sustained"], tflops_burst=p["bf16_tflops"],
+                    hbm_gbs=p["hbm_gbs"], source="measured")
+    return dict(tflops_sustained=1400.0, tflops_burst=1590.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.proc = None
+        self.lines = []
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if not self.proc:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = [l for (t, l) in self.lines if t0 <= t <= t1 + 0.2] or [l for (_, l) in self.lines]
+        for line in rows:
+            f = [x.strip() for x in line.split(",")]
+            try:
+                sm.append(float(f[0]))
+                mx = max(mx, float(f[1]))
+            except Exception:
+                continue
+            for nme, val in zip(names, f[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(nme)
+        if not sm:
+            return None
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def load_positions(rank, batch):
+    name = "positions_fmt2_uniform.npz" if rank % 2 == 0 else "positions_fmt2_split.npz"
+    p = np.load(os.path.join(ROOT, "tests", "golden", name))
+    masks, values = p["masks"], p["values"]
+    reps = -(-batch // masks.shape[0])
+    masks = np.tile(masks, (reps, 1))[:batch]
+    values = np.tile(values, (reps, 1))[:batch]
+    return np.ascontiguousarray(np.roll(masks, rank * 17, axis=0)), np.ascontiguousarray(np.roll(values, rank * 17, axis=0))
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline: the reference's own blas backend (oracle/_ref/ref_eval, built from the reference
+# sources by oracle/build_ref.py) or, when that binary is absent, the numpy port in oracle/.
+# ------------------------------------------------------------------------------------------------
+def cpu_reference(sample_positions, repeats, threads=None):
+    from lc0_b200 import mknet, netproto, weights
+    threads = threads or os.cpu_count() or 1
+    masks, values = load_positions(0, sample_positions)
+    ref_bin = os.path.join(ROOT, "oracle", "_ref", "ref_eval")
+    net = mknet.make_net(NET)
+    if os.path.exists(ref_bin):
+        with tempfile.TemporaryDirectory() as tmp:
+            npath = os.path.join(tmp, "net.pb")
+            netproto.write_net(npath, net, compress=False)
+            ppath = os.path.join(tmp, "p.pos")
+            with open(ppath, "wb") as f:
+                f.write(b"LC0POS1\0")
+                f.write(np.array([sample_positions, 2], "<i4").tobytes())
+                f.write(masks.astype("<u8").tobytes())
+                f.write(values.astype("<f4").tobytes())
+                f.write(np.zeros(sample_positions, "<i4").tobytes())
+                f.write(np.zeros(sample_positions, "<i4").tobytes())
+                f.write(np.full((sample_positions, 256), -1, "<i2").tobytes())
+            r = subprocess.run([ref_bin, "blas", npath, ppath, "-", "threads=%d,batch_size=%d" % (threads, sample_positions),
+                                str(repeats)], capture_output=True, text=True)
+            if r.returncode == 0 and "evals_per_s=" in r.stdout:
+                v = float(r.stdout.split("evals_per_s=")[1].split()[0])
+                return dict(value=v, unit=UNIT, cores=threads, kind="reference",
+                            sample="%d positions x %d repeats of the %s net through the reference blas backend "
+                                   "(OpenBLAS, %d threads)" % (sample_positions, repeats, NET, threads))
+    from oracle import oracle
+    meta, t = weights.flatten(netproto.parse_net(netproto.encode("Net", net)))
+    oracle.forward(meta, t, masks[:2], values[:2])
+    t0 = time.time()
+    for _ in range(repeats):
+        oracle.forward(meta, t, masks, values)
+    dt = time.time() - t0
+    return dict(value=sample_positions * repeats / dt, unit=UNIT, cores=threads, kind="port",
+                sample="%d positions x %d repeats of the %s net through the numpy port of the blas backend"
+                       % (sample_positions, repeats, NET))
+
+
+def run_reference(args, rank):
+    """--impl reference: the reference's CPU implementation on the host cores.  One step = one evaluation of
+    a 32-position sample (ref_eval performs one untimed warm-up evaluation itself before the timed repeats);
+    ranks other than 0 exit without work."""
+    if rank != 0:
+        return
+    sample = 32
+    t0 = time.time()
+    base = cpu_reference(sample, max(1, args.steps))
+    dt = time.time() - t0
+    v = base["value"]
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1000.0 * sample / v, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "BT4-class net: 15 encoder layers, embedding 1024, 32 heads, dff 1536, smolgen "
+                                   "32/256/256; reference CPU backend, %d-position sample per step" % sample,
+                       "wall_seconds_including_load": dt},
+            "cpu_baseline": base,
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=1024)
+    ap.add_argument("--precision", default="fp16")
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    from lc0_b200 import mknet, network
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    net = mknet.make_net(NET)
+    nw = network.Network(net, dict(gpu=local_rank, max_batch=args.batch, precision=args.precision))
+    del net
+    info = nw.info
+    B = args.batch
+    masks, values = load_positions(rank, B)
+    d_masks = torch.from_numpy(masks.view(np.int64)).cuda()
+    d_values = torch.from_numpy(values).cuda()
+    d_policy = torch.empty(B, 1858, dtype=torch.float32, device="cuda")
+    d_qdm = torch.empty(B, 3, dtype=torch.float32, device="cuda")
+    stream = torch.cuda.ExternalStream(nw.stream())
+
+    def step_device():
+        nw.enqueue_device(d_masks.data_ptr(), d_values.data_ptr(), B, d_policy.data_ptr(), d_qdm.data_ptr())
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing (value) ----
+    for _ in range(args.warmup):
+        step_device()
+    nw.sync()
+    status = nw.device_status()
+    if status:
+        raise RuntimeError("device status word = %d (a bounded wait gave up)" % status)
+    nw.set_profiling(True)
+    nw.get_profile(reset=True)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    time.sleep(0.25)
+    l0 = nw.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step_device()
+    e1.record(stream)
+    nw.sync()
+    t1 = time.time()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = nw.launch_count() - l0
+    clocks = sampler.stop(t0, t1)
+    prof = nw.get_profile(reset=True)
+    nw.set_profiling(False)
+    if world > 1:
+        tt = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    value = world * B * args.steps / (ms / 1000.0)
+
+    # ---- end-to-end timing through the computation API (host buffers) ----
+    def step_host():
+        c = nw.new_computation()
+        c.add_inputs(masks, values)
+        c.compute_blocking()
+        q = c.get_q_val(0)
+        c.close()
+        return q
+
+    for _ in range(2):
+        step_host()
+    barrier()
+    th0 = time.time()
+    for _ in range(args.steps):
+        step_host()
+    torch.cuda.synchronize()
+    th = time.time() - th0
+    if world > 1:
+        tt = torch.tensor([th], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        th = float(tt.item())
+    e2e_value = world * B * args.steps / th
+
+    if rank == 0:
+        peaks = read_peaks()
+        g = prof["gemm_tc"]
+        achieved = g["work"] / (g["ms"] * 1e-3) / 1e12 if g["ms"] > 0 else 0.0
+        total_ms = sum(v["ms"] for v in prof.values())
+        roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05 GEMM, all launches of the timed region)",
+                    "achieved": achieved, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["tflops_sustained"], "peak_source": peaks["source"] + " sustained bf16",
+                    "launches": g["launches"], "share_of_step": g["ms"] / total_ms if total_ms else None,
+                    "traffic": None}
+        other = {}
+        for k in ("attention", "layer_norm"):
+            v = prof[k]
+            if v["ms"] > 0:
+                gbs = v["work"] / (v["ms"] * 1e-3) / 1e9
+                other[k] = {"GBps": gbs, "frac_hbm": gbs / peaks["hbm_gbs"], "ms_per_step": v["ms"] / args.steps,
+                            "launches": v["launches"]}
+        for k in ("gemm_tc", "gemm_fma", "other"):
+            other.setdefault(k, {})["ms_per_step"] = prof[k]["ms"] / args.steps
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": args.precision, "data": "synthetic",
+            "config": {"workload": "BT4-class net: 15 encoder layers, embedding 1024, 32 heads, dff 1536, smolgen "
+                                   "32/256/256, attention policy, WDL + moves-left; batch %d per GPU" % B,
+                       "batch_per_gpu": B, "global_batch": B * world, "parallelism": "replicated weights, batch split",
+                       "l2": "per-step working set (weights %.2f GB + activations) exceeds the 126 MB L2"
+                             % (info.weight_bytes / 1e9)},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(B * 112 * 12),
+                    "d2h_bytes_per_step": int(B * (1858 + 3) * 4), "ms_per_step": 1000.0 * th / args.steps},
+            "gpu_launches": int(launches),
+            "roofline": roofline,
+            "kernel_classes": other,
+            "flops_per_eval": info.flops_per_position,
+            "model_tflops": value / world * info.flops_per_position / 1e12,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_reference(32, 4)
+        print(json.dumps(line), flush=True)
+    nw.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

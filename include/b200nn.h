@@ -130,6 +130,16 @@ long long b200_net_launch_count(const b200_net* net);
 /* Device status word written by kernels whose bounded waits gave up (0 = none). */
 int b200_net_device_status(b200_net* net);
 
+/* Per-kernel-class timing with CUDA events recorded on the evaluation stream around every launch
+ * (off by default).  Classes: 0 tensor-core GEMM, 1 FMA GEMM, 2 attention, 3 LayerNorm, 4 other.
+ * b200_net_get_profile waits for the recorded events and returns, per class, the summed device time
+ * in ms, the summed algorithmic work (FLOPs for the GEMM classes, bytes for the others) and the number
+ * of launches; arrays of B200_PROFILE_CLASSES entries.  The reference has the DEBUG_RAW_NPS timing
+ * ifdef in its forward pass for the same purpose (src/neural/backends/cuda/network_cuda.cc:715-717). */
+#define B200_PROFILE_CLASSES 5
+int b200_net_set_profiling(b200_net* net, int enabled);
+int b200_net_get_profile(b200_net* net, double* ms, double* work, long long* launches, int reset);
+
 /* ---- Stand-alone operators (unit-test and profiling surface of the same kernels) --------------
  * All pointers are device pointers on the current device; `stream` is a cudaStream_t or NULL.
  * b200_op_expand_planes: 112 (mask,value) pairs per position -> dense [n][112][64] values of

@@ -70,6 +70,8 @@ SIGNATURES = {
     "b200_net_stream": (_P, [_P]),
     "b200_net_launch_count": (ctypes.c_longlong, [_P]),
     "b200_net_device_status": (_I, [_P]),
+    "b200_net_set_profiling": (_I, [_P, _I]),
+    "b200_net_get_profile": (_I, [_P, _P, _P, _P, _I]),
     "b200_op_expand_planes": (_I, [_P, _P, _I, _P, _I, _P]),
     "b200_op_gemm": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "b200_op_layer_norm": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _P]),

@@ -16,6 +16,7 @@
 #include <cuda.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -79,6 +80,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most one of this thread's bulk groups still reads its shared-memory source.
+__device__ __forceinline__ void tma_store_wait_read1() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -125,6 +140,35 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   return d;
 }
 
+// Activation of a register array with the selection hoisted out of the element loop.
+template <int N>
+__device__ __forceinline__ void apply_activation(float (&v)[N], int act) {
+  switch (act) {
+    case ACT_RELU:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = fmaxf(v[j], 0.f);
+      break;
+    case ACT_RELU_2:
+#pragma unroll
+      for (int j = 0; j < N; ++j) { const float t = fmaxf(v[j], 0.f); v[j] = t * t; }
+      break;
+    case ACT_MISH:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = mish_f(v[j]);
+      break;
+    case ACT_SWISH:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = v[j] / (1.0f + __expf(-v[j]));
+      break;
+    case ACT_NONE:
+      break;
+    default:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = activate<true>(v[j], act);
+      break;
+  }
+}
+
 template <typename T> struct FmtCode;
 template <> struct FmtCode<__half> { static constexpr uint32_t v = 0; };
 template <> struct FmtCode<__nv_bfloat16> { static constexpr uint32_t v = 1; };
@@ -141,7 +185,8 @@ template <int BN> struct TileCfg {
   static constexpr int kStageBytes = (BM + BN) * BK * 2;
   static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kEpiBytes = 2 * BM * 128;  // two 128-row x 128-byte staging buffers for TMA stores
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 struct TcParams {
@@ -155,23 +200,27 @@ struct TcParams {
   float scale, alpha;
   int out_f32;
   int* status;
+  int debug;
+  int tma_store;  // 1: 16-bit output staged in shared memory and written with TMA stores
 };
 
 template <typename T, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-               const TcParams p) {
+               const __grid_constant__ CUtensorMap tmap_c, const TcParams p) {
   using Cfg = TileCfg<BN>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* bar_mem = smem + S * Cfg::kStageBytes;
+  uint8_t* epi_mem = smem + S * Cfg::kStageBytes;
+  uint8_t* bar_mem = epi_mem + Cfg::kEpiBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_mem);       // [S]
   uint64_t* empty_bar = full_bar + S;                               // [S]
   uint64_t* tfull_bar = empty_bar + S;                              // [2]
   uint64_t* tempty_bar = tfull_bar + 2;                             // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epi_ok = abort_flag + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
@@ -213,6 +262,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t ph = (it / S) & 1;
           if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, 1)) { ok = false; break; }
           const uint32_t fb = smem_u32(&full_bar[s]);
+          if (p.debug & 8) { mbar_arrive(fb); continue; }
           mbar_expect_tx(fb, Cfg::kStageBytes);
           const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
           tma_load_2d(sa, &tmap_a, kb * BK, m0, fb);
@@ -241,6 +291,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint64_t bdesc = make_smem_desc(sa + BM * BK * 2);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
+            if (p.debug & 4) break;
             // advancing 16 elements (32 bytes) along K inside the swizzle row = +2 in the address field
             tcgen05_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
@@ -253,21 +304,69 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ---------------- epilogue (warps 2..5) ----------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
     const T* skip = reinterpret_cast<const T*>(p.skip);
-    uint32_t tile_it = 0;
+    uint32_t tile_it = 0, chunk_it = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
       const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
       const int m0 = (t / n_tiles) * BM, n0 = (t % n_tiles) * BN;
-      if (!mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4)) break;
+      // One thread does the bounded wait and publishes the outcome, so that all four epilogue warps take the
+      // same decision and nobody is left behind at a named barrier.
+      if (warp == 2 && lane == 0) *epi_ok = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4) ? 1 : 0;
+      epilogue_barrier();
+      if (!*epi_ok) break;
       tcgen05_fence_after();
       const int m = m0 + quarter * 32 + lane;
       const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      if (p.tma_store) {
+        // Fast path: 64-column slabs -> registers -> swizzled shared memory -> TMA store (clips the M/N tails).
+        const int row = quarter * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+          const int nb = n0 + c0;
+          if (nb >= p.N) break;  // uniform over the CTA
+          uint8_t* buf = epi_mem + (chunk_it & 1) * (BM * 128);
+          if (warp == 2 && lane == 0) tma_store_wait_read1();  // the store that last read this buffer is done
+          epilogue_barrier();
+          uint32_t r0[32], r1[32];
+          tmem_ld32(trow + c0, r0);
+          tmem_ld32(trow + c0 + 32, r1);
+          tmem_ld_wait();
+          float b0 = 0.f, b1 = 0.f;
+          if (p.bias) {
+            if (nb + lane < p.N) b0 = __ldg(p.bias + nb + lane);
+            if (nb + 32 + lane < p.N) b1 = __ldg(p.bias + nb + 32 + lane);
+          }
+          float v[64];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = fmaf(__uint_as_float(r0[j]), p.scale, __shfl_sync(0xffffffffu, b0, j));
+            v[32 + j] = fmaf(__uint_as_float(r1[j]), p.scale, __shfl_sync(0xffffffffu, b1, j));
+          }
+          apply_activation(v, p.act);
+          uint8_t* srow = buf + row * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            __align__(16) T o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = from_f<T>(v[c * 8 + i]);
+            *reinterpret_cast<uint4*>(srow + ((c ^ (row & 7)) << 4)) = *reinterpret_cast<const uint4*>(o);
+          }
+          fence_async_smem();
+          epilogue_barrier();
+          if (warp == 2 && lane == 0) {
+            tma_store_2d(&tmap_c, nb, m0, smem_u32(buf));
+            tma_store_commit();
+          }
+          ++chunk_it;
+        }
+      } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (p.debug & 2) break;
         uint32_t r[32];
         tmem_ld32(trow + c0, r);
         tmem_ld_wait();
         const int nb = n0 + c0;
-        if (m < p.M && nb < p.N) {
+        if (m < p.M && nb < p.N && !(p.debug & 1)) {
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -315,10 +414,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
       }
+      }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
     }
+    if (warp == 2 && lane == 0) tma_store_wait_all();  // stores must complete before the CTA exits
   }
 
   __syncwarp();
@@ -412,13 +513,21 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
   if (e != cudaSuccess) return e;
   e = get_map(g.W, g.ldw, g.N, g.K, BN, prec, &mw);
   if (e != cudaSuccess) return e;
+  const bool tma_store = !g.out_f32 && !g.skip && (g.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(g.C) & 15) == 0;
+  CUtensorMap mc = ma;
+  if (tma_store) {
+    e = get_map(g.C, g.ldc, g.M, g.N, BM, prec, &mc);
+    if (e != cudaSuccess) return e;
+  }
   TcParams p;
+  p.tma_store = tma_store ? 1 : 0;
   p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.skip = g.skip; p.ldskip = g.ldskip;
   p.M = g.M; p.N = g.N; p.K = g.K; p.act = g.act; p.scale = g.scale; p.alpha = g.alpha;
   p.out_f32 = g.out_f32 ? 1 : 0; p.status = status;
+  { const char* d = getenv("B200_GEMM_DEBUG"); p.debug = d ? atoi(d) : 0; }
   const int tiles = ceil_div(g.M, BM) * ceil_div(g.N, BN);
   const int grid = tiles < sm_count ? tiles : sm_count;
-  gemm_tc_kernel<T, BN><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, p);
+  gemm_tc_kernel<T, BN><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, p);
   return cudaGetLastError();
 }
 

@@ -187,6 +187,48 @@ struct NetBase {
   b200_net_info info{};
   b200_net_options opt{};
   std::atomic<long long> launches{0};
+  // Optional per-kernel-class timing with CUDA events on the evaluation stream.
+  enum { K_GEMM_TC = 0, K_GEMM_FMA = 1, K_ATTENTION = 2, K_LAYERNORM = 3, K_OTHER = 4, K_CLASSES = 5 };
+  bool profiling = false;
+  struct Span { int cls; cudaEvent_t a, b; double work; };
+  std::vector<Span> spans;
+  std::vector<cudaEvent_t> event_pool;
+  double prof_ms[K_CLASSES] = {0}, prof_work[K_CLASSES] = {0};
+  long long prof_launches[K_CLASSES] = {0};
+  cudaEvent_t get_event() {
+    if (!event_pool.empty()) {
+      cudaEvent_t e = event_pool.back();
+      event_pool.pop_back();
+      return e;
+    }
+    cudaEvent_t e;
+    cudaEventCreate(&e);
+    return e;
+  }
+  // Brackets one launch: begin() before, end() after (no-ops unless profiling is on).
+  void span_begin(cudaStream_t st, int cls, double work) {
+    if (!profiling) return;
+    Span sp{cls, get_event(), get_event(), work};
+    cudaEventRecord(sp.a, st);
+    spans.push_back(sp);
+  }
+  void span_end(cudaStream_t st) {
+    if (!profiling) return;
+    cudaEventRecord(spans.back().b, st);
+  }
+  void collect_spans() {
+    for (auto& sp : spans) {
+      float ms = 0.f;
+      if (cudaEventSynchronize(sp.b) == cudaSuccess && cudaEventElapsedTime(&ms, sp.a, sp.b) == cudaSuccess) {
+        prof_ms[sp.cls] += ms;
+        prof_work[sp.cls] += sp.work;
+        prof_launches[sp.cls]++;
+      }
+      event_pool.push_back(sp.a);
+      event_pool.push_back(sp.b);
+    }
+    spans.clear();
+  }
   virtual int eval_device(int slot, const void* d_masks, const void* d_values, int n, void* d_policy,
                           void* d_qdm, bool sync) = 0;
   virtual int eval_staged(int slot, const uint64_t* masks, const float* values, int n) = 0;
@@ -724,18 +766,26 @@ struct Net : NetBase {
   }
   void run_gemm(cudaStream_t st, const GemmParams& p) {
     launches++;
+    const double flops = 2.0 * p.M * (double)p.N * p.K * p.batch;
     if constexpr (sizeof(T) == 2) {
       if (use_tc && p.M >= 64 && gemm_tc_supported(p)) {
+        span_begin(st, K_GEMM_TC, flops);
         CK(launch_gemm_tc<T>(p, d_status, sm_count, st));
+        span_end(st);
         return;
       }
     }
+    span_begin(st, K_GEMM_FMA, flops);
     CK(launch_gemm_simt<T>(p, st));
+    span_end(st);
   }
   void ln(cudaStream_t st, T* out, const T* x, const T* skip, const float* g, const float* b, int rows, int Cc,
           float a, float eps, const float* gm = nullptr, const float* ga = nullptr) {
     launches++;
+    // algorithmic bytes: read x (+ skip), write out
+    span_begin(st, K_LAYERNORM, (double)rows * Cc * sizeof(T) * (skip ? 3 : 2));
     CK(launch_layer_norm<T>(out, x, skip, g, b, gm, ga, rows, Cc, a, eps, st));
+    span_end(st);
   }
 
   void encoder_layer(Slot& s, const EncoderW<T>& e, int n, T*& x, T*& x1) {
@@ -754,8 +804,11 @@ struct Net : NetBase {
     }
     gemm(st, x, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE);  // :341-350, :408-412
     launches++;
+    // algorithmic bytes: read Q, K, V (+ bias), write the head outputs
+    span_begin(st, K_ATTENTION, (double)R * E * sizeof(T) * 4 + (bias ? (double)n * H * 4096 * sizeof(T) : 0.0));
     CK(launch_attention<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
                            1.0f / sqrtf((float)depth), st));  // :352-439
+    span_end(st);
     gemm(st, s.att, E, e.proj, s.y, E, R, ACT_NONE);           // :441-445
     ln(st, x1, s.y, x, e.ln1g, e.ln1b, R, E, alpha, ln_eps);   // :447-452
     gemm(st, x1, E, e.ffn1, s.ffn, e.ffn1.out, R, act_ffn);    // :454-458
@@ -842,8 +895,7 @@ struct Net : NetBase {
       p.W = s.pk; p.ldw = pol_dm; p.strideW = 64LL * pol_dm;
       p.C = s.logits; p.ldc = 64; p.strideC = 4096; p.out_f32 = true;
       p.M = 64; p.N = 64; p.K = pol_dm; p.batch = n; p.scale = 1.0f / sqrtf((float)pol_dm);
-      launches++;
-      CK(launch_gemm_simt<T>(p, st));
+      run_gemm(st, p);
       launches++;
       CK(launch_policy_attn_gather<T>(s.logits, s.pk, pol_w4, pol_dm, d_attn_src, n, d_policy, st));
     } else if (policy_fmt == POLICY_CONVOLUTION) {
@@ -1124,6 +1176,30 @@ int b200_net_sync(b200_net* net) {
 void* b200_net_stream(b200_net* net) { return net ? (void*)net->impl->stream(0) : nullptr; }
 long long b200_net_launch_count(const b200_net* net) { return net ? net->impl->launches.load() : 0; }
 int b200_net_device_status(b200_net* net) { return net ? net->impl->device_status() : 0; }
+
+int b200_net_set_profiling(b200_net* net, int enabled) {
+  if (!net) return B200_ERR_INVALID;
+  net->impl->collect_spans();
+  net->impl->profiling = enabled != 0;
+  return B200_OK;
+}
+int b200_net_get_profile(b200_net* net, double* ms, double* work, long long* launches, int reset) {
+  if (!net || !ms || !work || !launches) return B200_ERR_INVALID;
+  NetBase* nb = net->impl.get();
+  cudaSetDevice(nb->opt.gpu);
+  nb->collect_spans();
+  for (int i = 0; i < NetBase::K_CLASSES; ++i) {
+    ms[i] = nb->prof_ms[i];
+    work[i] = nb->prof_work[i];
+    launches[i] = nb->prof_launches[i];
+    if (reset) {
+      nb->prof_ms[i] = 0;
+      nb->prof_work[i] = 0;
+      nb->prof_launches[i] = 0;
+    }
+  }
+  return B200_OK;
+}
 
 // ---- stand-alone operators ----------------------------------------------------------------------
 int b200_op_expand_planes(const void* d_masks, const void* d_values, int n, void* d_out, int precision,

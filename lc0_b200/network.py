@@ -194,6 +194,20 @@ class Network:
     def device_status(self):
         return self._lib.b200_net_device_status(self._handle)
 
+    PROFILE_CLASSES = ("gemm_tc", "gemm_fma", "attention", "layer_norm", "other")
+
+    def set_profiling(self, enabled):
+        _lib.check(self._lib.b200_net_set_profiling(self._handle, 1 if enabled else 0))
+
+    def get_profile(self, reset=True):
+        """{class: dict(ms, work, launches)}: device time, algorithmic FLOPs (GEMMs) or bytes."""
+        k = len(self.PROFILE_CLASSES)
+        ms, work, cnt = np.zeros(k), np.zeros(k), np.zeros(k, np.int64)
+        _lib.check(self._lib.b200_net_get_profile(self._handle, ms.ctypes.data, work.ctypes.data,
+                                                  cnt.ctypes.data, 1 if reset else 0))
+        return {c: dict(ms=float(ms[i]), work=float(work[i]), launches=int(cnt[i]))
+                for i, c in enumerate(self.PROFILE_CLASSES)}
+
     def close(self):
         if self._handle:
             self._lib.b200_net_destroy(self._handle)

@@ -1,0 +1,87 @@
+"""Stand-alone operator entry points of the C ABI against the oracle's restatements."""
+import numpy as np
+import pytest
+
+from lc0_b200 import _lib
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+DT = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}
+
+
+@pytest.mark.parametrize("prec", [0, 1, 2])
+@pytest.mark.parametrize("n", [1, 3, 64, 257])
+def test_expand_planes_bit_exact(lib, prec, n):
+    rng = np.random.default_rng(n)
+    masks = rng.integers(0, 2 ** 63, size=(n, 112), dtype=np.uint64) * np.uint64(2) + rng.integers(0, 2, size=(n, 112)).astype(np.uint64)
+    values = rng.choice(np.array([1.0, 0.5, 0.25, 3.0, 99.0], np.float32), size=(n, 112))
+    want = oracle.expand_planes(masks, values)
+    dm = torch.from_numpy(masks.view(np.int64)).cuda()
+    dv = torch.from_numpy(values).cuda()
+    out = torch.zeros(n, 112, 64, dtype=DT[prec], device="cuda")
+    _lib.check(lib.b200_op_expand_planes(dm.data_ptr(), dv.data_ptr(), n, out.data_ptr(), prec, None))
+    torch.cuda.synchronize()
+    assert np.array_equal(out.float().cpu().numpy(), want)  # all test values are exact in every type
+
+
+def test_expand_planes_empty(lib):
+    _lib.check(lib.b200_op_expand_planes(None, None, 0, None, 0, None))
+
+
+@pytest.mark.parametrize("prec", [1, 2])
+@pytest.mark.parametrize("shape", [(128, 64, 64), (64, 256, 512), (1000, 1024, 1024), (333, 200, 72),
+                                   (8192, 3072, 1024), (4096, 1024, 1536), (130, 4096, 256), (2048, 32, 1024)])
+@pytest.mark.parametrize("act", [oracle.ACT_NONE, oracle.ACT_RELU_2, oracle.ACT_MISH])
+def test_tensor_core_gemm(lib, prec, shape, act):
+    M, N, K = shape
+    torch.manual_seed(M + N + K)
+    A = (torch.randn(M, K, device="cuda") * 0.5).to(DT[prec])
+    W = (torch.randn(N, K, device="cuda") * (K ** -0.5)).to(DT[prec])
+    b = torch.randn(N, device="cuda") * 0.1
+    C = torch.zeros(M, N, dtype=DT[prec], device="cuda")
+    _lib.check(lib.b200_op_gemm(A.data_ptr(), W.data_ptr(), b.data_ptr(), C.data_ptr(), M, N, K, act, prec, 1, None))
+    torch.cuda.synchronize()
+    ref = oracle.fc(A.float().cpu().numpy(), W.float().cpu().numpy().reshape(-1), b.cpu().numpy(), act, N)
+    got = C.float().cpu().numpy()
+    eps = 2.0 ** -10 if prec == 1 else 2.0 ** -7  # output rounding of the storage type
+    assert np.all(np.abs(got - ref) <= eps * np.abs(ref) + 2e-3)
+
+
+@pytest.mark.parametrize("prec", [0, 1, 2])
+def test_fma_gemm(lib, prec):
+    M, N, K = 77, 130, 45
+    torch.manual_seed(0)
+    A = (torch.randn(M, K, device="cuda")).to(DT[prec])
+    W = (torch.randn(N, K, device="cuda") * 0.2).to(DT[prec])
+    b = torch.randn(N, device="cuda")
+    C = torch.zeros(M, N, dtype=DT[prec], device="cuda")
+    _lib.check(lib.b200_op_gemm(A.data_ptr(), W.data_ptr(), b.data_ptr(), C.data_ptr(), M, N, K, oracle.ACT_SWISH, prec, 0, None))
+    torch.cuda.synchronize()
+    ref = oracle.fc(A.float().cpu().numpy(), W.float().cpu().numpy().reshape(-1), b.cpu().numpy(), oracle.ACT_SWISH, N)
+    tol = {0: 1e-5, 1: 2e-3, 2: 1.6e-2}[prec]
+    assert np.abs(C.float().cpu().numpy() - ref).max() <= tol * max(1.0, np.abs(ref).max())
+
+
+def test_gemm_tc_rejects_fp32(lib):
+    assert lib.b200_op_gemm(None, None, None, None, 128, 128, 64, 3, 0, 1, None) == _lib.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("prec", [0, 1, 2])
+@pytest.mark.parametrize("C", [64, 256, 1024, 8192])
+def test_layer_norm(lib, prec, C):
+    rows = 130
+    torch.manual_seed(C)
+    x = torch.randn(rows, C, device="cuda").to(DT[prec])
+    skip = torch.randn(rows, C, device="cuda").to(DT[prec])
+    gam = torch.randn(C, device="cuda") * 0.1 + 1
+    bet = torch.randn(C, device="cuda") * 0.1
+    out = torch.zeros(rows, C, dtype=DT[prec], device="cuda")
+    _lib.check(lib.b200_op_layer_norm(out.data_ptr(), x.data_ptr(), skip.data_ptr(), gam.data_ptr(), bet.data_ptr(),
+                                      rows, C, 0.43, 1e-3, prec, None))
+    torch.cuda.synchronize()
+    ref = oracle.layer_norm(x.float().cpu().numpy(), 0.43, skip.float().cpu().numpy(), gam.cpu().numpy(),
+                            bet.cpu().numpy(), 1e-3)
+    tol = {0: 2e-5, 1: 4e-3, 2: 3e-2}[prec]
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= tol

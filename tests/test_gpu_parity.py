@@ -1,0 +1,138 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and the recorded reference outputs."""
+import numpy as np
+import pytest
+
+from conftest import load_case
+from lc0_b200 import _lib, network, weights
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+ALL = ["cfg1_mini", "cfg2_mini", "cfg3_mini", "cfg4_mini", "cfg1", "cfg2", "cfg3", "cfg4_2layer"]
+# fp32 verification mode: error relative to the largest logit of the batch (north star: <= 1e-5).
+FP32_REL = 1e-5
+# fp16 storage with fp32 accumulation (north star: policy softmax and WDL/Q/M max-abs <= 2e-3).
+HALF_ATOL = 2e-3
+
+
+def _softmax_err_and_argmax(got, want, pos, n):
+    worst, agree, decided = 0.0, 0, 0
+    for i in range(n):
+        lg = pos["legal"][i][:pos["n_legal"][i]]
+        a = oracle.legal_softmax(got[i], lg)
+        b = oracle.legal_softmax(want[i], lg)
+        worst = max(worst, float(np.abs(a - b).max()))
+        top = np.sort(b)[::-1]
+        if len(top) < 2 or top[0] - top[1] > 2 * HALF_ATOL:  # near-ties may legitimately flip
+            decided += 1
+            agree += int(a.argmax() == b.argmax())
+    return worst, agree, decided
+
+
+@pytest.mark.parametrize("name", ALL)
+def test_fp32_mode_matches_reference(name):
+    net, pos, n, g = load_case(name)
+    nw = network.Network(net, "precision=fp32,max_batch=%d" % n)
+    out = nw.evaluate(pos["masks"][:n], pos["values"][:n])
+    nw.close()
+    scale = float(np.abs(g["policy"]).max())
+    assert np.abs(out["policy"] - g["policy"]).max() <= FP32_REL * scale
+    for k in ("q", "d", "m"):
+        assert np.abs(out[k] - g[k]).max() <= FP32_REL * max(1.0, float(np.abs(g[k]).max()))
+    worst, agree, decided = _softmax_err_and_argmax(out["policy"], g["policy"], pos, n)
+    assert agree == decided
+
+
+@pytest.mark.parametrize("tc", [True, False])
+@pytest.mark.parametrize("name", ALL)
+def test_fp16_mode_within_tolerance(name, tc):
+    net, pos, n, g = load_case(name)
+    nw = network.Network(net, "precision=fp16,max_batch=%d,tensor_cores=%d" % (n, int(tc)))
+    out = nw.evaluate(pos["masks"][:n], pos["values"][:n])
+    assert nw.device_status() == 0
+    nw.close()
+    worst, agree, decided = _softmax_err_and_argmax(out["policy"], g["policy"], pos, n)
+    assert worst <= HALF_ATOL
+    assert agree == decided
+    assert np.abs(out["q"] - g["q"]).max() <= HALF_ATOL
+    assert np.abs(out["d"] - g["d"]).max() <= HALF_ATOL
+    assert np.all(np.abs(out["m"] - g["m"]) <= HALF_ATOL * np.maximum(1.0, np.abs(g["m"])))
+
+
+@pytest.mark.parametrize("name", ["cfg3_mini", "cfg4_mini", "cfg4_2layer", "cfg2_mini"])
+def test_bf16_mode_runs_close(name):
+    """bf16 keeps 8 mantissa bits in the residual stream: looser bound, reported for completeness."""
+    net, pos, n, g = load_case(name)
+    nw = network.Network(net, "precision=bf16,max_batch=%d" % n)
+    out = nw.evaluate(pos["masks"][:n], pos["values"][:n])
+    nw.close()
+    worst, agree, decided = _softmax_err_and_argmax(out["policy"], g["policy"], pos, n)
+    assert worst <= HALF_ATOL
+    assert np.abs(out["q"] - g["q"]).max() <= 1e-2
+
+
+def test_full_bt4_class_net_fp16_against_reference():
+    """The full 15-layer BT4-class network on the recorded reference outputs."""
+    net, pos, n, g = load_case("cfg4")
+    nw = network.Network(net, "precision=fp16,max_batch=%d" % n)
+    out = nw.evaluate(pos["masks"][:n], pos["values"][:n])
+    assert nw.device_status() == 0
+    nw.close()
+    worst, agree, decided = _softmax_err_and_argmax(out["policy"], g["policy"], pos, n)
+    assert worst <= HALF_ATOL and agree == decided
+    assert np.abs(out["q"] - g["q"]).max() <= HALF_ATOL
+    assert np.abs(out["d"] - g["d"]).max() <= HALF_ATOL
+    assert np.all(np.abs(out["m"] - g["m"]) <= HALF_ATOL * np.maximum(1.0, np.abs(g["m"])))
+
+
+def test_computation_api_and_batch_shapes():
+    """AddInput one by one, odd batch sizes, and independence of a sample from its batch neighbours."""
+    net, pos, n, g = load_case("cfg4_mini")
+    nw = network.Network(net, "precision=fp32,max_batch=40")
+    ref = nw.evaluate(pos["masks"][:n], pos["values"][:n])
+    for count in (1, 2, 3, 7, 31):
+        c = nw.new_computation()
+        for i in range(count):
+            c.add_input(pos["masks"][i], pos["values"][i])
+        assert c.get_batch_size() == count
+        c.compute_blocking()
+        for i in range(count):
+            np.testing.assert_allclose(c.policy(i), ref["policy"][i], atol=2e-6)
+            assert abs(c.get_q_val(i) - ref["q"][i]) < 2e-6
+            assert abs(c.get_d_val(i) - ref["d"][i]) < 2e-6
+            assert abs(c.get_m_val(i) - ref["m"][i]) < 2e-6
+            assert c.get_p_val(i, 5) == c.policy(i)[5]
+        c.close()
+    empty = nw.new_computation()
+    empty.compute_blocking()
+    assert empty.get_batch_size() == 0
+    c = nw.new_computation()
+    c.add_inputs(pos["masks"][:32], pos["values"][:32])
+    with pytest.raises(_lib.B200Error, match="max_batch"):
+        c.add_inputs(pos["masks"][:32], pos["values"][:32])
+    nw.close()
+
+
+def test_mlh_option_and_head_errors():
+    net, pos, n, g = load_case("cfg3_mini")
+    nw = network.Network(net, "precision=fp32,max_batch=8,mlh=false")
+    out = nw.evaluate(pos["masks"][:4], pos["values"][:4])
+    assert np.all(out["m"] == 0) and nw.get_capabilities()["moves_left"] == 0
+    nw.close()
+    with pytest.raises(weights.WeightsError):
+        network.Network(net, "policy_head=optimistic")
+    with pytest.raises(_lib.B200Error, match="Invalid GPU Id"):
+        network.Network(net, "gpu=99")
+
+
+def test_large_batch_consistency():
+    """Batch 1024 in fp16 equals the same positions evaluated in chunks (tile tails, many CTAs per GEMM)."""
+    net, pos, n, g = load_case("cfg4_mini")
+    nw = network.Network(net, "precision=fp16,max_batch=1024")
+    masks, values = pos["masks"], pos["values"]
+    big = nw.evaluate(masks, values)
+    small = nw.evaluate(masks[:100], values[:100])
+    assert nw.device_status() == 0
+    nw.close()
+    np.testing.assert_allclose(big["policy"][:100], small["policy"], atol=1e-6)
+    np.testing.assert_allclose(big["q"][:100], small["q"], atol=1e-6)
