@@ -250,22 +250,100 @@ layer_norm_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restr
   }
 }
 
+// Warp-per-row variant for C <= 2048: a lane holds kChunks 16-byte pieces of the row (piece index
+// lane + 32 * i), the reductions are pure shuffles and a 128-thread CTA normalises four rows.
+template <typename T, int kChunks>
+__global__ void __launch_bounds__(128)
+layer_norm_warp_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restrict__ skip,
+                       const float* __restrict__ gamma, const float* __restrict__ beta,
+                       const float* __restrict__ gate_mult, const float* __restrict__ gate_add, int rows, int C,
+                       float alpha, float eps) {
+  const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const T* xr = x + row * C;
+  const T* sr = skip ? skip + row * C : nullptr;
+  Vec8<T> a[kChunks], b[kChunks];
+#pragma unroll
+  for (int i = 0; i < kChunks; ++i) {
+    const int c = (lane + 32 * i) * 8;
+    if (c < C) {
+      a[i] = *reinterpret_cast<const Vec8<T>*>(xr + c);
+      if (sr) b[i] = *reinterpret_cast<const Vec8<T>*>(sr + c);
+    }
+  }
+  float v[kChunks][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kChunks; ++i) {
+    const int c = (lane + 32 * i) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float t = 0.f;
+      if (c < C) {
+        t = to_f(a[i].v[j]) * alpha;
+        if (sr) t += to_f(b[i].v[j]);
+      }
+      v[i][j] = t;
+      sum += t;
+    }
+  }
+  const float mean = warp_sum(sum) / C;
+  float var = 0.f;
+#pragma unroll
+  for (int i = 0; i < kChunks; ++i) {
+    const int c = (lane + 32 * i) * 8;
+    if (c < C) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float d = v[i][j] - mean;
+        var += d * d;
+      }
+    }
+  }
+  var = warp_sum(var) / C;
+  const float den = 1.0f / sqrtf(var + eps);
+  const int sq = int(row & 63);
+#pragma unroll
+  for (int i = 0; i < kChunks; ++i) {
+    const int c = (lane + 32 * i) * 8;
+    if (c < C) {
+      const float4 g0 = *reinterpret_cast<const float4*>(gamma + c), g1 = *reinterpret_cast<const float4*>(gamma + c + 4);
+      const float4 b0 = *reinterpret_cast<const float4*>(beta + c), b1 = *reinterpret_cast<const float4*>(beta + c + 4);
+      const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      Vec8<T> o;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float t = bb[j] + gg[j] * (v[i][j] - mean) * den;
+        if (gate_mult) t = t * gate_mult[(long long)sq * C + c + j] + gate_add[(long long)sq * C + c + j];
+        o.v[j] = from_f<T>(t);
+      }
+      *reinterpret_cast<Vec8<T>*>(out + row * C + c) = o;
+    }
+  }
+}
+
 template <typename T>
 cudaError_t launch_layer_norm(T* out, const T* x, const T* skip, const float* gamma, const float* beta,
                               const float* gate_mult, const float* gate_add, int rows, int C, float alpha,
                               float eps, cudaStream_t s) {
   if (rows <= 0) return cudaSuccess;
   if (C % 8 != 0 || C > 8192) return cudaErrorInvalidValue;
+#define LNW_LAUNCH(CH)                                                                                      \
+  layer_norm_warp_kernel<T, CH><<<ceil_div(rows, 4), 128, 0, s>>>(out, x, skip, gamma, beta, gate_mult,     \
+                                                                   gate_add, rows, C, alpha, eps)
 #define LN_LAUNCH(TH, ST)                                                                          \
   layer_norm_kernel<T, TH, ST><<<rows, TH, 0, s>>>(out, x, skip, gamma, beta, gate_mult, gate_add, C, \
                                                     alpha, eps)
-  if (C <= 256) LN_LAUNCH(32, 1);
-  else if (C <= 512) LN_LAUNCH(64, 1);
-  else if (C <= 1024) LN_LAUNCH(128, 1);
-  else if (C <= 2048) LN_LAUNCH(256, 1);
+  if (C <= 256) LNW_LAUNCH(1);
+  else if (C <= 512) LNW_LAUNCH(2);
+  else if (C <= 1024) LNW_LAUNCH(4);
+  else if (C <= 2048) LNW_LAUNCH(8);
   else if (C <= 4096) LN_LAUNCH(256, 2);
   else LN_LAUNCH(256, 4);
 #undef LN_LAUNCH
+#undef LNW_LAUNCH
   return cudaGetLastError();
 }
 

@@ -51,6 +51,13 @@ template <typename T>
 cudaError_t launch_attention(const T* q, const T* k, const T* v, long long ld, const T* bias, T* out,
                              long long ldo, int n, int heads, int depth, float scale, cudaStream_t s);
 
+// Tensor-core version of the same operator for 16-bit storage and depth 32 or 64 (attention_tc.cu).
+bool attention_tc_supported(long long ld, long long ldo, int depth, const void* q, const void* k, const void* v,
+                            const void* bias, const void* out);
+template <typename T>
+cudaError_t launch_attention_tc(const T* q, const T* k, const T* v, long long ld, const T* bias, T* out,
+                                long long ldo, int n, int heads, int depth, float scale, cudaStream_t s);
+
 // Attention policy: promotion logits + gather to 1858 (network_blas.cc:873-914).
 // logits: fp32 [n][64*64] (already scaled), kp: [n*64][dm] keys, w4: fp32 [4][dm].
 template <typename T>

@@ -806,8 +806,17 @@ struct Net : NetBase {
     launches++;
     // algorithmic bytes: read Q, K, V (+ bias), write the head outputs
     span_begin(st, K_ATTENTION, (double)R * E * sizeof(T) * 4 + (bias ? (double)n * H * 4096 * sizeof(T) : 0.0));
-    CK(launch_attention<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
-                           1.0f / sqrtf((float)depth), st));  // :352-439
+    bool done = false;
+    if constexpr (sizeof(T) == 2) {
+      if (use_tc && attention_tc_supported(3 * E, E, depth, s.qkv, s.qkv + E, s.qkv + 2 * E, bias, s.att)) {
+        CK(launch_attention_tc<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
+                                  1.0f / sqrtf((float)depth), st));  // :352-439
+        done = true;
+      }
+    }
+    if (!done)
+      CK(launch_attention<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
+                             1.0f / sqrtf((float)depth), st));
     span_end(st);
     gemm(st, s.att, E, e.proj, s.y, E, R, ACT_NONE);           // :441-445
     ln(st, x1, s.y, x, e.ln1g, e.ln1b, R, E, alpha, ln_eps);   // :447-452
