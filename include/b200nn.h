@@ -153,6 +153,12 @@ int b200_op_expand_planes(const void* d_masks, const void* d_values, int n, void
                           int precision, void* stream);
 int b200_op_gemm(const void* A, const void* W, const float* bias, void* C, int M, int N, int K,
                  int activation, int precision, int use_tc, void* stream);
+/* b200_op_policy_attention: tail of the attention policy head for n positions: logits = Q K^T / sqrt(dm)
+ *   per position (64x64), promotion offsets from the rank-8 keys and `w4` ([4][dm], fp32), and the gather of
+ *   the 1858 move logits (network_blas.cc:850-914).  q, k: [n*64][dm] in `precision`; scratch_logits: n*4096
+ *   floats of device memory the caller provides; policy: [n][1858] fp32. */
+int b200_op_policy_attention(const void* q, const void* k, const float* w4, int dm, int n, float* scratch_logits,
+                             float* policy, int precision, void* stream);
 int b200_op_layer_norm(void* out, const void* x, const void* skip, const float* gamma,
                        const float* beta, int rows, int C, float alpha, float eps, int precision,
                        void* stream);

@@ -93,4 +93,7 @@ cudaError_t launch_bias_skip_act(const T* x, const float* bias, const T* skip, T
 template <typename T>
 cudaError_t launch_nhwc_to_nchw(const T* x, T* y, int C, int n, cudaStream_t s);
 
+// Host copy of the 1858-entry attention-policy gather table (slot in the 64*64 + 8*24 raw vector per move).
+const short* attn_policy_src_table();
+
 }  // namespace b200

@@ -119,6 +119,9 @@ static const Tables& tables() {
   return t;
 }
 
+// Host copy of the attention-policy gather table (1858 slots), shared with other translation units.
+const short* attn_policy_src_table() { return tables().attn_src.data(); }
+
 }  // namespace b200
 
 using namespace b200;
@@ -1257,6 +1260,41 @@ int b200_op_gemm(const void* A, const void* W, const float* bias, void* C, int M
   auto run = [&](auto tag) -> int {
     using T = decltype(tag);
     B200_CUDA(launch_gemm_simt<T>(p, (cudaStream_t)stream));
+    return B200_OK;
+  };
+  return by_precision(precision, [&] { return run(float()); }, [&] { return run(__half()); },
+                      [&] { return run(__nv_bfloat16()); });
+}
+
+int b200_op_policy_attention(const void* q, const void* k, const float* w4, int dm, int n, float* scratch_logits,
+                             float* policy, int precision, void* stream) {
+  if (n < 0 || dm <= 0 || (n > 0 && (!q || !k || !w4 || !scratch_logits || !policy))) {
+    set_error("b200_op_policy_attention: bad argument");
+    return B200_ERR_INVALID;
+  }
+  if (n == 0) return B200_OK;
+  // Gather table in device memory, uploaded once per device.
+  static std::mutex mu;
+  static short* d_src[64] = {nullptr};
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!d_src[dev & 63]) {
+      B200_CUDA(cudaMalloc(&d_src[dev & 63], 1858 * sizeof(short)));
+      B200_CUDA(cudaMemcpy(d_src[dev & 63], attn_policy_src_table(), 1858 * sizeof(short), cudaMemcpyHostToDevice));
+    }
+  }
+  const short* src = d_src[dev & 63];
+  auto run = [&](auto tag) -> int {
+    using T = decltype(tag);
+    GemmParams p;
+    p.A = q; p.lda = dm; p.strideA = 64LL * dm;
+    p.W = k; p.ldw = dm; p.strideW = 64LL * dm;
+    p.C = scratch_logits; p.ldc = 64; p.strideC = 4096; p.out_f32 = true;
+    p.M = 64; p.N = 64; p.K = dm; p.batch = n; p.scale = 1.0f / sqrtf((float)dm);
+    B200_CUDA(launch_gemm_simt<T>(p, (cudaStream_t)stream));
+    B200_CUDA(launch_policy_attn_gather<T>(scratch_logits, (const T*)k, w4, dm, src, n, policy, (cudaStream_t)stream));
     return B200_OK;
   };
   return by_precision(precision, [&] { return run(float()); }, [&] { return run(__half()); },

@@ -85,3 +85,34 @@ def test_layer_norm(lib, prec, C):
                             bet.cpu().numpy(), 1e-3)
     tol = {0: 2e-5, 1: 4e-3, 2: 3e-2}[prec]
     assert np.abs(out.float().cpu().numpy() - ref).max() <= tol
+
+
+def _policy_reference(q, k, w4):
+    """Attention-policy tail restated with the oracle's table (network_blas.cc:850-914)."""
+    from oracle import tables
+    n, _, dm = q.shape
+    logits = np.matmul(q, k.transpose(0, 2, 1)) / np.sqrt(np.float32(dm))
+    off = np.einsum("njk,ik->nij", k[:, 56:64, :], w4)
+    off[:, :3, :] += off[:, 3:4, :]
+    promo = logits[:, 48:56, 56:64][:, :, :, None] + off[:, :3, :].transpose(0, 2, 1)[:, None, :, :]
+    raw = np.concatenate([logits.reshape(n, 4096), promo.reshape(n, 192)], axis=1)
+    pmap = tables.attn_policy_map()
+    out = np.zeros((n, 1858), np.float32)
+    out[:, pmap[pmap >= 0]] = raw[:, pmap >= 0]
+    return out
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+@pytest.mark.parametrize("n,dm", [(1, 64), (5, 96), (33, 256)])
+def test_policy_attention_op(lib, prec, n, dm):
+    torch.manual_seed(n * dm)
+    q = torch.randn(n, 64, dm, device="cuda").to(DT[prec])
+    k = torch.randn(n, 64, dm, device="cuda").to(DT[prec])
+    w4 = torch.randn(4, dm, device="cuda") * 0.1
+    scratch = torch.empty(n, 4096, device="cuda")
+    pol = torch.zeros(n, 1858, device="cuda")
+    _lib.check(lib.b200_op_policy_attention(q.data_ptr(), k.data_ptr(), w4.data_ptr(), dm, n, scratch.data_ptr(),
+                                            pol.data_ptr(), prec, None))
+    torch.cuda.synchronize()
+    want = _policy_reference(q.float().cpu().numpy(), k.float().cpu().numpy(), w4.cpu().numpy())
+    assert np.abs(pol.cpu().numpy() - want).max() <= 2e-4 * max(1.0, np.abs(want).max())
