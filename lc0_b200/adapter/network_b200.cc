@@ -1,0 +1,245 @@
+// lc0 plug-in for the B200 backend: the one translation unit that includes lc0 headers.
+//
+// It derives lczero::Network / lczero::NetworkComputation (src/neural/network.h:56-126), flattens the
+// decoded weights (lczero::MultiHeadWeights, src/neural/network_legacy.h:178-229) into the named tensors
+// the C ABI of include/b200nn.h expects, and registers the factory with REGISTER_NETWORK
+// (src/neural/factory.h:111-142) under the names "b200" (fp16), "b200-bf16" and "b200-fp32".
+// Build: add this file to lc0's source list and link libb200nn.so; this file is GPL-3
+// like lc0 because it includes lc0 headers, the library behind the C ABI contains no lc0 code.
+//
+// Options (parsed like the reference CUDA backend's, src/neural/backends/cuda/network_cuda.cc:210-254):
+//   gpu=<id>  max_batch=<n> (default 1024)  slots=<n> (concurrent computations, default 2)
+//   policy_head=<name>  value_head=<name>  mlh=<bool>  tensor_cores=<bool>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "include/b200nn.h"
+#include "neural/factory.h"
+#include "neural/network_legacy.h"
+#include "neural/tables/activation_function.h"
+#include "utils/exception.h"
+
+namespace lczero {
+namespace {
+
+void Check(int rc) {
+  if (rc != B200_OK) throw Exception(std::string("b200 backend: ") + b200_last_error());
+}
+
+class B200Network;
+
+class B200Computation : public NetworkComputation {
+ public:
+  explicit B200Computation(b200_net* net, bool wdl, bool mlh) : wdl_(wdl), mlh_(mlh) {
+    Check(b200_comp_create(net, &comp_));
+  }
+  ~B200Computation() override { b200_comp_destroy(comp_); }
+
+  void AddInput(InputPlanes&& input) override {
+    if (input.size() != static_cast<size_t>(kInputPlanes)) throw Exception("b200 backend: expected 112 input planes");
+    uint64_t masks[kInputPlanes];
+    float values[kInputPlanes];
+    for (int i = 0; i < kInputPlanes; ++i) {
+      masks[i] = input[i].mask;
+      values[i] = input[i].value;
+    }
+    Check(b200_comp_add_input(comp_, masks, values));
+  }
+  void ComputeBlocking() override { Check(b200_comp_compute(comp_)); }
+  int GetBatchSize() const override { return b200_comp_batch_size(comp_); }
+  float GetQVal(int sample) const override { return b200_comp_q(comp_, sample); }
+  float GetDVal(int sample) const override { return wdl_ ? b200_comp_d(comp_, sample) : 0.0f; }
+  float GetMVal(int sample) const override { return mlh_ ? b200_comp_m(comp_, sample) : 0.0f; }
+  float GetPVal(int sample, int move_id) const override { return b200_comp_p(comp_, sample, move_id); }
+
+ private:
+  b200_comp* comp_ = nullptr;
+  bool wdl_, mlh_;
+};
+
+class Builder {
+ public:
+  Builder() { Check(b200_builder_create(&b_)); }
+  ~Builder() { b200_builder_destroy(b_); }
+  void Int(const char* key, long long v) { Check(b200_builder_set_int(b_, key, v)); }
+  void Tensor(const std::string& name, const std::vector<float>& v) {
+    if (!v.empty()) Check(b200_builder_add_tensor(b_, name.c_str(), v.data(), v.size()));
+  }
+  void Conv(const std::string& p, const BaseWeights::ConvBlock& c) {
+    Tensor(p + ".weights", c.weights);  // batch norm is already folded by ConvBlock's constructor
+    Tensor(p + ".biases", c.biases);
+  }
+  void Encoder(const std::string& p, const BaseWeights::EncoderLayer& e) {
+    Tensor(p + ".mha.q_w", e.mha.q_w);
+    Tensor(p + ".mha.q_b", e.mha.q_b);
+    Tensor(p + ".mha.k_w", e.mha.k_w);
+    Tensor(p + ".mha.k_b", e.mha.k_b);
+    Tensor(p + ".mha.v_w", e.mha.v_w);
+    Tensor(p + ".mha.v_b", e.mha.v_b);
+    Tensor(p + ".mha.dense_w", e.mha.dense_w);
+    Tensor(p + ".mha.dense_b", e.mha.dense_b);
+    if (e.mha.has_smolgen) {
+      const auto& s = e.mha.smolgen;
+      Tensor(p + ".mha.smolgen.compress", s.compress);
+      Tensor(p + ".mha.smolgen.dense1_w", s.dense1_w);
+      Tensor(p + ".mha.smolgen.dense1_b", s.dense1_b);
+      Tensor(p + ".mha.smolgen.ln1_gammas", s.ln1_gammas);
+      Tensor(p + ".mha.smolgen.ln1_betas", s.ln1_betas);
+      Tensor(p + ".mha.smolgen.dense2_w", s.dense2_w);
+      Tensor(p + ".mha.smolgen.dense2_b", s.dense2_b);
+      Tensor(p + ".mha.smolgen.ln2_gammas", s.ln2_gammas);
+      Tensor(p + ".mha.smolgen.ln2_betas", s.ln2_betas);
+    }
+    Tensor(p + ".ln1_gammas", e.ln1_gammas);
+    Tensor(p + ".ln1_betas", e.ln1_betas);
+    Tensor(p + ".ffn.dense1_w", e.ffn.dense1_w);
+    Tensor(p + ".ffn.dense1_b", e.ffn.dense1_b);
+    Tensor(p + ".ffn.dense2_w", e.ffn.dense2_w);
+    Tensor(p + ".ffn.dense2_b", e.ffn.dense2_b);
+    Tensor(p + ".ln2_gammas", e.ln2_gammas);
+    Tensor(p + ".ln2_betas", e.ln2_betas);
+  }
+  b200_builder* get() const { return b_; }
+
+ private:
+  b200_builder* b_ = nullptr;
+};
+
+class B200Network : public Network {
+ public:
+  B200Network(const WeightsFile& file, const OptionsDict& options, int precision)
+      : capabilities_{file.format().network_format().input(), file.format().network_format().output(),
+                      file.format().network_format().moves_left()} {
+    const auto nf = file.format().network_format();
+    using NF = pblczero::NetworkFormat;
+    const MultiHeadWeights weights(file.weights());
+
+    const std::string policy_head = options.GetOrDefault<std::string>("policy_head", "vanilla");
+    if (weights.policy_heads.count(policy_head) == 0)
+      throw Exception("The policy head you specified '" + policy_head + "' does not exist in this net.");
+    const std::string value_head = options.GetOrDefault<std::string>("value_head", "winner");
+    if (weights.value_heads.count(value_head) == 0)
+      throw Exception("The value head you specified '" + value_head + "' does not exist in this net.");
+    const auto& ph = weights.policy_heads.at(policy_head);
+    const auto& vh = weights.value_heads.at(value_head);
+
+    // Activation resolution as in the reference backends (network_blas.cc:1010-1028).
+    const int default_act =
+        nf.default_activation() == NF::DEFAULT_ACTIVATION_MISH ? ACTIVATION_MISH : ACTIVATION_RELU;
+    const int smolgen_act =
+        nf.smolgen_activation() == NF::ACTIVATION_DEFAULT ? default_act : static_cast<int>(nf.smolgen_activation());
+    const int ffn_act =
+        nf.ffn_activation() == NF::ACTIVATION_DEFAULT ? default_act : static_cast<int>(nf.ffn_activation());
+
+    Builder b;
+    b.Int("input_format", nf.input());
+    b.Int("output_format", nf.output());
+    b.Int("network", nf.network());
+    b.Int("policy", nf.policy());
+    b.Int("value", nf.value());
+    b.Int("moves_left", nf.moves_left());
+    b.Int("input_embedding", nf.input_embedding());
+    b.Int("default_activation", default_act);
+    b.Int("smolgen_activation", smolgen_act);
+    b.Int("ffn_activation", ffn_act);
+    b.Int("headcount", weights.encoder_head_count);
+    b.Int("pol_headcount", ph.pol_encoder_head_count);
+
+    b.Conv("input", weights.input);
+    for (size_t i = 0; i < weights.residual.size(); ++i) {
+      const auto& r = weights.residual[i];
+      const std::string p = "residual." + std::to_string(i);
+      b.Conv(p + ".conv1", r.conv1);
+      b.Conv(p + ".conv2", r.conv2);
+      if (r.has_se) {
+        b.Tensor(p + ".se.w1", r.se.w1);
+        b.Tensor(p + ".se.b1", r.se.b1);
+        b.Tensor(p + ".se.w2", r.se.w2);
+        b.Tensor(p + ".se.b2", r.se.b2);
+      }
+    }
+    b.Tensor("ip_emb_preproc_w", weights.ip_emb_preproc_w);
+    b.Tensor("ip_emb_preproc_b", weights.ip_emb_preproc_b);
+    b.Tensor("ip_emb_w", weights.ip_emb_w);
+    b.Tensor("ip_emb_b", weights.ip_emb_b);
+    b.Tensor("ip_emb_ln_gammas", weights.ip_emb_ln_gammas);
+    b.Tensor("ip_emb_ln_betas", weights.ip_emb_ln_betas);
+    b.Tensor("ip_mult_gate", weights.ip_mult_gate);
+    b.Tensor("ip_add_gate", weights.ip_add_gate);
+    b.Tensor("ip_emb_ffn.dense1_w", weights.ip_emb_ffn.dense1_w);
+    b.Tensor("ip_emb_ffn.dense1_b", weights.ip_emb_ffn.dense1_b);
+    b.Tensor("ip_emb_ffn.dense2_w", weights.ip_emb_ffn.dense2_w);
+    b.Tensor("ip_emb_ffn.dense2_b", weights.ip_emb_ffn.dense2_b);
+    b.Tensor("ip_emb_ffn_ln_gammas", weights.ip_emb_ffn_ln_gammas);
+    b.Tensor("ip_emb_ffn_ln_betas", weights.ip_emb_ffn_ln_betas);
+    for (size_t i = 0; i < weights.encoder.size(); ++i) b.Encoder("encoder." + std::to_string(i), weights.encoder[i]);
+    b.Tensor("smolgen_w", weights.smolgen_w);
+    b.Conv("moves_left", weights.moves_left);
+    b.Tensor("ip_mov_w", weights.ip_mov_w);
+    b.Tensor("ip_mov_b", weights.ip_mov_b);
+    b.Tensor("ip1_mov_w", weights.ip1_mov_w);
+    b.Tensor("ip1_mov_b", weights.ip1_mov_b);
+    b.Tensor("ip2_mov_w", weights.ip2_mov_w);
+    b.Tensor("ip2_mov_b", weights.ip2_mov_b);
+
+    b.Tensor("policy.ip_pol_w", ph.ip_pol_w);
+    b.Tensor("policy.ip_pol_b", ph.ip_pol_b);
+    b.Tensor("policy.ip2_pol_w", ph.ip2_pol_w);
+    b.Tensor("policy.ip2_pol_b", ph.ip2_pol_b);
+    b.Tensor("policy.ip3_pol_w", ph.ip3_pol_w);
+    b.Tensor("policy.ip3_pol_b", ph.ip3_pol_b);
+    b.Tensor("policy.ip4_pol_w", ph.ip4_pol_w);
+    b.Conv("policy.policy1", ph.policy1);
+    b.Conv("policy.policy", ph.policy);
+    for (size_t i = 0; i < ph.pol_encoder.size(); ++i)
+      b.Encoder("policy.pol_encoder." + std::to_string(i), ph.pol_encoder[i]);
+    b.Conv("value.value", vh.value);
+    b.Tensor("value.ip_val_w", vh.ip_val_w);
+    b.Tensor("value.ip_val_b", vh.ip_val_b);
+    b.Tensor("value.ip1_val_w", vh.ip1_val_w);
+    b.Tensor("value.ip1_val_b", vh.ip1_val_b);
+    b.Tensor("value.ip2_val_w", vh.ip2_val_w);
+    b.Tensor("value.ip2_val_b", vh.ip2_val_b);
+
+    b200_net_options opt{};
+    opt.gpu = options.GetOrDefault<int>("gpu", 0);
+    opt.max_batch = options.GetOrDefault<int>("max_batch", 1024);
+    opt.slots = options.GetOrDefault<int>("slots", 2);
+    opt.precision = precision;
+    opt.mlh = options.GetOrDefault<bool>("mlh", true) ? 1 : 0;
+    opt.flags = options.GetOrDefault<bool>("tensor_cores", true) ? 0 : B200_FLAG_NO_TENSOR_CORES;
+    Check(b200_net_create(b.get(), &opt, &net_));
+    Check(b200_net_get_info(net_, &info_));
+    if (!info_.has_mlh) capabilities_.moves_left = NF::MOVES_LEFT_NONE;
+  }
+  ~B200Network() override { b200_net_destroy(net_); }
+
+  const NetworkCapabilities& GetCapabilities() const override { return capabilities_; }
+  std::unique_ptr<NetworkComputation> NewComputation() override {
+    return std::make_unique<B200Computation>(net_, info_.wdl != 0, info_.has_mlh != 0);
+  }
+  int GetThreads() const override { return 2; }  // one thread fills a batch while the other computes
+  bool IsCpu() const override { return false; }
+  int GetMiniBatchSize() const override { return 2 * info_.sm_count; }
+  int GetPreferredBatchStep() const override { return 1; }
+
+ private:
+  NetworkCapabilities capabilities_;
+  b200_net* net_ = nullptr;
+  b200_net_info info_{};
+};
+
+template <int kPrecision>
+std::unique_ptr<Network> MakeB200Network(const std::optional<WeightsFile>& w, const OptionsDict& options) {
+  if (!w) throw Exception("The b200 backend requires a network file.");
+  return std::make_unique<B200Network>(*w, options, kPrecision);
+}
+
+// Below the reference's own GPU backends (cuda-auto is 104) so that adding the plug-in never changes the default.
+REGISTER_NETWORK("b200", MakeB200Network<B200_PREC_FP16>, 90)
+REGISTER_NETWORK("b200-bf16", MakeB200Network<B200_PREC_BF16>, 89)
+REGISTER_NETWORK("b200-fp32", MakeB200Network<B200_PREC_FP32>, 88)
+
+}  // namespace
+}  // namespace lczero

@@ -1,0 +1,80 @@
+"""The backend driven by lc0 itself: the reference's factory, loader and `check` decorator.
+
+Uses oracle/_ref/ref_eval and lc0_ref (the reference's sources compiled with the plug-in TU
+lc0_b200/adapter/network_b200.cc by `python oracle/build_ref.py --adapter`); skipped when they are absent.
+"""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, load_case
+from lc0_b200 import mknet
+
+pytestmark = pytest.mark.gpu
+REF = os.path.join(ROOT, "oracle", "_ref")
+
+
+def _has_plugin():
+    exe = os.path.join(REF, "lc0_ref")
+    if not os.path.exists(exe):
+        return False
+    r = subprocess.run([exe, "backendbench", "--help"], capture_output=True, text=True)
+    return "b200" in r.stdout + r.stderr
+
+
+needs_plugin = pytest.mark.skipif(not _has_plugin(), reason="lc0 with the b200 plug-in is not built")
+
+
+def _write_pos(path, pos, n):
+    with open(path, "wb") as f:
+        f.write(b"LC0POS1\0")
+        f.write(np.array([n, int(pos["input_format"])], "<i4").tobytes())
+        f.write(np.ascontiguousarray(pos["masks"][:n], "<u8").tobytes())
+        f.write(np.ascontiguousarray(pos["values"][:n], "<f4").tobytes())
+        f.write(np.zeros(2 * n, "<i4").tobytes())
+        f.write(np.full((n, 256), -1, "<i2").tobytes())
+
+
+@needs_plugin
+@pytest.mark.parametrize("name", ["cfg4_mini", "cfg2_mini"])
+def test_registered_backend_through_lc0_factory(tmp_path, name):
+    net, pos, n, g = load_case(name)
+    npath, ppath, opath = str(tmp_path / "n.pb.gz"), str(tmp_path / "p.pos"), str(tmp_path / "o.bin")
+    mknet.write_net(name, npath)
+    _write_pos(ppath, pos, n)
+    r = subprocess.run([os.path.join(REF, "ref_eval"), "b200-fp32", npath, ppath, opath, "max_batch=64"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    raw = np.fromfile(opath, "<f4", offset=12)
+    pol = raw[:n * 1858].reshape(n, 1858)
+    q, d, m = raw[n * 1858:].reshape(3, n)
+    scale = np.abs(g["policy"]).max()
+    assert np.abs(pol - g["policy"]).max() <= 1e-5 * scale
+    assert np.abs(q - g["q"]).max() <= 1e-5 and np.abs(d - g["d"]).max() <= 1e-5
+    assert np.abs(m - g["m"]).max() <= 1e-5 * max(1.0, np.abs(g["m"]).max())
+
+
+@needs_plugin
+def test_unknown_option_is_fatal_like_other_backends(tmp_path):
+    npath, ppath = str(tmp_path / "n.pb.gz"), str(tmp_path / "p.pos")
+    mknet.write_net("cfg3_mini", npath)
+    net, pos, n, g = load_case("cfg3_mini")
+    _write_pos(ppath, pos, 2)
+    r = subprocess.run([os.path.join(REF, "ref_eval"), "b200", npath, ppath, "-", "gpu=99"], capture_output=True, text=True)
+    assert r.returncode != 0 and "Invalid GPU Id" in r.stderr
+
+
+@needs_plugin
+def test_lc0_backendbench_and_check_decorator(tmp_path):
+    npath = str(tmp_path / "n.pb.gz")
+    mknet.write_net("cfg3_mini", npath)
+    exe = os.path.join(REF, "lc0_ref")
+    r = subprocess.run([exe, "backendbench", "--weights=" + npath, "--backend=check",
+                        "--backend-opts=mode=check,freq=1.0,atol=1e-4,rtol=1e-3,(backend=b200-fp32),(backend=blas)",
+                        "--batches=2", "--start-batch-size=8", "--max-batch-size=16", "--batch-step=8"],
+                       capture_output=True, text=True, timeout=300)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-2000:]
+    assert "Check passed" in out or "passed" in out.lower(), out[-2000:]
