@@ -159,6 +159,20 @@ int b200_op_gemm(const void* A, const void* W, const float* bias, void* C, int M
  *   floats of device memory the caller provides; policy: [n][1858] fp32. */
 int b200_op_policy_attention(const void* q, const void* k, const float* w4, int dm, int n, float* scratch_logits,
                              float* policy, int precision, void* stream);
+/* b200_op_policy_attention_static: the same operator for callers that cannot hand over scratch memory.
+ *   It has no counterpart in the reference.  lc0's search threads call the backend from a hot loop where a
+ *   cudaMalloc would synchronise the device, and some hosts give every free byte to their own pool at
+ *   start-up; neither can allocate n*4096 floats per call.  Here the scratch is a fixed array inside the
+ *   library (4 MiB, held by every GPU that loads the library until the process exits), so the call
+ *   allocates nothing, on the device or through any allocating library routine.
+ *   Limit: n <= B200_STATIC_POLICY_MAX_POSITIONS, larger batches are refused with B200_ERR_INVALID.
+ *   The first call on each device looks up the array's device address and uploads the gather table; make
+ *   that first call before any stream capture begins.  All calls share the one array (it keeps the last
+ *   call's logits; nothing in it needs clearing), so two calls whose kernels may overlap on the GPU race:
+ *   issue them on one stream or order them yourself. */
+#define B200_STATIC_POLICY_MAX_POSITIONS 256
+int b200_op_policy_attention_static(const void* q, const void* k, const float* w4, int dm, int n, float* policy,
+                                    int precision, void* stream);
 int b200_op_layer_norm(void* out, const void* x, const void* skip, const float* gamma,
                        const float* beta, int rows, int C, float alpha, float eps, int precision,
                        void* stream);

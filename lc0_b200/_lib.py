@@ -75,6 +75,7 @@ SIGNATURES = {
     "b200_op_expand_planes": (_I, [_P, _P, _I, _P, _I, _P]),
     "b200_op_gemm": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "b200_op_policy_attention": (_I, [_P, _P, _P, _I, _I, _P, _P, _I, _P]),
+    "b200_op_policy_attention_static": (_I, [_P, _P, _P, _I, _I, _P, _I, _P]),
     "b200_op_layer_norm": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _P]),
 }
 
