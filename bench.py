@@ -185,7 +185,7 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from lc0_b200 import mknet, network
+    from lc0_b200 import mknet, network, sharding
 
     torch.cuda.set_device(local_rank)
     if world > 1:
@@ -239,10 +239,7 @@ def main():
     clocks = sampler.stop(t0, t1)
     prof = nw.get_profile(reset=True)
     nw.set_profiling(False)
-    if world > 1:
-        tt = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms = float(tt.item())
+    ms = sharding.gather_max(ms, dist if world > 1 else None)
     value = world * B * args.steps / (ms / 1000.0)
 
     # ---- end-to-end timing through the computation API (host buffers) ----
@@ -262,10 +259,7 @@ def main():
         step_host()
     torch.cuda.synchronize()
     th = time.time() - th0
-    if world > 1:
-        tt = torch.tensor([th], device="cuda", dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        th = float(tt.item())
+    th = sharding.gather_max(th, dist if world > 1 else None)
     e2e_value = world * B * args.steps / th
 
     if rank == 0:
