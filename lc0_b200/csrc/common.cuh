@@ -45,12 +45,14 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float
 }
 
 // Activations in fp32, formulas as in src/neural/backends/shared/activation.cc:51-94.
+// Fast variant for 16-bit storage: one ex2.approx and one rcp.approx per element.
 __device__ __forceinline__ float mish_f(float v) {
-  const float e = __expf(v);
+  const float e = __expf(fminf(v, 30.0f));  // keeps n finite; mish(v) == v to fp32 precision beyond that
   const float n = e * e + 2.0f * e;
-  const float d = v / (n + 2.0f);
+  const float d = __fdividef(v, n + 2.0f);
   return v <= -0.125f ? n * d : v - 2.0f * d;
 }
+__device__ __forceinline__ float swish_f(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 // Accurate variants (expf) are used in the fp32 verification mode.
 template <bool kFast>
 __device__ __forceinline__ float activate(float v, int act) {
@@ -70,7 +72,7 @@ __device__ __forceinline__ float activate(float v, int act) {
       const float alpha = 1.67326324f, scale = 1.05070098f;
       return v > 0.f ? scale * v : scale * alpha * ((kFast ? __expf(v) : expf(v)) - 1.0f);
     }
-    case ACT_SWISH: return v / (1.0f + (kFast ? __expf(-v) : expf(-v)));
+    case ACT_SWISH: return kFast ? swish_f(v) : v / (1.0f + expf(-v));
     default: return v;
   }
 }

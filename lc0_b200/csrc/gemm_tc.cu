@@ -80,6 +80,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// 4D tile load (channels, file, rank, position); coordinates may lie outside the tensor, those elements are
+// zero-filled, which is exactly the zero padding of a same-padded convolution on the 8x8 board.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                    reinterpret_cast<uint64_t>(map)),
@@ -127,6 +136,47 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+
+// ---- CTA-pair (cta_group::2) helpers -------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion is signalled on a barrier that may live in the peer CTA of the pair (no multicast:
+// each CTA of the pair fetches its own half of the operands).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                     uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with the 128-byte
 // swizzle (what a TMA box of 64 16-bit elements x R rows with CU_TENSOR_MAP_SWIZZLE_128B produces):
 // start address >> 4 in bits [0,14), stride between 8-row groups (1024 B) >> 4 in bits [32,46),
@@ -158,7 +208,7 @@ __device__ __forceinline__ void apply_activation(float (&v)[N], int act) {
       break;
     case ACT_SWISH:
 #pragma unroll
-      for (int j = 0; j < N; ++j) v[j] = v[j] / (1.0f + __expf(-v[j]));
+      for (int j = 0; j < N; ++j) v[j] = swish_f(v[j]);
       break;
     case ACT_NONE:
       break;
@@ -200,8 +250,8 @@ struct TcParams {
   float scale, alpha;
   int out_f32;
   int* status;
-  int debug;
   int tma_store;  // 1: 16-bit output staged in shared memory and written with TMA stores
+  int conv_cblocks;  // > 0: 3x3 convolution, number of 64-channel blocks of the input (k_blocks = 9 * conv_cblocks)
 };
 
 template <typename T, int BN>
@@ -225,7 +275,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
   const int tiles = m_tiles * n_tiles;
-  const int k_blocks = (p.K + BK - 1) / BK;
+  const int k_blocks = p.conv_cblocks > 0 ? 9 * p.conv_cblocks : (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -262,11 +312,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t ph = (it / S) & 1;
           if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, 1)) { ok = false; break; }
           const uint32_t fb = smem_u32(&full_bar[s]);
-          if (p.debug & 8) { mbar_arrive(fb); continue; }
           mbar_expect_tx(fb, Cfg::kStageBytes);
           const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
-          tma_load_2d(sa, &tmap_a, kb * BK, m0, fb);
-          tma_load_2d(sa + BM * BK * 2, &tmap_w, kb * BK, n0, fb);
+          if (p.conv_cblocks > 0) {
+            // k-block = (filter tap, 64-channel block): the A tile is the board shifted by the tap.
+            const int tap = kb / p.conv_cblocks, cb = kb - tap * p.conv_cblocks;
+            tma_load_4d(sa, &tmap_a, cb * BK, tap % 3 - 1, tap / 3 - 1, m0 >> 6, fb);
+            tma_load_2d(sa + BM * BK * 2, &tmap_w, cb * BK, tap * p.N + n0, fb);
+          } else {
+            tma_load_2d(sa, &tmap_a, kb * BK, m0, fb);
+            tma_load_2d(sa + BM * BK * 2, &tmap_w, kb * BK, n0, fb);
+          }
         }
       }
     }
@@ -291,7 +347,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint64_t bdesc = make_smem_desc(sa + BM * BK * 2);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            if (p.debug & 4) break;
             // advancing 16 elements (32 bytes) along K inside the swizzle row = +2 in the address field
             tcgen05_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
@@ -361,12 +416,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (p.debug & 2) break;
         uint32_t r[32];
         tmem_ld32(trow + c0, r);
         tmem_ld_wait();
         const int nb = n0 + c0;
-        if (m < p.M && nb < p.N && !(p.debug & 1)) {
+        if (m < p.M && nb < p.N) {
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -439,6 +493,205 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs (one TPC) computes a 256x256 tile with
+// tcgen05.mma.cta_group::2 (M = 256: 128 rows per CTA; each CTA stages its 128 rows of A and its 128
+// of the 256 W rows, so a CTA moves 32 KB per k-block instead of 48 KB).  The MMAs are issued by the
+// even CTA; operand arrival from both CTAs is counted on its `full` barriers, stage release and
+// accumulator hand-over are signalled to both CTAs with one tcgen05.commit per CTA, and the odd CTA's
+// epilogue warps release the accumulator with remote mbarrier arrivals.
+// ------------------------------------------------------------------------------------------------
+struct PairCfg {
+  static constexpr int BN = 256;
+  static constexpr int kStageBytes = (BM + BN / 2) * BK * 2;  // 32 KB per CTA
+  static constexpr int kStages = 6;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kEpiBytes = 2 * BM * 128;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 256;
+};
+
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                    const __grid_constant__ CUtensorMap tmap_c, const TcParams p) {
+  using Cfg = PairCfg;
+  constexpr int S = Cfg::kStages;
+  constexpr int BN = Cfg::BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi_mem = smem + S * Cfg::kStageBytes;
+  uint8_t* bar_mem = epi_mem + Cfg::kEpiBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_mem);  // [S]  waited on by the even CTA only
+  uint64_t* empty_bar = full_bar + S;                          // [S]  per CTA
+  uint64_t* tfull_bar = empty_bar + S;                         // [2]  per CTA
+  uint64_t* tempty_bar = tfull_bar + 2;                        // [2]  even CTA: 4 local + 4 remote arrivals
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epi_ok = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int m_tiles = (p.M + 2 * BM - 1) / (2 * BM), n_tiles = (p.N + BN - 1) / BN;
+  const int tiles = m_tiles * n_tiles;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(smem_u32(&full_bar[i]), 1);
+      mbar_init(smem_u32(&empty_bar[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&tfull_bar[i]), 1);
+      mbar_init(smem_u32(&tempty_bar[i]), 8);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // one warp of each CTA of the pair takes part in the allocation
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)Cfg::kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = pair; t < tiles && ok; t += pairs) {
+        const int m0 = (t / n_tiles) * (2 * BM) + (int)rank * BM;
+        const int n0 = (t % n_tiles) * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, 1)) { ok = false; break; }
+          const uint32_t fb_local = smem_u32(&full_bar[s]);
+          if (rank == 0) mbar_expect_tx(fb_local, 2 * Cfg::kStageBytes);  // both CTAs' bytes land on this barrier
+          const uint32_t fb = mapa(fb_local, 0);
+          const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
+          tma_load_2d_pair(sa, &tmap_a, kb * BK, m0, fb);
+          tma_load_2d_pair(sa + BM * BK * 2, &tmap_w, kb * BK, n0, fb);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (even CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (FmtCode<T>::v << 7) | (FmtCode<T>::v << 10) |
+                                 ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int t = pair; t < tiles && ok; t += pairs, ++tile_it) {
+        const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
+        if (!mbar_wait(smem_u32(&tempty_bar[acc]), aph ^ 1, abort_flag, 2)) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, 3)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
+          const uint64_t adesc = make_smem_desc(sa);
+          const uint64_t bdesc = make_smem_desc(sa + BM * BK * 2);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            tcgen05_mma_f16_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          const uint32_t eb = smem_u32(&empty_bar[s]);
+          tcgen05_commit_pair(mapa(eb, 0));  // frees the stage in both CTAs once the MMAs have read it
+          tcgen05_commit_pair(mapa(eb, 1));
+        }
+        if (ok) {
+          const uint32_t tb = smem_u32(&tfull_bar[acc]);
+          tcgen05_commit_pair(mapa(tb, 0));
+          tcgen05_commit_pair(mapa(tb, 1));
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
+    const int quarter = warp & 3;
+    uint32_t tile_it = 0, chunk_it = 0;
+    for (int t = pair; t < tiles; t += pairs, ++tile_it) {
+      const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
+      const int m0 = (t / n_tiles) * (2 * BM) + (int)rank * BM, n0 = (t % n_tiles) * BN;
+      if (warp == 2 && lane == 0) *epi_ok = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4) ? 1 : 0;
+      epilogue_barrier();
+      if (!*epi_ok) break;
+      tcgen05_fence_after();
+      const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      const int row = quarter * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 64) {
+        const int nb = n0 + c0;
+        if (nb >= p.N) break;  // uniform over the CTA
+        uint8_t* buf = epi_mem + (chunk_it & 1) * (BM * 128);
+        if (warp == 2 && lane == 0) tma_store_wait_read1();
+        epilogue_barrier();
+        uint32_t r0[32], r1[32];
+        tmem_ld32(trow + c0, r0);
+        tmem_ld32(trow + c0 + 32, r1);
+        tmem_ld_wait();
+        float b0 = 0.f, b1 = 0.f;
+        if (p.bias) {
+          if (nb + lane < p.N) b0 = __ldg(p.bias + nb + lane);
+          if (nb + 32 + lane < p.N) b1 = __ldg(p.bias + nb + 32 + lane);
+        }
+        float v[64];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          v[j] = fmaf(__uint_as_float(r0[j]), p.scale, __shfl_sync(0xffffffffu, b0, j));
+          v[32 + j] = fmaf(__uint_as_float(r1[j]), p.scale, __shfl_sync(0xffffffffu, b1, j));
+        }
+        apply_activation(v, p.act);
+        uint8_t* srow = buf + row * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          __align__(16) T o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = from_f<T>(v[c * 8 + i]);
+          *reinterpret_cast<uint4*>(srow + ((c ^ (row & 7)) << 4)) = *reinterpret_cast<const uint4*>(o);
+        }
+        fence_async_smem();
+        epilogue_barrier();
+        if (warp == 2 && lane == 0) {
+          tma_store_2d(&tmap_c, nb, m0, smem_u32(buf));
+          tma_store_commit();
+        }
+        ++chunk_it;
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&tempty_bar[acc]), 0));
+    }
+    if (warp == 2 && lane == 0) tma_store_wait_all();
+  }
+
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, 200 + *abort_flag);
+    __syncthreads();
+  }
+  cluster_sync_all();  // neither CTA releases tensor or shared memory while its peer may still touch it
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)Cfg::kTmemCols)
+                 : "memory");
+  }
+}
+
 // ---- host side ------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -493,6 +746,26 @@ cudaError_t get_map(const void* ptr, long long ld, int rows, int cols, int box_r
   return cudaSuccess;
 }
 
+// 4D map over a token-major activation [positions][8][8][channels]; box = 64 channels x 8 x 8 x 2 boards
+// (128 GEMM rows).  Not cached: convolution inputs are few and the encode call is a host-side pure function.
+cudaError_t make_board_map(const void* ptr, int channels, int positions, int prec, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_encode) return cudaErrorNotReady;
+  cuuint64_t dims[4] = {(cuuint64_t)channels, 8, 8, (cuuint64_t)positions};
+  cuuint64_t strides[3] = {(cuuint64_t)channels * 2, (cuuint64_t)channels * 16, (cuuint64_t)channels * 128};
+  cuuint32_t box[4] = {(cuuint32_t)BK, 8, 8, 2};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = g_encode(out, prec == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                        const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (4D) failed with CUresult " + std::to_string((int)r));
+    return cudaErrorInvalidValue;
+  }
+  return cudaSuccess;
+}
+
 template <typename T, int BN>
 cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream_t s) {
   using Cfg = TileCfg<BN>;
@@ -509,9 +782,16 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
   }
   CUtensorMap ma, mw;
   const int prec = TypeTag<T>::prec;
-  cudaError_t e = get_map(g.A, g.lda, g.M, g.K, BM, prec, &ma);
-  if (e != cudaSuccess) return e;
-  e = get_map(g.W, g.ldw, g.N, g.K, BN, prec, &mw);
+  cudaError_t e;
+  if (g.conv_cin > 0) {
+    e = make_board_map(g.A, g.conv_cin, g.M / 64, prec, &ma);
+    if (e != cudaSuccess) return e;
+    e = get_map(g.W, g.conv_cin, 9 * g.N, g.conv_cin, BN, prec, &mw);
+  } else {
+    e = get_map(g.A, g.lda, g.M, g.K, BM, prec, &ma);
+    if (e != cudaSuccess) return e;
+    e = get_map(g.W, g.ldw, g.N, g.K, BN, prec, &mw);
+  }
   if (e != cudaSuccess) return e;
   const bool tma_store = !g.out_f32 && !g.skip && (g.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(g.C) & 15) == 0;
   CUtensorMap mc = ma;
@@ -524,10 +804,45 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
   p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.skip = g.skip; p.ldskip = g.ldskip;
   p.M = g.M; p.N = g.N; p.K = g.K; p.act = g.act; p.scale = g.scale; p.alpha = g.alpha;
   p.out_f32 = g.out_f32 ? 1 : 0; p.status = status;
-  { const char* d = getenv("B200_GEMM_DEBUG"); p.debug = d ? atoi(d) : 0; }
+  p.conv_cblocks = g.conv_cin > 0 ? ceil_div(g.conv_cin, BK) : 0;
   const int tiles = ceil_div(g.M, BM) * ceil_div(g.N, BN);
   const int grid = tiles < sm_count ? tiles : sm_count;
   gemm_tc_kernel<T, BN><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, p);
+  return cudaGetLastError();
+}
+
+
+template <typename T>
+cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStream_t s) {
+  using Cfg = PairCfg;
+  static std::atomic<unsigned long long> attr_mask{0};
+  int dev = 0;
+  cudaError_t de = cudaGetDevice(&dev);
+  if (de != cudaSuccess) return de;
+  if (!(attr_mask.load() >> (dev & 63) & 1ull)) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_mask.fetch_or(1ull << (dev & 63));
+  }
+  CUtensorMap ma, mw, mc;
+  const int prec = TypeTag<T>::prec;
+  cudaError_t e = get_map(g.A, g.lda, g.M, g.K, BM, prec, &ma);
+  if (e != cudaSuccess) return e;
+  e = get_map(g.W, g.ldw, g.N, g.K, Cfg::BN / 2, prec, &mw);
+  if (e != cudaSuccess) return e;
+  e = get_map(g.C, g.ldc, g.M, g.N, BM, prec, &mc);
+  if (e != cudaSuccess) return e;
+  TcParams p;
+  p.tma_store = 1;
+  p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.skip = nullptr; p.ldskip = 0;
+  p.M = g.M; p.N = g.N; p.K = g.K; p.act = g.act; p.scale = g.scale; p.alpha = g.alpha;
+  p.out_f32 = 0; p.status = status;
+  p.conv_cblocks = 0;
+  const int tiles = ceil_div(g.M, 2 * BM) * ceil_div(g.N, Cfg::BN);
+  const int max_pairs = sm_count / 2;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  gemm_tc_pair_kernel<T><<<2 * pairs, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, p);
   return cudaGetLastError();
 }
 
@@ -547,6 +862,8 @@ cudaError_t gemm_tc_init() {
 
 bool gemm_tc_supported(const GemmParams& p) {
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (p.conv_cin > 0)
+    return p.batch == 1 && p.M >= 64 && (p.M % 64) == 0 && p.N >= 8 && (p.conv_cin % 8) == 0 && al16(p.A) && al16(p.W);
   return p.batch == 1 && p.M >= 1 && p.N >= 8 && p.K >= 8 && (p.K % 8) == 0 && (p.lda % 8) == 0 &&
          (p.ldw % 8) == 0 && al16(p.A) && al16(p.W);
 }
@@ -555,6 +872,14 @@ template <typename T>
 cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaStream_t s) {
   if (p.M <= 0 || p.N <= 0) return cudaSuccess;
   if (!gemm_tc_supported(p)) return cudaErrorInvalidValue;
+  // Large problems with 16-bit output go to the CTA-pair kernel (256x256 tiles).
+  static const bool pair_enabled = [] {
+    const char* e = getenv("B200_GEMM_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  const bool tma_store_ok = !p.out_f32 && !p.skip && (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
+  if (pair_enabled && tma_store_ok && p.conv_cin == 0 && p.M >= 512 && p.N > 128)
+    return launch_pair<T>(p, status, sm_count, s);
   // Wide tiles amortise the A-tile loads; narrow problems take the smallest tile that covers N.
   if (p.N > 128) return launch_bn<T, 256>(p, status, sm_count, s);
   if (p.N > 64) return launch_bn<T, 128>(p, status, sm_count, s);

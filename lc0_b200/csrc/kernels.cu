@@ -312,11 +312,20 @@ layer_norm_warp_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __
       const float4 b0 = *reinterpret_cast<const float4*>(beta + c), b1 = *reinterpret_cast<const float4*>(beta + c + 4);
       const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
       const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      float gm[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f}, ga[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (gate_mult) {
+        const float4 m0 = *reinterpret_cast<const float4*>(gate_mult + (long long)sq * C + c);
+        const float4 m1 = *reinterpret_cast<const float4*>(gate_mult + (long long)sq * C + c + 4);
+        const float4 a0 = *reinterpret_cast<const float4*>(gate_add + (long long)sq * C + c);
+        const float4 a1 = *reinterpret_cast<const float4*>(gate_add + (long long)sq * C + c + 4);
+        gm[0] = m0.x; gm[1] = m0.y; gm[2] = m0.z; gm[3] = m0.w; gm[4] = m1.x; gm[5] = m1.y; gm[6] = m1.z; gm[7] = m1.w;
+        ga[0] = a0.x; ga[1] = a0.y; ga[2] = a0.z; ga[3] = a0.w; ga[4] = a1.x; ga[5] = a1.y; ga[6] = a1.z; ga[7] = a1.w;
+      }
       Vec8<T> o;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float t = bb[j] + gg[j] * (v[i][j] - mean) * den;
-        if (gate_mult) t = t * gate_mult[(long long)sq * C + c + j] + gate_add[(long long)sq * C + c + j];
+        t = t * gm[j] + ga[j];
         o.v[j] = from_f<T>(t);
       }
       *reinterpret_cast<Vec8<T>*>(out + row * C + c) = o;

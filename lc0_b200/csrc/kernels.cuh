@@ -16,6 +16,9 @@ struct GemmParams {
   int act = ACT_NONE;
   float scale = 1.0f, alpha = 1.0f;
   bool out_f32 = false;  // C holds float even when the storage type is 16-bit
+  // 3x3 convolution mode of the tensor-core kernel (conv_cin > 0): A is the token-major activation
+  // [M = positions*64][conv_cin] (8x8 boards), W is [9][N][conv_cin] (tap-major filters), K is ignored.
+  int conv_cin = 0;
 };
 
 template <typename T> cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t s);

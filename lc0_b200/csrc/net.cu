@@ -782,6 +782,25 @@ struct Net : NetBase {
     CK(launch_gemm_simt<T>(p, st));
     span_end(st);
   }
+  // 3x3 convolution: tensor-core kernel (TMA board tiles with zero-filled halo) for 16-bit storage, FMA otherwise.
+  void conv3(cudaStream_t st, const T* x, const ConvW<T>& c, const float* bias, T* y, int n, int act) {
+    if constexpr (sizeof(T) == 2) {
+      GemmParams p;
+      p.A = x; p.W = c.w; p.bias = bias; p.C = y; p.ldc = c.cout; p.M = n * 64; p.N = c.cout; p.K = 9 * c.cin;
+      p.act = act; p.conv_cin = c.cin; p.lda = c.cin; p.ldw = c.cin;
+      if (use_tc && (c.cout % 8) == 0 && gemm_tc_supported(p)) {
+        launches++;
+        span_begin(st, K_GEMM_TC, 2.0 * p.M * (double)p.N * p.K);
+        CK(launch_gemm_tc<T>(p, d_status, sm_count, st));
+        span_end(st);
+        return;
+      }
+    }
+    launches++;
+    span_begin(st, K_GEMM_FMA, 2.0 * n * 64 * (double)c.cout * 9 * c.cin);
+    CK(launch_conv3x3<T>(x, c.cin, c.w, bias, y, c.cout, n, act, st));
+    span_end(st);
+  }
   void ln(cudaStream_t st, T* out, const T* x, const T* skip, const float* g, const float* b, int rows, int Cc,
           float a, float eps, const float* gm = nullptr, const float* ga = nullptr) {
     launches++;
@@ -837,14 +856,11 @@ struct Net : NetBase {
     if (!res.empty() || !attn_body) {  // network_blas.cc:564-601
       launches++;
       CK(launch_expand_tokens<T>(d_masks, d_values, n, nullptr, (const T*)nullptr, 0, 112, s.tokens, st));
-      launches++;
-      CK(launch_conv3x3<T>(s.tokens, 112, conv_in.w, conv_in.b, s.x, C, n, act_default, st));
+      conv3(st, s.tokens, conv_in, conv_in.b, s.x, n, act_default);
       T *cur = s.x, *tmp = s.x1, *tmp2 = s.y;
       for (const auto& r : res) {
-        launches++;
-        CK(launch_conv3x3<T>(cur, C, r.c1.w, r.c1.b, tmp, C, n, act_default, st));
-        launches++;
-        CK(launch_conv3x3<T>(tmp, C, r.c2.w, nullptr, tmp2, C, n, ACT_NONE, st));
+        conv3(st, cur, r.c1, r.c1.b, tmp, n, act_default);
+        conv3(st, tmp, r.c2, nullptr, tmp2, n, ACT_NONE);
         launches++;
         if (r.se) {
           CK(launch_se<T>(tmp2, r.c2.b, cur, r.se_w1, r.se_b1, r.se_w2, r.se_b2, tmp, C, r.se_k, n, act_default, st));
@@ -911,11 +927,9 @@ struct Net : NetBase {
       launches++;
       CK(launch_policy_attn_gather<T>(s.logits, s.pk, pol_w4, pol_dm, d_attn_src, n, d_policy, st));
     } else if (policy_fmt == POLICY_CONVOLUTION) {
-      launches++;
       T* t1 = s.y;  // free: the tower ping-pongs between x and x1
-      CK(launch_conv3x3<T>(flow, C, pol_conv1.w, pol_conv1.b, t1, C, n, act_default, st));
-      launches++;
-      CK(launch_conv3x3<T>(t1, C, pol_conv2.w, pol_conv2.b, s.praw, pol_planes, n, ACT_NONE, st));
+      conv3(st, flow, pol_conv1, pol_conv1.b, t1, n, act_default);
+      conv3(st, t1, pol_conv2, pol_conv2.b, s.praw, n, ACT_NONE);
       launches++;
       CK(launch_policy_gather<T>(s.praw, 64LL * pol_planes, d_conv_src, n, d_policy, st));
     } else {
