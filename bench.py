@@ -31,6 +31,16 @@ sys.path.insert(0, ROOT)
 METRIC = "nn_evals_per_sec"
 UNIT = "evals/s"
 NET = "cfg4"
+# configuration -> (network, batch per step, position set, precision, description)
+CONFIGS = {
+    "cfg1": ("cfg1", 64, 1, "fp32", "residual CNN 10x128 + SE, classical policy, WDL"),
+    "cfg2": ("cfg2", 256, 1, "fp16", "residual CNN 20x256 + SE, convolutional policy (80 planes), WDL + moves-left"),
+    "cfg3": ("cfg3", 512, 2, "fp16", "attention body 10 layers, embedding 256, 8 heads, dff 512, Mish, attention policy"),
+    "cfg4": ("cfg4", 1024, 2, "fp16", "BT4-class net: 15 encoder layers, embedding 1024, 32 heads, dff 1536, smolgen "
+                                      "32/256/256, attention policy, WDL + moves-left"),
+    "cfg5": ("cfg4", 8192, 2, "fp16", "BT4-class net (as cfg4), 8192 positions per step split evenly over the GPUs, "
+                                      "50/50 opening / late-middlegame positions"),
+}
 
 
 def read_peaks():
@@ -90,8 +100,11 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def load_positions(rank, batch):
-    name = "positions_fmt2_uniform.npz" if rank % 2 == 0 else "positions_fmt2_split.npz"
+def load_positions(rank, batch, fmt=2, split=False):
+    if fmt == 1:
+        name = "positions_fmt1_uniform.npz"
+    else:
+        name = "positions_fmt2_split.npz" if (split or rank % 2 == 1) else "positions_fmt2_uniform.npz"
     p = np.load(os.path.join(ROOT, "tests", "golden", name))
     masks, values = p["masks"], p["values"]
     reps = -(-batch // masks.shape[0])
@@ -169,8 +182,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--batch", type=int, default=1024)
-    ap.add_argument("--precision", default="fp16")
+    ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS))
+    ap.add_argument("--batch", type=int, default=0, help="positions per GPU per step (default: the configuration's)")
+    ap.add_argument("--precision", default="", help="fp16 | bf16 | fp32 (default: the configuration's)")
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -191,12 +205,17 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    net = mknet.make_net(NET)
+    net_name, cfg_batch, pos_fmt, cfg_prec, cfg_desc = CONFIGS[args.config]
+    if not args.precision:
+        args.precision = cfg_prec
+    if not args.batch:
+        args.batch = cfg_batch // world if args.config == "cfg5" else cfg_batch
+    net = mknet.make_net(net_name)
     nw = network.Network(net, dict(gpu=local_rank, max_batch=args.batch, precision=args.precision))
     del net
     info = nw.info
     B = args.batch
-    masks, values = load_positions(rank, B)
+    masks, values = load_positions(rank, B, pos_fmt, split=args.config == "cfg5")
     d_masks = torch.from_numpy(masks.view(np.int64)).cuda()
     d_values = torch.from_numpy(values).cuda()
     d_policy = torch.empty(B, 1858, dtype=torch.float32, device="cuda")
@@ -262,6 +281,28 @@ def main():
     th = sharding.gather_max(th, dist if world > 1 else None)
     e2e_value = world * B * args.steps / th
 
+    # ---- latency of one batch-256 computation through the same API (p50 / p99 over 40 calls) ----
+    lat = None
+    if B >= 256:
+        m256, v256 = masks[:256], values[:256]
+
+        def step256():
+            c = nw.new_computation()
+            c.add_inputs(m256, v256)
+            c.compute_blocking()
+            c.get_q_val(0)
+            c.close()
+
+        for _ in range(3):
+            step256()
+        samples = []
+        for _ in range(40):
+            t_a = time.perf_counter()
+            step256()
+            samples.append((time.perf_counter() - t_a) * 1000.0)
+        lat = {"batch": 256, "p50_ms": float(np.percentile(samples, 50)), "p99_ms": float(np.percentile(samples, 99)),
+               "calls": len(samples), "path": "NewComputation/AddInput/ComputeBlocking/GetQVal with host buffers"}
+
     if rank == 0:
         peaks = read_peaks()
         g = prof["gemm_tc"]
@@ -281,12 +322,12 @@ def main():
                             "launches": v["launches"]}
         for k in ("gemm_tc", "gemm_fma", "other"):
             other.setdefault(k, {})["ms_per_step"] = prof[k]["ms"] / args.steps
+            other[k]["launches"] = prof[k]["launches"]
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": args.precision, "data": "synthetic",
-            "config": {"workload": "BT4-class net: 15 encoder layers, embedding 1024, 32 heads, dff 1536, smolgen "
-                                   "32/256/256, attention policy, WDL + moves-left; batch %d per GPU" % B,
+            "config": {"workload": "%s: %s; batch %d per GPU" % (args.config, cfg_desc, B),
                        "batch_per_gpu": B, "global_batch": B * world, "parallelism": "replicated weights, batch split",
                        "l2": "per-step working set (weights %.2f GB + activations) exceeds the 126 MB L2"
                              % (info.weight_bytes / 1e9)},
@@ -296,10 +337,11 @@ def main():
             "gpu_launches": int(launches),
             "roofline": roofline,
             "kernel_classes": other,
+            "latency": lat,
             "flops_per_eval": info.flops_per_position,
             "model_tflops": value / world * info.flops_per_position / 1e12,
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and args.config in ("cfg4", "cfg5"):
             line["cpu_baseline"] = cpu_reference(32, 4)
         print(json.dumps(line), flush=True)
     nw.close()

@@ -748,10 +748,100 @@ se_kernel(const T* __restrict__ x, const float* __restrict__ conv_bias, const T*
   }
 }
 
+// Vectorised variant (C % 8 == 0): 16-byte loads, the sample's 64 x C tile is kept in shared memory between the
+// pooling pass and the scaling pass, partial sums over square groups are reduced through shared memory.
+template <typename T, bool kFast>
+__global__ void __launch_bounds__(256)
+se_vec_kernel(const T* __restrict__ x, const float* __restrict__ conv_bias, const T* __restrict__ skip,
+              const float* __restrict__ w1, const float* __restrict__ b1, const float* __restrict__ w2,
+              const float* __restrict__ b2, T* __restrict__ y, int C, int se_k, int act) {
+  extern __shared__ __align__(16) uint8_t se_sm[];
+  T* xs = reinterpret_cast<T*>(se_sm);                          // [64][C]
+  float* partial = reinterpret_cast<float*>(xs + 64 * C);       // [nsqg][C]  (nsqg * C == 2048)
+  float* pool = partial + 2048;                                 // [C]
+  float* hid = pool + C;                                        // [se_k]
+  float* z = hid + se_k;                                        // [2C]
+  const int n = blockIdx.x, tid = threadIdx.x;
+  const int cgs = C / 8;            // channel groups of 8
+  const int nsqg = 256 / cgs;       // square groups working in parallel
+  const int cg = tid % cgs, sqg = tid / cgs;
+  const T* xg = x + (long long)n * 64 * C;
+  if (sqg < nsqg) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int sq = sqg; sq < 64; sq += nsqg) {
+      const Vec8<T> v = *reinterpret_cast<const Vec8<T>*>(xg + sq * C + cg * 8);
+      *reinterpret_cast<Vec8<T>*>(xs + sq * C + cg * 8) = v;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += to_f(v.v[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) partial[sqg * C + cg * 8 + j] = acc[j];
+  }
+  __syncthreads();
+  for (int c = tid; c < C; c += 256) {
+    float a = 0.f;
+    for (int g = 0; g < nsqg; ++g) a += partial[g * C + c];
+    pool[c] = a / 64.0f + conv_bias[c];
+  }
+  __syncthreads();
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int o = warp; o < se_k; o += 8) {
+    float a = 0.f;
+    for (int c = lane; c < C; c += 32) a = fmaf(pool[c], w1[o * C + c], a);
+    a = warp_sum(a);
+    if (lane == 0) hid[o] = activate<false>(a + b1[o], act);
+  }
+  __syncthreads();
+  for (int o = tid; o < 2 * C; o += 256) {
+    float a = b2[o];
+    for (int c = 0; c < se_k; ++c) a = fmaf(hid[c], w2[o * se_k + c], a);
+    // first C outputs become the sigmoid gate, the rest the shift (with the gate times the conv bias folded in)
+    z[o] = a;
+  }
+  __syncthreads();
+  for (int c = tid; c < C; c += 256) {
+    const float g = 1.0f / (1.0f + expf(-z[c]));
+    z[C + c] += g * conv_bias[c];
+    z[c] = g;
+  }
+  __syncthreads();
+  const T* sg = skip + (long long)n * 64 * C;
+  T* yg = y + (long long)n * 64 * C;
+  if (sqg < nsqg) {
+    float g[8], sh[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      g[j] = z[cg * 8 + j];
+      sh[j] = z[C + cg * 8 + j];
+    }
+    for (int sq = sqg; sq < 64; sq += nsqg) {
+      const Vec8<T> v = *reinterpret_cast<const Vec8<T>*>(xs + sq * C + cg * 8);
+      const Vec8<T> r = *reinterpret_cast<const Vec8<T>*>(sg + sq * C + cg * 8);
+      Vec8<T> o;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o.v[j] = from_f<T>(activate<kFast>(g[j] * to_f(v.v[j]) + to_f(r.v[j]) + sh[j], act));
+      *reinterpret_cast<Vec8<T>*>(yg + sq * C + cg * 8) = o;
+    }
+  }
+}
+
 template <typename T>
 cudaError_t launch_se(const T* x, const float* conv_bias, const T* skip, const float* w1, const float* b1,
                       const float* w2, const float* b2, T* y, int C, int se_k, int n, int act, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
+  const int cgs = C / 8;
+  if (C % 8 == 0 && cgs <= 256 && 256 % cgs == 0) {
+    const size_t smem = (size_t)64 * C * sizeof(T) + (size_t)(2048 + 3 * C + se_k) * sizeof(float);
+    if (smem <= 200 * 1024) {
+      if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(se_vec_kernel<T, (sizeof(T) == 2)>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+      }
+      se_vec_kernel<T, (sizeof(T) == 2)><<<n, 256, smem, s>>>(x, conv_bias, skip, w1, b1, w2, b2, y, C, se_k, act);
+      return cudaGetLastError();
+    }
+  }
   const size_t smem = (size_t)(3 * C + se_k) * sizeof(float);
   se_kernel<T, (sizeof(T) == 2)><<<n, 256, smem, s>>>(x, conv_bias, skip, w1, b1, w2, b2, y, C, se_k, act);
   return cudaGetLastError();

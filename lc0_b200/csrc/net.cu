@@ -782,6 +782,14 @@ struct Net : NetBase {
     CK(launch_gemm_simt<T>(p, st));
     span_end(st);
   }
+  // Any other kernel: counted, and timed under the class "other" (work = algorithmic bytes).
+  template <typename F>
+  void other(cudaStream_t st, double bytes, F&& launch) {
+    launches++;
+    span_begin(st, K_OTHER, bytes);
+    CK(launch());
+    span_end(st);
+  }
   // 3x3 convolution: tensor-core kernel (TMA board tiles with zero-filled halo) for 16-bit storage, FMA otherwise.
   void conv3(cudaStream_t st, const T* x, const ConvW<T>& c, const float* bias, T* y, int n, int act) {
     if constexpr (sizeof(T) == 2) {
@@ -854,19 +862,19 @@ struct Net : NetBase {
     int body_ch = 0;
     CK(cudaMemsetAsync(d_qdm, 0, (size_t)n * 3 * sizeof(float), st));
     if (!res.empty() || !attn_body) {  // network_blas.cc:564-601
-      launches++;
-      CK(launch_expand_tokens<T>(d_masks, d_values, n, nullptr, (const T*)nullptr, 0, 112, s.tokens, st));
+      other(st, (double)R * 112 * sizeof(T), [&] {
+        return launch_expand_tokens<T>(d_masks, d_values, n, nullptr, (const T*)nullptr, 0, 112, s.tokens, st);
+      });
       conv3(st, s.tokens, conv_in, conv_in.b, s.x, n, act_default);
       T *cur = s.x, *tmp = s.x1, *tmp2 = s.y;
       for (const auto& r : res) {
         conv3(st, cur, r.c1, r.c1.b, tmp, n, act_default);
         conv3(st, tmp, r.c2, nullptr, tmp2, n, ACT_NONE);
-        launches++;
-        if (r.se) {
-          CK(launch_se<T>(tmp2, r.c2.b, cur, r.se_w1, r.se_b1, r.se_w2, r.se_b2, tmp, C, r.se_k, n, act_default, st));
-        } else {
-          CK(launch_bias_skip_act<T>(tmp2, r.c2.b, cur, tmp, C, R, act_default, st));
-        }
+        other(st, 3.0 * R * C * sizeof(T), [&] {
+          return r.se ? launch_se<T>(tmp2, r.c2.b, cur, r.se_w1, r.se_b1, r.se_w2, r.se_b2, tmp, C, r.se_k, n,
+                                     act_default, st)
+                      : launch_bias_skip_act<T>(tmp2, r.c2.b, cur, tmp, C, R, act_default, st);
+        });
         std::swap(cur, tmp);
       }
       flow = cur;
@@ -875,14 +883,15 @@ struct Net : NetBase {
     }
     if (attn_body) {  // network_blas.cc:603-721
       if (emb_fmt == EMB_PE_DENSE) {
-        launches++;
-        CK(launch_expand_pre12<T>(d_masks, d_values, n, s.pre, st));
+        other(st, (double)n * 768 * sizeof(T), [&] { return launch_expand_pre12<T>(d_masks, d_values, n, s.pre, st); });
         gemm(st, s.pre, 768, emb_pre, s.pe, 64 * pe_ch, n, ACT_NONE);
-        launches++;
-        CK(launch_expand_tokens<T>(d_masks, d_values, n, nullptr, s.pe, pe_ch, cin, s.tokens, st));
+        other(st, (double)R * (cin + pe_ch) * sizeof(T), [&] {
+          return launch_expand_tokens<T>(d_masks, d_values, n, nullptr, s.pe, pe_ch, cin, s.tokens, st);
+        });
       } else {
-        launches++;
-        CK(launch_expand_tokens<T>(d_masks, d_values, n, pos_enc, (const T*)nullptr, pe_ch, cin, s.tokens, st));
+        other(st, (double)R * cin * sizeof(T), [&] {
+          return launch_expand_tokens<T>(d_masks, d_values, n, pos_enc, (const T*)nullptr, pe_ch, cin, s.tokens, st);
+        });
       }
       T *x = s.x, *x1 = s.x1;
       gemm(st, s.tokens, cin, emb, x, E, R, act_default);
@@ -893,8 +902,7 @@ struct Net : NetBase {
         ln(st, x1, s.y, x, emb_ffn_lng, emb_ffn_lnb, R, E, alpha, 1e-3f);
         std::swap(x, x1);
       } else if (gate_mult) {
-        launches++;
-        CK(launch_gate<T>(x, gate_mult, gate_add, R, E, st));
+        other(st, 2.0 * R * E * sizeof(T), [&] { return launch_gate<T>(x, gate_mult, gate_add, R, E, st); });
       }
       for (const auto& e : enc) encoder_layer(s, e, n, x, x1);
       flow = x;
@@ -904,14 +912,16 @@ struct Net : NetBase {
     // ---- value head (network_blas.cc:725-772) ----
     gemm(st, flow, body_ch, val_emb, s.vtok, val_emb.out, R, act_default);
     gemm(st, s.vtok, 64 * val_emb.out, val_fc1, s.vhid, val_fc1.out, n, act_default);
-    launches++;
-    CK(launch_head_final<T>(s.vhid, val_fc1.out, val_w2, val_b2, wdl ? 0 : 1, n, d_qdm, st));
+    other(st, (double)n * val_fc1.out * sizeof(T), [&] {
+      return launch_head_final<T>(s.vhid, val_fc1.out, val_w2, val_b2, wdl ? 0 : 1, n, d_qdm, st);
+    });
     // ---- moves-left head (:775-803) ----
     if (mlh) {
       gemm(st, flow, body_ch, mov_emb, s.mtok, mov_emb.out, R, act_default);
       gemm(st, s.mtok, 64 * mov_emb.out, mov_fc1, s.mhid, mov_fc1.out, n, act_default);
-      launches++;
-      CK(launch_head_final<T>(s.mhid, mov_fc1.out, mov_w2, mov_b2, 2, n, d_qdm, st));
+      other(st, (double)n * mov_fc1.out * sizeof(T), [&] {
+        return launch_head_final<T>(s.mhid, mov_fc1.out, mov_w2, mov_b2, 2, n, d_qdm, st);
+      });
     }
     // ---- policy head (:806-968) ----
     if (policy_fmt == POLICY_ATTENTION) {
@@ -924,14 +934,16 @@ struct Net : NetBase {
       p.C = s.logits; p.ldc = 64; p.strideC = 4096; p.out_f32 = true;
       p.M = 64; p.N = 64; p.K = pol_dm; p.batch = n; p.scale = 1.0f / sqrtf((float)pol_dm);
       run_gemm(st, p);
-      launches++;
-      CK(launch_policy_attn_gather<T>(s.logits, s.pk, pol_w4, pol_dm, d_attn_src, n, d_policy, st));
+      other(st, (double)n * (4096 + 1858) * 4, [&] {
+        return launch_policy_attn_gather<T>(s.logits, s.pk, pol_w4, pol_dm, d_attn_src, n, d_policy, st);
+      });
     } else if (policy_fmt == POLICY_CONVOLUTION) {
       T* t1 = s.y;  // free: the tower ping-pongs between x and x1
       conv3(st, flow, pol_conv1, pol_conv1.b, t1, n, act_default);
       conv3(st, t1, pol_conv2, pol_conv2.b, s.praw, n, ACT_NONE);
-      launches++;
-      CK(launch_policy_gather<T>(s.praw, 64LL * pol_planes, d_conv_src, n, d_policy, st));
+      other(st, (double)n * 1858 * (4 + sizeof(T)), [&] {
+        return launch_policy_gather<T>(s.praw, 64LL * pol_planes, d_conv_src, n, d_policy, st);
+      });
     } else {
       gemm(st, flow, C, pol_c1x1, s.praw, pol_planes, R, act_default);
       gemm(st, s.praw, 64 * pol_planes, pol_fc, nullptr, 1858, n, ACT_NONE, nullptr, 0, 1.f, true, d_policy);
