@@ -27,7 +27,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 16-bit elements = one 128-byte swizzle row
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two groups of four)
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -102,7 +102,13 @@ __device__ __forceinline__ void tma_store_wait_read1() {
 }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// Named barrier of one epilogue group (four warps); group 0 uses barrier 1, group 1 barrier 2.
+__device__ __forceinline__ void epilogue_barrier(int group) {
+  asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read0() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
 __device__ __forceinline__ void tcgen05_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -231,14 +237,6 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
          ((uint32_t)(BM >> 4) << 24);
 }
 
-template <int BN> struct TileCfg {
-  static constexpr int kStageBytes = (BM + BN) * BK * 2;
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
-  static constexpr int kEpiBytes = 2 * BM * 128;  // two 128-row x 128-byte staging buffers for TMA stores
-  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-};
-
 struct TcParams {
   const float* bias;
   void* C;
@@ -253,6 +251,94 @@ struct TcParams {
   int tma_store;  // 1: 16-bit output staged in shared memory and written with TMA stores
   int conv_cblocks;  // > 0: 3x3 convolution, number of 64-channel blocks of the input (k_blocks = 9 * conv_cblocks)
 };
+
+// One 64-column slab of the epilogue fast path, executed by one group of four warps: TMEM -> registers ->
+// scale/bias/activation -> 128B-swizzled staging buffer -> TMA store.  A group alternates between its two
+// buffers; its leader makes sure the store that last used `buf` has finished reading it.
+// Packs two floats into one 32-bit pair of T; fp16 saturates to the largest finite value (min/max on the
+// packed pair after the conversion turns an overflowed inf back into 65504).
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  const __half2 mx = __half2half2(__ushort_as_half((unsigned short)0x7BFF));
+  h = __hmax2(__hmin2(h, mx), __hneg2(mx));
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// One 64-column slab of the epilogue fast path, executed by one group of four warps: TMEM -> registers ->
+// scale/bias/activation -> 128B-swizzled staging buffer -> TMA store.  A group alternates between its two
+// buffers; its leader makes sure the store that last used `buf` has finished reading it.  The 64 bias values
+// of the slab are fetched with two coalesced loads per lane and redistributed through a 256-byte per-warp
+// shared-memory scratch (`wbias`) as broadcast float4 reads.
+template <typename T>
+__device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorMap* tmap_c, uint8_t* buf, int group,
+                                              bool leader, uint32_t taddr, int row, int lane, int m0, int nb,
+                                              float* wbias) {
+  if (p.bias) {
+    wbias[lane] = (nb + lane < p.N) ? __ldg(p.bias + nb + lane) : 0.f;
+    wbias[32 + lane] = (nb + 32 + lane < p.N) ? __ldg(p.bias + nb + 32 + lane) : 0.f;
+  }
+  if (leader) tma_store_wait_read1();  // the store issued two slabs ago (same buffer) has been read out
+  epilogue_barrier(group);             // also orders the wbias writes before the reads below
+  uint32_t r0[32], r1[32];
+  tmem_ld32(taddr, r0);
+  tmem_ld32(taddr + 32, r1);
+  tmem_ld_wait();
+  float v[64];
+  if (p.bias) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      const float4 ba = *reinterpret_cast<const float4*>(wbias + j);
+      const float4 bb = *reinterpret_cast<const float4*>(wbias + 32 + j);
+      v[j] = fmaf(__uint_as_float(r0[j]), p.scale, ba.x);
+      v[j + 1] = fmaf(__uint_as_float(r0[j + 1]), p.scale, ba.y);
+      v[j + 2] = fmaf(__uint_as_float(r0[j + 2]), p.scale, ba.z);
+      v[j + 3] = fmaf(__uint_as_float(r0[j + 3]), p.scale, ba.w);
+      v[32 + j] = fmaf(__uint_as_float(r1[j]), p.scale, bb.x);
+      v[32 + j + 1] = fmaf(__uint_as_float(r1[j + 1]), p.scale, bb.y);
+      v[32 + j + 2] = fmaf(__uint_as_float(r1[j + 2]), p.scale, bb.z);
+      v[32 + j + 3] = fmaf(__uint_as_float(r1[j + 3]), p.scale, bb.w);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      v[j] = __uint_as_float(r0[j]) * p.scale;
+      v[32 + j] = __uint_as_float(r1[j]) * p.scale;
+    }
+  }
+  apply_activation(v, p.act);
+  uint8_t* srow = buf + row * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 o;
+    o.x = pack_pair<T>(v[c * 8 + 0], v[c * 8 + 1]);
+    o.y = pack_pair<T>(v[c * 8 + 2], v[c * 8 + 3]);
+    o.z = pack_pair<T>(v[c * 8 + 4], v[c * 8 + 5]);
+    o.w = pack_pair<T>(v[c * 8 + 6], v[c * 8 + 7]);
+    *reinterpret_cast<uint4*>(srow + ((c ^ (row & 7)) << 4)) = o;
+  }
+  fence_async_smem();
+  epilogue_barrier(group);
+  if (leader) {
+    tma_store_2d(tmap_c, nb, m0, smem_u32(buf));
+    tma_store_commit();
+  }
+}
+
+template <int BN> struct TileCfg {
+  // stages + 64 KB of epilogue staging + 3.3 KB must stay below the 227 KB a CTA may use
+  static constexpr int kStageBytes = (BM + BN) * BK * 2;
+  static constexpr int kStages = BN == 256 ? 3 : (BN == 128 ? 4 : 6);
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int kEpiBytes = 4 * BM * 128;  // 2 groups x 2 staging buffers of 128 rows x 128 bytes
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ +
+                                    2048 /*bias scratch*/;
+};
+
 
 template <typename T, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -271,6 +357,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* epi_ok = abort_flag + 1;
+  float* wbias = reinterpret_cast<float*>(bar_mem + 256) + ((threadIdx.x >> 5) & 7) * 64;  // per-warp scratch
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
@@ -284,7 +371,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&tfull_bar[i]), 1);
-      mbar_init(smem_u32(&tempty_bar[i]), 4);
+      mbar_init(smem_u32(&tempty_bar[i]), 8);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -356,66 +443,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5) ----------------
+    // ---------------- epilogue (warps 2..9: two groups of four warps, alternating 64-column slabs) ----------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
+    const int group = (warp - 2) >> 2;
+    const bool leader = ((warp - 2) & 3) == 0 && lane == 0;
     const T* skip = reinterpret_cast<const T*>(p.skip);
-    uint32_t tile_it = 0, chunk_it = 0;
+    uint8_t* gbuf = epi_mem + group * (2 * BM * 128);
+    uint32_t tile_it = 0, slab_it = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
       const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
       const int m0 = (t / n_tiles) * BM, n0 = (t % n_tiles) * BN;
-      // One thread does the bounded wait and publishes the outcome, so that all four epilogue warps take the
-      // same decision and nobody is left behind at a named barrier.
-      if (warp == 2 && lane == 0) *epi_ok = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4) ? 1 : 0;
-      epilogue_barrier();
-      if (!*epi_ok) break;
+      // One thread per group does the bounded wait and publishes the outcome, so that the four warps of the
+      // group take the same decision and nobody is left behind at a named barrier.
+      if (leader) epi_ok[group] = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4) ? 1 : 0;
+      epilogue_barrier(group);
+      if (!epi_ok[group]) break;
       tcgen05_fence_after();
       const int m = m0 + quarter * 32 + lane;
       const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       if (p.tma_store) {
         // Fast path: 64-column slabs -> registers -> swizzled shared memory -> TMA store (clips the M/N tails).
-        const int row = quarter * 32 + lane;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 64) {
-          const int nb = n0 + c0;
-          if (nb >= p.N) break;  // uniform over the CTA
-          uint8_t* buf = epi_mem + (chunk_it & 1) * (BM * 128);
-          if (warp == 2 && lane == 0) tma_store_wait_read1();  // the store that last read this buffer is done
-          epilogue_barrier();
-          uint32_t r0[32], r1[32];
-          tmem_ld32(trow + c0, r0);
-          tmem_ld32(trow + c0 + 32, r1);
-          tmem_ld_wait();
-          float b0 = 0.f, b1 = 0.f;
-          if (p.bias) {
-            if (nb + lane < p.N) b0 = __ldg(p.bias + nb + lane);
-            if (nb + 32 + lane < p.N) b1 = __ldg(p.bias + nb + 32 + lane);
-          }
-          float v[64];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            v[j] = fmaf(__uint_as_float(r0[j]), p.scale, __shfl_sync(0xffffffffu, b0, j));
-            v[32 + j] = fmaf(__uint_as_float(r1[j]), p.scale, __shfl_sync(0xffffffffu, b1, j));
-          }
-          apply_activation(v, p.act);
-          uint8_t* srow = buf + row * 128;
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            __align__(16) T o[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = from_f<T>(v[c * 8 + i]);
-            *reinterpret_cast<uint4*>(srow + ((c ^ (row & 7)) << 4)) = *reinterpret_cast<const uint4*>(o);
-          }
-          fence_async_smem();
-          epilogue_barrier();
-          if (warp == 2 && lane == 0) {
-            tma_store_2d(&tmap_c, nb, m0, smem_u32(buf));
-            tma_store_commit();
-          }
-          ++chunk_it;
+        for (int c0 = group * 64; c0 < BN; c0 += 128) {
+          if (n0 + c0 >= p.N) break;  // uniform over the group
+          epilogue_slab<T>(p, &tmap_c, gbuf + (slab_it & 1) * (BM * 128), group, leader, trow + c0,
+                           quarter * 32 + lane, lane, m0, n0 + c0, wbias);
+          ++slab_it;
         }
       } else {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = group * 32; c0 < BN; c0 += 64) {
         uint32_t r[32];
         tmem_ld32(trow + c0, r);
         tmem_ld_wait();
@@ -473,7 +530,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
     }
-    if (warp == 2 && lane == 0) tma_store_wait_all();  // stores must complete before the CTA exits
+    if (leader) tma_store_wait_all();  // stores must complete before the CTA exits
   }
 
   __syncwarp();
@@ -505,10 +562,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 struct PairCfg {
   static constexpr int BN = 256;
   static constexpr int kStageBytes = (BM + BN / 2) * BK * 2;  // 32 KB per CTA
-  static constexpr int kStages = 6;
+  static constexpr int kStages = 4;
   static constexpr int kTmemCols = 512;
-  static constexpr int kEpiBytes = 2 * BM * 128;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 256;
+  static constexpr int kEpiBytes = 4 * BM * 128;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 256 + 2048;
 };
 
 template <typename T>
@@ -529,6 +586,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* epi_ok = abort_flag + 1;
+  float* wbias = reinterpret_cast<float*>(bar_mem + 256) + ((threadIdx.x >> 5) & 7) * 64;  // per-warp scratch
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -544,7 +602,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&tfull_bar[i]), 1);
-      mbar_init(smem_u32(&tempty_bar[i]), 8);
+      mbar_init(smem_u32(&tempty_bar[i]), 16);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -617,62 +675,32 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
+    // ---------------- epilogue (warps 2..9 of both CTAs, two groups alternating 64-column slabs) ----------------
     const int quarter = warp & 3;
-    uint32_t tile_it = 0, chunk_it = 0;
+    const int group = (warp - 2) >> 2;
+    const bool leader = ((warp - 2) & 3) == 0 && lane == 0;
+    uint8_t* gbuf = epi_mem + group * (2 * BM * 128);
+    uint32_t tile_it = 0, slab_it = 0;
     for (int t = pair; t < tiles; t += pairs, ++tile_it) {
       const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
       const int m0 = (t / n_tiles) * (2 * BM) + (int)rank * BM, n0 = (t % n_tiles) * BN;
-      if (warp == 2 && lane == 0) *epi_ok = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4) ? 1 : 0;
-      epilogue_barrier();
-      if (!*epi_ok) break;
+      if (leader) epi_ok[group] = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4) ? 1 : 0;
+      epilogue_barrier(group);
+      if (!epi_ok[group]) break;
       tcgen05_fence_after();
       const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-      const int row = quarter * 32 + lane;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 64) {
-        const int nb = n0 + c0;
-        if (nb >= p.N) break;  // uniform over the CTA
-        uint8_t* buf = epi_mem + (chunk_it & 1) * (BM * 128);
-        if (warp == 2 && lane == 0) tma_store_wait_read1();
-        epilogue_barrier();
-        uint32_t r0[32], r1[32];
-        tmem_ld32(trow + c0, r0);
-        tmem_ld32(trow + c0 + 32, r1);
-        tmem_ld_wait();
-        float b0 = 0.f, b1 = 0.f;
-        if (p.bias) {
-          if (nb + lane < p.N) b0 = __ldg(p.bias + nb + lane);
-          if (nb + 32 + lane < p.N) b1 = __ldg(p.bias + nb + 32 + lane);
-        }
-        float v[64];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          v[j] = fmaf(__uint_as_float(r0[j]), p.scale, __shfl_sync(0xffffffffu, b0, j));
-          v[32 + j] = fmaf(__uint_as_float(r1[j]), p.scale, __shfl_sync(0xffffffffu, b1, j));
-        }
-        apply_activation(v, p.act);
-        uint8_t* srow = buf + row * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          __align__(16) T o[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] = from_f<T>(v[c * 8 + i]);
-          *reinterpret_cast<uint4*>(srow + ((c ^ (row & 7)) << 4)) = *reinterpret_cast<const uint4*>(o);
-        }
-        fence_async_smem();
-        epilogue_barrier();
-        if (warp == 2 && lane == 0) {
-          tma_store_2d(&tmap_c, nb, m0, smem_u32(buf));
-          tma_store_commit();
-        }
-        ++chunk_it;
+      for (int c0 = group * 64; c0 < BN; c0 += 128) {
+        if (n0 + c0 >= p.N) break;  // uniform over the group
+        epilogue_slab<T>(p, &tmap_c, gbuf + (slab_it & 1) * (BM * 128), group, leader, trow + c0,
+                         quarter * 32 + lane, lane, m0, n0 + c0, wbias);
+        ++slab_it;
       }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&tempty_bar[acc]), 0));
     }
-    if (warp == 2 && lane == 0) tma_store_wait_all();
+    if (leader) tma_store_wait_all();
   }
 
   __syncwarp();
