@@ -155,6 +155,43 @@ def cpu_reference(sample_positions, repeats, threads=None):
                        % (sample_positions, repeats, NET))
 
 
+def run_reference_cuda(args, rank):
+    """--impl reference-cuda (extra, not part of the driver contract): the reference's own CUDA backend
+    (`cuda-fp16`: cuBLAS GEMMs + its SIMT kernels, built for sm_100 by `oracle/build_ref.py --cuda`) on the same
+    GPU, same network, same batch, through lc0's NetworkComputation API with host buffers."""
+    if rank != 0:
+        return
+    from lc0_b200 import mknet, netproto
+    exe = os.path.join(ROOT, "oracle", "_ref", "ref_eval_cuda")
+    if not os.path.exists(exe):
+        print(json.dumps({"impl": "reference-cuda", "unavailable": "oracle/_ref/ref_eval_cuda is not built"}))
+        return
+    net_name, cfg_batch, pos_fmt, cfg_prec, cfg_desc = CONFIGS[args.config]
+    B = args.batch or cfg_batch
+    backend = "cuda" if (args.precision or cfg_prec) == "fp32" else "cuda-fp16"
+    masks, values = load_positions(0, B, pos_fmt)
+    with tempfile.TemporaryDirectory() as tmp:
+        npath, ppath = os.path.join(tmp, "net.pb"), os.path.join(tmp, "p.pos")
+        netproto.write_net(npath, mknet.make_net(net_name), compress=False)
+        with open(ppath, "wb") as f:
+            f.write(b"LC0POS1\0")
+            f.write(np.array([B, 2], "<i4").tobytes())
+            f.write(masks.astype("<u8").tobytes())
+            f.write(values.astype("<f4").tobytes())
+            f.write(np.zeros(2 * B, "<i4").tobytes())
+            f.write(np.full((B, 256), -1, "<i2").tobytes())
+        r = subprocess.run([exe, backend, npath, ppath, "-", "max_batch=%d" % B, str(max(1, args.steps))],
+                           capture_output=True, text=True, timeout=900)
+    if r.returncode != 0 or "evals_per_s=" not in r.stdout:
+        print(json.dumps({"impl": "reference-cuda", "unavailable": (r.stderr or r.stdout)[-300:]}))
+        return
+    v = float(r.stdout.split("evals_per_s=")[1].split()[0])
+    print(json.dumps({"impl": "reference-cuda", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": 1,
+                      "steps": args.steps, "ms_per_step": 1000.0 * B / v, "dtype": "fp16" if backend == "cuda-fp16" else "fp32",
+                      "config": {"workload": "%s: %s; batch %d; reference backend %s" % (args.config, cfg_desc, B, backend)},
+                      "e2e": {"value": v, "unit": UNIT}}), flush=True)
+
+
 def run_reference(args, rank):
     """--impl reference: the reference's CPU implementation on the host cores.  One step = one evaluation of
     a 32-position sample (ref_eval performs one untimed warm-up evaluation itself before the timed repeats);
@@ -195,6 +232,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank)
+        return 0
+    if args.impl == "reference-cuda":
+        run_reference_cuda(args, rank)
         return 0
 
     import torch

@@ -77,11 +77,39 @@ def run(cmd):
         raise SystemExit(1)
 
 
+def build_cuda_reference(ref, obj, flags, common_objs, main_objs, link, jobs):
+    """The reference's plain-CUDA backend as meson builds it with -Dplain_cuda=true -Dcudnn=false -Dcutlass=false
+    (meson.build:539-581): layers.cc and network_cuda.cc with the host compiler, common_kernels.cu and
+    fp16_kernels.cu with nvcc for sm_100, linked against cuBLAS."""
+    cuda_home = "/usr/local/cuda"
+    nvcc = os.path.join(cuda_home, "bin", "nvcc")
+    cdir = os.path.join(ref, "src/neural/backends/cuda")
+    inc = ["-I" + cdir, "-I" + os.path.join(cuda_home, "include")]
+    objs = []
+    for src in ("layers.cc", "network_cuda.cc"):
+        o = os.path.join(obj, "cuda_" + src + ".o")
+        if not os.path.exists(o):
+            run(["g++"] + flags + inc + ["-c", os.path.join(cdir, src), "-o", o])
+        objs.append(o)
+    for src in ("common_kernels.cu", "fp16_kernels.cu"):
+        o = os.path.join(obj, "cuda_" + src + ".o")
+        if not os.path.exists(o):
+            run([nvcc, "-arch=compute_100", "-code=sm_100", "-O3", "-std=c++20", "-Xcompiler", "-fPIC", "-w", "-DNO_PEXT"] +
+                [f for f in flags if f.startswith("-I")] + inc + ["-c", os.path.join(cdir, src), "-o", o])
+        objs.append(o)
+    lib64 = os.path.join(cuda_home, "lib64")
+    run(["g++", "-o", os.path.join(OUT, "ref_eval_cuda")] + common_objs + objs + main_objs + link +
+        ["-L" + lib64, "-lcublas", "-lcudart", "-Wl,-rpath," + lib64])
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 4)
     ap.add_argument("--opt", default="-O2")
+    ap.add_argument("--cuda", action="store_true",
+                    help="also build oracle/_ref/ref_eval_cuda: the reference's own CUDA backend (cuBLAS GEMMs + its "
+                         "SIMT kernels, no cuDNN / CUTLASS) for same-GPU comparison runs")
     ap.add_argument("--adapter", action="store_true",
                     help="also compile lc0_b200/adapter/network_b200.cc into lc0_ref/ref_eval")
     args = ap.parse_args()
@@ -145,6 +173,8 @@ def main():
     run(["g++", "-o", os.path.join(OUT, "ref_eval")] + common_objs + adapter_objs + objof("ref_eval.cc") + link)
     run(["g++", "-o", os.path.join(OUT, "mkpos")] + common_objs + objof("mkpos.cc") + link)
     run(["g++", "-o", os.path.join(OUT, "lc0_ref")] + common_objs + adapter_objs + objof("src/main.cc") + link)
+    if args.cuda:
+        build_cuda_reference(ref, obj, flags, common_objs, objof("ref_eval.cc"), link, args.jobs)
     print("built", OUT, "(blas flavour: %s)" % ("OpenBLAS " + blas if blas else "absent, eigen-shim only"))
     return 0
 
