@@ -74,7 +74,8 @@ typedef struct b200_net_options {
 } b200_net_options;
 
 enum {
-  B200_FLAG_NO_TENSOR_CORES = 1 /* force the plain FMA matrix kernels in fp16/bf16 mode */
+  B200_FLAG_NO_TENSOR_CORES = 1, /* force the plain FMA matrix kernels in fp16/bf16 mode */
+  B200_FLAG_NO_GRAPHS = 2        /* launch kernels one by one instead of replaying captured CUDA graphs */
 };
 
 typedef struct b200_net_info {

@@ -13,6 +13,7 @@ OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_NOMEM, ERR_TIMEOUT = range(6)
 PREC_FP32, PREC_FP16, PREC_BF16 = 0, 1, 2
 PRECISIONS = {"fp32": PREC_FP32, "fp16": PREC_FP16, "bf16": PREC_BF16}
 FLAG_NO_TENSOR_CORES = 1
+FLAG_NO_GRAPHS = 2
 POLICY_SIZE = 1858
 INPUT_PLANES = 112
 

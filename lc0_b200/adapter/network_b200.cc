@@ -9,7 +9,7 @@
 //
 // Options (parsed like the reference CUDA backend's, src/neural/backends/cuda/network_cuda.cc:210-254):
 //   gpu=<id>  max_batch=<n> (default 1024)  slots=<n> (concurrent computations, default 2)
-//   policy_head=<name>  value_head=<name>  mlh=<bool>  tensor_cores=<bool>
+//   policy_head=<name>  value_head=<name>  mlh=<bool>  tensor_cores=<bool>  graph_capture=<bool>
 #include <memory>
 #include <string>
 #include <vector>
@@ -208,7 +208,8 @@ class B200Network : public Network {
     opt.slots = options.GetOrDefault<int>("slots", 2);
     opt.precision = precision;
     opt.mlh = options.GetOrDefault<bool>("mlh", true) ? 1 : 0;
-    opt.flags = options.GetOrDefault<bool>("tensor_cores", true) ? 0 : B200_FLAG_NO_TENSOR_CORES;
+    opt.flags = (options.GetOrDefault<bool>("tensor_cores", true) ? 0 : B200_FLAG_NO_TENSOR_CORES) |
+                (options.GetOrDefault<bool>("graph_capture", true) ? 0 : B200_FLAG_NO_GRAPHS);
     Check(b200_net_create(b.get(), &opt, &net_));
     Check(b200_net_get_info(net_, &info_));
     if (!info_.has_mlh) capabilities_.moves_left = NF::MOVES_LEFT_NONE;

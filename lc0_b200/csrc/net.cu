@@ -9,11 +9,13 @@
 #include <atomic>
 #include <cmath>
 #include <condition_variable>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <memory>
 #include <mutex>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "../../include/b200nn.h"
@@ -314,6 +316,9 @@ struct Net : NetBase {
   std::vector<Slot> slots;
 
   ~Net() override {
+    for (auto& cache : graph_cache)
+      for (auto& kv : cache)
+        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     for (auto& s : slots) {
       if (s.stream) cudaStreamDestroy(s.stream);
       if (s.h_masks) cudaFreeHost(s.h_masks);
@@ -950,10 +955,93 @@ struct Net : NetBase {
     }
   }
 
+  // ---- CUDA graphs: the launch sequence of one evaluation is captured per (batch size, buffers) the second
+  // time it is requested and replayed afterwards (the reference captures per batch size too,
+  // backends/cuda/network_cuda.cc:690-706).  Profiling needs event records between kernels, so it bypasses graphs.
+  struct GraphKey {
+    int n, staged;
+    const void *a, *b, *c, *d;
+    bool operator<(const GraphKey& o) const {
+      return std::tie(n, staged, a, b, c, d) < std::tie(o.n, o.staged, o.a, o.b, o.c, o.d);
+    }
+  };
+  struct GraphEntry {
+    int seen = 0;
+    cudaGraphExec_t exec = nullptr;
+    long long launches = 0;
+  };
+  std::vector<std::map<GraphKey, GraphEntry>> graph_cache;  // per slot
+
+  void enqueue_staged(Slot& s, int n) {
+    CK(cudaMemcpyAsync(s.d_masks, s.h_masks, (size_t)n * 112 * 8, cudaMemcpyHostToDevice, s.stream));
+    CK(cudaMemcpyAsync(s.d_values, s.h_values, (size_t)n * 112 * 4, cudaMemcpyHostToDevice, s.stream));
+    forward(s, s.d_masks, s.d_values, n, s.d_policy, s.d_qdm);
+    CK(cudaMemcpyAsync(s.h_policy, s.d_policy, (size_t)n * 1858 * 4, cudaMemcpyDeviceToHost, s.stream));
+    CK(cudaMemcpyAsync(s.h_qdm, s.d_qdm, (size_t)n * 3 * 4, cudaMemcpyDeviceToHost, s.stream));
+  }
+
+  template <typename F>
+  void run_or_replay(int slot, const GraphKey& key, F&& enqueue) {
+    Slot& s = slots[slot];
+    const bool use_graphs = !(opt.flags & B200_FLAG_NO_GRAPHS) && !profiling;
+    if (!use_graphs) {
+      enqueue();
+      return;
+    }
+    if (graph_cache.size() != slots.size()) graph_cache.resize(slots.size());
+    auto& cache = graph_cache[slot];
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+      if (cache.size() >= 64) {  // bounded: beyond that, new shapes simply run eagerly
+        enqueue();
+        return;
+      }
+      it = cache.emplace(key, GraphEntry{}).first;
+    }
+    GraphEntry& e = it->second;
+    if (e.exec) {
+      CK(cudaGraphLaunch(e.exec, s.stream));
+      launches += e.launches;
+      return;
+    }
+    if (++e.seen < 2) {  // first request: plain launches (also performs every one-time attribute set-up)
+      enqueue();
+      return;
+    }
+    const long long before = launches.load();
+    CK(cudaStreamBeginCapture(s.stream, cudaStreamCaptureModeThreadLocal));
+    cudaGraph_t graph = nullptr;
+    try {
+      enqueue();
+    } catch (...) {
+      cudaStreamEndCapture(s.stream, &graph);
+      if (graph) cudaGraphDestroy(graph);
+      throw;
+    }
+    CK(cudaStreamEndCapture(s.stream, &graph));
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ie != cudaSuccess) {
+      cudaGetLastError();
+      e.seen = -1000000;  // do not try again
+      launches = before;
+      enqueue();
+      return;
+    }
+    e.exec = exec;
+    e.launches = launches.load() - before;
+    launches = before;
+    CK(cudaGraphLaunch(e.exec, s.stream));
+    launches += e.launches;
+  }
+
   int eval_device(int slot, const void* d_masks, const void* d_values, int n, void* d_policy, void* d_qdm,
                   bool sync) override {
     Slot& s = slots[slot];
-    forward(s, (const uint64_t*)d_masks, (const float*)d_values, n, (float*)d_policy, (float*)d_qdm);
+    run_or_replay(slot, GraphKey{n, 0, d_masks, d_values, d_policy, d_qdm}, [&] {
+      forward(s, (const uint64_t*)d_masks, (const float*)d_values, n, (float*)d_policy, (float*)d_qdm);
+    });
     if (sync) CK(cudaStreamSynchronize(s.stream));
     return B200_OK;
   }
@@ -961,11 +1049,7 @@ struct Net : NetBase {
     Slot& s = slots[slot];
     if (masks != s.h_masks) memcpy(s.h_masks, masks, (size_t)n * 112 * 8);
     if (values != s.h_values) memcpy(s.h_values, values, (size_t)n * 112 * 4);
-    CK(cudaMemcpyAsync(s.d_masks, s.h_masks, (size_t)n * 112 * 8, cudaMemcpyHostToDevice, s.stream));
-    CK(cudaMemcpyAsync(s.d_values, s.h_values, (size_t)n * 112 * 4, cudaMemcpyHostToDevice, s.stream));
-    forward(s, s.d_masks, s.d_values, n, s.d_policy, s.d_qdm);
-    CK(cudaMemcpyAsync(s.h_policy, s.d_policy, (size_t)n * 1858 * 4, cudaMemcpyDeviceToHost, s.stream));
-    CK(cudaMemcpyAsync(s.h_qdm, s.d_qdm, (size_t)n * 3 * 4, cudaMemcpyDeviceToHost, s.stream));
+    run_or_replay(slot, GraphKey{n, 1, nullptr, nullptr, nullptr, nullptr}, [&] { enqueue_staged(s, n); });
     CK(cudaStreamSynchronize(s.stream));
     return B200_OK;
   }

@@ -15,7 +15,7 @@ import numpy as np
 from . import _lib, netproto, weights as _weights
 
 _KNOWN_OPTIONS = {"gpu", "max_batch", "precision", "slots", "mlh", "policy_head", "value_head",
-                  "tensor_cores"}
+                  "tensor_cores", "graph_capture"}
 
 
 def parse_options(opts):
@@ -136,7 +136,8 @@ class Network:
             o = _lib.NetOptions(gpu=int(opts.get("gpu", 0)), max_batch=int(opts.get("max_batch", 1024)),
                                 precision=_lib.PRECISIONS[prec], slots=int(opts.get("slots", 1)),
                                 mlh=1 if _as_bool(opts.get("mlh", True)) else 0,
-                                flags=0 if _as_bool(opts.get("tensor_cores", True)) else _lib.FLAG_NO_TENSOR_CORES)
+                                flags=(0 if _as_bool(opts.get("tensor_cores", True)) else _lib.FLAG_NO_TENSOR_CORES) |
+                                      (0 if _as_bool(opts.get("graph_capture", True)) else _lib.FLAG_NO_GRAPHS))
             h = ctypes.c_void_p()
             _lib.check(lib.b200_net_create(b, ctypes.byref(o), ctypes.byref(h)))
             self._handle = h

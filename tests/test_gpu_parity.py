@@ -136,3 +136,25 @@ def test_large_batch_consistency():
     nw.close()
     np.testing.assert_allclose(big["policy"][:100], small["policy"], atol=1e-6)
     np.testing.assert_allclose(big["q"][:100], small["q"], atol=1e-6)
+
+
+def test_graph_replay_matches_plain_launches():
+    """The captured CUDA graph (third and later calls of a shape) gives the same numbers as plain launches."""
+    net, pos, n, g = load_case("cfg4_mini")
+    plain = network.Network(net, "precision=fp16,max_batch=32,graph_capture=0")
+    want = plain.evaluate(pos["masks"][:n], pos["values"][:n])
+    plain.close()
+    nw = network.Network(net, "precision=fp16,max_batch=32")
+    for i in range(4):  # plain, capture + replay, replay, replay
+        got = nw.evaluate(pos["masks"][:n], pos["values"][:n])
+        np.testing.assert_array_equal(got["policy"], want["policy"])
+        np.testing.assert_array_equal(got["q"], want["q"])
+    # a different batch size gets its own graph (tiny batches route some products to the FMA kernel, hence atol)
+    for i in range(3):
+        other = nw.evaluate(pos["masks"][:5], pos["values"][:5])
+        np.testing.assert_allclose(other["policy"], want["policy"][:5], atol=HALF_ATOL)
+    count = nw.launch_count()
+    nw.evaluate(pos["masks"][:n], pos["values"][:n])
+    assert nw.launch_count() > count  # replays are still counted as kernel launches
+    assert nw.device_status() == 0
+    nw.close()
