@@ -250,11 +250,38 @@ struct TcParams {
   int* status;
   int tma_store;  // 1: 16-bit output staged in shared memory and written with TMA stores
   int conv_cblocks;  // > 0: 3x3 convolution, number of 64-channel blocks of the input (k_blocks = 9 * conv_cblocks)
+  // folded LayerNorm (see GemmParams)
+  const float* a_stats; const float* colsum; float a_inv_c, a_eps;
+  int res_mode;  // 0 none, 1 add the residual tile, 2 add the normalised residual tile
+  const float* res_stats; const float* res_gamma; const float* res_beta; float res_inv_c, res_eps;
+  float* out_stats;
 };
 
-// One 64-column slab of the epilogue fast path, executed by one group of four warps: TMEM -> registers ->
-// scale/bias/activation -> 128B-swizzled staging buffer -> TMA store.  A group alternates between its two
-// buffers; its leader makes sure the store that last used `buf` has finished reading it.
+// Per-thread (= per output row) state of the folded-LayerNorm epilogue.
+struct RowCtx {
+  float mean_a = 0.f, rstd_a = 1.f, mean_r = 0.f, rstd_r = 1.f, sum = 0.f, sumsq = 0.f;
+};
+__device__ __forceinline__ void load_row_ctx(const TcParams& p, int m, RowCtx& rc) {
+  rc.sum = 0.f;
+  rc.sumsq = 0.f;
+  if (p.a_stats && m < p.M) {
+    const float2 st = *reinterpret_cast<const float2*>(p.a_stats + 2 * (long long)m);
+    rc.mean_a = st.x * p.a_inv_c;
+    rc.rstd_a = rsqrtf(fmaxf(st.y * p.a_inv_c - rc.mean_a * rc.mean_a, 0.f) + p.a_eps);
+  }
+  if (p.res_mode == 2 && m < p.M) {
+    const float2 st = *reinterpret_cast<const float2*>(p.res_stats + 2 * (long long)m);
+    rc.mean_r = st.x * p.res_inv_c;
+    rc.rstd_r = rsqrtf(fmaxf(st.y * p.res_inv_c - rc.mean_r * rc.mean_r, 0.f) + p.res_eps);
+  }
+}
+__device__ __forceinline__ void flush_row_ctx(const TcParams& p, int m, const RowCtx& rc) {
+  if (p.out_stats && m < p.M) {
+    atomicAdd(p.out_stats + 2 * (long long)m, rc.sum);
+    atomicAdd(p.out_stats + 2 * (long long)m + 1, rc.sumsq);
+  }
+}
+
 // Packs two floats into one 32-bit pair of T; fp16 saturates to the largest finite value (min/max on the
 // packed pair after the conversion turns an overflowed inf back into 65504).
 template <typename T> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
@@ -270,48 +297,97 @@ template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float l
 }
 
 // One 64-column slab of the epilogue fast path, executed by one group of four warps: TMEM -> registers ->
-// scale/bias/activation -> 128B-swizzled staging buffer -> TMA store.  A group alternates between its two
-// buffers; its leader makes sure the store that last used `buf` has finished reading it.  The 64 bias values
-// of the slab are fetched with two coalesced loads per lane and redistributed through a 256-byte per-warp
-// shared-memory scratch (`wbias`) as broadcast float4 reads.
+// scale / folded-LayerNorm correction / bias / activation / residual -> 128B-swizzled staging buffer -> TMA store.
+// A group alternates between its two buffers; its leader makes sure the store that last used `buf` has finished
+// reading it.  Per-column vectors (bias, colsum, residual gamma / beta) are fetched with coalesced loads and
+// redistributed through a per-warp shared-memory scratch (`wvec`, 4 x 64 floats) as broadcast float4 reads.
+// The residual tile is fetched by TMA into the staging buffer itself (completion on `res_bar`), combined in place.
 template <typename T>
-__device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorMap* tmap_c, uint8_t* buf, int group,
+__device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorMap* tmap_c, const CUtensorMap* tmap_r,
+                                              uint8_t* buf, uint32_t res_bar, uint32_t res_parity, int group,
                                               bool leader, uint32_t taddr, int row, int lane, int m0, int nb,
-                                              float* wbias) {
-  if (p.bias) {
-    wbias[lane] = (nb + lane < p.N) ? __ldg(p.bias + nb + lane) : 0.f;
-    wbias[32 + lane] = (nb + 32 + lane < p.N) ? __ldg(p.bias + nb + 32 + lane) : 0.f;
+                                              float* wvec, RowCtx& rc, volatile int* abort_flag, volatile int* res_ok) {
+  auto col = [&](const float* src, int i) { return (src && nb + i < p.N) ? __ldg(src + nb + i) : 0.f; };
+  if (p.bias) { wvec[lane] = col(p.bias, lane); wvec[32 + lane] = col(p.bias, 32 + lane); }
+  if (p.a_stats) { wvec[64 + lane] = col(p.colsum, lane); wvec[96 + lane] = col(p.colsum, 32 + lane); }
+  if (p.res_mode == 2) {
+    wvec[128 + lane] = col(p.res_gamma, lane); wvec[160 + lane] = col(p.res_gamma, 32 + lane);
+    wvec[192 + lane] = col(p.res_beta, lane); wvec[224 + lane] = col(p.res_beta, 32 + lane);
   }
-  if (leader) tma_store_wait_read1();  // the store issued two slabs ago (same buffer) has been read out
-  epilogue_barrier(group);             // also orders the wbias writes before the reads below
+  if (leader) {
+    tma_store_wait_read1();  // the store issued two slabs ago (same buffer) has been read out
+    if (p.res_mode) {
+      mbar_expect_tx(res_bar, BM * 128);
+      tma_load_2d(smem_u32(buf), tmap_r, nb, m0, res_bar);
+    }
+  }
+  epilogue_barrier(group);  // also orders the wvec writes before the reads below
   uint32_t r0[32], r1[32];
   tmem_ld32(taddr, r0);
   tmem_ld32(taddr + 32, r1);
   tmem_ld_wait();
   float v[64];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    v[j] = __uint_as_float(r0[j]) * p.scale;
+    v[32 + j] = __uint_as_float(r1[j]) * p.scale;
+  }
+  if (p.a_stats) {
+#pragma unroll
+    for (int j = 0; j < 64; j += 4) {
+      const float4 cs = *reinterpret_cast<const float4*>(wvec + 64 + j);
+      v[j] = rc.rstd_a * (v[j] - rc.mean_a * cs.x);
+      v[j + 1] = rc.rstd_a * (v[j + 1] - rc.mean_a * cs.y);
+      v[j + 2] = rc.rstd_a * (v[j + 2] - rc.mean_a * cs.z);
+      v[j + 3] = rc.rstd_a * (v[j + 3] - rc.mean_a * cs.w);
+    }
+  }
   if (p.bias) {
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      const float4 ba = *reinterpret_cast<const float4*>(wbias + j);
-      const float4 bb = *reinterpret_cast<const float4*>(wbias + 32 + j);
-      v[j] = fmaf(__uint_as_float(r0[j]), p.scale, ba.x);
-      v[j + 1] = fmaf(__uint_as_float(r0[j + 1]), p.scale, ba.y);
-      v[j + 2] = fmaf(__uint_as_float(r0[j + 2]), p.scale, ba.z);
-      v[j + 3] = fmaf(__uint_as_float(r0[j + 3]), p.scale, ba.w);
-      v[32 + j] = fmaf(__uint_as_float(r1[j]), p.scale, bb.x);
-      v[32 + j + 1] = fmaf(__uint_as_float(r1[j + 1]), p.scale, bb.y);
-      v[32 + j + 2] = fmaf(__uint_as_float(r1[j + 2]), p.scale, bb.z);
-      v[32 + j + 3] = fmaf(__uint_as_float(r1[j + 3]), p.scale, bb.w);
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      v[j] = __uint_as_float(r0[j]) * p.scale;
-      v[32 + j] = __uint_as_float(r1[j]) * p.scale;
+    for (int j = 0; j < 64; j += 4) {
+      const float4 b = *reinterpret_cast<const float4*>(wvec + j);
+      v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
     }
   }
   apply_activation(v, p.act);
   uint8_t* srow = buf + row * 128;
+  if (p.res_mode) {
+    // One thread does the bounded wait for the residual tile; a failed wait raises the abort flag and the
+    // (then meaningless) result is still written so that every thread keeps the same barrier sequence.
+    if (leader) res_ok[group] = mbar_wait(res_bar, res_parity, abort_flag, 5) ? 1 : 0;
+    epilogue_barrier(group);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 u = *reinterpret_cast<const uint4*>(srow + ((c ^ (row & 7)) << 4));
+      const T* e = reinterpret_cast<const T*>(&u);
+      float s[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s[i] = to_f(e[i]);
+      if (p.res_mode == 2) {
+        const float4 g0 = *reinterpret_cast<const float4*>(wvec + 128 + c * 8);
+        const float4 g1 = *reinterpret_cast<const float4*>(wvec + 132 + c * 8);
+        const float4 b0 = *reinterpret_cast<const float4*>(wvec + 192 + c * 8);
+        const float4 b1 = *reinterpret_cast<const float4*>(wvec + 196 + c * 8);
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] = (s[i] - rc.mean_r) * rc.rstd_r * gg[i] + bb[i];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[c * 8 + i] = p.alpha * v[c * 8 + i] + s[i];
+    }
+  }
+  if (p.out_stats) {
+    float a = 0.f, q = 0.f;
+    if (nb + 64 <= p.N) {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) { a += v[j]; q = fmaf(v[j], v[j], q); }
+    } else {
+      for (int j = 0; j < 64 && nb + j < p.N; ++j) { a += v[j]; q = fmaf(v[j], v[j], q); }
+    }
+    rc.sum += a;
+    rc.sumsq += q;
+  }
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
     uint4 o;
@@ -336,14 +412,15 @@ template <int BN> struct TileCfg {
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int kEpiBytes = 4 * BM * 128;  // 2 groups x 2 staging buffers of 128 rows x 128 bytes
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ +
-                                    2048 /*bias scratch*/;
+                                    8192 /*per-warp column vectors*/;
 };
 
 
 template <typename T, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-               const __grid_constant__ CUtensorMap tmap_c, const TcParams p) {
+               const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_r,
+               const TcParams p) {
   using Cfg = TileCfg<BN>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -356,8 +433,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint64_t* tempty_bar = tfull_bar + 2;                             // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* epi_ok = abort_flag + 1;
-  float* wbias = reinterpret_cast<float*>(bar_mem + 256) + ((threadIdx.x >> 5) & 7) * 64;  // per-warp scratch
+  volatile int* epi_ok = abort_flag + 1;                     // [2]
+  volatile int* res_ok = epi_ok + 2;                         // [2]
+  uint64_t* res_bar = reinterpret_cast<uint64_t*>(bar_mem + 192);  // [2 groups][2 buffers]
+  float* wvec = reinterpret_cast<float*>(bar_mem + 256) + ((threadIdx.x >> 5) & 7) * 256;  // per-warp scratch
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
@@ -373,6 +452,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       mbar_init(smem_u32(&tfull_bar[i]), 1);
       mbar_init(smem_u32(&tempty_bar[i]), 8);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&res_bar[i]), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -463,13 +543,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       if (p.tma_store) {
         // Fast path: 64-column slabs -> registers -> swizzled shared memory -> TMA store (clips the M/N tails).
+        RowCtx rc;
+        load_row_ctx(p, m, rc);
 #pragma unroll 1
         for (int c0 = group * 64; c0 < BN; c0 += 128) {
           if (n0 + c0 >= p.N) break;  // uniform over the group
-          epilogue_slab<T>(p, &tmap_c, gbuf + (slab_it & 1) * (BM * 128), group, leader, trow + c0,
-                           quarter * 32 + lane, lane, m0, n0 + c0, wbias);
+          epilogue_slab<T>(p, &tmap_c, &tmap_r, gbuf + (slab_it & 1) * (BM * 128),
+                           smem_u32(&res_bar[group * 2 + (slab_it & 1)]), (slab_it >> 1) & 1, group, leader, trow + c0,
+                           quarter * 32 + lane, lane, m0, n0 + c0, wvec, rc, abort_flag, res_ok);
           ++slab_it;
         }
+        flush_row_ctx(p, m, rc);
       } else {
 #pragma unroll 1
       for (int c0 = group * 32; c0 < BN; c0 += 64) {
@@ -565,13 +649,14 @@ struct PairCfg {
   static constexpr int kStages = 4;
   static constexpr int kTmemCols = 512;
   static constexpr int kEpiBytes = 4 * BM * 128;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 256 + 2048;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 256 + 8192;
 };
 
 template <typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                    const __grid_constant__ CUtensorMap tmap_c, const TcParams p) {
+                    const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_r,
+                    const TcParams p) {
   using Cfg = PairCfg;
   constexpr int S = Cfg::kStages;
   constexpr int BN = Cfg::BN;
@@ -585,8 +670,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint64_t* tempty_bar = tfull_bar + 2;                        // [2]  even CTA: 4 local + 4 remote arrivals
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* epi_ok = abort_flag + 1;
-  float* wbias = reinterpret_cast<float*>(bar_mem + 256) + ((threadIdx.x >> 5) & 7) * 64;  // per-warp scratch
+  volatile int* epi_ok = abort_flag + 1;                     // [2]
+  volatile int* res_ok = epi_ok + 2;                         // [2]
+  uint64_t* res_bar = reinterpret_cast<uint64_t*>(bar_mem + 192);  // [2 groups][2 buffers]
+  float* wvec = reinterpret_cast<float*>(bar_mem + 256) + ((threadIdx.x >> 5) & 7) * 256;  // per-warp scratch
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -604,6 +691,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       mbar_init(smem_u32(&tfull_bar[i]), 1);
       mbar_init(smem_u32(&tempty_bar[i]), 16);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&res_bar[i]), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -689,13 +777,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (!epi_ok[group]) break;
       tcgen05_fence_after();
       const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      const int m = m0 + quarter * 32 + lane;
+      RowCtx rc;
+      load_row_ctx(p, m, rc);
 #pragma unroll 1
       for (int c0 = group * 64; c0 < BN; c0 += 128) {
         if (n0 + c0 >= p.N) break;  // uniform over the group
-        epilogue_slab<T>(p, &tmap_c, gbuf + (slab_it & 1) * (BM * 128), group, leader, trow + c0,
-                         quarter * 32 + lane, lane, m0, n0 + c0, wbias);
+        epilogue_slab<T>(p, &tmap_c, &tmap_r, gbuf + (slab_it & 1) * (BM * 128),
+                         smem_u32(&res_bar[group * 2 + (slab_it & 1)]), (slab_it >> 1) & 1, group, leader, trow + c0,
+                         quarter * 32 + lane, lane, m0, n0 + c0, wvec, rc, abort_flag, res_ok);
         ++slab_it;
       }
+      flush_row_ctx(p, m, rc);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&tempty_bar[acc]), 0));
@@ -774,6 +867,14 @@ cudaError_t get_map(const void* ptr, long long ld, int rows, int cols, int box_r
   return cudaSuccess;
 }
 
+void fill_folded(TcParams& p, const GemmParams& g) {
+  p.a_stats = g.a_stats; p.colsum = g.colsum; p.a_inv_c = g.a_inv_c; p.a_eps = g.a_eps;
+  p.res_mode = g.res ? (g.res_stats ? 2 : 1) : 0;
+  p.res_stats = g.res_stats; p.res_gamma = g.res_gamma; p.res_beta = g.res_beta;
+  p.res_inv_c = g.res_inv_c; p.res_eps = g.res_eps;
+  p.out_stats = g.out_stats;
+}
+
 // 4D map over a token-major activation [positions][8][8][channels]; box = 64 channels x 8 x 8 x 2 boards
 // (128 GEMM rows).  Not cached: convolution inputs are few and the encode call is a host-side pure function.
 cudaError_t make_board_map(const void* ptr, int channels, int positions, int prec, CUtensorMap* out) {
@@ -827,7 +928,16 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
     e = get_map(g.C, g.ldc, g.M, g.N, BM, prec, &mc);
     if (e != cudaSuccess) return e;
   }
+  const bool folded = g.a_stats || g.res || g.out_stats;
+  if (folded && !tma_store) return cudaErrorInvalidValue;  // the folded-LayerNorm modes live in the TMA-store epilogue
+  CUtensorMap mr = mc;
+  if (g.res) {
+    if ((g.ldres % 8) != 0 || (reinterpret_cast<uintptr_t>(g.res) & 15) != 0) return cudaErrorInvalidValue;
+    e = get_map(g.res, g.ldres, g.M, g.N, BM, prec, &mr);
+    if (e != cudaSuccess) return e;
+  }
   TcParams p;
+  fill_folded(p, g);
   p.tma_store = tma_store ? 1 : 0;
   p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.skip = g.skip; p.ldskip = g.ldskip;
   p.M = g.M; p.N = g.N; p.K = g.K; p.act = g.act; p.scale = g.scale; p.alpha = g.alpha;
@@ -835,7 +945,7 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
   p.conv_cblocks = g.conv_cin > 0 ? ceil_div(g.conv_cin, BK) : 0;
   const int tiles = ceil_div(g.M, BM) * ceil_div(g.N, BN);
   const int grid = tiles < sm_count ? tiles : sm_count;
-  gemm_tc_kernel<T, BN><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, p);
+  gemm_tc_kernel<T, BN><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, p);
   return cudaGetLastError();
 }
 
@@ -861,7 +971,14 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   if (e != cudaSuccess) return e;
   e = get_map(g.C, g.ldc, g.M, g.N, BM, prec, &mc);
   if (e != cudaSuccess) return e;
+  CUtensorMap mr = mc;
+  if (g.res) {
+    if ((g.ldres % 8) != 0 || (reinterpret_cast<uintptr_t>(g.res) & 15) != 0) return cudaErrorInvalidValue;
+    e = get_map(g.res, g.ldres, g.M, g.N, BM, prec, &mr);
+    if (e != cudaSuccess) return e;
+  }
   TcParams p;
+  fill_folded(p, g);
   p.tma_store = 1;
   p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.skip = nullptr; p.ldskip = 0;
   p.M = g.M; p.N = g.N; p.K = g.K; p.act = g.act; p.scale = g.scale; p.alpha = g.alpha;
@@ -870,7 +987,7 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   const int tiles = ceil_div(g.M, 2 * BM) * ceil_div(g.N, Cfg::BN);
   const int max_pairs = sm_count / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  gemm_tc_pair_kernel<T><<<2 * pairs, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, p);
+  gemm_tc_pair_kernel<T><<<2 * pairs, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, p);
   return cudaGetLastError();
 }
 

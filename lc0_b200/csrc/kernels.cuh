@@ -19,6 +19,24 @@ struct GemmParams {
   // 3x3 convolution mode of the tensor-core kernel (conv_cin > 0): A is the token-major activation
   // [M = positions*64][conv_cin] (8x8 boards), W is [9][N][conv_cin] (tap-major filters), K is ignored.
   int conv_cin = 0;
+  // ---- folded LayerNorm (tensor-core kernel only) ----------------------------------------------------------
+  // The rows of A are LayerNorm *inputs* u whose normalisation x = (u - mean) * rstd * gamma + beta was folded
+  // into this product: W holds W * gamma, `colsum[n]` = sum_k (W * gamma)[n][k], `bias` holds beta . W^T + b and
+  // `a_stats` the per-row (sum, sum of squares) of u.  Then x . W^T + b = rstd * (u . (W gamma)^T - mean * colsum) + bias.
+  const float* a_stats = nullptr;
+  const float* colsum = nullptr;
+  float a_inv_c = 0.f, a_eps = 0.f;
+  // Residual input added after the activation: out = alpha * act(...) + s, where s is read from `res`
+  // ([M][N], leading dimension ldres) and, when res_stats is set, normalised on the fly:
+  // s = (res - mean) * rstd * res_gamma[n] + res_beta[n].
+  const void* res = nullptr; long long ldres = 0;
+  const float* res_stats = nullptr;
+  const float* res_gamma = nullptr;
+  const float* res_beta = nullptr;
+  float res_inv_c = 0.f, res_eps = 0.f;
+  // Per-row (sum, sum of squares) of the outputs, accumulated with atomic adds into out_stats[M][2]
+  // (the caller zeroes it), so that the next product can fold the LayerNorm of this output.
+  float* out_stats = nullptr;
 };
 
 template <typename T> cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t s);

@@ -164,6 +164,9 @@ template <typename T> struct Dense {
   T* w = nullptr;        // [out][in]
   float* b = nullptr;    // [out] or nullptr
   int out = 0, in = 0;
+  // Set when the LayerNorm that feeds this layer is folded into it: w holds W * gamma (per input column),
+  // b holds b + beta . W^T, and colsum[n] = sum_k (W * gamma)[n][k] of the stored (rounded) weights.
+  float* colsum = nullptr;
 };
 
 template <typename T> struct EncoderW {
@@ -269,6 +272,9 @@ struct Net : NetBase {
   DeviceAllocs walloc, salloc;
   int sm_count = 148;
   bool use_tc = false;
+  // LayerNorms of the encoder stack folded into the neighbouring tensor-core products (16-bit storage only).
+  bool fold_ln = false;
+  bool fold_heads = false;  // the heads' first products fold the last LayerNorm too (else it is materialised)
   int* d_status = nullptr;
 
   // format
@@ -309,6 +315,7 @@ struct Net : NetBase {
     T *tokens = nullptr, *pre = nullptr, *pe = nullptr;
     T *x = nullptr, *x1 = nullptr, *y = nullptr, *qkv = nullptr, *att = nullptr, *ffn = nullptr;
     T *sg_c = nullptr, *sg_h1 = nullptr, *sg_h2 = nullptr, *sg_bias = nullptr;
+    float *stats1 = nullptr, *stats2 = nullptr;  // per-row (sum, sum of squares) of the folded LayerNorm inputs
     T *pemb = nullptr, *pq = nullptr, *pk = nullptr, *praw = nullptr;
     float* logits = nullptr;
     T *vtok = nullptr, *vhid = nullptr, *mtok = nullptr, *mhid = nullptr;
@@ -369,6 +376,40 @@ struct Net : NetBase {
     if (!bname.empty()) d.b = up_f32(bname, out);
     return d;
   }
+  // Dense layer whose input LayerNorm (gamma, beta) is folded into the weights (see Dense::colsum).
+  Dense<T> dense_folded(const std::vector<float>& w, const std::vector<float>* b, int out, int in,
+                        const std::vector<float>& gamma, const std::vector<float>& beta) {
+    if (w.size() != (size_t)out * in || gamma.size() != (size_t)in || beta.size() != (size_t)in)
+      throw Fail{B200_ERR_INVALID, "weights: size mismatch while folding a LayerNorm"};
+    std::vector<T> wt((size_t)out * in);
+    std::vector<float> cs(out), bias(out);
+    for (int o = 0; o < out; ++o) {
+      double sum = 0.0, bsum = b ? (double)(*b)[o] : 0.0;
+      for (int k = 0; k < in; ++k) {
+        const float orig = w[(size_t)o * in + k];
+        const T q = host_cast<T>(orig * gamma[k]);
+        wt[(size_t)o * in + k] = q;
+        sum += (double)static_cast<float>(q);
+        bsum += (double)beta[k] * orig;
+      }
+      cs[o] = (float)sum;
+      bias[o] = (float)bsum;
+    }
+    Dense<T> d;
+    d.out = out;
+    d.in = in;
+    d.w = (T*)walloc.alloc(wt.size() * sizeof(T));
+    CK(cudaMemcpy(d.w, wt.data(), wt.size() * sizeof(T), cudaMemcpyHostToDevice));
+    d.b = up_f32(bias);
+    d.colsum = up_f32(cs);
+    return d;
+  }
+  Dense<T> dense_maybe_folded(const std::string& wname, const std::string& bname, int out, int in,
+                              const std::vector<float>* gamma, const std::vector<float>* beta) {
+    if (!gamma) return dense(wname, bname, out, in);
+    return dense_folded(need(wname, (size_t)out * in), bname.empty() ? nullptr : &need(bname, out), out, in, *gamma,
+                        *beta);
+  }
   // FC that consumes a channel-major flatten [c*64 + sq] in the file; our activations are square-major.
   Dense<T> dense_chw(const std::string& wname, const std::string& bname, int out, int planes) {
     const std::vector<float>& w = need(wname, (size_t)out * planes * 64);
@@ -406,12 +447,22 @@ struct Net : NetBase {
     if (encoder_gemm) info.gemm_flops_per_position += f;
   }
 
+  // LayerNorm parameters folded into the heads' first products: the last encoder layer's second LayerNorm.
+  const std::vector<float>* head_gamma() const {
+    return (fold_heads && layers > 0) ? &need("encoder." + std::to_string(layers - 1) + ".ln2_gammas", E) : nullptr;
+  }
+  const std::vector<float>* head_beta() const {
+    return (fold_heads && layers > 0) ? &need("encoder." + std::to_string(layers - 1) + ".ln2_betas", E) : nullptr;
+  }
   long long geti(const std::string& k, long long def = 0) const {
     auto it = bld->ints.find(k);
     return it == bld->ints.end() ? def : it->second;
   }
 
-  EncoderW<T> load_encoder(const std::string& p, int emb, int heads) {
+  // in_gamma / in_beta: parameters of the LayerNorm whose output feeds this layer when that LayerNorm is folded
+  // into the consuming products (nullptr: the layer input is a materialised activation).
+  EncoderW<T> load_encoder(const std::string& p, int emb, int heads, const std::vector<float>* in_gamma,
+                           const std::vector<float>* in_beta) {
     EncoderW<T> e;
     const int dm = (int)size_of(p + ".mha.q_b");
     if (dm <= 0 || dm % heads) throw Fail{B200_ERR_INVALID, "weights: bad attention width in " + p};
@@ -423,13 +474,21 @@ struct Net : NetBase {
       w.insert(w.end(), ww.begin(), ww.end());
       b.insert(b.end(), bb.begin(), bb.end());
     }
-    e.qkv.out = 3 * dm;
-    e.qkv.in = emb;
-    e.qkv.w = up_T(w);
-    e.qkv.b = up_f32(b);
+    if (in_gamma) {
+      e.qkv = dense_folded(w, &b, 3 * dm, emb, *in_gamma, *in_beta);
+    } else {
+      e.qkv.out = 3 * dm;
+      e.qkv.in = emb;
+      e.qkv.w = up_T(w);
+      e.qkv.b = up_f32(b);
+    }
     e.proj = dense(p + ".mha.dense_w", p + ".mha.dense_b", emb, dm);
     const int dff = (int)size_of(p + ".ffn.dense1_b");
-    e.ffn1 = dense(p + ".ffn.dense1_w", p + ".ffn.dense1_b", dff, emb);
+    if (fold_ln)
+      e.ffn1 = dense_folded(need(p + ".ffn.dense1_w", (size_t)dff * emb), &need(p + ".ffn.dense1_b", dff), dff, emb,
+                            need(p + ".ln1_gammas", emb), need(p + ".ln1_betas", emb));
+    else
+      e.ffn1 = dense(p + ".ffn.dense1_w", p + ".ffn.dense1_b", dff, emb);
     e.ffn2 = dense(p + ".ffn.dense2_w", p + ".ffn.dense2_b", emb, dff);
     e.ln1g = up_f32(p + ".ln1_gammas", emb);
     e.ln1b = up_f32(p + ".ln1_betas", emb);
@@ -445,7 +504,7 @@ struct Net : NetBase {
       const int hc = (int)size_of(p + ".mha.smolgen.compress") / emb;
       const int hid = (int)size_of(p + ".mha.smolgen.dense1_b");
       const int gen = (int)size_of(p + ".mha.smolgen.dense2_b");
-      e.sg_compress = dense(p + ".mha.smolgen.compress", "", hc, emb);
+      e.sg_compress = dense_maybe_folded(p + ".mha.smolgen.compress", "", hc, emb, in_gamma, in_beta);
       e.sg_d1 = dense(p + ".mha.smolgen.dense1_w", p + ".mha.smolgen.dense1_b", hid, 64 * hc);
       e.sg_d2 = dense(p + ".mha.smolgen.dense2_w", p + ".mha.smolgen.dense2_b", gen, hid);
       e.sg_ln1g = up_f32(p + ".mha.smolgen.ln1_gammas", hid);
@@ -502,6 +561,22 @@ struct Net : NetBase {
                                              std::to_string(prop.major) + std::to_string(prop.minor)};
       CK(gemm_tc_init());
     }
+    fold_ln = use_tc && attn_body && !(getenv("B200_FOLD_LN") && getenv("B200_FOLD_LN")[0] == '0');
+    // Folding needs every product that consumes or produces a folded LayerNorm to be eligible for the tensor-core
+    // kernel's TMA epilogue: output widths that are multiples of 8.
+    auto foldable = [](size_t width) { return width >= 8 && width % 8 == 0; };
+    if (fold_ln) {
+      if (!foldable(size_of("ip_emb_b"))) fold_ln = false;
+      for (int i = 0; fold_ln && size_of("encoder." + std::to_string(i) + ".mha.q_w"); ++i) {
+        const std::string p = "encoder." + std::to_string(i);
+        if (!foldable(size_of(p + ".ffn.dense1_b")) || size_of(p + ".mha.q_b") != size_of("ip_emb_b")) fold_ln = false;
+        const size_t cs = size_of(p + ".mha.smolgen.compress");
+        if (cs && !foldable(cs / size_of("ip_emb_b"))) fold_ln = false;
+      }
+    }
+    fold_heads = fold_ln && foldable(size_of("value.ip_val_b")) &&
+                 (!mlh || foldable(size_of("ip_mov_b"))) &&
+                 (policy_fmt != POLICY_ATTENTION || foldable(size_of("policy.ip_pol_b")));
     d_status = (int*)walloc.alloc(sizeof(int));
     CK(cudaMemset(d_status, 0, sizeof(int)));
 
@@ -597,7 +672,12 @@ struct Net : NetBase {
       }
       max_dff = emb_dff;
       for (int i = 0; i < layers; ++i) {
-        enc.push_back(load_encoder("encoder." + std::to_string(i), E, H));
+        const std::vector<float>*g = nullptr, *bt = nullptr;
+        if (fold_ln && i > 0) {
+          g = &need("encoder." + std::to_string(i - 1) + ".ln2_gammas", E);
+          bt = &need("encoder." + std::to_string(i - 1) + ".ln2_betas", E);
+        }
+        enc.push_back(load_encoder("encoder." + std::to_string(i), E, H, g, bt));
         max_dff = std::max(max_dff, enc.back().ffn1.out);
       }
       if (sg_gen) smolgen_w = dense("smolgen_w", "", 4096, sg_gen / H);
@@ -607,7 +687,7 @@ struct Net : NetBase {
     if (policy_fmt == POLICY_ATTENTION) {
       const int pe = (int)size_of("policy.ip_pol_b");
       pol_dm = (int)size_of("policy.ip2_pol_b");
-      pol_emb = dense("policy.ip_pol_w", "policy.ip_pol_b", pe, body_ch);
+      pol_emb = dense_maybe_folded("policy.ip_pol_w", "policy.ip_pol_b", pe, body_ch, head_gamma(), head_beta());
       pol_q = dense("policy.ip2_pol_w", "policy.ip2_pol_b", pol_dm, pe);
       pol_k = dense("policy.ip3_pol_w", "policy.ip3_pol_b", pol_dm, pe);
       pol_w4 = up_f32("policy.ip4_pol_w", (size_t)4 * pol_dm);
@@ -644,7 +724,7 @@ struct Net : NetBase {
       int vp;
       if (attn_body) {
         vp = (int)size_of("value.ip_val_b");
-        val_emb = dense("value.ip_val_w", "value.ip_val_b", vp, E);
+        val_emb = dense_maybe_folded("value.ip_val_w", "value.ip_val_b", vp, E, head_gamma(), head_beta());
         val_fc1 = dense("value.ip1_val_w", "value.ip1_val_b", vh, vp * 64);
       } else {
         vp = (int)size_of("value.value.biases");
@@ -663,7 +743,7 @@ struct Net : NetBase {
       int mp;
       if (attn_body) {
         mp = (int)size_of("ip_mov_b");
-        mov_emb = dense("ip_mov_w", "ip_mov_b", mp, E);
+        mov_emb = dense_maybe_folded("ip_mov_w", "ip_mov_b", mp, E, head_gamma(), head_beta());
         mov_fc1 = dense("ip1_mov_w", "ip1_mov_b", mh, mp * 64);
       } else {
         mp = (int)size_of("moves_left.biases");
@@ -732,6 +812,10 @@ struct Net : NetBase {
           s.y = A(R * E);
         }
         s.qkv = A(R * 3 * E);
+        if (fold_ln) {
+          s.stats1 = (float*)salloc.alloc(R * 2 * sizeof(float));
+          s.stats2 = (float*)salloc.alloc(R * 2 * sizeof(float));
+        }
         s.att = A(R * E);
         s.ffn = A(R * std::max(max_dff, 8));
         if (sg_gen) {
@@ -772,6 +856,38 @@ struct Net : NetBase {
     p.skip = skip; p.ldskip = ldskip; p.alpha = alpha_; p.out_f32 = out_f32;
     run_gemm(st, p);
   }
+  // A LayerNorm output that is either materialised (stats == nullptr) or kept as its un-normalised input `u`
+  // with per-row statistics and the LayerNorm's parameters.
+  struct LNState {
+    const T* u = nullptr;
+    const float* stats = nullptr;
+    const float* gamma = nullptr;
+    const float* beta = nullptr;
+  };
+  // Product whose A operand is `in` (folded when in.stats is set); optional residual `res` added as
+  // alpha * act(...) + LN(res) and optional accumulation of output row statistics.
+  void gemm_ln(cudaStream_t st, const LNState& in, long long lda, const Dense<T>& d, T* Cout, long long ldc, int M,
+               int act, const LNState* res = nullptr, float alpha_ = 1.f, float* out_stats = nullptr) {
+    GemmParams p;
+    p.A = in.u; p.lda = lda; p.W = d.w; p.ldw = d.in; p.bias = d.b;
+    p.C = Cout; p.ldc = ldc; p.M = M; p.N = d.out; p.K = d.in; p.act = act;
+    if (in.stats) {
+      if (!d.colsum) throw Fail{B200_ERR_INVALID, "internal: folded input for a layer without folded weights"};
+      p.a_stats = in.stats; p.colsum = d.colsum; p.a_inv_c = 1.0f / d.in; p.a_eps = ln_eps;
+    }
+    if (res) {
+      p.res = res->u; p.ldres = d.out; p.alpha = alpha_;
+      if (res->stats) {
+        p.res_stats = res->stats; p.res_gamma = res->gamma; p.res_beta = res->beta;
+        p.res_inv_c = 1.0f / d.out; p.res_eps = ln_eps;
+      }
+    }
+    if (out_stats) {
+      CK(cudaMemsetAsync(out_stats, 0, (size_t)M * 2 * sizeof(float), st));
+      p.out_stats = out_stats;
+    }
+    run_gemm(st, p);
+  }
   void run_gemm(cudaStream_t st, const GemmParams& p) {
     launches++;
     const double flops = 2.0 * p.M * (double)p.N * p.K * p.batch;
@@ -783,6 +899,8 @@ struct Net : NetBase {
         return;
       }
     }
+    if (p.a_stats || p.res || p.out_stats)
+      throw Fail{B200_ERR_UNSUPPORTED, "internal: folded LayerNorm product outside the tensor-core kernel"};
     span_begin(st, K_GEMM_FMA, flops);
     CK(launch_gemm_simt<T>(p, st));
     span_end(st);
@@ -823,13 +941,17 @@ struct Net : NetBase {
     span_end(st);
   }
 
-  void encoder_layer(Slot& s, const EncoderW<T>& e, int n, T*& x, T*& x1) {
+  // `in` describes the layer input: buffer x, materialised for the first layer, afterwards the un-normalised
+  // sum of the previous layer with its statistics.  With folding the two LayerNorms of the layer never run as
+  // kernels: out-proj and FFN2 add the (normalised-on-the-fly) residual and accumulate row statistics, QKV,
+  // the smolgen compression and FFN1 apply the normalisation as a row scale plus a rank-1 correction.
+  void encoder_layer(Slot& s, const EncoderW<T>& e, int n, T*& x, T*& x1, LNState& in) {
     cudaStream_t st = s.stream;
     const int R = n * 64;
     const int depth = E / H;
     const T* bias = nullptr;
     if (e.smolgen) {  // network_blas.cc:300-339
-      gemm(st, x, E, e.sg_compress, s.sg_c, sg_hc, R, ACT_NONE);
+      gemm_ln(st, in, E, e.sg_compress, s.sg_c, sg_hc, R, ACT_NONE);
       gemm(st, s.sg_c, 64 * sg_hc, e.sg_d1, s.sg_h1, sg_hid, n, act_smolgen);
       ln(st, s.sg_h1, s.sg_h1, nullptr, e.sg_ln1g, e.sg_ln1b, n, sg_hid, 1.f, 1e-3f);
       gemm(st, s.sg_h1, sg_hid, e.sg_d2, s.sg_h2, sg_gen, n, act_smolgen);
@@ -837,7 +959,7 @@ struct Net : NetBase {
       gemm(st, s.sg_h2, sg_gen / H, smolgen_w, s.sg_bias, 4096, n * H, ACT_NONE);
       bias = s.sg_bias;
     }
-    gemm(st, x, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE);  // :341-350, :408-412
+    gemm_ln(st, in, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE);  // :341-350, :408-412
     launches++;
     // algorithmic bytes: read Q, K, V (+ bias), write the head outputs
     span_begin(st, K_ATTENTION, (double)R * E * sizeof(T) * 4 + (bias ? (double)n * H * 4096 * sizeof(T) : 0.0));
@@ -853,11 +975,21 @@ struct Net : NetBase {
       CK(launch_attention<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
                              1.0f / sqrtf((float)depth), st));
     span_end(st);
+    if (fold_ln) {
+      LNState att{s.att, nullptr, nullptr, nullptr}, ffn{s.ffn, nullptr, nullptr, nullptr};
+      gemm_ln(st, att, E, e.proj, x1, E, R, ACT_NONE, &in, alpha, s.stats1);      // u1 = alpha * proj + x
+      LNState mid{x1, s.stats1, e.ln1g, e.ln1b};
+      gemm_ln(st, mid, E, e.ffn1, s.ffn, e.ffn1.out, R, act_ffn);                  // relu2(LN1(u1) W1 + b1)
+      gemm_ln(st, ffn, e.ffn1.out, e.ffn2, x, E, R, ACT_NONE, &mid, alpha, s.stats2);  // u2 = alpha * ffn + LN1(u1)
+      in = LNState{x, s.stats2, e.ln2g, e.ln2b};
+      return;
+    }
     gemm(st, s.att, E, e.proj, s.y, E, R, ACT_NONE);           // :441-445
     ln(st, x1, s.y, x, e.ln1g, e.ln1b, R, E, alpha, ln_eps);   // :447-452
     gemm(st, x1, E, e.ffn1, s.ffn, e.ffn1.out, R, act_ffn);    // :454-458
     gemm(st, s.ffn, e.ffn1.out, e.ffn2, s.y, E, R, ACT_NONE);  // :460-463
     ln(st, x, s.y, x1, e.ln2g, e.ln2b, R, E, alpha, ln_eps);   // :465-470
+    in = LNState{x, nullptr, nullptr, nullptr};
   }
 
   void forward(Slot& s, const uint64_t* d_masks, const float* d_values, int n, float* d_policy, float* d_qdm) {
@@ -865,6 +997,7 @@ struct Net : NetBase {
     const int R = n * 64;
     T* flow = nullptr;  // output of the body, [R][body_ch]
     int body_ch = 0;
+    LNState body_in;    // attention bodies: how the heads must read `flow` (folded LayerNorm or materialised)
     CK(cudaMemsetAsync(d_qdm, 0, (size_t)n * 3 * sizeof(float), st));
     if (!res.empty() || !attn_body) {  // network_blas.cc:564-601
       other(st, (double)R * 112 * sizeof(T), [&] {
@@ -909,20 +1042,27 @@ struct Net : NetBase {
       } else if (gate_mult) {
         other(st, 2.0 * R * E * sizeof(T), [&] { return launch_gate<T>(x, gate_mult, gate_add, R, E, st); });
       }
-      for (const auto& e : enc) encoder_layer(s, e, n, x, x1);
+      body_in = LNState{x, nullptr, nullptr, nullptr};
+      for (const auto& e : enc) encoder_layer(s, e, n, x, x1, body_in);
+      if (body_in.stats && !fold_heads) {  // materialise the last LayerNorm for heads that cannot fold it
+        ln(st, x1, x, nullptr, body_in.gamma, body_in.beta, R, E, 1.f, ln_eps);
+        std::swap(x, x1);
+        body_in = LNState{x, nullptr, nullptr, nullptr};
+      }
       flow = x;
       body_ch = E;
     }
 
     // ---- value head (network_blas.cc:725-772) ----
-    gemm(st, flow, body_ch, val_emb, s.vtok, val_emb.out, R, act_default);
+    LNState head_in = attn_body ? body_in : LNState{flow, nullptr, nullptr, nullptr};
+    gemm_ln(st, head_in, body_ch, val_emb, s.vtok, val_emb.out, R, act_default);
     gemm(st, s.vtok, 64 * val_emb.out, val_fc1, s.vhid, val_fc1.out, n, act_default);
     other(st, (double)n * val_fc1.out * sizeof(T), [&] {
       return launch_head_final<T>(s.vhid, val_fc1.out, val_w2, val_b2, wdl ? 0 : 1, n, d_qdm, st);
     });
     // ---- moves-left head (:775-803) ----
     if (mlh) {
-      gemm(st, flow, body_ch, mov_emb, s.mtok, mov_emb.out, R, act_default);
+      gemm_ln(st, head_in, body_ch, mov_emb, s.mtok, mov_emb.out, R, act_default);
       gemm(st, s.mtok, 64 * mov_emb.out, mov_fc1, s.mhid, mov_fc1.out, n, act_default);
       other(st, (double)n * mov_fc1.out * sizeof(T), [&] {
         return launch_head_final<T>(s.mhid, mov_fc1.out, mov_w2, mov_b2, 2, n, d_qdm, st);
@@ -930,7 +1070,7 @@ struct Net : NetBase {
     }
     // ---- policy head (:806-968) ----
     if (policy_fmt == POLICY_ATTENTION) {
-      gemm(st, flow, body_ch, pol_emb, s.pemb, pol_emb.out, R, attn_body ? act_default : ACT_SELU);
+      gemm_ln(st, head_in, body_ch, pol_emb, s.pemb, pol_emb.out, R, attn_body ? act_default : ACT_SELU);
       gemm(st, s.pemb, pol_emb.out, pol_q, s.pq, pol_dm, R, ACT_NONE);
       gemm(st, s.pemb, pol_emb.out, pol_k, s.pk, pol_dm, R, ACT_NONE);
       GemmParams p;  // per-position Q.K^T, scaled
