@@ -204,6 +204,108 @@ attention_tc_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* _
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Attention policy head tail on tensor cores, one CTA (4 warps) per position:
+//   logits = Q K^T / sqrt(dm)  (64 x 64, dm streamed through shared memory in 64-wide double-buffered chunks),
+//   promotion offsets from the rank-8 keys, and the gather of the 1858 move logits, written as fp32.
+// Reference: network_blas.cc:850-914; GPU twins: a batched cuBLAS call, promotion_logits_kernel and
+// policyMap_kernel (backends/cuda/layers.cc:1898-1979, common_kernels.cu:1116-1201, :703-734).
+// ------------------------------------------------------------------------------------------------
+constexpr int kPolRow = 64 * 2 + 16;          // bytes per staged row (64 values + padding)
+constexpr int kPolStage = 2 * 64 * kPolRow;   // Q chunk + K chunk
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+policy_attn_tc_kernel(const T* __restrict__ q, const T* __restrict__ k, const float* __restrict__ w4, int dm,
+                      const short* __restrict__ src_slot, float scale, float* __restrict__ policy) {
+  extern __shared__ __align__(16) uint8_t sm[];
+  __shared__ float off[4][8];
+  const int n = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const T* qn = q + (long long)n * 64 * dm;
+  const T* kn = k + (long long)n * 64 * dm;
+  const int chunks = (dm + 63) / 64;
+  auto stage_load = [&](int c, int st) {
+    uint8_t* sq = sm + st * kPolStage;
+    uint8_t* sk = sq + 64 * kPolRow;
+    for (int i = tid; i < 64 * 8; i += 128) {
+      const int r = i >> 3, ch = i & 7;
+      const int col = c * 64 + ch * 8;
+      if (col < dm) {  // dm is a multiple of 8
+        cp_async16(sq + r * kPolRow + ch * 16, qn + (long long)r * dm + col);
+        cp_async16(sk + r * kPolRow + ch * 16, kn + (long long)r * dm + col);
+      } else {
+        *reinterpret_cast<uint4*>(sq + r * kPolRow + ch * 16) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(sk + r * kPolRow + ch * 16) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float s[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+  stage_load(0, 0);
+  const int m0 = warp * 16;
+  for (int c = 0; c < chunks; ++c) {
+    if (c + 1 < chunks) {
+      stage_load(c + 1, (c + 1) & 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const uint8_t* sq = sm + (c & 1) * kPolStage;
+    const uint8_t* sk = sq + 64 * kPolRow;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      uint32_t a[4];
+      ldmatrix_x4(a, sq + (m0 + (lane & 15)) * kPolRow + (ks * 16 + (lane >> 4) * 8) * 2);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b[4];
+        ldmatrix_x4(b, sk + (np * 16 + (lane & 7) + (lane >> 4) * 8) * kPolRow + (ks * 16 + ((lane >> 3) & 1) * 8) * 2);
+        mma16816<T>(s[2 * np], a, b[0], b[1]);
+        mma16816<T>(s[2 * np + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();  // the stage may be overwritten by the load issued in the next iteration
+  }
+  // promotion offsets: 4 x 8 dot products of the rank-8 keys with w4 (4 per warp... 8 per warp over 4 warps)
+  for (int t = warp * 8; t < warp * 8 + 8; ++t) {
+    const int i = t >> 3, j = t & 7;
+    const T* key = kn + (long long)(56 + j) * dm;
+    float a = 0.f;
+    for (int cc = lane; cc < dm; cc += 32) a = fmaf(to_f(key[cc]), w4[i * dm + cc], a);
+    a = warp_sum(a);
+    if (lane == 0) off[i][j] = a;
+  }
+  // logits to shared memory (fp32 [64][65]), reusing the staging area
+  float* lg = reinterpret_cast<float*>(sm);
+  const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+    lg[(m0 + g) * 65 + nt * 8 + 2 * t4] = s[nt][0] * scale;
+    lg[(m0 + g) * 65 + nt * 8 + 2 * t4 + 1] = s[nt][1] * scale;
+    lg[(m0 + g + 8) * 65 + nt * 8 + 2 * t4] = s[nt][2] * scale;
+    lg[(m0 + g + 8) * 65 + nt * 8 + 2 * t4 + 1] = s[nt][3] * scale;
+  }
+  __syncthreads();
+  for (int j = tid; j < 1858; j += 128) {
+    const int slot = src_slot[j];
+    float v;
+    if (slot < 4096) {
+      v = lg[(slot >> 6) * 65 + (slot & 63)];
+    } else {
+      const int r = slot - 4096;  // 24 * from_file + 3 * to_file + piece
+      const int kf = r / 24, rem = r - kf * 24, jf = rem / 3, i = rem - jf * 3;
+      v = lg[(48 + kf) * 65 + 56 + jf] + off[i][jf] + off[3][jf];
+    }
+    policy[(long long)n * 1858 + j] = v;
+  }
+}
+
 }  // namespace
 
 bool attention_tc_supported(long long ld, long long ldo, int depth, const void* q, const void* k, const void* v,
@@ -234,5 +336,26 @@ template cudaError_t launch_attention_tc<__nv_bfloat16>(const __nv_bfloat16*, co
                                                         const __nv_bfloat16*, long long, const __nv_bfloat16*,
                                                         __nv_bfloat16*, long long, int, int, int, float,
                                                         cudaStream_t);
+
+}  // namespace b200
+
+namespace b200 {
+
+bool policy_attn_tc_supported(int dm, const void* q, const void* k) {
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return dm >= 8 && (dm % 8) == 0 && al(q) && al(k);
+}
+
+template <typename T>
+cudaError_t launch_policy_attn_tc(const T* q, const T* k, const float* w4, int dm, const short* src_slot, int n,
+                                  float* policy, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  policy_attn_tc_kernel<T><<<n, 128, 2 * kPolStage, s>>>(q, k, w4, dm, src_slot, 1.0f / sqrtf((float)dm), policy);
+  return cudaGetLastError();
+}
+template cudaError_t launch_policy_attn_tc<__half>(const __half*, const __half*, const float*, int, const short*, int,
+                                                   float*, cudaStream_t);
+template cudaError_t launch_policy_attn_tc<__nv_bfloat16>(const __nv_bfloat16*, const __nv_bfloat16*, const float*, int,
+                                                          const short*, int, float*, cudaStream_t);
 
 }  // namespace b200

@@ -1023,11 +1023,15 @@ cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaS
     return !(e && e[0] == '0');
   }();
   const bool tma_store_ok = !p.out_f32 && !p.skip && (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
-  if (pair_enabled && tma_store_ok && p.conv_cin == 0 && p.M >= 512 && p.N > 128)
+  if (pair_enabled && tma_store_ok && p.conv_cin == 0 && p.M >= 512 && p.N > 128 &&
+      (long long)ceil_div(p.M, 2 * BM) * ceil_div(p.N, 256) >= sm_count / 4)
     return launch_pair<T>(p, status, sm_count, s);
-  // Wide tiles amortise the A-tile loads; narrow problems take the smallest tile that covers N.
-  if (p.N > 128) return launch_bn<T, 256>(p, status, sm_count, s);
-  if (p.N > 64) return launch_bn<T, 128>(p, status, sm_count, s);
+  // Wide tiles amortise the A-tile loads; narrow problems take the smallest tile that covers N, and skinny
+  // problems (few rows) the widest tile that still yields at least half an SM count of CTAs.
+  auto tiles = [&](int bn) { return (long long)ceil_div(p.M, BM) * ceil_div(p.N, bn); };
+  if (p.N > 128 && (tiles(256) >= sm_count / 2 || p.N <= 128)) return launch_bn<T, 256>(p, status, sm_count, s);
+  if (p.N > 64 && (tiles(128) >= sm_count / 2 || p.N <= 64)) return launch_bn<T, 128>(p, status, sm_count, s);
+  if (p.N > 128 && tiles(64) < sm_count / 8) return launch_bn<T, 256>(p, status, sm_count, s);
   return launch_bn<T, 64>(p, status, sm_count, s);
 }
 

@@ -349,8 +349,8 @@ cudaError_t launch_layer_norm(T* out, const T* x, const T* skip, const float* ga
   else if (C <= 512) LNW_LAUNCH(2);
   else if (C <= 1024) LNW_LAUNCH(4);
   else if (C <= 2048) LNW_LAUNCH(8);
-  else if (C <= 4096) LN_LAUNCH(256, 2);
-  else LN_LAUNCH(256, 4);
+  else if (C <= 4096) LN_LAUNCH(512, 1);  // few, wide rows (smolgen): one 16-byte piece per thread
+  else LN_LAUNCH(1024, 1);
 #undef LN_LAUNCH
 #undef LNW_LAUNCH
   return cudaGetLastError();

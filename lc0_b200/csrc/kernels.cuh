@@ -84,6 +84,11 @@ cudaError_t launch_attention_tc(const T* q, const T* k, const T* v, long long ld
 template <typename T>
 cudaError_t launch_policy_attn_gather(const float* logits, const T* kp, const float* w4, int dm,
                                       const short* src_slot, int n, float* policy, cudaStream_t s);
+// Tensor-core version of the whole tail (Q K^T, promotion offsets, gather) for 16-bit storage (attention_tc.cu).
+bool policy_attn_tc_supported(int dm, const void* q, const void* k);
+template <typename T>
+cudaError_t launch_policy_attn_tc(const T* q, const T* k, const float* w4, int dm, const short* src_slot, int n,
+                                  float* policy, cudaStream_t s);
 // Generic gather for conv policy: policy[n][j] = raw[n][src[j]] (raw row stride ld), T -> fp32.
 template <typename T>
 cudaError_t launch_policy_gather(const T* raw, long long ld, const short* src_slot, int n, float* policy,

@@ -1073,15 +1073,27 @@ struct Net : NetBase {
       gemm_ln(st, head_in, body_ch, pol_emb, s.pemb, pol_emb.out, R, attn_body ? act_default : ACT_SELU);
       gemm(st, s.pemb, pol_emb.out, pol_q, s.pq, pol_dm, R, ACT_NONE);
       gemm(st, s.pemb, pol_emb.out, pol_k, s.pk, pol_dm, R, ACT_NONE);
-      GemmParams p;  // per-position Q.K^T, scaled
-      p.A = s.pq; p.lda = pol_dm; p.strideA = 64LL * pol_dm;
-      p.W = s.pk; p.ldw = pol_dm; p.strideW = 64LL * pol_dm;
-      p.C = s.logits; p.ldc = 64; p.strideC = 4096; p.out_f32 = true;
-      p.M = 64; p.N = 64; p.K = pol_dm; p.batch = n; p.scale = 1.0f / sqrtf((float)pol_dm);
-      run_gemm(st, p);
-      other(st, (double)n * (4096 + 1858) * 4, [&] {
-        return launch_policy_attn_gather<T>(s.logits, s.pk, pol_w4, pol_dm, d_attn_src, n, d_policy, st);
-      });
+      bool done = false;
+      if constexpr (sizeof(T) == 2) {
+        if (use_tc && policy_attn_tc_supported(pol_dm, s.pq, s.pk)) {
+          launches++;
+          span_begin(st, K_OTHER, 2.0 * R * pol_dm * sizeof(T) + (double)n * 1858 * 4);
+          CK(launch_policy_attn_tc<T>(s.pq, s.pk, pol_w4, pol_dm, d_attn_src, n, d_policy, st));
+          span_end(st);
+          done = true;
+        }
+      }
+      if (!done) {
+        GemmParams p;  // per-position Q.K^T, scaled
+        p.A = s.pq; p.lda = pol_dm; p.strideA = 64LL * pol_dm;
+        p.W = s.pk; p.ldw = pol_dm; p.strideW = 64LL * pol_dm;
+        p.C = s.logits; p.ldc = 64; p.strideC = 4096; p.out_f32 = true;
+        p.M = 64; p.N = 64; p.K = pol_dm; p.batch = n; p.scale = 1.0f / sqrtf((float)pol_dm);
+        run_gemm(st, p);
+        other(st, (double)n * (4096 + 1858) * 4, [&] {
+          return launch_policy_attn_gather<T>(s.logits, s.pk, pol_w4, pol_dm, d_attn_src, n, d_policy, st);
+        });
+      }
     } else if (policy_fmt == POLICY_CONVOLUTION) {
       T* t1 = s.y;  // free: the tower ping-pongs between x and x1
       conv3(st, flow, pol_conv1, pol_conv1.b, t1, n, act_default);
