@@ -239,14 +239,59 @@ struct NetBase {
   }
   virtual int eval_device(int slot, const void* d_masks, const void* d_values, int n, void* d_policy,
                           void* d_qdm, bool sync) = 0;
-  virtual int eval_staged(int slot, const uint64_t* masks, const float* values, int n) = 0;
+  // Pinned host staging of one computation: inputs are written here by AddInput, results are read from here,
+  // so a computation costs no host-side copies beyond the caller's own (the reference pools its InputsOutputs
+  // the same way, backends/cuda/network_cuda.cc:1066-1083).
+  struct HostSet {
+    uint64_t* masks = nullptr;
+    float *values = nullptr, *policy = nullptr, *qdm = nullptr;
+    int id = 0;
+  };
+  std::mutex host_mu;
+  std::vector<HostSet*> host_free, host_all;
+  HostSet* acquire_host() {
+    {
+      std::lock_guard<std::mutex> l(host_mu);
+      if (!host_free.empty()) {
+        HostSet* h = host_free.back();
+        host_free.pop_back();
+        return h;
+      }
+    }
+    const size_t nb = (size_t)opt.max_batch;
+    auto h = std::make_unique<HostSet>();
+    if (cudaSetDevice(opt.gpu) != cudaSuccess || cudaMallocHost(&h->masks, nb * 112 * 8) != cudaSuccess ||
+        cudaMallocHost(&h->values, nb * 112 * 4) != cudaSuccess ||
+        cudaMallocHost(&h->policy, nb * 1858 * 4) != cudaSuccess || cudaMallocHost(&h->qdm, nb * 3 * 4) != cudaSuccess) {
+      if (h->masks) cudaFreeHost(h->masks);
+      if (h->values) cudaFreeHost(h->values);
+      if (h->policy) cudaFreeHost(h->policy);
+      cudaGetLastError();
+      throw Fail{B200_ERR_NOMEM, "cannot allocate pinned host staging for a computation"};
+    }
+    std::lock_guard<std::mutex> l(host_mu);
+    h->id = (int)host_all.size() + 1;
+    host_all.push_back(h.get());
+    return h.release();
+  }
+  void release_host(HostSet* h) {
+    std::lock_guard<std::mutex> l(host_mu);
+    host_free.push_back(h);
+  }
+  void free_host_sets() {
+    for (HostSet* h : host_all) {
+      cudaFreeHost(h->masks);
+      cudaFreeHost(h->values);
+      cudaFreeHost(h->policy);
+      cudaFreeHost(h->qdm);
+      delete h;
+    }
+    host_all.clear();
+    host_free.clear();
+  }
+  virtual int eval_staged(int slot, HostSet& hs, int n) = 0;
   virtual cudaStream_t stream(int slot) = 0;
   virtual int device_status() = 0;
-  // pinned host staging of a slot
-  virtual uint64_t* h_masks(int slot) = 0;
-  virtual float* h_values(int slot) = 0;
-  virtual float* h_policy(int slot) = 0;
-  virtual float* h_qdm(int slot) = 0;
   // slot pool
   std::mutex mu;
   std::condition_variable cv;
@@ -309,9 +354,8 @@ struct Net : NetBase {
 
   struct Slot {
     cudaStream_t stream = nullptr;
-    uint64_t *d_masks = nullptr, *h_masks = nullptr;
-    float *d_values = nullptr, *h_values = nullptr;
-    float *d_policy = nullptr, *h_policy = nullptr, *d_qdm = nullptr, *h_qdm = nullptr;
+    uint64_t* d_masks = nullptr;
+    float *d_values = nullptr, *d_policy = nullptr, *d_qdm = nullptr;
     T *tokens = nullptr, *pre = nullptr, *pe = nullptr;
     T *x = nullptr, *x1 = nullptr, *y = nullptr, *qkv = nullptr, *att = nullptr, *ffn = nullptr;
     T *sg_c = nullptr, *sg_h1 = nullptr, *sg_h2 = nullptr, *sg_bias = nullptr;
@@ -328,11 +372,8 @@ struct Net : NetBase {
         if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     for (auto& s : slots) {
       if (s.stream) cudaStreamDestroy(s.stream);
-      if (s.h_masks) cudaFreeHost(s.h_masks);
-      if (s.h_values) cudaFreeHost(s.h_values);
-      if (s.h_policy) cudaFreeHost(s.h_policy);
-      if (s.h_qdm) cudaFreeHost(s.h_qdm);
     }
+    free_host_sets();
     walloc.release();
     salloc.release();
   }
@@ -789,10 +830,6 @@ struct Net : NetBase {
       s.d_values = (float*)salloc.alloc(nb * 112 * 4);
       s.d_policy = (float*)salloc.alloc(nb * 1858 * 4);
       s.d_qdm = (float*)salloc.alloc(nb * 3 * 4);
-      CK(cudaMallocHost(&s.h_masks, nb * 112 * 8));
-      CK(cudaMallocHost(&s.h_values, nb * 112 * 4));
-      CK(cudaMallocHost(&s.h_policy, nb * 1858 * 4));
-      CK(cudaMallocHost(&s.h_qdm, nb * 3 * 4));
       const int body_ch = attn_body ? E : C;
       if (!res.empty() || !attn_body) {
         s.tokens = A(R * 112);
@@ -1124,12 +1161,12 @@ struct Net : NetBase {
   };
   std::vector<std::map<GraphKey, GraphEntry>> graph_cache;  // per slot
 
-  void enqueue_staged(Slot& s, int n) {
-    CK(cudaMemcpyAsync(s.d_masks, s.h_masks, (size_t)n * 112 * 8, cudaMemcpyHostToDevice, s.stream));
-    CK(cudaMemcpyAsync(s.d_values, s.h_values, (size_t)n * 112 * 4, cudaMemcpyHostToDevice, s.stream));
+  void enqueue_staged(Slot& s, HostSet& hs, int n) {
+    CK(cudaMemcpyAsync(s.d_masks, hs.masks, (size_t)n * 112 * 8, cudaMemcpyHostToDevice, s.stream));
+    CK(cudaMemcpyAsync(s.d_values, hs.values, (size_t)n * 112 * 4, cudaMemcpyHostToDevice, s.stream));
     forward(s, s.d_masks, s.d_values, n, s.d_policy, s.d_qdm);
-    CK(cudaMemcpyAsync(s.h_policy, s.d_policy, (size_t)n * 1858 * 4, cudaMemcpyDeviceToHost, s.stream));
-    CK(cudaMemcpyAsync(s.h_qdm, s.d_qdm, (size_t)n * 3 * 4, cudaMemcpyDeviceToHost, s.stream));
+    CK(cudaMemcpyAsync(hs.policy, s.d_policy, (size_t)n * 1858 * 4, cudaMemcpyDeviceToHost, s.stream));
+    CK(cudaMemcpyAsync(hs.qdm, s.d_qdm, (size_t)n * 3 * 4, cudaMemcpyDeviceToHost, s.stream));
   }
 
   template <typename F>
@@ -1197,11 +1234,10 @@ struct Net : NetBase {
     if (sync) CK(cudaStreamSynchronize(s.stream));
     return B200_OK;
   }
-  int eval_staged(int slot, const uint64_t* masks, const float* values, int n) override {
+  int eval_staged(int slot, HostSet& hs, int n) override {
     Slot& s = slots[slot];
-    if (masks != s.h_masks) memcpy(s.h_masks, masks, (size_t)n * 112 * 8);
-    if (values != s.h_values) memcpy(s.h_values, values, (size_t)n * 112 * 4);
-    run_or_replay(slot, GraphKey{n, 1, nullptr, nullptr, nullptr, nullptr}, [&] { enqueue_staged(s, n); });
+    // the captured copy nodes embed the host set's addresses, so each host set gets its own graph
+    run_or_replay(slot, GraphKey{n, hs.id, nullptr, nullptr, nullptr, nullptr}, [&] { enqueue_staged(s, hs, n); });
     CK(cudaStreamSynchronize(s.stream));
     return B200_OK;
   }
@@ -1211,25 +1247,21 @@ struct Net : NetBase {
     cudaMemcpy(&v, d_status, sizeof(int), cudaMemcpyDeviceToHost);
     return v;
   }
-  uint64_t* h_masks(int slot) override { return slots[slot].h_masks; }
-  float* h_values(int slot) override { return slots[slot].h_values; }
-  float* h_policy(int slot) override { return slots[slot].h_policy; }
-  float* h_qdm(int slot) override { return slots[slot].h_qdm; }
 };
 
 }  // namespace b200
 
 struct b200_net {
-  std::unique_ptr<NetBase> impl;
+  // Shared with the computations created from it: a computation that is destroyed after b200_net_destroy keeps
+  // the network's resources alive until it is gone too (lc0 never does this, garbage-collected hosts may).
+  std::shared_ptr<NetBase> impl;
 };
 
 // A computation owns host copies of its inputs and, after compute, of its outputs; the device
 // workspace slot is held only while computing.
 struct b200_comp {
-  b200_net* net;
-  std::vector<uint64_t> masks;
-  std::vector<float> values;
-  std::vector<float> policy, qdm;
+  std::shared_ptr<NetBase> net;
+  NetBase::HostSet* hs = nullptr;  // pinned staging, taken from the network's pool at the first AddInput
   int n = 0;
   bool computed = false;
 };
@@ -1318,7 +1350,7 @@ int b200_net_create(const b200_builder* b, const b200_net_options* opt, b200_net
     } else {
       throw Fail{B200_ERR_INVALID, "unknown precision " + std::to_string(o.precision)};
     }
-    *out = new b200_net{std::move(impl)};
+    *out = new b200_net{std::shared_ptr<NetBase>(std::move(impl))};
     return B200_OK;
   });
 }
@@ -1337,19 +1369,21 @@ int b200_comp_create(b200_net* net, b200_comp** out) {
   if (!net || !out) return B200_ERR_INVALID;
   return guarded([&] {
     *out = new b200_comp();
-    (*out)->net = net;
+    (*out)->net = net->impl;
     return B200_OK;
   });
 }
 int b200_comp_add_inputs(b200_comp* c, const uint64_t* masks, const float* values, int n) {
   if (!c || !masks || !values || n < 0) return B200_ERR_INVALID;
   return guarded([&] {
-    if (c->n + n > c->net->impl->opt.max_batch)
-      throw Fail{B200_ERR_INVALID, "computation exceeds max_batch=" + std::to_string(c->net->impl->opt.max_batch)};
-    c->masks.insert(c->masks.end(), masks, masks + (size_t)n * 112);
-    c->values.insert(c->values.end(), values, values + (size_t)n * 112);
+    if (c->n + n > c->net->opt.max_batch)
+      throw Fail{B200_ERR_INVALID, "computation exceeds max_batch=" + std::to_string(c->net->opt.max_batch)};
+    if (n == 0) return (int)B200_OK;
+    if (!c->hs) c->hs = c->net->acquire_host();
+    memcpy(c->hs->masks + (size_t)c->n * 112, masks, (size_t)n * 112 * 8);
+    memcpy(c->hs->values + (size_t)c->n * 112, values, (size_t)n * 112 * 4);
     c->n += n;
-    return B200_OK;
+    return (int)B200_OK;
   });
 }
 int b200_comp_add_input(b200_comp* c, const uint64_t* masks, const float* values) {
@@ -1358,20 +1392,14 @@ int b200_comp_add_input(b200_comp* c, const uint64_t* masks, const float* values
 int b200_comp_compute(b200_comp* c) {
   if (!c) return B200_ERR_INVALID;
   return guarded([&] {
-    NetBase* nb = c->net->impl.get();
-    c->policy.resize((size_t)c->n * 1858);
-    c->qdm.resize((size_t)c->n * 3);
+    NetBase* nb = c->net.get();
     c->computed = true;
     if (c->n == 0) return (int)B200_OK;
     CK(cudaSetDevice(nb->opt.gpu));
     const int slot = nb->acquire();
     int rc;
     try {
-      rc = nb->eval_staged(slot, c->masks.data(), c->values.data(), c->n);
-      if (rc == B200_OK) {
-        memcpy(c->policy.data(), nb->h_policy(slot), c->policy.size() * 4);
-        memcpy(c->qdm.data(), nb->h_qdm(slot), c->qdm.size() * 4);
-      }
+      rc = nb->eval_staged(slot, *c->hs, c->n);
     } catch (...) {
       nb->release(slot);
       throw;
@@ -1381,12 +1409,18 @@ int b200_comp_compute(b200_comp* c) {
   });
 }
 int b200_comp_batch_size(const b200_comp* c) { return c ? c->n : 0; }
-float b200_comp_q(const b200_comp* c, int s) { return c->qdm[(size_t)s * 3 + 0]; }
-float b200_comp_d(const b200_comp* c, int s) { return c->qdm[(size_t)s * 3 + 1]; }
-float b200_comp_m(const b200_comp* c, int s) { return c->qdm[(size_t)s * 3 + 2]; }
-float b200_comp_p(const b200_comp* c, int s, int move_id) { return c->policy[(size_t)s * 1858 + move_id]; }
-const float* b200_comp_policy(const b200_comp* c, int s) { return c->policy.data() + (size_t)s * 1858; }
-void b200_comp_destroy(b200_comp* c) { delete c; }
+// Accessors are valid after b200_comp_compute for 0 <= sample < batch size.
+float b200_comp_q(const b200_comp* c, int s) { return c->hs->qdm[(size_t)s * 3 + 0]; }
+float b200_comp_d(const b200_comp* c, int s) { return c->hs->qdm[(size_t)s * 3 + 1]; }
+float b200_comp_m(const b200_comp* c, int s) { return c->hs->qdm[(size_t)s * 3 + 2]; }
+float b200_comp_p(const b200_comp* c, int s, int move_id) { return c->hs->policy[(size_t)s * 1858 + move_id]; }
+const float* b200_comp_policy(const b200_comp* c, int s) { return c->hs->policy + (size_t)s * 1858; }
+void b200_comp_destroy(b200_comp* c) {
+  if (!c) return;
+  if (c->hs) c->net->release_host(c->hs);
+  if (c->net.use_count() == 1) cudaSetDevice(c->net->opt.gpu);  // this computation frees the network's device memory
+  delete c;
+}
 
 int b200_net_eval_host(b200_net* net, const uint64_t* masks, const float* values, int n, float* policy,
                        float* q, float* d, float* m) {
@@ -1397,24 +1431,28 @@ int b200_net_eval_host(b200_net* net, const uint64_t* masks, const float* values
       throw Fail{B200_ERR_INVALID, "batch " + std::to_string(n) + " exceeds max_batch=" + std::to_string(nb->opt.max_batch)};
     if (n == 0) return (int)B200_OK;
     CK(cudaSetDevice(nb->opt.gpu));
+    NetBase::HostSet* hs = nb->acquire_host();
+    memcpy(hs->masks, masks, (size_t)n * 112 * 8);
+    memcpy(hs->values, values, (size_t)n * 112 * 4);
     const int slot = nb->acquire();
     int rc;
     try {
-      rc = nb->eval_staged(slot, masks, values, n);
+      rc = nb->eval_staged(slot, *hs, n);
       if (rc == B200_OK) {
-        if (policy) memcpy(policy, nb->h_policy(slot), (size_t)n * 1858 * 4);
-        const float* qdm = nb->h_qdm(slot);
+        if (policy) memcpy(policy, hs->policy, (size_t)n * 1858 * 4);
         for (int i = 0; i < n; ++i) {
-          if (q) q[i] = qdm[i * 3];
-          if (d) d[i] = qdm[i * 3 + 1];
-          if (m) m[i] = qdm[i * 3 + 2];
+          if (q) q[i] = hs->qdm[i * 3];
+          if (d) d[i] = hs->qdm[i * 3 + 1];
+          if (m) m[i] = hs->qdm[i * 3 + 2];
         }
       }
     } catch (...) {
       nb->release(slot);
+      nb->release_host(hs);
       throw;
     }
     nb->release(slot);
+    nb->release_host(hs);
     return rc;
   });
 }

@@ -158,3 +158,21 @@ def test_graph_replay_matches_plain_launches():
     assert nw.launch_count() > count  # replays are still counted as kernel launches
     assert nw.device_status() == 0
     nw.close()
+
+
+def test_computation_may_outlive_its_network():
+    """A garbage-collected host may destroy the network before its computations: results stay readable."""
+    net, pos, n, g = load_case("cfg3_mini")
+    nw = network.Network(net, "precision=fp32,max_batch=8")
+    comps = []
+    for i in range(3):
+        c = nw.new_computation()
+        c.add_inputs(pos["masks"][:4], pos["values"][:4])
+        c.compute_blocking()
+        comps.append(c)
+    want = comps[0].policy(2)
+    nw.close()
+    for c in comps:
+        np.testing.assert_array_equal(c.policy(2), want)
+        assert abs(c.get_q_val(1) - g["q"][1]) < 1e-5
+        c.close()
