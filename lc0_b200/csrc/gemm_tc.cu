@@ -241,8 +241,6 @@ struct TcParams {
   const float* bias;
   void* C;
   long long ldc;
-  const void* skip;
-  long long ldskip;
   int M, N, K;
   int act;
   float scale, alpha;
@@ -527,7 +525,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
     const int group = (warp - 2) >> 2;
     const bool leader = ((warp - 2) & 3) == 0 && lane == 0;
-    const T* skip = reinterpret_cast<const T*>(p.skip);
     uint8_t* gbuf = epi_mem + group * (2 * BM * 128);
     uint32_t tile_it = 0, slab_it = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
@@ -569,20 +566,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             float x = __uint_as_float(r[j]) * p.scale;
             if (p.bias && n < p.N) x += __ldg(p.bias + n);
             v[j] = activate<true>(x, p.act);
-          }
-          if (skip) {
-            const T* srow = skip + (long long)m * p.ldskip + nb;
-            if (nb + 32 <= p.N && (p.ldskip & 7) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                const uint4 u = *reinterpret_cast<const uint4*>(srow + j);
-                const T* e = reinterpret_cast<const T*>(&u);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[j + i] = p.alpha * v[j + i] + to_f(e[i]);
-              }
-            } else {
-              for (int j = 0; j < 32 && nb + j < p.N; ++j) v[j] = p.alpha * v[j] + to_f(srow[j]);
-            }
           }
           if (p.out_f32) {
             float* crow = reinterpret_cast<float*>(p.C) + (long long)m * p.ldc + nb;
@@ -922,7 +905,7 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
     e = get_map(g.W, g.ldw, g.N, g.K, BN, prec, &mw);
   }
   if (e != cudaSuccess) return e;
-  const bool tma_store = !g.out_f32 && !g.skip && (g.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(g.C) & 15) == 0;
+  const bool tma_store = !g.out_f32 && (g.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(g.C) & 15) == 0;
   CUtensorMap mc = ma;
   if (tma_store) {
     e = get_map(g.C, g.ldc, g.M, g.N, BM, prec, &mc);
@@ -939,7 +922,7 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
   TcParams p;
   fill_folded(p, g);
   p.tma_store = tma_store ? 1 : 0;
-  p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.skip = g.skip; p.ldskip = g.ldskip;
+  p.bias = g.bias; p.C = g.C; p.ldc = g.ldc;
   p.M = g.M; p.N = g.N; p.K = g.K; p.act = g.act; p.scale = g.scale; p.alpha = g.alpha;
   p.out_f32 = g.out_f32 ? 1 : 0; p.status = status;
   p.conv_cblocks = g.conv_cin > 0 ? ceil_div(g.conv_cin, BK) : 0;
@@ -980,7 +963,7 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   TcParams p;
   fill_folded(p, g);
   p.tma_store = 1;
-  p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.skip = nullptr; p.ldskip = 0;
+  p.bias = g.bias; p.C = g.C; p.ldc = g.ldc;
   p.M = g.M; p.N = g.N; p.K = g.K; p.act = g.act; p.scale = g.scale; p.alpha = g.alpha;
   p.out_f32 = 0; p.status = status;
   p.conv_cblocks = 0;
@@ -1016,13 +999,13 @@ bool gemm_tc_supported(const GemmParams& p) {
 template <typename T>
 cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaStream_t s) {
   if (p.M <= 0 || p.N <= 0) return cudaSuccess;
-  if (!gemm_tc_supported(p)) return cudaErrorInvalidValue;
+  if (!gemm_tc_supported(p) || p.skip) return cudaErrorInvalidValue;  // residuals go through `res`
   // Large problems with 16-bit output go to the CTA-pair kernel (256x256 tiles).
   static const bool pair_enabled = [] {
     const char* e = getenv("B200_GEMM_PAIR");
     return !(e && e[0] == '0');
   }();
-  const bool tma_store_ok = !p.out_f32 && !p.skip && (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
+  const bool tma_store_ok = !p.out_f32 && (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
   if (pair_enabled && tma_store_ok && p.conv_cin == 0 && p.M >= 512 && p.N > 128 &&
       (long long)ceil_div(p.M, 2 * BM) * ceil_div(p.N, 256) >= sm_count / 4)
     return launch_pair<T>(p, status, sm_count, s);

@@ -569,23 +569,6 @@ cudaError_t launch_policy_gather(const T* raw, long long ld, const short* src_sl
   return cudaGetLastError();
 }
 
-template <typename T>
-__global__ void copy_to_f32_kernel(const T* __restrict__ src, long long ld, long long total, int cols,
-                                   float* __restrict__ dst) {
-  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  if (idx >= total) return;
-  const long long r = idx / cols;
-  dst[idx] = to_f(src[r * ld + (idx - r * cols)]);
-}
-
-template <typename T>
-cudaError_t launch_copy_to_f32(const T* src, long long ld, int rows, int cols, float* dst, cudaStream_t s) {
-  const long long total = (long long)rows * cols;
-  if (total <= 0) return cudaSuccess;
-  copy_to_f32_kernel<T><<<ceil_div(total, 256), 256, 0, s>>>(src, ld, total, cols, dst);
-  return cudaGetLastError();
-}
-
 // ------------------------------------------------------------------------------------------------
 // Last layer of the value / moves-left heads (reference: network_blas.cc:747-772 and :797-802;
 // the reference CUDA backend leaves the WDL softmax to the host, network_cuda.cc:991-1014).
@@ -867,24 +850,6 @@ cudaError_t launch_bias_skip_act(const T* x, const float* bias, const T* skip, T
   return cudaGetLastError();
 }
 
-template <typename T>
-__global__ void nhwc_to_nchw_kernel(const T* __restrict__ x, T* __restrict__ y, int C, long long total) {
-  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  if (idx >= total) return;
-  const long long n = idx / (64LL * C);
-  const int r = int(idx - n * 64 * C);
-  const int c = r / 64, sq = r - c * 64;
-  y[idx] = x[(n * 64 + sq) * C + c];
-}
-
-template <typename T>
-cudaError_t launch_nhwc_to_nchw(const T* x, T* y, int C, int n, cudaStream_t s) {
-  const long long total = (long long)n * 64 * C;
-  if (total <= 0) return cudaSuccess;
-  nhwc_to_nchw_kernel<T><<<ceil_div(total, 256), 256, 0, s>>>(x, y, C, total);
-  return cudaGetLastError();
-}
-
 #define INSTANTIATE(T)                                                                                        \
   template cudaError_t launch_gemm_simt<T>(const GemmParams&, cudaStream_t);                                  \
   template cudaError_t launch_expand_planes<T>(const uint64_t*, const float*, int, T*, cudaStream_t);         \
@@ -899,7 +864,6 @@ cudaError_t launch_nhwc_to_nchw(const T* x, T* y, int C, int n, cudaStream_t s) 
   template cudaError_t launch_policy_attn_gather<T>(const float*, const T*, const float*, int, const short*,  \
                                                     int, float*, cudaStream_t);                               \
   template cudaError_t launch_policy_gather<T>(const T*, long long, const short*, int, float*, cudaStream_t); \
-  template cudaError_t launch_copy_to_f32<T>(const T*, long long, int, int, float*, cudaStream_t);            \
   template cudaError_t launch_head_final<T>(const T*, int, const float*, const float*, int, int, float*,      \
                                             cudaStream_t);                                                    \
   template cudaError_t launch_conv3x3<T>(const T*, int, const T*, const float*, T*, int, int, int,            \
@@ -907,8 +871,7 @@ cudaError_t launch_nhwc_to_nchw(const T* x, T* y, int C, int n, cudaStream_t s) 
   template cudaError_t launch_se<T>(const T*, const float*, const T*, const float*, const float*,             \
                                     const float*, const float*, T*, int, int, int, int, cudaStream_t);        \
   template cudaError_t launch_bias_skip_act<T>(const T*, const float*, const T*, T*, int, int, int,           \
-                                               cudaStream_t);                                                 \
-  template cudaError_t launch_nhwc_to_nchw<T>(const T*, T*, int, int, cudaStream_t);
+                                               cudaStream_t);
 
 INSTANTIATE(float)
 INSTANTIATE(__half)

@@ -93,8 +93,6 @@ cudaError_t launch_policy_attn_tc(const T* q, const T* k, const float* w4, int d
 template <typename T>
 cudaError_t launch_policy_gather(const T* raw, long long ld, const short* src_slot, int n, float* policy,
                                  cudaStream_t s);
-template <typename T>
-cudaError_t launch_copy_to_f32(const T* src, long long ld, int rows, int cols, float* dst, cudaStream_t s);
 
 // Final tiny layers of the value / moves-left heads, one warp per sample:
 // mode 0: 3 logits -> softmax -> (q = w - l, d); mode 1: 1 output -> tanh -> q, d = 0;
@@ -115,9 +113,6 @@ cudaError_t launch_se(const T* x, const float* conv_bias, const T* skip, const f
 template <typename T>
 cudaError_t launch_bias_skip_act(const T* x, const float* bias, const T* skip, T* y, int C, int rows, int act,
                                  cudaStream_t s);
-// NHWC [n][64][C] -> channel-major flatten [n][C*64] (what the reference's FC layers after a 1x1 conv see).
-template <typename T>
-cudaError_t launch_nhwc_to_nchw(const T* x, T* y, int C, int n, cudaStream_t s);
 
 // Host copy of the 1858-entry attention-policy gather table (slot in the 64*64 + 8*24 raw vector per move).
 const short* attn_policy_src_table();

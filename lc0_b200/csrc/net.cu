@@ -822,6 +822,7 @@ struct Net : NetBase {
   void alloc_slots() {
     const size_t nb = (size_t)opt.max_batch, R = nb * 64;
     slots.resize(opt.slots);
+    graph_cache.resize(opt.slots);
     auto A = [&](size_t elems) { return (T*)salloc.alloc(elems * sizeof(T)); };
     for (int si = 0; si < opt.slots; ++si) {
       Slot& s = slots[si];
@@ -1177,7 +1178,6 @@ struct Net : NetBase {
       enqueue();
       return;
     }
-    if (graph_cache.size() != slots.size()) graph_cache.resize(slots.size());
     auto& cache = graph_cache[slot];
     auto it = cache.find(key);
     if (it == cache.end()) {

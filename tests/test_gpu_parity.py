@@ -176,3 +176,35 @@ def test_computation_may_outlive_its_network():
         np.testing.assert_array_equal(c.policy(2), want)
         assert abs(c.get_q_val(1) - g["q"][1]) < 1e-5
         c.close()
+
+
+def test_concurrent_computations_on_two_slots():
+    """Two host threads drive their own computations at the same time (lc0 runs several search threads)."""
+    import threading
+    net, pos, n, g = load_case("cfg4_mini")
+    nw = network.Network(net, "precision=fp16,max_batch=32,slots=2")
+    want = nw.evaluate(pos["masks"][:n], pos["values"][:n])
+    errors = []
+
+    def worker(offset):
+        try:
+            for it in range(12):
+                count = 5 + (it + offset) % 20
+                c = nw.new_computation()
+                c.add_inputs(pos["masks"][:count], pos["values"][:count])
+                c.compute_blocking()
+                got = np.stack([c.policy(i) for i in range(count)])
+                if np.abs(got - want["policy"][:count]).max() > HALF_ATOL:
+                    errors.append(("mismatch", offset, it))
+                c.close()
+        except Exception as e:  # pragma: no cover
+            errors.append(e)
+
+    threads = [threading.Thread(target=worker, args=(k,)) for k in range(3)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert nw.device_status() == 0
+    nw.close()
