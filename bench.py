@@ -100,7 +100,7 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def load_positions(rank, batch, fmt=2, split=False):
+def load_positions(rank, batch, fmt=2, split=False, with_moves=False):
     if fmt == 1:
         name = "positions_fmt1_uniform.npz"
     else:
@@ -110,7 +110,13 @@ def load_positions(rank, batch, fmt=2, split=False):
     reps = -(-batch // masks.shape[0])
     masks = np.tile(masks, (reps, 1))[:batch]
     values = np.tile(values, (reps, 1))[:batch]
-    return np.ascontiguousarray(np.roll(masks, rank * 17, axis=0)), np.ascontiguousarray(np.roll(values, rank * 17, axis=0))
+    roll = lambda a: np.ascontiguousarray(np.roll(a, rank * 17, axis=0))
+    if with_moves:
+        legal = np.tile(p["legal"], (reps, 1))[:batch]
+        legal = np.where(legal < 0, 0, legal).astype(np.uint16)
+        n_legal = np.tile(p["n_legal"], reps)[:batch].astype(np.int32)
+        return roll(masks), roll(values), roll(legal), roll(n_legal)
+    return roll(masks), roll(values)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -330,6 +336,28 @@ def main():
     th = sharding.gather_max(th, dist if world > 1 else None)
     e2e_value = world * B * args.steps / th
 
+    # ---- the same with the legal-move softmax on the device and compact return (no 1858-logit vectors cross PCIe) ----
+    _, _, legal, n_legal = load_positions(rank, B, pos_fmt, split=args.config == "cfg5", with_moves=True)
+
+    def step_compact():
+        c = nw.new_computation()
+        c.set_policy_options(1.0, compact=True)
+        c.add_inputs_with_moves(masks, values, legal, n_legal)
+        c.compute_blocking()
+        q = c.get_q_val(0)
+        c.close()
+        return q
+
+    for _ in range(3):
+        step_compact()
+    barrier()
+    tc0 = time.time()
+    for _ in range(args.steps):
+        step_compact()
+    torch.cuda.synchronize()
+    tcs = sharding.gather_max(time.time() - tc0, dist if world > 1 else None)
+    compact_value = world * B * args.steps / tcs
+
     # ---- latency of one batch-256 computation through the same API (p50 / p99 over 40 calls) ----
     lat = None
     if B >= 256:
@@ -385,6 +413,10 @@ def main():
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(B * 112 * 12),
                     "d2h_bytes_per_step": int(B * (1858 + 3) * 4), "ms_per_step": 1000.0 * th / args.steps},
+            "e2e_compact_policy": {"value": compact_value, "unit": UNIT,
+                                   "h2d_bytes_per_step": int(B * (112 * 12 + 256 * 2 + 4)),
+                                   "d2h_bytes_per_step": int(B * (256 * 4 + 12)),
+                                   "what": "legal-move policy softmax on the device, only per-move probabilities returned"},
             "gpu_launches": int(launches),
             "roofline": roofline,
             "kernel_classes": other,

@@ -109,6 +109,21 @@ float b200_comp_p(const b200_comp* c, int sample, int move_id);             /* G
 const float* b200_comp_policy(const b200_comp* c, int sample);              /* 1858 raw logits */
 void b200_comp_destroy(b200_comp* c);
 
+/* Legal-move policy on the device: what lc0's new-API wrapper does on the host after ComputeBlocking
+ * (NetworkAsBackendComputation::SoftmaxPolicy, src/neural/wrapper.cc:135-156: gather GetPVal for every legal move,
+ * subtract the maximum, FastExp((p - max) * inv_temperature) of src/utils/fastmath.h:59-86, normalise).
+ * b200_comp_add_input_with_moves adds one position together with the policy indices of its legal moves
+ * (MoveToNNIndex(move, transform), at most 256); b200_comp_legal_policy returns a pointer to that position's
+ * probabilities in move order.  With compact != 0 the 1858-logit vectors are not copied to the host at all
+ * (GetPVal / b200_comp_policy are then undefined): 1 KB instead of 7.4 KB per position crosses PCIe. */
+int b200_comp_add_input_with_moves(b200_comp* c, const uint64_t* masks, const float* values,
+                                   const uint16_t* move_ids, int n_moves);
+/* n positions at once: move_ids is [n][256] (rows padded), n_moves [n]. */
+int b200_comp_add_inputs_with_moves(b200_comp* c, const uint64_t* masks, const float* values,
+                                    const uint16_t* move_ids, const int* n_moves, int n);
+int b200_comp_set_policy_options(b200_comp* c, float inv_temperature, int compact);
+int b200_comp_legal_policy(const b200_comp* c, int sample, const float** probs, int* n_moves);
+
 /* ---- Whole-batch entry points ----------------------------------------------------------------
  * b200_net_eval_host: one call = add n inputs, compute, copy results out.  Host pointers;
  *   H2D and D2H copies are part of the call.  policy [n][1858], q/d/m [n]; any may be NULL.

@@ -64,6 +64,10 @@ SIGNATURES = {
     "b200_comp_p": (_F, [_P, _I, _I]),
     "b200_comp_policy": (ctypes.POINTER(_F), [_P, _I]),
     "b200_comp_destroy": (None, [_P]),
+    "b200_comp_add_input_with_moves": (_I, [_P, _P, _P, _P, _I]),
+    "b200_comp_add_inputs_with_moves": (_I, [_P, _P, _P, _P, _P, _I]),
+    "b200_comp_set_policy_options": (_I, [_P, _F, _I]),
+    "b200_comp_legal_policy": (_I, [_P, _I, ctypes.POINTER(ctypes.POINTER(_F)), ctypes.POINTER(_I)]),
     "b200_net_eval_host": (_I, [_P, _P, _P, _I, _P, _P, _P, _P]),
     "b200_net_eval_device": (_I, [_P, _P, _P, _I, _P, _P]),
     "b200_net_enqueue_device": (_I, [_P, _P, _P, _I, _P, _P]),

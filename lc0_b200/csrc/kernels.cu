@@ -850,6 +850,64 @@ cudaError_t launch_bias_skip_act(const T* x, const float* bias, const T* skip, T
   return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------------------
+// Legal-move softmax (reference: NetworkAsBackendComputation::SoftmaxPolicy, neural/wrapper.cc:135-156).
+// One warp per position.  The exponential is the reference's FastExp restated with explicitly unfused
+// multiplies and adds, and the total is accumulated sequentially in move order, so that the result is
+// bit-identical to the host formula applied to the same logits.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float fast_exp_ref(float x) {
+  const float a = __fmul_rn(1.442695040f, x);
+  int e;
+  if (a < 0.f) {
+    if (a < -126.f) return 0.f;
+    e = (int)__fadd_rn(a, -1.0f);
+  } else {
+    e = (int)a;
+  }
+  float out = __fadd_rn(a, -(float)e);
+  out = __fadd_rn(1.0f, __fmul_rn(out, __fadd_rn(0.6602339f, __fmul_rn(0.33976606f, out))));
+  return __int_as_float(__float_as_int(out) + (int)((unsigned)e << 23));
+}
+
+__global__ void __launch_bounds__(128)
+legal_softmax_kernel(const float* __restrict__ policy, const unsigned short* __restrict__ move_ids,
+                     const int* __restrict__ n_moves, int n, float inv_t, float* __restrict__ probs) {
+  __shared__ float vals[4][kLegalStride];
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sample = blockIdx.x * 4 + w;
+  if (sample >= n) return;
+  int cnt = n_moves[sample];
+  cnt = cnt < 0 ? 0 : (cnt > kLegalStride ? kLegalStride : cnt);
+  const unsigned short* ids = move_ids + (long long)sample * kLegalStride;
+  const float* pol = policy + (long long)sample * 1858;
+  float mx = -INFINITY;
+  for (int i = lane; i < cnt; i += 32) {
+    const int id = ids[i] < 1858 ? ids[i] : 1857;
+    const float v = pol[id];
+    vals[w][i] = v;
+    mx = fmaxf(mx, v);
+  }
+  mx = warp_max(mx);
+  __syncwarp();
+  for (int i = lane; i < cnt; i += 32) vals[w][i] = fast_exp_ref(__fmul_rn(__fadd_rn(vals[w][i], -mx), inv_t));
+  __syncwarp();
+  float total = 0.f;
+  if (lane == 0)
+    for (int i = 0; i < cnt; ++i) total = __fadd_rn(total, vals[w][i]);
+  total = __shfl_sync(0xffffffffu, total, 0);
+  const float scale = total > 0.f ? __fdiv_rn(1.0f, total) : 1.0f;
+  float* out = probs + (long long)sample * kLegalStride;
+  for (int i = lane; i < cnt; i += 32) out[i] = __fmul_rn(vals[w][i], scale);
+}
+
+cudaError_t launch_legal_softmax(const float* policy, const unsigned short* move_ids, const int* n_moves, int n,
+                                 float inv_temperature, float* probs, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  legal_softmax_kernel<<<ceil_div(n, 4), 128, 0, s>>>(policy, move_ids, n_moves, n, inv_temperature, probs);
+  return cudaGetLastError();
+}
+
 #define INSTANTIATE(T)                                                                                        \
   template cudaError_t launch_gemm_simt<T>(const GemmParams&, cudaStream_t);                                  \
   template cudaError_t launch_expand_planes<T>(const uint64_t*, const float*, int, T*, cudaStream_t);         \

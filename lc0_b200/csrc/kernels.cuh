@@ -94,6 +94,13 @@ template <typename T>
 cudaError_t launch_policy_gather(const T* raw, long long ld, const short* src_slot, int n, float* policy,
                                  cudaStream_t s);
 
+// Legal-move policy softmax on the device: probs[n][i] = FastExp((logit[move_ids[n][i]] - max) * inv_t) / total for
+// the first n_moves[n] entries (stride kLegalStride), same arithmetic and order as the reference's caller-side
+// SoftmaxPolicy (src/neural/wrapper.cc:135-156) with FastExp of src/utils/fastmath.h:59-86.
+constexpr int kLegalStride = 256;
+cudaError_t launch_legal_softmax(const float* policy, const unsigned short* move_ids, const int* n_moves, int n,
+                                 float inv_temperature, float* probs, cudaStream_t s);
+
 // Final tiny layers of the value / moves-left heads, one warp per sample:
 // mode 0: 3 logits -> softmax -> (q = w - l, d); mode 1: 1 output -> tanh -> q, d = 0;
 // mode 2: 1 output -> relu -> m.  h: [n][k]; w: fp32 [outs][k]; b: fp32 [outs]; qdm: [n][3].

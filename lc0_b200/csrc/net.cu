@@ -245,6 +245,10 @@ struct NetBase {
   struct HostSet {
     uint64_t* masks = nullptr;
     float *values = nullptr, *policy = nullptr, *qdm = nullptr;
+    // legal-move policy: per position up to kLegalStride policy indices in, probabilities out
+    unsigned short* move_ids = nullptr;
+    int* n_moves = nullptr;
+    float* probs = nullptr;
     int id = 0;
   };
   std::mutex host_mu;
@@ -262,10 +266,16 @@ struct NetBase {
     auto h = std::make_unique<HostSet>();
     if (cudaSetDevice(opt.gpu) != cudaSuccess || cudaMallocHost(&h->masks, nb * 112 * 8) != cudaSuccess ||
         cudaMallocHost(&h->values, nb * 112 * 4) != cudaSuccess ||
-        cudaMallocHost(&h->policy, nb * 1858 * 4) != cudaSuccess || cudaMallocHost(&h->qdm, nb * 3 * 4) != cudaSuccess) {
+        cudaMallocHost(&h->policy, nb * 1858 * 4) != cudaSuccess || cudaMallocHost(&h->qdm, nb * 3 * 4) != cudaSuccess ||
+        cudaMallocHost(&h->move_ids, nb * kLegalStride * 2) != cudaSuccess ||
+        cudaMallocHost(&h->n_moves, nb * 4) != cudaSuccess ||
+        cudaMallocHost(&h->probs, nb * kLegalStride * 4) != cudaSuccess) {
       if (h->masks) cudaFreeHost(h->masks);
       if (h->values) cudaFreeHost(h->values);
       if (h->policy) cudaFreeHost(h->policy);
+      if (h->qdm) cudaFreeHost(h->qdm);
+      if (h->move_ids) cudaFreeHost(h->move_ids);
+      if (h->n_moves) cudaFreeHost(h->n_moves);
       cudaGetLastError();
       throw Fail{B200_ERR_NOMEM, "cannot allocate pinned host staging for a computation"};
     }
@@ -284,12 +294,17 @@ struct NetBase {
       cudaFreeHost(h->values);
       cudaFreeHost(h->policy);
       cudaFreeHost(h->qdm);
+      cudaFreeHost(h->move_ids);
+      cudaFreeHost(h->n_moves);
+      cudaFreeHost(h->probs);
       delete h;
     }
     host_all.clear();
     host_free.clear();
   }
-  virtual int eval_staged(int slot, HostSet& hs, int n) = 0;
+  // policy_mode: 0 full 1858-logit policy, 1 full policy + legal-move probabilities, 2 legal-move probabilities
+  // only (the 1858-logit vectors stay on the device).
+  virtual int eval_staged(int slot, HostSet& hs, int n, int policy_mode, float inv_temperature) = 0;
   virtual cudaStream_t stream(int slot) = 0;
   virtual int device_status() = 0;
   // slot pool
@@ -356,6 +371,9 @@ struct Net : NetBase {
     cudaStream_t stream = nullptr;
     uint64_t* d_masks = nullptr;
     float *d_values = nullptr, *d_policy = nullptr, *d_qdm = nullptr;
+    unsigned short* d_move_ids = nullptr;
+    int* d_n_moves = nullptr;
+    float* d_probs = nullptr;
     T *tokens = nullptr, *pre = nullptr, *pe = nullptr;
     T *x = nullptr, *x1 = nullptr, *y = nullptr, *qkv = nullptr, *att = nullptr, *ffn = nullptr;
     T *sg_c = nullptr, *sg_h1 = nullptr, *sg_h2 = nullptr, *sg_bias = nullptr;
@@ -831,6 +849,9 @@ struct Net : NetBase {
       s.d_values = (float*)salloc.alloc(nb * 112 * 4);
       s.d_policy = (float*)salloc.alloc(nb * 1858 * 4);
       s.d_qdm = (float*)salloc.alloc(nb * 3 * 4);
+      s.d_move_ids = (unsigned short*)salloc.alloc(nb * kLegalStride * 2);
+      s.d_n_moves = (int*)salloc.alloc(nb * 4);
+      s.d_probs = (float*)salloc.alloc(nb * kLegalStride * 4);
       const int body_ch = attn_body ? E : C;
       if (!res.empty() || !attn_body) {
         s.tokens = A(R * 112);
@@ -1162,11 +1183,22 @@ struct Net : NetBase {
   };
   std::vector<std::map<GraphKey, GraphEntry>> graph_cache;  // per slot
 
-  void enqueue_staged(Slot& s, HostSet& hs, int n) {
+  void enqueue_staged(Slot& s, HostSet& hs, int n, int policy_mode, float inv_t) {
     CK(cudaMemcpyAsync(s.d_masks, hs.masks, (size_t)n * 112 * 8, cudaMemcpyHostToDevice, s.stream));
     CK(cudaMemcpyAsync(s.d_values, hs.values, (size_t)n * 112 * 4, cudaMemcpyHostToDevice, s.stream));
+    if (policy_mode) {
+      CK(cudaMemcpyAsync(s.d_move_ids, hs.move_ids, (size_t)n * kLegalStride * 2, cudaMemcpyHostToDevice, s.stream));
+      CK(cudaMemcpyAsync(s.d_n_moves, hs.n_moves, (size_t)n * 4, cudaMemcpyHostToDevice, s.stream));
+    }
     forward(s, s.d_masks, s.d_values, n, s.d_policy, s.d_qdm);
-    CK(cudaMemcpyAsync(hs.policy, s.d_policy, (size_t)n * 1858 * 4, cudaMemcpyDeviceToHost, s.stream));
+    if (policy_mode) {
+      other(s.stream, (double)n * kLegalStride * 6, [&] {
+        return launch_legal_softmax(s.d_policy, s.d_move_ids, s.d_n_moves, n, inv_t, s.d_probs, s.stream);
+      });
+      CK(cudaMemcpyAsync(hs.probs, s.d_probs, (size_t)n * kLegalStride * 4, cudaMemcpyDeviceToHost, s.stream));
+    }
+    if (policy_mode != 2)
+      CK(cudaMemcpyAsync(hs.policy, s.d_policy, (size_t)n * 1858 * 4, cudaMemcpyDeviceToHost, s.stream));
     CK(cudaMemcpyAsync(hs.qdm, s.d_qdm, (size_t)n * 3 * 4, cudaMemcpyDeviceToHost, s.stream));
   }
 
@@ -1234,10 +1266,14 @@ struct Net : NetBase {
     if (sync) CK(cudaStreamSynchronize(s.stream));
     return B200_OK;
   }
-  int eval_staged(int slot, HostSet& hs, int n) override {
+  int eval_staged(int slot, HostSet& hs, int n, int policy_mode, float inv_t) override {
     Slot& s = slots[slot];
-    // the captured copy nodes embed the host set's addresses, so each host set gets its own graph
-    run_or_replay(slot, GraphKey{n, hs.id, nullptr, nullptr, nullptr, nullptr}, [&] { enqueue_staged(s, hs, n); });
+    // The captured copy nodes embed the host set's addresses and the softmax launch its temperature, so each
+    // (host set, policy mode, temperature) gets its own graph; the temperature's bits ride in a pointer field.
+    uint32_t tbits;
+    memcpy(&tbits, &inv_t, 4);
+    run_or_replay(slot, GraphKey{n, hs.id * 4 + policy_mode, nullptr, nullptr, nullptr, (const void*)(uintptr_t)tbits},
+                  [&] { enqueue_staged(s, hs, n, policy_mode, inv_t); });
     CK(cudaStreamSynchronize(s.stream));
     return B200_OK;
   }
@@ -1263,6 +1299,9 @@ struct b200_comp {
   std::shared_ptr<NetBase> net;
   NetBase::HostSet* hs = nullptr;  // pinned staging, taken from the network's pool at the first AddInput
   int n = 0;
+  int with_moves = 0;    // inputs added together with their legal moves
+  bool compact = false;  // return only legal-move probabilities (no 1858-logit vectors)
+  float inv_temperature = 1.0f;
   bool computed = false;
 };
 
@@ -1382,6 +1421,7 @@ int b200_comp_add_inputs(b200_comp* c, const uint64_t* masks, const float* value
     if (!c->hs) c->hs = c->net->acquire_host();
     memcpy(c->hs->masks + (size_t)c->n * 112, masks, (size_t)n * 112 * 8);
     memcpy(c->hs->values + (size_t)c->n * 112, values, (size_t)n * 112 * 4);
+    for (int i = 0; i < n; ++i) c->hs->n_moves[c->n + i] = 0;
     c->n += n;
     return (int)B200_OK;
   });
@@ -1399,7 +1439,8 @@ int b200_comp_compute(b200_comp* c) {
     const int slot = nb->acquire();
     int rc;
     try {
-      rc = nb->eval_staged(slot, *c->hs, c->n);
+      const int mode = c->with_moves ? (c->compact ? 2 : 1) : 0;
+      rc = nb->eval_staged(slot, *c->hs, c->n, mode, c->inv_temperature);
     } catch (...) {
       nb->release(slot);
       throw;
@@ -1415,6 +1456,47 @@ float b200_comp_d(const b200_comp* c, int s) { return c->hs->qdm[(size_t)s * 3 +
 float b200_comp_m(const b200_comp* c, int s) { return c->hs->qdm[(size_t)s * 3 + 2]; }
 float b200_comp_p(const b200_comp* c, int s, int move_id) { return c->hs->policy[(size_t)s * 1858 + move_id]; }
 const float* b200_comp_policy(const b200_comp* c, int s) { return c->hs->policy + (size_t)s * 1858; }
+int b200_comp_add_input_with_moves(b200_comp* c, const uint64_t* masks, const float* values,
+                                   const uint16_t* move_ids, int n_moves) {
+  if (!c || !move_ids || n_moves < 0 || n_moves > kLegalStride) {
+    set_error("b200_comp_add_input_with_moves: bad argument (at most 256 legal moves per position)");
+    return B200_ERR_INVALID;
+  }
+  for (int i = 0; i < n_moves; ++i)
+    if (move_ids[i] >= 1858) {
+      set_error("b200_comp_add_input_with_moves: policy index out of range");
+      return B200_ERR_INVALID;
+    }
+  const int rc = b200_comp_add_inputs(c, masks, values, 1);
+  if (rc != B200_OK) return rc;
+  const int idx = c->n - 1;
+  memcpy(c->hs->move_ids + (size_t)idx * kLegalStride, move_ids, (size_t)n_moves * 2);
+  c->hs->n_moves[idx] = n_moves;
+  c->with_moves++;
+  return B200_OK;
+}
+int b200_comp_add_inputs_with_moves(b200_comp* c, const uint64_t* masks, const float* values,
+                                    const uint16_t* move_ids, const int* n_moves, int n) {
+  if (!c || !masks || !values || !move_ids || !n_moves || n < 0) return B200_ERR_INVALID;
+  for (int i = 0; i < n; ++i) {
+    const int rc = b200_comp_add_input_with_moves(c, masks + (size_t)i * 112, values + (size_t)i * 112,
+                                                  move_ids + (size_t)i * kLegalStride, n_moves[i]);
+    if (rc != B200_OK) return rc;
+  }
+  return B200_OK;
+}
+int b200_comp_set_policy_options(b200_comp* c, float inv_temperature, int compact) {
+  if (!c || !(inv_temperature > 0.f)) return B200_ERR_INVALID;
+  c->inv_temperature = inv_temperature;
+  c->compact = compact != 0;
+  return B200_OK;
+}
+int b200_comp_legal_policy(const b200_comp* c, int sample, const float** probs, int* n_moves) {
+  if (!c || !probs || !n_moves || !c->computed || !c->with_moves || sample < 0 || sample >= c->n) return B200_ERR_INVALID;
+  *probs = c->hs->probs + (size_t)sample * kLegalStride;
+  *n_moves = c->hs->n_moves[sample];
+  return B200_OK;
+}
 void b200_comp_destroy(b200_comp* c) {
   if (!c) return;
   if (c->hs) c->net->release_host(c->hs);
@@ -1437,7 +1519,7 @@ int b200_net_eval_host(b200_net* net, const uint64_t* masks, const float* values
     const int slot = nb->acquire();
     int rc;
     try {
-      rc = nb->eval_staged(slot, *hs, n);
+      rc = nb->eval_staged(slot, *hs, n, 0, 1.0f);
       if (rc == B200_OK) {
         if (policy) memcpy(policy, hs->policy, (size_t)n * 1858 * 4);
         for (int i = 0; i < n; ++i) {

@@ -59,6 +59,39 @@ class NetworkComputation:
             raise ValueError("add_input expects 112 masks and 112 values")
         _lib.check(self._lib.b200_comp_add_input(self._h, m.ctypes.data, v.ctypes.data))
 
+    def add_input_with_moves(self, masks, values, move_ids):
+        """AddInput plus the policy indices of the position's legal moves (MoveToNNIndex of each move); the
+        legal-move softmax then runs on the device (see `legal_policy`)."""
+        m = np.ascontiguousarray(masks, np.uint64).reshape(-1)
+        v = np.ascontiguousarray(values, np.float32).reshape(-1)
+        ids = np.ascontiguousarray(move_ids, np.uint16).reshape(-1)
+        if m.size != 112 or v.size != 112:
+            raise ValueError("add_input expects 112 masks and 112 values")
+        _lib.check(self._lib.b200_comp_add_input_with_moves(self._h, m.ctypes.data, v.ctypes.data, ids.ctypes.data,
+                                                            ids.size))
+
+    def add_inputs_with_moves(self, masks, values, move_ids, n_moves):
+        """Batch form: move_ids [n][256] (rows padded), n_moves [n]."""
+        m = np.ascontiguousarray(masks, np.uint64).reshape(-1, 112)
+        v = np.ascontiguousarray(values, np.float32).reshape(-1, 112)
+        ids = np.ascontiguousarray(move_ids, np.uint16).reshape(-1, 256)
+        cnt = np.ascontiguousarray(n_moves, np.int32).reshape(-1)
+        if not (m.shape[0] == v.shape[0] == ids.shape[0] == cnt.shape[0]):
+            raise ValueError("masks, values, move_ids and n_moves must describe the same number of positions")
+        _lib.check(self._lib.b200_comp_add_inputs_with_moves(self._h, m.ctypes.data, v.ctypes.data, ids.ctypes.data,
+                                                             cnt.ctypes.data, m.shape[0]))
+
+    def set_policy_options(self, temperature=1.0, compact=False):
+        """Policy softmax temperature (the wrapper multiplies by 1/temperature) and compact return."""
+        _lib.check(self._lib.b200_comp_set_policy_options(self._h, 1.0 / float(temperature), 1 if compact else 0))
+
+    def legal_policy(self, sample):
+        """Probabilities of the sample's legal moves, in the order the moves were given."""
+        p = ctypes.POINTER(ctypes.c_float)()
+        n = ctypes.c_int()
+        _lib.check(self._lib.b200_comp_legal_policy(self._h, sample, ctypes.byref(p), ctypes.byref(n)))
+        return np.ctypeslib.as_array(p, shape=(n.value,)).copy() if n.value else np.zeros(0, np.float32)
+
     def add_inputs(self, masks, values):
         m = np.ascontiguousarray(masks, np.uint64).reshape(-1, 112)
         v = np.ascontiguousarray(values, np.float32).reshape(-1, 112)

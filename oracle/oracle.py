@@ -328,6 +328,32 @@ def _gather(raw, pmap):
     return out
 
 
+def fast_exp(x):
+    """`FastExp` / `FastExp2` (utils/fastmath.h:59-86) on float32 arrays, operation by operation."""
+    a = (F32(1.442695040) * np.asarray(x, F32)).astype(F32)
+    neg = a < 0
+    e = np.where(neg, (a - F32(1)).astype(F32), a).astype(np.int32)  # C cast truncates toward zero
+    out = (a - e.astype(F32)).astype(F32)
+    out = (F32(1) + out * (F32(0.6602339) + F32(0.33976606) * out).astype(F32)).astype(F32)
+    bits = out.view(np.int32) + (e.astype(np.uint32) << np.uint32(23)).astype(np.int32)
+    res = bits.view(F32)
+    return np.where(a < F32(-126), F32(0), res).astype(F32)
+
+
+def softmax_policy(policy_row, move_ids, inv_temperature=1.0):
+    """`NetworkAsBackendComputation::SoftmaxPolicy` (neural/wrapper.cc:135-156): legal-move softmax with FastExp
+    and a sequentially accumulated total."""
+    v = np.asarray(policy_row, F32)[np.asarray(move_ids, np.int64)]
+    if v.size == 0:
+        return v
+    e = fast_exp(((v - v.max()) * F32(inv_temperature)).astype(F32))
+    total = F32(0)
+    for t in e:
+        total = F32(total + t)
+    scale = F32(1) / total if total > 0 else F32(1)
+    return (e * scale).astype(F32)
+
+
 def legal_softmax(policy_row, legal_indices):
     """Softmax over the legal moves only, temperature 1 (what the caller does with
     GetPVal, neural/wrapper.cc:135-156)."""

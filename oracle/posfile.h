@@ -8,6 +8,7 @@
 // Result file:
 //   char magic[8] = "LC0OUT1\0"; int32 n;
 //   float policy[n][1858]; float q[n]; float d[n]; float m[n];
+//   float legal_probs[n][256]  (legal-move softmax at temperature 1, zero padded)
 #pragma once
 #include <cstdint>
 #include <cstdio>

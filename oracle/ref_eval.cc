@@ -10,12 +10,15 @@
 //               "evals_per_s=<v> n=<n> repeat=<r> seconds=<s>" on stdout.
 #include <chrono>
 #include <cstdlib>
+#include <algorithm>
 #include <iostream>
+#include <limits>
 
 #include "chess/board.h"
 #include "neural/factory.h"
 #include "neural/loader.h"
 #include "oracle/posfile.h"
+#include "utils/fastmath.h"
 #include "utils/optionsdict.h"
 
 using namespace lczero;
@@ -71,6 +74,20 @@ int main(int argc, char** argv) {
       fwrite(v.data(), 4, n, f);
       for (int s = 0; s < n; ++s) v[s] = comp->GetMVal(s);
       fwrite(v.data(), 4, n, f);
+      // Legal-move softmax at temperature 1 with the reference's own FastExp, in the order and arithmetic of
+      // NetworkAsBackendComputation::SoftmaxPolicy (neural/wrapper.cc:135-156); float probs[n][256].
+      std::vector<float> probs(size_t(n) * 256, 0.0f);
+      for (int s = 0; s < n; ++s) {
+        const int cnt = std::min(pf.n_legal[s], 256);
+        float* dst = &probs[size_t(s) * 256];
+        float max_p = -std::numeric_limits<float>::infinity();
+        for (int i = 0; i < cnt; ++i) max_p = std::max(max_p, dst[i] = comp->GetPVal(s, pf.legal[size_t(s) * 256 + i]));
+        float total = 0.0f;
+        for (int i = 0; i < cnt; ++i) total = total + (dst[i] = FastExp((dst[i] - max_p) * 1.0f));
+        const float scale = total > 0.0f ? 1.0f / total : 1.0f;
+        for (int i = 0; i < cnt; ++i) dst[i] *= scale;
+      }
+      fwrite(probs.data(), 4, probs.size(), f);
       fclose(f);
     }
     if (repeat > 0) {

@@ -4,7 +4,8 @@
    position encoder (oracle/_ref/mkpos): packed planes + legal-move policy indices.
 2. golden_<net>.npz outputs of the reference's `blas` backend (oracle/_ref/ref_eval)
    for the seeded synthetic network <net> on the first positions of the matching
-   position set.  These pin the numpy oracle; the reference has no vectors of its own.
+   position set, plus the legal-move softmax the reference's wrapper applies to them (computed by ref_eval with the
+   reference's own FastExp).  These pin the numpy oracle; the reference has no vectors of its own.
 
 usage: python tests/golden/make_golden.py   (after python oracle/build_ref.py)
 """
@@ -69,10 +70,11 @@ def read_out(path):
     b = open(path, "rb").read()
     assert b[:7] == b"LC0OUT1"
     n = int(np.frombuffer(b[8:12], "<i4")[0])
-    a = np.frombuffer(b, "<f4", n * 1861, 12)
+    a = np.frombuffer(b, "<f4", n * (1861 + 256), 12)
     pol = a[:n * 1858].reshape(n, 1858)
-    q, d, m = a[n * 1858:].reshape(3, n)
-    return dict(policy=pol, q=q, d=d, m=m)
+    q, d, m = a[n * 1858:n * 1861].reshape(3, n)
+    legal_probs = a[n * 1861:].reshape(n, 256)
+    return dict(policy=pol, q=q, d=d, m=m, legal_probs=legal_probs)
 
 
 def main():

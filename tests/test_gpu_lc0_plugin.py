@@ -49,7 +49,7 @@ def test_registered_backend_through_lc0_factory(tmp_path, name):
     assert r.returncode == 0, r.stderr
     raw = np.fromfile(opath, "<f4", offset=12)
     pol = raw[:n * 1858].reshape(n, 1858)
-    q, d, m = raw[n * 1858:].reshape(3, n)
+    q, d, m = raw[n * 1858:n * 1861].reshape(3, n)
     scale = np.abs(g["policy"]).max()
     assert np.abs(pol - g["policy"]).max() <= 1e-5 * scale
     assert np.abs(q - g["q"]).max() <= 1e-5 and np.abs(d - g["d"]).max() <= 1e-5

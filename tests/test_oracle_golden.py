@@ -73,3 +73,21 @@ def test_activation_formulas():
     np.testing.assert_allclose(oracle.activate(x, oracle.ACT_MISH), x * np.tanh(sp), atol=1e-6)
     np.testing.assert_allclose(oracle.activate(x, oracle.ACT_RELU_2), np.where(x > 0, x * x, 0))
     np.testing.assert_allclose(oracle.activate(x, oracle.ACT_SWISH), x / (1 + np.exp(-x)), atol=1e-6)
+
+
+@pytest.mark.parametrize("name", ["cfg1_mini", "cfg4_mini", "cfg3"])
+def test_softmax_policy_restatement_is_bit_exact(name):
+    """oracle.softmax_policy / fast_exp against the reference's own FastExp applied by ref_eval."""
+    net, pos, n, g = load_case(name)
+    for i in range(n):
+        ids = pos["legal"][i][:pos["n_legal"][i]]
+        got = oracle.softmax_policy(g["policy"][i], ids)
+        assert np.array_equal(got, g["legal_probs"][i][:len(ids)])
+        assert np.all(g["legal_probs"][i][len(ids):] == 0)
+
+
+def test_fast_exp_edges():
+    x = np.array([0.0, -1e-3, -0.5, -1.0, -10.0, -87.0, -88.0, -200.0], np.float32)
+    y = oracle.fast_exp(x)
+    assert y[0] == 1.0 and y[-1] == 0.0
+    np.testing.assert_allclose(y[:6], np.exp(x[:6].astype(np.float64)), rtol=4e-3)  # FastExp is a 2nd-order fit
