@@ -4,6 +4,9 @@
 // decoded weights (lczero::MultiHeadWeights, src/neural/network_legacy.h:178-229) into the named tensors
 // the C ABI of include/b200nn.h expects, and registers the factory with REGISTER_NETWORK
 // (src/neural/factory.h:111-142) under the names "b200" (fp16), "b200-bf16" and "b200-fp32".
+// It also registers "b200-native", a direct lczero::Backend (src/neural/backend.h:64-133) that skips the
+// Network-to-Backend wrapper of src/neural/wrapper.cc: the legal-move policy softmax of that wrapper runs on the
+// device and only the legal moves' probabilities come back to the host.
 // Build: add this file to lc0's source list and link libb200nn.so; this file is GPL-3
 // like lc0 because it includes lc0 headers, the library behind the C ABI contains no lc0 code.
 //
@@ -14,9 +17,16 @@
 #include <string>
 #include <vector>
 
+#include <mutex>
+
 #include "include/b200nn.h"
+#include "neural/backend.h"
+#include "neural/encoder.h"
 #include "neural/factory.h"
+#include "neural/loader.h"
 #include "neural/network_legacy.h"
+#include "neural/register.h"
+#include "neural/shared_params.h"
 #include "neural/tables/activation_function.h"
 #include "utils/exception.h"
 
@@ -224,6 +234,8 @@ class B200Network : public Network {
   bool IsCpu() const override { return false; }
   int GetMiniBatchSize() const override { return 2 * info_.sm_count; }
   int GetPreferredBatchStep() const override { return 1; }
+  b200_net* net() const { return net_; }
+  const b200_net_info& info() const { return info_; }
 
  private:
   NetworkCapabilities capabilities_;
@@ -241,6 +253,151 @@ std::unique_ptr<Network> MakeB200Network(const std::optional<WeightsFile>& w, co
 REGISTER_NETWORK("b200", MakeB200Network<B200_PREC_FP16>, 90)
 REGISTER_NETWORK("b200-bf16", MakeB200Network<B200_PREC_BF16>, 89)
 REGISTER_NETWORK("b200-fp32", MakeB200Network<B200_PREC_FP32>, 88)
+
+
+// ---- native Backend ---------------------------------------------------------------------------------------------
+// Same contract as NetworkAsBackend (src/neural/wrapper.cc:48-101) with two differences: the batch limit is the
+// network's max_batch option instead of the wrapper's fixed 1024, and EvalResultPtr::p is filled from the device's
+// legal-move softmax (same FastExp arithmetic and summation order, so the numbers are bit-identical to the wrapper's).
+
+FillEmptyHistory ParseHistoryFill(const std::string& s) {
+  if (s == "fen_only") return FillEmptyHistory::FEN_ONLY;
+  if (s == "always") return FillEmptyHistory::ALWAYS;
+  return FillEmptyHistory::NO;
+}
+
+class B200Backend : public Backend {
+ public:
+  B200Backend(std::unique_ptr<B200Network> network, const OptionsDict& options)
+      : network_(std::move(network)),
+        backend_opts_(options.Get<std::string>(SharedBackendParams::kBackendOptionsId)),
+        weights_path_(options.Get<std::string>(SharedBackendParams::kWeightsId)) {
+    UpdateConfiguration(options);
+  }
+
+  BackendAttributes GetAttributes() const override {
+    const NetworkCapabilities& caps = network_->GetCapabilities();
+    BackendAttributes a;
+    a.has_mlh = caps.has_mlh();
+    a.has_wdl = caps.has_wdl();
+    a.runs_on_cpu = false;
+    a.suggested_num_search_threads = network_->GetThreads();
+    a.recommended_batch_size = network_->GetMiniBatchSize();
+    a.maximum_batch_size = network_->info().max_batch;
+    return a;
+  }
+  std::unique_ptr<BackendComputation> CreateComputation() override;
+
+  UpdateConfigurationResult UpdateConfiguration(const OptionsDict& options) override {
+    Backend::UpdateConfiguration(options);
+    if (backend_opts_ != options.Get<std::string>(SharedBackendParams::kBackendOptionsId)) return NEED_RESTART;
+    if (weights_path_ != options.Get<std::string>(SharedBackendParams::kWeightsId)) return NEED_RESTART;
+    inv_temperature_ = 1.0f / options.Get<float>(SharedBackendParams::kPolicySoftmaxTemp);
+    history_fill_ = ParseHistoryFill(options.Get<std::string>(SharedBackendParams::kHistoryFill));
+    return UPDATE_OK;
+  }
+
+ private:
+  friend class B200BackendComputation;
+  std::unique_ptr<B200Network> network_;
+  const std::string backend_opts_;
+  const std::string weights_path_;
+  float inv_temperature_ = 1.0f;
+  FillEmptyHistory history_fill_ = FillEmptyHistory::NO;
+};
+
+class B200BackendComputation : public BackendComputation {
+ public:
+  explicit B200BackendComputation(B200Backend* backend)
+      : backend_(backend),
+        input_format_(backend->network_->GetCapabilities().input_format),
+        wdl_(backend->network_->info().wdl != 0),
+        mlh_(backend->network_->info().has_mlh != 0) {
+    Check(b200_comp_create(backend->network_->net(), &comp_));
+    Check(b200_comp_set_policy_options(comp_, backend->inv_temperature_, /*compact=*/1));
+    results_.reserve(256);
+  }
+  ~B200BackendComputation() override { b200_comp_destroy(comp_); }
+
+  size_t UsedBatchSize() const override { return results_.size(); }
+
+  AddInputResult AddInput(const EvalPosition& pos, EvalResultPtr result) override {
+    int transform;
+    const InputPlanes planes =
+        EncodePositionForNN(input_format_, pos.pos, 8, backend_->history_fill_, &transform);
+    uint64_t masks[kInputPlanes];
+    float values[kInputPlanes];
+    for (int i = 0; i < kInputPlanes; ++i) {
+      masks[i] = planes[i].mask;
+      values[i] = planes[i].value;
+    }
+    uint16_t ids[256];
+    int n_moves = 0;
+    if (!result.p.empty()) {
+      if (pos.legal_moves.size() > 256 || result.p.size() != pos.legal_moves.size())
+        throw Exception("b200 backend: bad legal-move list");
+      for (const Move& m : pos.legal_moves) ids[n_moves++] = MoveToNNIndex(m, transform);
+    }
+    // The search may add inputs to one computation from several threads (the wrapper uses an atomic vector).
+    std::lock_guard<std::mutex> lock(mutex_);
+    Check(b200_comp_add_input_with_moves(comp_, masks, values, ids, n_moves));
+    results_.push_back(result);
+    return ENQUEUED_FOR_EVAL;
+  }
+
+  void ComputeBlocking() override {
+    if (results_.empty()) return;
+    Check(b200_comp_compute(comp_));
+    for (size_t i = 0; i < results_.size(); ++i) {
+      const EvalResultPtr& r = results_[i];
+      if (r.q) *r.q = b200_comp_q(comp_, i);
+      if (r.d) *r.d = wdl_ ? b200_comp_d(comp_, i) : 0.0f;
+      if (r.m) *r.m = mlh_ ? b200_comp_m(comp_, i) : 0.0f;
+      if (!r.p.empty()) {
+        const float* probs = nullptr;
+        int n = 0;
+        Check(b200_comp_legal_policy(comp_, i, &probs, &n));
+        std::copy(probs, probs + n, r.p.begin());
+      }
+    }
+  }
+
+ private:
+  B200Backend* backend_;
+  pblczero::NetworkFormat::InputFormat input_format_;
+  bool wdl_, mlh_;
+  b200_comp* comp_ = nullptr;
+  std::mutex mutex_;
+  std::vector<EvalResultPtr> results_;
+};
+
+std::unique_ptr<BackendComputation> B200Backend::CreateComputation() {
+  return std::make_unique<B200BackendComputation>(this);
+}
+
+class B200BackendFactory : public BackendFactory {
+ public:
+  int GetPriority() const override { return 87; }
+  std::string_view GetName() const override { return "b200-native"; }
+  // Option handling as in NetworkAsBackendFactory::Create (src/neural/wrapper.cc:182-198); precision=<fp16|bf16|fp32>.
+  std::unique_ptr<Backend> Create(const OptionsDict& options) override {
+    OptionsDict network_options;
+    network_options.AddSubdictFromString(options.Get<std::string>(SharedBackendParams::kBackendOptionsId));
+    const std::optional<WeightsFile> weights = LoadWeights(options.Get<std::string>(SharedBackendParams::kWeightsId));
+    if (!weights) throw Exception("The b200 backend requires a network file.");
+    const std::string prec = network_options.GetOrDefault<std::string>("precision", "fp16");
+    int precision;
+    if (prec == "fp16") precision = B200_PREC_FP16;
+    else if (prec == "bf16") precision = B200_PREC_BF16;
+    else if (prec == "fp32") precision = B200_PREC_FP32;
+    else throw Exception("b200 backend: unknown precision '" + prec + "'");
+    auto network = std::make_unique<B200Network>(*weights, network_options, precision);
+    network_options.CheckAllOptionsRead("b200-native");
+    return std::make_unique<B200Backend>(std::move(network), options);
+  }
+};
+
+[[maybe_unused]] static BackendManager::Register reg_b200_native(std::make_unique<B200BackendFactory>());
 
 }  // namespace
 }  // namespace lczero

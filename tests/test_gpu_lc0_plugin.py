@@ -78,3 +78,46 @@ def test_lc0_backendbench_and_check_decorator(tmp_path):
     out = r.stdout + r.stderr
     assert r.returncode == 0, out[-2000:]
     assert "Check passed" in out or "passed" in out.lower(), out[-2000:]
+
+
+def _search(exe, npath, backend, opts, nodes=400, positions=3):
+    cmd = [exe, "benchmark", "--weights=" + npath, "--backend=" + backend, "--nodes=%d" % nodes, "--threads=1",
+           "--num-positions=%d" % positions]
+    if opts:
+        cmd.append("--backend-opts=" + opts)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-2000:]
+    best = [l.split()[1] for l in out.splitlines() if l.startswith("bestmove")]
+    assert len(best) == positions, out[-2000:]
+    return best
+
+
+@needs_plugin
+def test_native_backend_searches_like_the_wrapped_network(tmp_path):
+    """lc0's own single-threaded search over the native Backend ("b200-native": legal-move softmax on the device,
+    compact return) picks the same moves as over the Network adapter behind lc0's wrapper (host softmax)."""
+    npath = str(tmp_path / "n.pb.gz")
+    mknet.write_net("cfg4_mini", npath)
+    exe = os.path.join(REF, "lc0_ref")
+    wrapped = _search(exe, npath, "b200", "")
+    native = _search(exe, npath, "b200-native", "")
+    assert native == wrapped
+    native32 = _search(exe, npath, "b200-native", "precision=fp32")
+    wrapped32 = _search(exe, npath, "b200-fp32", "")
+    assert native32 == wrapped32
+
+
+@needs_plugin
+def test_native_backend_backendbench_and_options(tmp_path):
+    npath = str(tmp_path / "n.pb.gz")
+    mknet.write_net("cfg3_mini", npath)
+    exe = os.path.join(REF, "lc0_ref")
+    r = subprocess.run([exe, "backendbench", "--weights=" + npath, "--backend=b200-native",
+                        "--backend-opts=max_batch=2048", "--batches=2", "--start-batch-size=512",
+                        "--max-batch-size=1024", "--batch-step=256"], capture_output=True, text=True, timeout=300)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0 and "1024" in out, out[-2000:]
+    r = subprocess.run([exe, "backendbench", "--weights=" + npath, "--backend=b200-native",
+                        "--backend-opts=precision=fp64", "--batches=1"], capture_output=True, text=True, timeout=300)
+    assert "unknown precision" in r.stdout + r.stderr
