@@ -158,8 +158,11 @@ __device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Arrival on a barrier of a CTA of the cluster.  Relaxed: the arrivals of this kernel only hand tensor memory back
+// to the MMA issuer (ordered by tcgen05.fence), no generic-proxy data is published through them; a release at
+// cluster scope here stalled the arriving thread for 2-3 thousand cycles per tile.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA load whose completion is signalled on a barrier that may live in the peer CTA of the pair (no multicast:
 // each CTA of the pair fetches its own half of the operands).
@@ -237,6 +240,14 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
          ((uint32_t)(BM >> 4) << 24);
 }
 
+#ifdef B200_TRACE
+// Development aid (not compiled into the library): clock64() checkpoints of CTA 0 of the pair kernel.
+__device__ long long g_trace[4096];
+#define TRACE(idx) do { if (blockIdx.x == 0 && (idx) < 4096) g_trace[(idx)] = clock64(); } while (0)
+#else
+#define TRACE(idx) do { } while (0)
+#endif
+
 struct TcParams {
   const float* bias;
   void* C;
@@ -304,7 +315,10 @@ template <typename T>
 __device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorMap* tmap_c, const CUtensorMap* tmap_r,
                                               uint8_t* buf, uint32_t res_bar, uint32_t res_parity, int group,
                                               bool leader, uint32_t taddr, int row, int lane, int m0, int nb,
-                                              float* wvec, RowCtx& rc, volatile int* abort_flag, volatile int* res_ok) {
+                                              float* wvec, RowCtx& rc, volatile int* abort_flag, volatile int* res_ok,
+                                              int tr = -1) {
+#define ETRACE(k) do { if (leader && tr >= 0) TRACE(tr + (k)); } while (0)
+  ETRACE(0);
   auto col = [&](const float* src, int i) { return (src && nb + i < p.N) ? __ldg(src + nb + i) : 0.f; };
   if (p.bias) { wvec[lane] = col(p.bias, lane); wvec[32 + lane] = col(p.bias, 32 + lane); }
   if (p.a_stats) { wvec[64 + lane] = col(p.colsum, lane); wvec[96 + lane] = col(p.colsum, 32 + lane); }
@@ -314,16 +328,19 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorM
   }
   if (leader) {
     tma_store_wait_read1();  // the store issued two slabs ago (same buffer) has been read out
+    ETRACE(1);
     if (p.res_mode) {
       mbar_expect_tx(res_bar, BM * 128);
       tma_load_2d(smem_u32(buf), tmap_r, nb, m0, res_bar);
     }
   }
   epilogue_barrier(group);  // also orders the wvec writes before the reads below
+  ETRACE(2);
   uint32_t r0[32], r1[32];
   tmem_ld32(taddr, r0);
   tmem_ld32(taddr + 32, r1);
   tmem_ld_wait();
+  ETRACE(3);
   float v[64];
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
@@ -395,12 +412,17 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorM
     o.w = pack_pair<T>(v[c * 8 + 6], v[c * 8 + 7]);
     *reinterpret_cast<uint4*>(srow + ((c ^ (row & 7)) << 4)) = o;
   }
+  ETRACE(4);
   fence_async_smem();
+  ETRACE(5);
   epilogue_barrier(group);
+  ETRACE(6);
   if (leader) {
     tma_store_2d(tmap_c, nb, m0, smem_u32(buf));
     tma_store_commit();
   }
+  ETRACE(7);
+#undef ETRACE
 }
 
 template <int BN> struct TileCfg {
@@ -706,6 +728,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (rank == 0) mbar_expect_tx(fb_local, 2 * Cfg::kStageBytes);  // both CTAs' bytes land on this barrier
           const uint32_t fb = mapa(fb_local, 0);
           const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
+          if (it < 256) TRACE(it);
           tma_load_2d_pair(sa, &tmap_a, kb * BK, m0, fb);
           tma_load_2d_pair(sa + BM * BK * 2, &tmap_w, kb * BK, n0, fb);
         }
@@ -722,12 +745,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
         if (!mbar_wait(smem_u32(&tempty_bar[acc]), aph ^ 1, abort_flag, 2)) break;
         tcgen05_fence_after();
+        if (tile_it < 64) TRACE(512 + tile_it);
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, 3)) { ok = false; break; }
           tcgen05_fence_after();
+          if (it < 256) TRACE(256 + it);
           const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
           const uint64_t adesc = make_smem_desc(sa);
           const uint64_t bdesc = make_smem_desc(sa + BM * BK * 2);
@@ -755,8 +780,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     for (int t = pair; t < tiles; t += pairs, ++tile_it) {
       const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
       const int m0 = (t / n_tiles) * (2 * BM) + (int)rank * BM, n0 = (t % n_tiles) * BN;
+      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 0);
       if (leader) epi_ok[group] = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4) ? 1 : 0;
+      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 1);
       epilogue_barrier(group);
+      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 2);
       if (!epi_ok[group]) break;
       tcgen05_fence_after();
       const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
@@ -768,12 +796,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (n0 + c0 >= p.N) break;  // uniform over the group
         epilogue_slab<T>(p, &tmap_c, &tmap_r, gbuf + (slab_it & 1) * (BM * 128),
                          smem_u32(&res_bar[group * 2 + (slab_it & 1)]), (slab_it >> 1) & 1, group, leader, trow + c0,
-                         quarter * 32 + lane, lane, m0, n0 + c0, wvec, rc, abort_flag, res_ok);
+                         quarter * 32 + lane, lane, m0, n0 + c0, wvec, rc, abort_flag, res_ok,
+#ifdef B200_TRACE
+                         slab_it < 32 ? 1024 + (group * 32 + (int)slab_it) * 8 : -1
+#else
+                         -1
+#endif
+        );
         ++slab_it;
       }
       flush_row_ctx(p, m, rc);
       tcgen05_fence_before();
       __syncwarp();
+      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 3);
       if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&tempty_bar[acc]), 0));
     }
     if (leader) tma_store_wait_all();
@@ -1022,3 +1057,9 @@ template cudaError_t launch_gemm_tc<__half>(const GemmParams&, int*, int, cudaSt
 template cudaError_t launch_gemm_tc<__nv_bfloat16>(const GemmParams&, int*, int, cudaStream_t);
 
 }  // namespace b200
+
+#ifdef B200_TRACE
+extern "C" int b200_trace_read(long long* out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, b200::g_trace, sizeof(long long) * n);
+}
+#endif

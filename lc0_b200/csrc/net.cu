@@ -225,9 +225,13 @@ struct NetBase {
     cudaEventRecord(spans.back().b, st);
   }
   void collect_spans() {
+    // B200_PROFILE_DUMP=<file>: append one "class work milliseconds" line per launch (development aid).
+    FILE* dump = nullptr;
+    if (const char* path = getenv("B200_PROFILE_DUMP")) dump = fopen(path, "a");
     for (auto& sp : spans) {
       float ms = 0.f;
       if (cudaEventSynchronize(sp.b) == cudaSuccess && cudaEventElapsedTime(&ms, sp.a, sp.b) == cudaSuccess) {
+        if (dump) fprintf(dump, "%d %.6g %.6f\n", sp.cls, sp.work, ms);
         prof_ms[sp.cls] += ms;
         prof_work[sp.cls] += sp.work;
         prof_launches[sp.cls]++;
@@ -235,6 +239,7 @@ struct NetBase {
       event_pool.push_back(sp.a);
       event_pool.push_back(sp.b);
     }
+    if (dump) fclose(dump);
     spans.clear();
   }
   virtual int eval_device(int slot, const void* d_masks, const void* d_values, int n, void* d_policy,
