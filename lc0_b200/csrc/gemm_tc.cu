@@ -27,7 +27,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 16-bit elements = one 128-byte swizzle row
-constexpr int kThreads = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two groups of four)
+constexpr int kThreads = 352;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two groups of four), warp 10 stores
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -102,13 +102,6 @@ __device__ __forceinline__ void tma_store_wait_read1() {
 }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// Named barrier of one epilogue group (four warps); group 0 uses barrier 1, group 1 barrier 2.
-__device__ __forceinline__ void epilogue_barrier(int group) {
-  asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
-}
-__device__ __forceinline__ void tma_store_wait_read0() {
-  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-}
 __device__ __forceinline__ void tcgen05_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -291,14 +284,12 @@ __device__ __forceinline__ void flush_row_ctx(const TcParams& p, int m, const Ro
   }
 }
 
-// Packs two floats into one 32-bit pair of T; fp16 saturates to the largest finite value (min/max on the
-// packed pair after the conversion turns an overflowed inf back into 65504).
+// Packs two floats into one 32-bit pair of T; fp16 saturates to the largest finite value.
 template <typename T> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
-  __half2 h = __floats2half2_rn(lo, hi);
-  const __half2 mx = __half2half2(__ushort_as_half((unsigned short)0x7BFF));
-  h = __hmax2(__hmin2(h, mx), __hneg2(mx));
-  return *reinterpret_cast<const uint32_t*>(&h);
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));  // first source -> upper half
+  return r;
 }
 template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
   const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
@@ -306,46 +297,66 @@ template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float l
 }
 
 // One 64-column slab of the epilogue fast path, executed by one group of four warps: TMEM -> registers ->
-// scale / folded-LayerNorm correction / bias / activation / residual -> 128B-swizzled staging buffer -> TMA store.
-// A group alternates between its two buffers; its leader makes sure the store that last used `buf` has finished
-// reading it.  Per-column vectors (bias, colsum, residual gamma / beta) are fetched with coalesced loads and
-// redistributed through a per-warp shared-memory scratch (`wvec`, 4 x 64 floats) as broadcast float4 reads.
-// The residual tile is fetched by TMA into the staging buffer itself (completion on `res_bar`), combined in place.
-template <typename T>
-__device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorMap* tmap_c, const CUtensorMap* tmap_r,
-                                              uint8_t* buf, uint32_t res_bar, uint32_t res_parity, int group,
-                                              bool leader, uint32_t taddr, int row, int lane, int m0, int nb,
-                                              float* wvec, RowCtx& rc, volatile int* abort_flag, volatile int* res_ok,
-                                              int tr = -1) {
-#define ETRACE(k) do { if (leader && tr >= 0) TRACE(tr + (k)); } while (0)
-  ETRACE(0);
+// scale / folded-LayerNorm correction / bias / activation / residual -> 128B-swizzled staging buffer, which the
+// store warp then writes out with a TMA store.  A group alternates between two buffers; `free_bar` completes when
+// the store that last used `buf` has finished reading it, `full_bar` (four arrivals, one per warp) tells the
+// store warp that the slab is staged.  No named barriers: the four warps only meet on those two barriers.
+// Per-column vectors (bias, colsum, residual gamma / beta) are fetched with coalesced loads one slab ahead
+// (`cr`) and redistributed through a per-warp shared-memory scratch (`wvec`, 4 x 64 floats) as broadcast float4 reads.  The residual tile
+// is fetched by TMA into the staging buffer itself (completion on `res_bar`) and combined in place.
+// Per-lane slice of the per-column vectors of one slab (columns lane and 32 + lane), fetched one slab ahead.
+struct ColRegs {
+  float bias0 = 0.f, bias1 = 0.f, cs0 = 0.f, cs1 = 0.f, g0 = 0.f, g1 = 0.f, be0 = 0.f, be1 = 0.f;
+};
+__device__ __forceinline__ void load_col_regs(const TcParams& p, int nb, int lane, ColRegs& c) {
   auto col = [&](const float* src, int i) { return (src && nb + i < p.N) ? __ldg(src + nb + i) : 0.f; };
-  if (p.bias) { wvec[lane] = col(p.bias, lane); wvec[32 + lane] = col(p.bias, 32 + lane); }
-  if (p.a_stats) { wvec[64 + lane] = col(p.colsum, lane); wvec[96 + lane] = col(p.colsum, 32 + lane); }
+  if (p.bias) { c.bias0 = col(p.bias, lane); c.bias1 = col(p.bias, 32 + lane); }
+  if (p.a_stats) { c.cs0 = col(p.colsum, lane); c.cs1 = col(p.colsum, 32 + lane); }
   if (p.res_mode == 2) {
-    wvec[128 + lane] = col(p.res_gamma, lane); wvec[160 + lane] = col(p.res_gamma, 32 + lane);
-    wvec[192 + lane] = col(p.res_beta, lane); wvec[224 + lane] = col(p.res_beta, 32 + lane);
+    c.g0 = col(p.res_gamma, lane); c.g1 = col(p.res_gamma, 32 + lane);
+    c.be0 = col(p.res_beta, lane); c.be1 = col(p.res_beta, 32 + lane);
   }
-  if (leader) {
-    tma_store_wait_read1();  // the store issued two slabs ago (same buffer) has been read out
-    ETRACE(1);
-    if (p.res_mode) {
+}
+
+template <typename T>
+__device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorMap* tmap_r, uint8_t* buf,
+                                              uint32_t res_bar, uint32_t free_bar, uint32_t full_bar, uint32_t use,
+                                              bool leader, uint32_t taddr, int row, int lane, int m0, int nb,
+                                              int next_nb, ColRegs& cr, float* wvec, RowCtx& rc,
+                                              volatile int* abort_flag) {
+  uint32_t r0[32], r1[32];
+  tmem_ld32(taddr, r0);
+  tmem_ld32(taddr + 32, r1);
+  __syncwarp();  // the previous slab's reads of wvec are done
+  if (p.bias) { wvec[lane] = cr.bias0; wvec[32 + lane] = cr.bias1; }
+  if (p.a_stats) { wvec[64 + lane] = cr.cs0; wvec[96 + lane] = cr.cs1; }
+  if (p.res_mode == 2) {
+    wvec[128 + lane] = cr.g0; wvec[160 + lane] = cr.g1;
+    wvec[192 + lane] = cr.be0; wvec[224 + lane] = cr.be1;
+  }
+  if (p.res_mode && leader) {
+    // the store that last used `buf` has been read out; fetch the residual tile into it
+    if (mbar_wait(free_bar, (use & 1) ^ 1, abort_flag, 6)) {
       mbar_expect_tx(res_bar, BM * 128);
       tma_load_2d(smem_u32(buf), tmap_r, nb, m0, res_bar);
     }
   }
-  epilogue_barrier(group);  // also orders the wvec writes before the reads below
-  ETRACE(2);
-  uint32_t r0[32], r1[32];
-  tmem_ld32(taddr, r0);
-  tmem_ld32(taddr + 32, r1);
+  __syncwarp();
+  if (next_nb >= 0) load_col_regs(p, next_nb, lane, cr);  // in flight during the arithmetic below
   tmem_ld_wait();
-  ETRACE(3);
   float v[64];
+  if (p.scale != 1.0f) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    v[j] = __uint_as_float(r0[j]) * p.scale;
-    v[32 + j] = __uint_as_float(r1[j]) * p.scale;
+    for (int j = 0; j < 32; ++j) {
+      v[j] = __uint_as_float(r0[j]) * p.scale;
+      v[32 + j] = __uint_as_float(r1[j]) * p.scale;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      v[j] = __uint_as_float(r0[j]);
+      v[32 + j] = __uint_as_float(r1[j]);
+    }
   }
   if (p.a_stats) {
 #pragma unroll
@@ -367,10 +378,9 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorM
   apply_activation(v, p.act);
   uint8_t* srow = buf + row * 128;
   if (p.res_mode) {
-    // One thread does the bounded wait for the residual tile; a failed wait raises the abort flag and the
-    // (then meaningless) result is still written so that every thread keeps the same barrier sequence.
-    if (leader) res_ok[group] = mbar_wait(res_bar, res_parity, abort_flag, 5) ? 1 : 0;
-    epilogue_barrier(group);
+    // Every thread waits for the residual tile itself (bounded; after a failed wait the result is meaningless and
+    // the status word says so).  The tile having landed also means that the buffer was free.
+    mbar_wait(res_bar, use & 1, abort_flag, 5);
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       const uint4 u = *reinterpret_cast<const uint4*>(srow + ((c ^ (row & 7)) << 4));
@@ -391,6 +401,8 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorM
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[c * 8 + i] = p.alpha * v[c * 8 + i] + s[i];
     }
+  } else {
+    mbar_wait(free_bar, (use & 1) ^ 1, abort_flag, 6);
   }
   if (p.out_stats) {
     float a = 0.f, q = 0.f;
@@ -412,17 +424,39 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorM
     o.w = pack_pair<T>(v[c * 8 + 6], v[c * 8 + 7]);
     *reinterpret_cast<uint4*>(srow + ((c ^ (row & 7)) << 4)) = o;
   }
-  ETRACE(4);
-  fence_async_smem();
-  ETRACE(5);
-  epilogue_barrier(group);
-  ETRACE(6);
-  if (leader) {
-    tma_store_2d(tmap_c, nb, m0, smem_u32(buf));
-    tma_store_commit();
+  fence_async_smem();  // this thread's writes are visible to the TMA store the store warp will issue
+  __syncwarp();
+  if (lane == 0) mbar_arrive(full_bar);
+}
+
+// The store warp's side of the fast path: for every slab of this CTA's tiles, in the order the epilogue groups
+// produce them, wait until the slab is staged, write it out with a TMA store, and hand a staging buffer back once
+// the store that used it has finished reading shared memory (one store stays in flight).
+__device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtensorMap* tmap_c, uint8_t* epi_mem,
+                                                uint64_t* stg_full, uint64_t* stg_free, int first_tile, int tile_step,
+                                                int tiles, int n_tiles, int tile_rows, int row_offset, int bn,
+                                                volatile int* abort_flag) {
+  uint32_t count[2] = {0, 0};
+  int prev = -1;
+  bool ok = true;
+  for (int t = first_tile; t < tiles && ok; t += tile_step) {
+    const int m0 = (t / n_tiles) * tile_rows + row_offset, n0 = (t % n_tiles) * bn;
+    for (int c0 = 0; c0 < bn; c0 += 64) {
+      if (n0 + c0 >= p.N) break;
+      const int g = (c0 >> 6) & 1;
+      const uint32_t s = count[g]++;
+      const int idx = g * 2 + (int)(s & 1);
+      if (!mbar_wait(smem_u32(&stg_full[idx]), (s >> 1) & 1, abort_flag, 7)) { ok = false; break; }
+      tma_store_2d(tmap_c, n0 + c0, m0, smem_u32(epi_mem + idx * (BM * 128)));
+      tma_store_commit();
+      if (prev >= 0) {
+        tma_store_wait_read1();
+        mbar_arrive(smem_u32(&stg_free[prev]));
+      }
+      prev = idx;
+    }
   }
-  ETRACE(7);
-#undef ETRACE
+  tma_store_wait_all();  // stores must complete before the CTA exits
 }
 
 template <int BN> struct TileCfg {
@@ -431,7 +465,7 @@ template <int BN> struct TileCfg {
   static constexpr int kStages = BN == 256 ? 3 : (BN == 128 ? 4 : 6);
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int kEpiBytes = 4 * BM * 128;  // 2 groups x 2 staging buffers of 128 rows x 128 bytes
-  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ +
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 512 /*barriers*/ +
                                     8192 /*per-warp column vectors*/;
 };
 
@@ -453,10 +487,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint64_t* tempty_bar = tfull_bar + 2;                             // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* epi_ok = abort_flag + 1;                     // [2]
-  volatile int* res_ok = epi_ok + 2;                         // [2]
-  uint64_t* res_bar = reinterpret_cast<uint64_t*>(bar_mem + 192);  // [2 groups][2 buffers]
-  float* wvec = reinterpret_cast<float*>(bar_mem + 256) + ((threadIdx.x >> 5) & 7) * 256;  // per-warp scratch
+  uint64_t* res_bar = reinterpret_cast<uint64_t*>(bar_mem + 192);   // [2 groups][2 buffers] residual tile landed
+  uint64_t* stg_full = reinterpret_cast<uint64_t*>(bar_mem + 256);  // [2 groups][2 buffers] slab staged (4 warps)
+  uint64_t* stg_free = stg_full + 4;                                // [2 groups][2 buffers] store has read the buffer
+  float* wvec = reinterpret_cast<float*>(bar_mem + 512) + ((threadIdx.x >> 5) & 7) * 256;  // per-warp scratch
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
@@ -472,7 +506,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       mbar_init(smem_u32(&tfull_bar[i]), 1);
       mbar_init(smem_u32(&tempty_bar[i]), 8);
     }
-    for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&res_bar[i]), 1);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(smem_u32(&res_bar[i]), 1);
+      mbar_init(smem_u32(&stg_full[i]), 4);
+      mbar_init(smem_u32(&stg_free[i]), 1);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -542,6 +580,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (ok) tcgen05_commit(smem_u32(&tfull_bar[acc]));
       }
     }
+  } else if (warp == 10) {
+    // ---------------- store warp: TMA stores of the staged slabs ----------------
+    if (lane == 0 && p.tma_store)
+      store_warp_loop(p, &tmap_c, epi_mem, stg_full, stg_free, blockIdx.x, gridDim.x, tiles, n_tiles, BM, 0, BN,
+                      abort_flag);
   } else {
     // ---------------- epilogue (warps 2..9: two groups of four warps, alternating 64-column slabs) ----------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
@@ -549,14 +592,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const bool leader = ((warp - 2) & 3) == 0 && lane == 0;
     uint8_t* gbuf = epi_mem + group * (2 * BM * 128);
     uint32_t tile_it = 0, slab_it = 0;
+    ColRegs cr;
+    int cr_nb = -1;  // first column of the slab whose vectors `cr` holds
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
       const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
       const int m0 = (t / n_tiles) * BM, n0 = (t % n_tiles) * BN;
-      // One thread per group does the bounded wait and publishes the outcome, so that the four warps of the
-      // group take the same decision and nobody is left behind at a named barrier.
-      if (leader) epi_ok[group] = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4) ? 1 : 0;
-      epilogue_barrier(group);
-      if (!epi_ok[group]) break;
+      // Every thread does its own bounded wait; the roles only meet on mbarriers, so a thread that gives up
+      // (the abort flag is then set and every other wait returns soon) leaves nobody behind at a barrier.
+      if (!mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4)) break;
       tcgen05_fence_after();
       const int m = m0 + quarter * 32 + lane;
       const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
@@ -567,9 +610,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll 1
         for (int c0 = group * 64; c0 < BN; c0 += 128) {
           if (n0 + c0 >= p.N) break;  // uniform over the group
-          epilogue_slab<T>(p, &tmap_c, &tmap_r, gbuf + (slab_it & 1) * (BM * 128),
-                           smem_u32(&res_bar[group * 2 + (slab_it & 1)]), (slab_it >> 1) & 1, group, leader, trow + c0,
-                           quarter * 32 + lane, lane, m0, n0 + c0, wvec, rc, abort_flag, res_ok);
+          const int idx = group * 2 + (int)(slab_it & 1);
+          if (cr_nb != n0 + c0) load_col_regs(p, n0 + c0, lane, cr);
+          // the slab this group handles next: further right in this tile, else the first one of its next tile
+          int next_nb = -1;
+          if (c0 + 128 < BN && n0 + c0 + 128 < p.N) {
+            next_nb = n0 + c0 + 128;
+          } else if (t + (int)gridDim.x < tiles) {
+            const int nn = ((t + (int)gridDim.x) % n_tiles) * BN + group * 64;
+            if (nn < p.N) next_nb = nn;
+          }
+          cr_nb = next_nb;
+          epilogue_slab<T>(p, &tmap_r, gbuf + (slab_it & 1) * (BM * 128), smem_u32(&res_bar[idx]),
+                           smem_u32(&stg_free[idx]), smem_u32(&stg_full[idx]), slab_it >> 1, leader, trow + c0,
+                           quarter * 32 + lane, lane, m0, n0 + c0, next_nb, cr, wvec, rc, abort_flag);
           ++slab_it;
         }
         flush_row_ctx(p, m, rc);
@@ -619,7 +673,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
     }
-    if (leader) tma_store_wait_all();  // stores must complete before the CTA exits
   }
 
   __syncwarp();
@@ -654,7 +707,7 @@ struct PairCfg {
   static constexpr int kStages = 4;
   static constexpr int kTmemCols = 512;
   static constexpr int kEpiBytes = 4 * BM * 128;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 256 + 8192;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 512 + 8192;
 };
 
 template <typename T>
@@ -675,10 +728,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint64_t* tempty_bar = tfull_bar + 2;                        // [2]  even CTA: 4 local + 4 remote arrivals
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* epi_ok = abort_flag + 1;                     // [2]
-  volatile int* res_ok = epi_ok + 2;                         // [2]
-  uint64_t* res_bar = reinterpret_cast<uint64_t*>(bar_mem + 192);  // [2 groups][2 buffers]
-  float* wvec = reinterpret_cast<float*>(bar_mem + 256) + ((threadIdx.x >> 5) & 7) * 256;  // per-warp scratch
+  uint64_t* res_bar = reinterpret_cast<uint64_t*>(bar_mem + 192);   // [2 groups][2 buffers]
+  uint64_t* stg_full = reinterpret_cast<uint64_t*>(bar_mem + 256);  // [2 groups][2 buffers]
+  uint64_t* stg_free = stg_full + 4;                                // [2 groups][2 buffers]
+  float* wvec = reinterpret_cast<float*>(bar_mem + 512) + ((threadIdx.x >> 5) & 7) * 256;  // per-warp scratch
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -696,7 +749,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       mbar_init(smem_u32(&tfull_bar[i]), 1);
       mbar_init(smem_u32(&tempty_bar[i]), 16);
     }
-    for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&res_bar[i]), 1);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(smem_u32(&res_bar[i]), 1);
+      mbar_init(smem_u32(&stg_full[i]), 4);
+      mbar_init(smem_u32(&stg_free[i]), 1);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -770,6 +827,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
       }
     }
+  } else if (warp == 10) {
+    // ---------------- store warp (both CTAs): TMA stores of the staged slabs ----------------
+    if (lane == 0)
+      store_warp_loop(p, &tmap_c, epi_mem, stg_full, stg_free, pair, pairs, tiles, n_tiles, 2 * BM, (int)rank * BM, BN,
+                      abort_flag);
   } else {
     // ---------------- epilogue (warps 2..9 of both CTAs, two groups alternating 64-column slabs) ----------------
     const int quarter = warp & 3;
@@ -777,16 +839,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const bool leader = ((warp - 2) & 3) == 0 && lane == 0;
     uint8_t* gbuf = epi_mem + group * (2 * BM * 128);
     uint32_t tile_it = 0, slab_it = 0;
+    ColRegs cr;
+    int cr_nb = -1;
     for (int t = pair; t < tiles; t += pairs, ++tile_it) {
       const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
       const int m0 = (t / n_tiles) * (2 * BM) + (int)rank * BM, n0 = (t % n_tiles) * BN;
       if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 0);
-      if (leader) epi_ok[group] = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4) ? 1 : 0;
-      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 1);
-      epilogue_barrier(group);
-      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 2);
-      if (!epi_ok[group]) break;
+      if (!mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4)) break;
       tcgen05_fence_after();
+      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 1);
       const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       const int m = m0 + quarter * 32 + lane;
       RowCtx rc;
@@ -794,24 +855,30 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll 1
       for (int c0 = group * 64; c0 < BN; c0 += 128) {
         if (n0 + c0 >= p.N) break;  // uniform over the group
-        epilogue_slab<T>(p, &tmap_c, &tmap_r, gbuf + (slab_it & 1) * (BM * 128),
-                         smem_u32(&res_bar[group * 2 + (slab_it & 1)]), (slab_it >> 1) & 1, group, leader, trow + c0,
-                         quarter * 32 + lane, lane, m0, n0 + c0, wvec, rc, abort_flag, res_ok,
-#ifdef B200_TRACE
-                         slab_it < 32 ? 1024 + (group * 32 + (int)slab_it) * 8 : -1
-#else
-                         -1
-#endif
-        );
+        const int idx = group * 2 + (int)(slab_it & 1);
+        if (cr_nb != n0 + c0) load_col_regs(p, n0 + c0, lane, cr);
+        int next_nb = -1;
+        if (c0 + 128 < BN && n0 + c0 + 128 < p.N) {
+          next_nb = n0 + c0 + 128;
+        } else if (t + pairs < tiles) {
+          const int nn = ((t + pairs) % n_tiles) * BN + group * 64;
+          if (nn < p.N) next_nb = nn;
+        }
+        cr_nb = next_nb;
+        if (leader && slab_it < 32) TRACE(1024 + (group * 32 + (int)slab_it) * 2);
+        epilogue_slab<T>(p, &tmap_r, gbuf + (slab_it & 1) * (BM * 128), smem_u32(&res_bar[idx]),
+                         smem_u32(&stg_free[idx]), smem_u32(&stg_full[idx]), slab_it >> 1, leader, trow + c0,
+                         quarter * 32 + lane, lane, m0, n0 + c0, next_nb, cr, wvec, rc, abort_flag);
+        if (leader && slab_it < 32) TRACE(1024 + (group * 32 + (int)slab_it) * 2 + 1);
         ++slab_it;
       }
       flush_row_ctx(p, m, rc);
       tcgen05_fence_before();
       __syncwarp();
-      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 3);
+      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 2);
       if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&tempty_bar[acc]), 0));
+      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 3);
     }
-    if (leader) tma_store_wait_all();
   }
 
   __syncwarp();
@@ -962,7 +1029,8 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
   p.out_f32 = g.out_f32 ? 1 : 0; p.status = status;
   p.conv_cblocks = g.conv_cin > 0 ? ceil_div(g.conv_cin, BK) : 0;
   const int tiles = ceil_div(g.M, BM) * ceil_div(g.N, BN);
-  const int grid = tiles < sm_count ? tiles : sm_count;
+  const int ctas = (g.cta_limit > 0 && g.cta_limit < sm_count) ? g.cta_limit : sm_count;
+  const int grid = tiles < ctas ? tiles : ctas;
   gemm_tc_kernel<T, BN><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, p);
   return cudaGetLastError();
 }
@@ -1003,7 +1071,7 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   p.out_f32 = 0; p.status = status;
   p.conv_cblocks = 0;
   const int tiles = ceil_div(g.M, 2 * BM) * ceil_div(g.N, Cfg::BN);
-  const int max_pairs = sm_count / 2;
+  const int max_pairs = ((g.cta_limit > 0 && g.cta_limit < sm_count) ? g.cta_limit : sm_count) / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   gemm_tc_pair_kernel<T><<<2 * pairs, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, p);
   return cudaGetLastError();

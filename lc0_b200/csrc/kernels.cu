@@ -41,6 +41,8 @@ cudaError_t launch_expand_planes(const uint64_t* masks, const float* values, int
 
 // Token-major expansion with positional-encoding concat (reference: network_blas.cc:631-652; GPU twin
 // preprocess_for_attention_body_kernel, backends/cuda/common_kernels.cu:1203-1244).
+template <typename T> struct __align__(16) Vec8 { T v[8]; };
+
 template <typename T>
 __global__ void expand_tokens_kernel(const uint64_t* __restrict__ masks, const float* __restrict__ values,
                                      const float* __restrict__ pe_static, const T* __restrict__ pe_dense,
@@ -68,11 +70,54 @@ __global__ void expand_tokens_kernel(const uint64_t* __restrict__ masks, const f
   }
 }
 
+// Same for row widths and encoding widths that are multiples of 8: a thread writes 8 channels (16 bytes for
+// 16-bit storage) at a time, dense positional encodings are copied as 16-byte pieces.
+template <typename T>
+__global__ void __launch_bounds__(256)
+expand_tokens_vec_kernel(const uint64_t* __restrict__ masks, const float* __restrict__ values,
+                         const float* __restrict__ pe_static, const T* __restrict__ pe_dense, int pe_ch, int cin,
+                         T* __restrict__ out) {
+  __shared__ uint64_t sm[112];
+  __shared__ float sv[112];
+  const int n = blockIdx.x;
+  for (int i = threadIdx.x; i < 112; i += blockDim.x) {
+    sm[i] = masks[(long long)n * 112 + i];
+    sv[i] = values[(long long)n * 112 + i];
+  }
+  __syncthreads();
+  T* o = out + (long long)n * 64 * cin;
+  const int vec_per_row = cin >> 3;
+  for (int idx = threadIdx.x; idx < 64 * vec_per_row; idx += blockDim.x) {
+    const int sq = idx / vec_per_row, c = (idx - sq * vec_per_row) << 3;
+    Vec8<T> r;
+    if (c < 112) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) r.v[i] = from_f<T>(((sm[c + i] >> sq) & 1) ? sv[c + i] : 0.f);
+    } else if (c < 112 + pe_ch) {
+      const int j = c - 112;
+      if (pe_dense) {
+        r = *reinterpret_cast<const Vec8<T>*>(pe_dense + ((long long)n * 64 + sq) * pe_ch + j);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r.v[i] = from_f<T>(pe_static[sq * pe_ch + j + i]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) r.v[i] = from_f<T>(0.f);
+    }
+    *reinterpret_cast<Vec8<T>*>(o + (long long)sq * cin + c) = r;
+  }
+}
+
 template <typename T>
 cudaError_t launch_expand_tokens(const uint64_t* masks, const float* values, int n, const float* pe_static,
                                  const T* pe_dense, int pe_ch, int cin, T* out, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
-  expand_tokens_kernel<T><<<n, 256, 0, s>>>(masks, values, pe_static, pe_dense, pe_ch, cin, out);
+  const bool aligned = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (reinterpret_cast<uintptr_t>(pe_dense) & 15) == 0;
+  if ((cin & 7) == 0 && (pe_ch & 7) == 0 && aligned)
+    expand_tokens_vec_kernel<T><<<n, 256, 0, s>>>(masks, values, pe_static, pe_dense, pe_ch, cin, out);
+  else
+    expand_tokens_kernel<T><<<n, 256, 0, s>>>(masks, values, pe_static, pe_dense, pe_ch, cin, out);
   return cudaGetLastError();
 }
 
@@ -185,7 +230,6 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
-template <typename T> struct __align__(16) Vec8 { T v[8]; };
 
 template <typename T, int kThreads, int kSteps>
 __global__ void __launch_bounds__(kThreads)
@@ -238,10 +282,14 @@ layer_norm_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restr
   for (int s = 0; s < kSteps; ++s) {
     const int c = (s * kThreads + threadIdx.x) * 8;
     if (c < C) {
+      const float4 g0 = *reinterpret_cast<const float4*>(gamma + c), g1 = *reinterpret_cast<const float4*>(gamma + c + 4);
+      const float4 b0 = *reinterpret_cast<const float4*>(beta + c), b1 = *reinterpret_cast<const float4*>(beta + c + 4);
+      const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
       Vec8<T> o;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        float t = beta[c + i] + gamma[c + i] * (v[s][i] - mean) * den;
+        float t = bb[i] + gg[i] * (v[s][i] - mean) * den;
         if (gate_mult) t = t * gate_mult[(long long)sq * C + c + i] + gate_add[(long long)sq * C + c + i];
         o.v[i] = from_f<T>(t);
       }
@@ -349,8 +397,8 @@ cudaError_t launch_layer_norm(T* out, const T* x, const T* skip, const float* ga
   else if (C <= 512) LNW_LAUNCH(2);
   else if (C <= 1024) LNW_LAUNCH(4);
   else if (C <= 2048) LNW_LAUNCH(8);
-  else if (C <= 4096) LN_LAUNCH(512, 1);  // few, wide rows (smolgen): one 16-byte piece per thread
-  else LN_LAUNCH(1024, 1);
+  else if (C <= 4096) LN_LAUNCH(256, 2);  // few, wide rows (smolgen): 256 threads, several 16-byte pieces each
+  else LN_LAUNCH(256, 4);
 #undef LN_LAUNCH
 #undef LNW_LAUNCH
   return cudaGetLastError();

@@ -37,6 +37,9 @@ struct GemmParams {
   // Per-row (sum, sum of squares) of the outputs, accumulated with atomic adds into out_stats[M][2]
   // (the caller zeroes it), so that the next product can fold the LayerNorm of this output.
   float* out_stats = nullptr;
+  // Upper bound on the CTAs (= SMs) the tensor-core kernel may occupy; 0 = all.  Lets a small product run beside a
+  // large one on another stream.
+  int cta_limit = 0;
 };
 
 template <typename T> cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t s);

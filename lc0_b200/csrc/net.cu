@@ -339,6 +339,7 @@ struct Net : NetBase {
   bool use_tc = false;
   // LayerNorms of the encoder stack folded into the neighbouring tensor-core products (16-bit storage only).
   bool fold_ln = false;
+  int side_sms = 0;  // SMs left to the side stream while the QKV product runs (0: everything on one stream)
   bool fold_heads = false;  // the heads' first products fold the last LayerNorm too (else it is materialised)
   int* d_status = nullptr;
 
@@ -374,6 +375,9 @@ struct Net : NetBase {
 
   struct Slot {
     cudaStream_t stream = nullptr;
+    cudaEvent_t compute_done = nullptr;  // recorded after the last kernel of an evaluation, before its result copies
+    cudaStream_t side = nullptr;         // smolgen's small products run here, beside the QKV product
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     uint64_t* d_masks = nullptr;
     float *d_values = nullptr, *d_policy = nullptr, *d_qdm = nullptr;
     unsigned short* d_move_ids = nullptr;
@@ -395,6 +399,10 @@ struct Net : NetBase {
         if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     for (auto& s : slots) {
       if (s.stream) cudaStreamDestroy(s.stream);
+      if (s.compute_done) cudaEventDestroy(s.compute_done);
+      if (s.side) cudaStreamDestroy(s.side);
+      if (s.ev_fork) cudaEventDestroy(s.ev_fork);
+      if (s.ev_join) cudaEventDestroy(s.ev_join);
     }
     free_host_sets();
     walloc.release();
@@ -625,6 +633,7 @@ struct Net : NetBase {
                                              std::to_string(prop.major) + std::to_string(prop.minor)};
       CK(gemm_tc_init());
     }
+    if (const char* v = getenv("B200_SIDE_SMS")) side_sms = atoi(v);
     fold_ln = use_tc && attn_body && !(getenv("B200_FOLD_LN") && getenv("B200_FOLD_LN")[0] == '0');
     // Folding needs every product that consumes or produces a folded LayerNorm to be eligible for the tensor-core
     // kernel's TMA epilogue: output widths that are multiples of 8.
@@ -850,6 +859,10 @@ struct Net : NetBase {
     for (int si = 0; si < opt.slots; ++si) {
       Slot& s = slots[si];
       CK(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+      CK(cudaEventCreateWithFlags(&s.compute_done, cudaEventDisableTiming));
+      CK(cudaStreamCreateWithFlags(&s.side, cudaStreamNonBlocking));
+      CK(cudaEventCreateWithFlags(&s.ev_fork, cudaEventDisableTiming));
+      CK(cudaEventCreateWithFlags(&s.ev_join, cudaEventDisableTiming));
       s.d_masks = (uint64_t*)salloc.alloc(nb * 112 * 8);
       s.d_values = (float*)salloc.alloc(nb * 112 * 4);
       s.d_policy = (float*)salloc.alloc(nb * 1858 * 4);
@@ -913,8 +926,9 @@ struct Net : NetBase {
   // ---- launch helpers ----
   void gemm(cudaStream_t st, const T* A, long long lda, const Dense<T>& d, T* Cout, long long ldc, int M, int act,
             const T* skip = nullptr, long long ldskip = 0, float alpha_ = 1.f, bool out_f32 = false,
-            void* cf32 = nullptr) {
+            void* cf32 = nullptr, int cta_limit = 0) {
     GemmParams p;
+    p.cta_limit = cta_limit;
     p.A = A; p.lda = lda; p.W = d.w; p.ldw = d.in; p.bias = d.b;
     p.C = out_f32 ? cf32 : (void*)Cout; p.ldc = ldc; p.M = M; p.N = d.out; p.K = d.in; p.act = act;
     p.skip = skip; p.ldskip = ldskip; p.alpha = alpha_; p.out_f32 = out_f32;
@@ -931,8 +945,10 @@ struct Net : NetBase {
   // Product whose A operand is `in` (folded when in.stats is set); optional residual `res` added as
   // alpha * act(...) + LN(res) and optional accumulation of output row statistics.
   void gemm_ln(cudaStream_t st, const LNState& in, long long lda, const Dense<T>& d, T* Cout, long long ldc, int M,
-               int act, const LNState* res = nullptr, float alpha_ = 1.f, float* out_stats = nullptr) {
+               int act, const LNState* res = nullptr, float alpha_ = 1.f, float* out_stats = nullptr,
+               int cta_limit = 0) {
     GemmParams p;
+    p.cta_limit = cta_limit;
     p.A = in.u; p.lda = lda; p.W = d.w; p.ldw = d.in; p.bias = d.b;
     p.C = Cout; p.ldc = ldc; p.M = M; p.N = d.out; p.K = d.in; p.act = act;
     if (in.stats) {
@@ -1014,16 +1030,31 @@ struct Net : NetBase {
     const int R = n * 64;
     const int depth = E / H;
     const T* bias = nullptr;
+    // With side_sms > 0 the small, latency-bound products of smolgen run on a second stream, confined to a few SMs,
+    // while the QKV product (which only needs the same layer input) runs on the others.  The per-kernel profiling
+    // pass keeps everything on one stream so that each kernel is timed alone.
+    const bool overlap = e.smolgen && side_sms > 0 && !profiling && use_tc && sizeof(T) == 2;
     if (e.smolgen) {  // network_blas.cc:300-339
-      gemm_ln(st, in, E, e.sg_compress, s.sg_c, sg_hc, R, ACT_NONE);
-      gemm(st, s.sg_c, 64 * sg_hc, e.sg_d1, s.sg_h1, sg_hid, n, act_smolgen);
-      ln(st, s.sg_h1, s.sg_h1, nullptr, e.sg_ln1g, e.sg_ln1b, n, sg_hid, 1.f, 1e-3f);
-      gemm(st, s.sg_h1, sg_hid, e.sg_d2, s.sg_h2, sg_gen, n, act_smolgen);
-      ln(st, s.sg_h2, s.sg_h2, nullptr, e.sg_ln2g, e.sg_ln2b, n, sg_gen, 1.f, 1e-3f);
+      cudaStream_t ss = overlap ? s.side : st;
+      const int lim = overlap ? side_sms : 0;
+      if (overlap) {
+        CK(cudaEventRecord(s.ev_fork, st));
+        CK(cudaStreamWaitEvent(ss, s.ev_fork, 0));
+        gemm_ln(st, in, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE, nullptr, 1.f, nullptr, sm_count - side_sms);
+      }
+      gemm_ln(ss, in, E, e.sg_compress, s.sg_c, sg_hc, R, ACT_NONE, nullptr, 1.f, nullptr, lim);
+      gemm(ss, s.sg_c, 64 * sg_hc, e.sg_d1, s.sg_h1, sg_hid, n, act_smolgen, nullptr, 0, 1.f, false, nullptr, lim);
+      ln(ss, s.sg_h1, s.sg_h1, nullptr, e.sg_ln1g, e.sg_ln1b, n, sg_hid, 1.f, 1e-3f);
+      gemm(ss, s.sg_h1, sg_hid, e.sg_d2, s.sg_h2, sg_gen, n, act_smolgen, nullptr, 0, 1.f, false, nullptr, lim);
+      ln(ss, s.sg_h2, s.sg_h2, nullptr, e.sg_ln2g, e.sg_ln2b, n, sg_gen, 1.f, 1e-3f);
+      if (overlap) {
+        CK(cudaEventRecord(s.ev_join, ss));
+        CK(cudaStreamWaitEvent(st, s.ev_join, 0));
+      }
       gemm(st, s.sg_h2, sg_gen / H, smolgen_w, s.sg_bias, 4096, n * H, ACT_NONE);
       bias = s.sg_bias;
     }
-    gemm_ln(st, in, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE);  // :341-350, :408-412
+    if (!overlap) gemm_ln(st, in, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE);  // :341-350, :408-412
     launches++;
     // algorithmic bytes: read Q, K, V (+ bias), write the head outputs
     span_begin(st, K_ATTENTION, (double)R * E * sizeof(T) * 4 + (bias ? (double)n * H * 4096 * sizeof(T) : 0.0));
@@ -1195,11 +1226,23 @@ struct Net : NetBase {
       CK(cudaMemcpyAsync(s.d_move_ids, hs.move_ids, (size_t)n * kLegalStride * 2, cudaMemcpyHostToDevice, s.stream));
       CK(cudaMemcpyAsync(s.d_n_moves, hs.n_moves, (size_t)n * 4, cudaMemcpyHostToDevice, s.stream));
     }
+    // Evaluations of different slots take turns on the GPU: the kernels of this one start after the kernels of the
+    // others (as of their latest launch), while its input copies above and their result copies overlap with the
+    // other's kernels.  Interleaving the kernels of two batches was slower than running the batches one at a time.
+    // Inside a stream capture the waits and the record become external event nodes.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    CK(cudaStreamIsCapturing(s.stream, &cap));
+    const bool capturing = cap == cudaStreamCaptureStatusActive;
+    for (auto& o : slots)
+      if (&o != &s) CK(cudaStreamWaitEvent(s.stream, o.compute_done, capturing ? cudaEventWaitExternal : 0));
     forward(s, s.d_masks, s.d_values, n, s.d_policy, s.d_qdm);
     if (policy_mode) {
       other(s.stream, (double)n * kLegalStride * 6, [&] {
         return launch_legal_softmax(s.d_policy, s.d_move_ids, s.d_n_moves, n, inv_t, s.d_probs, s.stream);
       });
+    }
+    CK(cudaEventRecordWithFlags(s.compute_done, s.stream, capturing ? cudaEventRecordExternal : 0));
+    if (policy_mode) {
       CK(cudaMemcpyAsync(hs.probs, s.d_probs, (size_t)n * kLegalStride * 4, cudaMemcpyDeviceToHost, s.stream));
     }
     if (policy_mode != 2)
