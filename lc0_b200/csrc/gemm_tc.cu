@@ -59,12 +59,25 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
+// Same with a suspend-time hint: the thread may sleep in hardware for up to `ns` nanoseconds (it is woken when the
+// phase completes), so a long wait costs few issue slots of the warps that share its scheduler.
+__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok;
+}
 // Bounded wait.  Returns false when the CTA is aborting (this or another role timed out).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
     if ((it & 63) == 0) {
       if (*abort_flag) return false;
       if (global_ns() - t0 > kWaitLimitNs) {
@@ -236,7 +249,8 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
 #ifdef B200_TRACE
 // Development aid (not compiled into the library): clock64() checkpoints of CTA 0 of the pair kernel.
 __device__ long long g_trace[4096];
-#define TRACE(idx) do { if (blockIdx.x == 0 && (idx) < 4096) g_trace[(idx)] = clock64(); } while (0)
+__device__ int g_trace_on;
+#define TRACE(idx) do { if (blockIdx.x == 0 && g_trace_on && (idx) < 4096) g_trace[(idx)] = clock64(); } while (0)
 #else
 #define TRACE(idx) do { } while (0)
 #endif
@@ -323,7 +337,9 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorM
                                               uint32_t res_bar, uint32_t free_bar, uint32_t full_bar, uint32_t use,
                                               bool leader, uint32_t taddr, int row, int lane, int m0, int nb,
                                               int next_nb, ColRegs& cr, float* wvec, RowCtx& rc,
-                                              volatile int* abort_flag) {
+                                              volatile int* abort_flag, int tr = -1) {
+#define ET(k) do { if (leader && tr >= 0) TRACE(tr + (k)); } while (0)
+  ET(0);
   uint32_t r0[32], r1[32];
   tmem_ld32(taddr, r0);
   tmem_ld32(taddr + 32, r1);
@@ -334,16 +350,11 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorM
     wvec[128 + lane] = cr.g0; wvec[160 + lane] = cr.g1;
     wvec[192 + lane] = cr.be0; wvec[224 + lane] = cr.be1;
   }
-  if (p.res_mode && leader) {
-    // the store that last used `buf` has been read out; fetch the residual tile into it
-    if (mbar_wait(free_bar, (use & 1) ^ 1, abort_flag, 6)) {
-      mbar_expect_tx(res_bar, BM * 128);
-      tma_load_2d(smem_u32(buf), tmap_r, nb, m0, res_bar);
-    }
-  }
   __syncwarp();
   if (next_nb >= 0) load_col_regs(p, next_nb, lane, cr);  // in flight during the arithmetic below
+  ET(1);
   tmem_ld_wait();
+  ET(2);
   float v[64];
   if (p.scale != 1.0f) {
 #pragma unroll
@@ -376,11 +387,13 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorM
     }
   }
   apply_activation(v, p.act);
+  ET(3);
   uint8_t* srow = buf + row * 128;
   if (p.res_mode) {
     // Every thread waits for the residual tile itself (bounded; after a failed wait the result is meaningless and
-    // the status word says so).  The tile having landed also means that the buffer was free.
+    // the status word says so).  The store warp fetched it after the buffer had become free.
     mbar_wait(res_bar, use & 1, abort_flag, 5);
+    ET(4);
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       const uint4 u = *reinterpret_cast<const uint4*>(srow + ((c ^ (row & 7)) << 4));
@@ -404,6 +417,7 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorM
   } else {
     mbar_wait(free_bar, (use & 1) ^ 1, abort_flag, 6);
   }
+  ET(5);
   if (p.out_stats) {
     float a = 0.f, q = 0.f;
     if (nb + 64 <= p.N) {
@@ -424,23 +438,66 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorM
     o.w = pack_pair<T>(v[c * 8 + 6], v[c * 8 + 7]);
     *reinterpret_cast<uint4*>(srow + ((c ^ (row & 7)) << 4)) = o;
   }
+  ET(6);
   fence_async_smem();  // this thread's writes are visible to the TMA store the store warp will issue
   __syncwarp();
   if (lane == 0) mbar_arrive(full_bar);
+  ET(7);
+#undef ET
 }
 
 // The store warp's side of the fast path: for every slab of this CTA's tiles, in the order the epilogue groups
 // produce them, wait until the slab is staged, write it out with a TMA store, and hand a staging buffer back once
-// the store that used it has finished reading shared memory (one store stays in flight).
-__device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtensorMap* tmap_c, uint8_t* epi_mem,
-                                                uint64_t* stg_full, uint64_t* stg_free, int first_tile, int tile_step,
-                                                int tiles, int n_tiles, int tile_rows, int row_offset, int bn,
+// the store that used it has finished reading shared memory (one store stays in flight).  With a residual input
+// the same thread fetches the residual tiles: two slabs ahead per group, each into the staging buffer its slab
+// will use, as soon as that buffer is free; the epilogue threads then only wait for the tile to have landed.
+struct SlabWalk {
+  const TcParams& p;
+  int first_tile, tile_step, tiles, n_tiles, tile_rows, row_offset, bn;
+  __device__ __forceinline__ int n0(int t) const { return (t % n_tiles) * bn; }
+  __device__ __forceinline__ int m0(int t) const { return (t / n_tiles) * tile_rows + row_offset; }
+  // cursor over the slabs of one epilogue group (columns g*64, g*64+128, ... of each tile)
+  struct Cursor { int t, c0; };
+  __device__ __forceinline__ void settle(Cursor& c, int g) const {
+    while (c.t < tiles && n0(c.t) + c.c0 >= p.N) { c.t += tile_step; c.c0 = g * 64; }
+  }
+  __device__ __forceinline__ Cursor begin(int g) const {
+    Cursor c{first_tile, g * 64};
+    settle(c, g);
+    return c;
+  }
+  __device__ __forceinline__ void next(Cursor& c, int g) const {
+    c.c0 += 128;
+    if (c.c0 >= bn || n0(c.t) + c.c0 >= p.N) { c.t += tile_step; c.c0 = g * 64; }
+    settle(c, g);
+  }
+};
+
+__device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtensorMap* tmap_c, const CUtensorMap* tmap_r,
+                                                uint8_t* epi_mem, uint64_t* stg_full, uint64_t* stg_free,
+                                                uint64_t* res_bar, int first_tile, int tile_step, int tiles,
+                                                int n_tiles, int tile_rows, int row_offset, int bn,
                                                 volatile int* abort_flag) {
+  const SlabWalk w{p, first_tile, tile_step, tiles, n_tiles, tile_rows, row_offset, bn};
+  SlabWalk::Cursor pf[2] = {w.begin(0), w.begin(1)};
+  uint32_t pf_count[2] = {0, 0};
+  auto fetch_residual = [&](int g) {
+    if (pf[g].t >= tiles) return;
+    const int idx = g * 2 + (int)(pf_count[g] & 1);
+    const uint32_t bar = smem_u32(&res_bar[idx]);
+    mbar_expect_tx(bar, BM * 128);
+    tma_load_2d(smem_u32(epi_mem + idx * (BM * 128)), tmap_r, w.n0(pf[g].t) + pf[g].c0, w.m0(pf[g].t), bar);
+    ++pf_count[g];
+    w.next(pf[g], g);
+  };
+  if (p.res_mode)
+    for (int k = 0; k < 2; ++k)
+      for (int g = 0; g < 2; ++g) fetch_residual(g);
   uint32_t count[2] = {0, 0};
   int prev = -1;
   bool ok = true;
   for (int t = first_tile; t < tiles && ok; t += tile_step) {
-    const int m0 = (t / n_tiles) * tile_rows + row_offset, n0 = (t % n_tiles) * bn;
+    const int m0 = w.m0(t), n0 = w.n0(t);
     for (int c0 = 0; c0 < bn; c0 += 64) {
       if (n0 + c0 >= p.N) break;
       const int g = (c0 >> 6) & 1;
@@ -451,7 +508,8 @@ __device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtenso
       tma_store_commit();
       if (prev >= 0) {
         tma_store_wait_read1();
-        mbar_arrive(smem_u32(&stg_free[prev]));
+        if (p.res_mode) fetch_residual(prev >> 1);  // the freed buffer is the one that group's slab after next uses
+        else mbar_arrive(smem_u32(&stg_free[prev]));
       }
       prev = idx;
     }
@@ -583,8 +641,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else if (warp == 10) {
     // ---------------- store warp: TMA stores of the staged slabs ----------------
     if (lane == 0 && p.tma_store)
-      store_warp_loop(p, &tmap_c, epi_mem, stg_full, stg_free, blockIdx.x, gridDim.x, tiles, n_tiles, BM, 0, BN,
-                      abort_flag);
+      store_warp_loop(p, &tmap_c, &tmap_r, epi_mem, stg_full, stg_free, res_bar, blockIdx.x, gridDim.x, tiles,
+                      n_tiles, BM, 0, BN, abort_flag);
   } else {
     // ---------------- epilogue (warps 2..9: two groups of four warps, alternating 64-column slabs) ----------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
@@ -830,8 +888,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   } else if (warp == 10) {
     // ---------------- store warp (both CTAs): TMA stores of the staged slabs ----------------
     if (lane == 0)
-      store_warp_loop(p, &tmap_c, epi_mem, stg_full, stg_free, pair, pairs, tiles, n_tiles, 2 * BM, (int)rank * BM, BN,
-                      abort_flag);
+      store_warp_loop(p, &tmap_c, &tmap_r, epi_mem, stg_full, stg_free, res_bar, pair, pairs, tiles, n_tiles,
+                      2 * BM, (int)rank * BM, BN, abort_flag);
   } else {
     // ---------------- epilogue (warps 2..9 of both CTAs, two groups alternating 64-column slabs) ----------------
     const int quarter = warp & 3;
@@ -865,11 +923,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (nn < p.N) next_nb = nn;
         }
         cr_nb = next_nb;
-        if (leader && slab_it < 32) TRACE(1024 + (group * 32 + (int)slab_it) * 2);
         epilogue_slab<T>(p, &tmap_r, gbuf + (slab_it & 1) * (BM * 128), smem_u32(&res_bar[idx]),
                          smem_u32(&stg_free[idx]), smem_u32(&stg_full[idx]), slab_it >> 1, leader, trow + c0,
-                         quarter * 32 + lane, lane, m0, n0 + c0, next_nb, cr, wvec, rc, abort_flag);
-        if (leader && slab_it < 32) TRACE(1024 + (group * 32 + (int)slab_it) * 2 + 1);
+                         quarter * 32 + lane, lane, m0, n0 + c0, next_nb, cr, wvec, rc, abort_flag,
+                         slab_it < 32 ? 1024 + (group * 32 + (int)slab_it) * 8 : -1);
         ++slab_it;
       }
       flush_row_ctx(p, m, rc);
@@ -1070,6 +1127,15 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   p.M = g.M; p.N = g.N; p.K = g.K; p.act = g.act; p.scale = g.scale; p.alpha = g.alpha;
   p.out_f32 = 0; p.status = status;
   p.conv_cblocks = 0;
+#ifdef B200_TRACE
+  {  // development aid: B200_TRACE_LAUNCH=<k> records the k-th launch of this kernel (default: every launch)
+    static std::atomic<int> counter{0};
+    const char* sel = getenv("B200_TRACE_LAUNCH");
+    const int on = (!sel || atoi(sel) == counter.load()) ? 1 : 0;
+    counter++;
+    cudaMemcpyToSymbolAsync(g_trace_on, &on, sizeof(int), 0, cudaMemcpyHostToDevice, s);
+  }
+#endif
   const int tiles = ceil_div(g.M, 2 * BM) * ceil_div(g.N, Cfg::BN);
   const int max_pairs = ((g.cta_limit > 0 && g.cta_limit < sm_count) ? g.cta_limit : sm_count) / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
