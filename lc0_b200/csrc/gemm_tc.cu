@@ -113,6 +113,9 @@ __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void tma_store_wait_read1() {
   asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
 }
+__device__ __forceinline__ void tma_store_wait_read0() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() {
@@ -333,16 +336,12 @@ __device__ __forceinline__ void load_col_regs(const TcParams& p, int nb, int lan
 }
 
 template <typename T>
-__device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorMap* tmap_r, uint8_t* buf,
-                                              uint32_t res_bar, uint32_t free_bar, uint32_t full_bar, uint32_t use,
-                                              bool leader, uint32_t taddr, int row, int lane, int m0, int nb,
-                                              int next_nb, ColRegs& cr, float* wvec, RowCtx& rc,
+__device__ __forceinline__ void epilogue_slab(const TcParams& p, uint8_t* buf, uint32_t res_bar, uint32_t free_bar,
+                                              uint32_t full_bar, uint32_t use, bool leader, uint32_t taddr, int row,
+                                              int lane, int nb, int next_nb, ColRegs& cr, float* wvec, RowCtx& rc,
                                               volatile int* abort_flag, int tr = -1) {
 #define ET(k) do { if (leader && tr >= 0) TRACE(tr + (k)); } while (0)
   ET(0);
-  uint32_t r0[32], r1[32];
-  tmem_ld32(taddr, r0);
-  tmem_ld32(taddr + 32, r1);
   __syncwarp();  // the previous slab's reads of wvec are done
   if (p.bias) { wvec[lane] = cr.bias0; wvec[32 + lane] = cr.bias1; }
   if (p.a_stats) { wvec[64 + lane] = cr.cs0; wvec[96 + lane] = cr.cs1; }
@@ -353,90 +352,97 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorM
   __syncwarp();
   if (next_nb >= 0) load_col_regs(p, next_nb, lane, cr);  // in flight during the arithmetic below
   ET(1);
-  tmem_ld_wait();
-  ET(2);
-  float v[64];
-  if (p.scale != 1.0f) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      v[j] = __uint_as_float(r0[j]) * p.scale;
-      v[32 + j] = __uint_as_float(r1[j]) * p.scale;
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      v[j] = __uint_as_float(r0[j]);
-      v[32 + j] = __uint_as_float(r1[j]);
-    }
-  }
-  if (p.a_stats) {
-#pragma unroll
-    for (int j = 0; j < 64; j += 4) {
-      const float4 cs = *reinterpret_cast<const float4*>(wvec + 64 + j);
-      v[j] = rc.rstd_a * (v[j] - rc.mean_a * cs.x);
-      v[j + 1] = rc.rstd_a * (v[j + 1] - rc.mean_a * cs.y);
-      v[j + 2] = rc.rstd_a * (v[j + 2] - rc.mean_a * cs.z);
-      v[j + 3] = rc.rstd_a * (v[j + 3] - rc.mean_a * cs.w);
-    }
-  }
-  if (p.bias) {
-#pragma unroll
-    for (int j = 0; j < 64; j += 4) {
-      const float4 b = *reinterpret_cast<const float4*>(wvec + j);
-      v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
-    }
-  }
-  apply_activation(v, p.act);
-  ET(3);
   uint8_t* srow = buf + row * 128;
-  if (p.res_mode) {
-    // Every thread waits for the residual tile itself (bounded; after a failed wait the result is meaningless and
-    // the status word says so).  The store warp fetched it after the buffer had become free.
-    mbar_wait(res_bar, use & 1, abort_flag, 5);
-    ET(4);
+  // The slab is processed as two halves of 32 columns (keeps the register footprint of an epilogue thread small
+  // enough for sixteen epilogue warps per CTA).
+#pragma unroll 1
+  for (int h = 0; h < 2; ++h) {
+    uint32_t r[32];
+    tmem_ld32(taddr + 32 * h, r);
+    tmem_ld_wait();
+    float v[32];
+    if (p.scale != 1.0f) {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const uint4 u = *reinterpret_cast<const uint4*>(srow + ((c ^ (row & 7)) << 4));
-      const T* e = reinterpret_cast<const T*>(&u);
-      float s[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) s[i] = to_f(e[i]);
-      if (p.res_mode == 2) {
-        const float4 g0 = *reinterpret_cast<const float4*>(wvec + 128 + c * 8);
-        const float4 g1 = *reinterpret_cast<const float4*>(wvec + 132 + c * 8);
-        const float4 b0 = *reinterpret_cast<const float4*>(wvec + 192 + c * 8);
-        const float4 b1 = *reinterpret_cast<const float4*>(wvec + 196 + c * 8);
-        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) s[i] = (s[i] - rc.mean_r) * rc.rstd_r * gg[i] + bb[i];
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[c * 8 + i] = p.alpha * v[c * 8 + i] + s[i];
-    }
-  } else {
-    mbar_wait(free_bar, (use & 1) ^ 1, abort_flag, 6);
-  }
-  ET(5);
-  if (p.out_stats) {
-    float a = 0.f, q = 0.f;
-    if (nb + 64 <= p.N) {
-#pragma unroll
-      for (int j = 0; j < 64; ++j) { a += v[j]; q = fmaf(v[j], v[j], q); }
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.scale;
     } else {
-      for (int j = 0; j < 64 && nb + j < p.N; ++j) { a += v[j]; q = fmaf(v[j], v[j], q); }
-    }
-    rc.sum += a;
-    rc.sumsq += q;
-  }
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    uint4 o;
-    o.x = pack_pair<T>(v[c * 8 + 0], v[c * 8 + 1]);
-    o.y = pack_pair<T>(v[c * 8 + 2], v[c * 8 + 3]);
-    o.z = pack_pair<T>(v[c * 8 + 4], v[c * 8 + 5]);
-    o.w = pack_pair<T>(v[c * 8 + 6], v[c * 8 + 7]);
-    *reinterpret_cast<uint4*>(srow + ((c ^ (row & 7)) << 4)) = o;
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    }
+    if (p.a_stats) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 cs = *reinterpret_cast<const float4*>(wvec + 64 + 32 * h + j);
+        v[j] = rc.rstd_a * (v[j] - rc.mean_a * cs.x);
+        v[j + 1] = rc.rstd_a * (v[j + 1] - rc.mean_a * cs.y);
+        v[j + 2] = rc.rstd_a * (v[j + 2] - rc.mean_a * cs.z);
+        v[j + 3] = rc.rstd_a * (v[j + 3] - rc.mean_a * cs.w);
+      }
+    }
+    if (p.bias) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 b = *reinterpret_cast<const float4*>(wvec + 32 * h + j);
+        v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
+      }
+    }
+    apply_activation(v, p.act);
+    if (h == 0) {
+      ET(2);
+      // Every thread does its own bounded wait (after a failed wait the result is meaningless and the status word
+      // says so): for the residual tile, which the store warp fetched into `buf` once the buffer was free, or
+      // for the buffer itself.
+      if (p.res_mode) mbar_wait(res_bar, use & 1, abort_flag, 5);
+      else mbar_wait(free_bar, (use & 1) ^ 1, abort_flag, 6);
+      ET(3);
+    }
+    if (p.res_mode) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int cc = 4 * h + c;
+        const uint4 u = *reinterpret_cast<const uint4*>(srow + ((cc ^ (row & 7)) << 4));
+        const T* e = reinterpret_cast<const T*>(&u);
+        float s[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] = to_f(e[i]);
+        if (p.res_mode == 2) {
+          const float4 g0 = *reinterpret_cast<const float4*>(wvec + 128 + cc * 8);
+          const float4 g1 = *reinterpret_cast<const float4*>(wvec + 132 + cc * 8);
+          const float4 b0 = *reinterpret_cast<const float4*>(wvec + 192 + cc * 8);
+          const float4 b1 = *reinterpret_cast<const float4*>(wvec + 196 + cc * 8);
+          const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+          const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+          const float sh = -rc.mean_r * rc.rstd_r;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) s[i] = fmaf(fmaf(s[i], rc.rstd_r, sh), gg[i], bb[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c * 8 + i] = fmaf(p.alpha, v[c * 8 + i], s[i]);
+      }
+    }
+    if (p.out_stats) {
+      float a = 0.f, q = 0.f;
+      const int nh = nb + 32 * h;
+      if (nh + 32 <= p.N) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { a += v[j]; q = fmaf(v[j], v[j], q); }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (nh + j < p.N) { a += v[j]; q = fmaf(v[j], v[j], q); }
+      }
+      rc.sum += a;
+      rc.sumsq += q;
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int cc = 4 * h + c;
+      uint4 o;
+      o.x = pack_pair<T>(v[c * 8 + 0], v[c * 8 + 1]);
+      o.y = pack_pair<T>(v[c * 8 + 2], v[c * 8 + 3]);
+      o.z = pack_pair<T>(v[c * 8 + 4], v[c * 8 + 5]);
+      o.w = pack_pair<T>(v[c * 8 + 6], v[c * 8 + 7]);
+      *reinterpret_cast<uint4*>(srow + ((cc ^ (row & 7)) << 4)) = o;
+    }
   }
   ET(6);
   fence_async_smem();  // this thread's writes are visible to the TMA store the store warp will issue
@@ -446,20 +452,21 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, const CUtensorM
 #undef ET
 }
 
-// The store warp's side of the fast path: for every slab of this CTA's tiles, in the order the epilogue groups
-// produce them, wait until the slab is staged, write it out with a TMA store, and hand a staging buffer back once
-// the store that used it has finished reading shared memory (one store stays in flight).  With a residual input
-// the same thread fetches the residual tiles: two slabs ahead per group, each into the staging buffer its slab
-// will use, as soon as that buffer is free; the epilogue threads then only wait for the tile to have landed.
+// A store thread's side of the fast path: for every slab of this CTA's tiles that belongs to the epilogue groups
+// [g_lo, g_hi), in the order the groups produce them, wait until the slab is staged, write it out with a TMA store,
+// and hand the staging buffer back once the store has finished reading shared memory (with two buffers per group
+// one store stays in flight, with one buffer the thread waits for the read right away).  With a residual input the
+// same thread fetches the residual tiles: kBufs slabs ahead per group, each into the staging buffer its slab will
+// use, as soon as that buffer is free; the epilogue threads then only wait for the tile to have landed.
 struct SlabWalk {
   const TcParams& p;
-  int first_tile, tile_step, tiles, n_tiles, tile_rows, row_offset, bn;
+  int first_tile, tile_step, tiles, n_tiles, tile_rows, row_offset, bn, groups;
   __device__ __forceinline__ int n0(int t) const { return (t % n_tiles) * bn; }
   __device__ __forceinline__ int m0(int t) const { return (t / n_tiles) * tile_rows + row_offset; }
-  // cursor over the slabs of one epilogue group (columns g*64, g*64+128, ... of each tile)
+  // cursor over the slabs of one epilogue group (columns g*64, (g + groups)*64, ... of each tile)
   struct Cursor { int t, c0; };
   __device__ __forceinline__ void settle(Cursor& c, int g) const {
-    while (c.t < tiles && n0(c.t) + c.c0 >= p.N) { c.t += tile_step; c.c0 = g * 64; }
+    while (c.t < tiles && (c.c0 >= bn || n0(c.t) + c.c0 >= p.N)) { c.t += tile_step; c.c0 = g * 64; }
   }
   __device__ __forceinline__ Cursor begin(int g) const {
     Cursor c{first_tile, g * 64};
@@ -467,51 +474,67 @@ struct SlabWalk {
     return c;
   }
   __device__ __forceinline__ void next(Cursor& c, int g) const {
-    c.c0 += 128;
+    c.c0 += 64 * groups;
     if (c.c0 >= bn || n0(c.t) + c.c0 >= p.N) { c.t += tile_step; c.c0 = g * 64; }
     settle(c, g);
   }
 };
 
+template <int kGroups, int kBufs>
 __device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtensorMap* tmap_c, const CUtensorMap* tmap_r,
                                                 uint8_t* epi_mem, uint64_t* stg_full, uint64_t* stg_free,
-                                                uint64_t* res_bar, int first_tile, int tile_step, int tiles,
-                                                int n_tiles, int tile_rows, int row_offset, int bn,
+                                                uint64_t* res_bar, int g_lo, int g_hi, int first_tile, int tile_step,
+                                                int tiles, int n_tiles, int tile_rows, int row_offset, int bn,
                                                 volatile int* abort_flag) {
-  const SlabWalk w{p, first_tile, tile_step, tiles, n_tiles, tile_rows, row_offset, bn};
-  SlabWalk::Cursor pf[2] = {w.begin(0), w.begin(1)};
-  uint32_t pf_count[2] = {0, 0};
+  const SlabWalk w{p, first_tile, tile_step, tiles, n_tiles, tile_rows, row_offset, bn, kGroups};
+  SlabWalk::Cursor pf[kGroups];
+  uint32_t pf_count[kGroups], count[kGroups];
+#pragma unroll
+  for (int g = 0; g < kGroups; ++g) {
+    pf[g] = w.begin(g);
+    pf_count[g] = 0;
+    count[g] = 0;
+  }
   auto fetch_residual = [&](int g) {
     if (pf[g].t >= tiles) return;
-    const int idx = g * 2 + (int)(pf_count[g] & 1);
+    const int idx = g * kBufs + (int)(pf_count[g] % kBufs);
     const uint32_t bar = smem_u32(&res_bar[idx]);
     mbar_expect_tx(bar, BM * 128);
     tma_load_2d(smem_u32(epi_mem + idx * (BM * 128)), tmap_r, w.n0(pf[g].t) + pf[g].c0, w.m0(pf[g].t), bar);
     ++pf_count[g];
     w.next(pf[g], g);
   };
+  // a staging buffer has been read out by its store: fetch the next residual tile into it, or tell the group
+  auto release = [&](int idx) {
+    if (p.res_mode) fetch_residual(idx / kBufs);
+    else mbar_arrive(smem_u32(&stg_free[idx]));
+  };
   if (p.res_mode)
-    for (int k = 0; k < 2; ++k)
-      for (int g = 0; g < 2; ++g) fetch_residual(g);
-  uint32_t count[2] = {0, 0};
+    for (int k = 0; k < kBufs; ++k)
+      for (int g = g_lo; g < g_hi; ++g) fetch_residual(g);
   int prev = -1;
   bool ok = true;
   for (int t = first_tile; t < tiles && ok; t += tile_step) {
     const int m0 = w.m0(t), n0 = w.n0(t);
     for (int c0 = 0; c0 < bn; c0 += 64) {
       if (n0 + c0 >= p.N) break;
-      const int g = (c0 >> 6) & 1;
+      const int g = (c0 >> 6) % kGroups;
+      if (g < g_lo || g >= g_hi) continue;
       const uint32_t s = count[g]++;
-      const int idx = g * 2 + (int)(s & 1);
-      if (!mbar_wait(smem_u32(&stg_full[idx]), (s >> 1) & 1, abort_flag, 7)) { ok = false; break; }
+      const int idx = g * kBufs + (int)(s % kBufs);
+      if (!mbar_wait(smem_u32(&stg_full[idx]), (s / kBufs) & 1, abort_flag, 7)) { ok = false; break; }
       tma_store_2d(tmap_c, n0 + c0, m0, smem_u32(epi_mem + idx * (BM * 128)));
       tma_store_commit();
-      if (prev >= 0) {
-        tma_store_wait_read1();
-        if (p.res_mode) fetch_residual(prev >> 1);  // the freed buffer is the one that group's slab after next uses
-        else mbar_arrive(smem_u32(&stg_free[prev]));
+      if (kBufs == 1) {
+        tma_store_wait_read0();
+        release(idx);
+      } else {
+        if (prev >= 0) {
+          tma_store_wait_read1();
+          release(prev);
+        }
+        prev = idx;
       }
-      prev = idx;
     }
   }
   tma_store_wait_all();  // stores must complete before the CTA exits
@@ -641,8 +664,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else if (warp == 10) {
     // ---------------- store warp: TMA stores of the staged slabs ----------------
     if (lane == 0 && p.tma_store)
-      store_warp_loop(p, &tmap_c, &tmap_r, epi_mem, stg_full, stg_free, res_bar, blockIdx.x, gridDim.x, tiles,
-                      n_tiles, BM, 0, BN, abort_flag);
+      store_warp_loop<2, 2>(p, &tmap_c, &tmap_r, epi_mem, stg_full, stg_free, res_bar, 0, 2, blockIdx.x, gridDim.x,
+                            tiles, n_tiles, BM, 0, BN, abort_flag);
   } else {
     // ---------------- epilogue (warps 2..9: two groups of four warps, alternating 64-column slabs) ----------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
@@ -679,9 +702,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (nn < p.N) next_nb = nn;
           }
           cr_nb = next_nb;
-          epilogue_slab<T>(p, &tmap_r, gbuf + (slab_it & 1) * (BM * 128), smem_u32(&res_bar[idx]),
-                           smem_u32(&stg_free[idx]), smem_u32(&stg_full[idx]), slab_it >> 1, leader, trow + c0,
-                           quarter * 32 + lane, lane, m0, n0 + c0, next_nb, cr, wvec, rc, abort_flag);
+          epilogue_slab<T>(p, gbuf + (slab_it & 1) * (BM * 128), smem_u32(&res_bar[idx]), smem_u32(&stg_free[idx]),
+                           smem_u32(&stg_full[idx]), slab_it >> 1, leader, trow + c0, quarter * 32 + lane, lane,
+                           n0 + c0, next_nb, cr, wvec, rc, abort_flag);
           ++slab_it;
         }
         flush_row_ctx(p, m, rc);
@@ -759,21 +782,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // accumulator hand-over are signalled to both CTAs with one tcgen05.commit per CTA, and the odd CTA's
 // epilogue warps release the accumulator with remote mbarrier arrivals.
 // ------------------------------------------------------------------------------------------------
-struct PairCfg {
+template <int kGroupsT> struct PairCfg {
   static constexpr int BN = 256;
   static constexpr int kStageBytes = (BM + BN / 2) * BK * 2;  // 32 KB per CTA
   static constexpr int kStages = 4;
   static constexpr int kTmemCols = 512;
+  // warp 0 TMA, warp 1 MMA, warps 2 and 3 stores (half of the epilogue groups each), then kGroups epilogue groups of
+  // four warps.  The 64 KB of staging are four buffers of 128 rows x 128 bytes: two groups with two buffers each
+  // (168 registers per thread; best when the main loop dominates) or four groups with one buffer each (96
+  // registers; twice the epilogue throughput, for products with few k-blocks per tile).
+  static constexpr int kGroups = kGroupsT;
+  static constexpr int kBufs = 4 / kGroupsT;
+  static constexpr int kThreads = 128 + 128 * kGroupsT;
   static constexpr int kEpiBytes = 4 * BM * 128;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 512 + 8192;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 512 + 16 * 1024 /*column vectors*/;
 };
 
-template <typename T>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+template <typename T, int kGroups>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<kGroups>::kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_r,
                     const TcParams p) {
-  using Cfg = PairCfg;
+  using Cfg = PairCfg<kGroups>;
+  constexpr int kBufs = Cfg::kBufs;
   constexpr int S = Cfg::kStages;
   constexpr int BN = Cfg::BN;
   extern __shared__ uint8_t smem_raw[];
@@ -783,13 +814,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_mem);  // [S]  waited on by the even CTA only
   uint64_t* empty_bar = full_bar + S;                          // [S]  per CTA
   uint64_t* tfull_bar = empty_bar + S;                         // [2]  per CTA
-  uint64_t* tempty_bar = tfull_bar + 2;                        // [2]  even CTA: 4 local + 4 remote arrivals
+  uint64_t* tempty_bar = tfull_bar + 2;                        // [2]  even CTA: one arrival per epilogue warp of both CTAs
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  uint64_t* res_bar = reinterpret_cast<uint64_t*>(bar_mem + 192);   // [2 groups][2 buffers]
-  uint64_t* stg_full = reinterpret_cast<uint64_t*>(bar_mem + 256);  // [2 groups][2 buffers]
-  uint64_t* stg_free = stg_full + 4;                                // [2 groups][2 buffers]
-  float* wvec = reinterpret_cast<float*>(bar_mem + 512) + ((threadIdx.x >> 5) & 7) * 256;  // per-warp scratch
+  uint64_t* res_bar = reinterpret_cast<uint64_t*>(bar_mem + 192);   // [kGroups][kBufs]
+  uint64_t* stg_full = reinterpret_cast<uint64_t*>(bar_mem + 256);  // [kGroups][kBufs]
+  uint64_t* stg_free = stg_full + 4;                                // [kGroups][kBufs]
+  float* wvec = reinterpret_cast<float*>(bar_mem + 512) + ((threadIdx.x >> 5) & 15) * 256;  // per-warp scratch
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -805,7 +836,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&tfull_bar[i]), 1);
-      mbar_init(smem_u32(&tempty_bar[i]), 16);
+      mbar_init(smem_u32(&tempty_bar[i]), 8 * kGroups);
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&res_bar[i]), 1);
@@ -885,56 +916,58 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
       }
     }
-  } else if (warp == 10) {
-    // ---------------- store warp (both CTAs): TMA stores of the staged slabs ----------------
+  } else if (warp == 2 || warp == 3) {
+    // ---------------- store warps (both CTAs): TMA stores of the staged slabs, half of the groups each ----------
     if (lane == 0)
-      store_warp_loop(p, &tmap_c, &tmap_r, epi_mem, stg_full, stg_free, res_bar, pair, pairs, tiles, n_tiles,
-                      2 * BM, (int)rank * BM, BN, abort_flag);
+      store_warp_loop<kGroups, kBufs>(p, &tmap_c, &tmap_r, epi_mem, stg_full, stg_free, res_bar,
+                                      (warp - 2) * (kGroups / 2), (warp - 1) * (kGroups / 2), pair, pairs, tiles, n_tiles,
+                                      2 * BM, (int)rank * BM, BN, abort_flag);
   } else {
-    // ---------------- epilogue (warps 2..9 of both CTAs, two groups alternating 64-column slabs) ----------------
+    // ---------------- epilogue (warps 4.. of both CTAs): group g handles the 64-column slabs g, g + kGroups, ... of
+    // every tile ----------------
     const int quarter = warp & 3;
-    const int group = (warp - 2) >> 2;
-    const bool leader = ((warp - 2) & 3) == 0 && lane == 0;
-    uint8_t* gbuf = epi_mem + group * (2 * BM * 128);
+    const int group = (warp - 4) >> 2;
+    const bool leader = ((warp - 4) & 3) == 0 && lane == 0;
     uint32_t tile_it = 0, slab_it = 0;
     ColRegs cr;
     int cr_nb = -1;
     for (int t = pair; t < tiles; t += pairs, ++tile_it) {
       const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
       const int m0 = (t / n_tiles) * (2 * BM) + (int)rank * BM, n0 = (t % n_tiles) * BN;
-      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 0);
+      if (leader && tile_it < 32) TRACE(2100 + (group * 32 + (int)tile_it) * 4 + 0);
       if (!mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4)) break;
       tcgen05_fence_after();
-      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 1);
+      if (leader && tile_it < 32) TRACE(2100 + (group * 32 + (int)tile_it) * 4 + 1);
       const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       const int m = m0 + quarter * 32 + lane;
       RowCtx rc;
       load_row_ctx(p, m, rc);
 #pragma unroll 1
-      for (int c0 = group * 64; c0 < BN; c0 += 128) {
+      for (int c0 = group * 64; c0 < BN; c0 += 64 * kGroups) {
         if (n0 + c0 >= p.N) break;  // uniform over the group
-        const int idx = group * 2 + (int)(slab_it & 1);
+        const int idx = group * kBufs + (int)(slab_it % kBufs);
         if (cr_nb != n0 + c0) load_col_regs(p, n0 + c0, lane, cr);
+        // the slab this group handles next: further right in this tile, else the first one of its next tile
         int next_nb = -1;
-        if (c0 + 128 < BN && n0 + c0 + 128 < p.N) {
-          next_nb = n0 + c0 + 128;
+        if (c0 + 64 * kGroups < BN && n0 + c0 + 64 * kGroups < p.N) {
+          next_nb = n0 + c0 + 64 * kGroups;
         } else if (t + pairs < tiles) {
           const int nn = ((t + pairs) % n_tiles) * BN + group * 64;
           if (nn < p.N) next_nb = nn;
         }
         cr_nb = next_nb;
-        epilogue_slab<T>(p, &tmap_r, gbuf + (slab_it & 1) * (BM * 128), smem_u32(&res_bar[idx]),
-                         smem_u32(&stg_free[idx]), smem_u32(&stg_full[idx]), slab_it >> 1, leader, trow + c0,
-                         quarter * 32 + lane, lane, m0, n0 + c0, next_nb, cr, wvec, rc, abort_flag,
+        epilogue_slab<T>(p, epi_mem + idx * (BM * 128), smem_u32(&res_bar[idx]), smem_u32(&stg_free[idx]),
+                         smem_u32(&stg_full[idx]), slab_it / kBufs, leader, trow + c0, quarter * 32 + lane, lane,
+                         n0 + c0, next_nb, cr, wvec, rc, abort_flag,
                          slab_it < 32 ? 1024 + (group * 32 + (int)slab_it) * 8 : -1);
         ++slab_it;
       }
       flush_row_ctx(p, m, rc);
       tcgen05_fence_before();
       __syncwarp();
-      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 2);
+      if (leader && tile_it < 32) TRACE(2100 + (group * 32 + (int)tile_it) * 4 + 2);
       if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&tempty_bar[acc]), 0));
-      if (leader && tile_it < 32) TRACE(1600 + (group * 32 + (int)tile_it) * 4 + 3);
+      if (leader && tile_it < 32) TRACE(2100 + (group * 32 + (int)tile_it) * 4 + 3);
     }
   }
 
@@ -1093,15 +1126,15 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
 }
 
 
-template <typename T>
+template <typename T, int kGroups>
 cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStream_t s) {
-  using Cfg = PairCfg;
+  using Cfg = PairCfg<kGroups>;
   static std::atomic<unsigned long long> attr_mask{0};
   int dev = 0;
   cudaError_t de = cudaGetDevice(&dev);
   if (de != cudaSuccess) return de;
   if (!(attr_mask.load() >> (dev & 63) & 1ull)) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<T, kGroups>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     attr_mask.fetch_or(1ull << (dev & 63));
@@ -1139,7 +1172,7 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   const int tiles = ceil_div(g.M, 2 * BM) * ceil_div(g.N, Cfg::BN);
   const int max_pairs = ((g.cta_limit > 0 && g.cta_limit < sm_count) ? g.cta_limit : sm_count) / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  gemm_tc_pair_kernel<T><<<2 * pairs, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, p);
+  gemm_tc_pair_kernel<T, kGroups><<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, p);
   return cudaGetLastError();
 }
 
@@ -1177,7 +1210,16 @@ cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaS
   const bool tma_store_ok = !p.out_f32 && (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
   if (pair_enabled && tma_store_ok && p.conv_cin == 0 && p.M >= 512 && p.N > 128 &&
       (long long)ceil_div(p.M, 2 * BM) * ceil_div(p.N, 256) >= sm_count / 4)
-    return launch_pair<T>(p, status, sm_count, s);
+  {
+    // Four epilogue groups when a tile has few k-blocks (the epilogue then sets the pace), two otherwise (fewer
+    // warps compete with the MMA issuer and the producer).  B200_PAIR_GROUPS=2|4 overrides.
+    static const int forced = [] {
+      const char* e = getenv("B200_PAIR_GROUPS");
+      return e ? atoi(e) : 0;
+    }();
+    const bool four = forced ? forced == 4 : p.K <= 8 * BK;
+    return four ? launch_pair<T, 4>(p, status, sm_count, s) : launch_pair<T, 2>(p, status, sm_count, s);
+  }
   // Wide tiles amortise the A-tile loads; narrow problems take the smallest tile that covers N, and skinny
   // problems (few rows) the widest tile that still yields at least half an SM count of CTAs.
   auto tiles = [&](int bn) { return (long long)ceil_div(p.M, BM) * ceil_div(p.N, bn); };
