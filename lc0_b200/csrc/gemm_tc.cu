@@ -274,6 +274,7 @@ struct TcParams {
   int res_mode;  // 0 none, 1 add the residual tile, 2 add the normalised residual tile
   const float* res_stats; const float* res_gamma; const float* res_beta; float res_inv_c, res_eps;
   float* out_stats;
+  int n_split;  // > 0: columns from here on are stored through the second output map
 };
 
 // Per-thread (= per output row) state of the folded-LayerNorm epilogue.
@@ -481,8 +482,8 @@ struct SlabWalk {
 };
 
 template <int kGroups, int kBufs>
-__device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtensorMap* tmap_c, const CUtensorMap* tmap_r,
-                                                uint8_t* epi_mem, uint64_t* stg_full, uint64_t* stg_free,
+__device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtensorMap* tmap_c, const CUtensorMap* tmap_c2,
+                                                const CUtensorMap* tmap_r, uint8_t* epi_mem, uint64_t* stg_full, uint64_t* stg_free,
                                                 uint64_t* res_bar, int g_lo, int g_hi, int first_tile, int tile_step,
                                                 int tiles, int n_tiles, int tile_rows, int row_offset, int bn,
                                                 volatile int* abort_flag) {
@@ -523,7 +524,10 @@ __device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtenso
       const uint32_t s = count[g]++;
       const int idx = g * kBufs + (int)(s % kBufs);
       if (!mbar_wait(smem_u32(&stg_full[idx]), (s / kBufs) & 1, abort_flag, 7)) { ok = false; break; }
-      tma_store_2d(tmap_c, n0 + c0, m0, smem_u32(epi_mem + idx * (BM * 128)));
+      if (p.n_split > 0 && n0 >= p.n_split)
+        tma_store_2d(tmap_c2, n0 + c0 - p.n_split, m0, smem_u32(epi_mem + idx * (BM * 128)));
+      else
+        tma_store_2d(tmap_c, n0 + c0, m0, smem_u32(epi_mem + idx * (BM * 128)));
       tma_store_commit();
       if (kBufs == 1) {
         tma_store_wait_read0();
@@ -664,7 +668,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else if (warp == 10) {
     // ---------------- store warp: TMA stores of the staged slabs ----------------
     if (lane == 0 && p.tma_store)
-      store_warp_loop<2, 2>(p, &tmap_c, &tmap_r, epi_mem, stg_full, stg_free, res_bar, 0, 2, blockIdx.x, gridDim.x,
+      store_warp_loop<2, 2>(p, &tmap_c, &tmap_c, &tmap_r, epi_mem, stg_full, stg_free, res_bar, 0, 2, blockIdx.x, gridDim.x,
                             tiles, n_tiles, BM, 0, BN, abort_flag);
   } else {
     // ---------------- epilogue (warps 2..9: two groups of four warps, alternating 64-column slabs) ----------------
@@ -782,6 +786,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // accumulator hand-over are signalled to both CTAs with one tcgen05.commit per CTA, and the odd CTA's
 // epilogue warps release the accumulator with remote mbarrier arrivals.
 // ------------------------------------------------------------------------------------------------
+// N of the MMA that computes a tile of which `remaining` columns exist: full width, or the remainder rounded up to 32.
+__host__ __device__ __forceinline__ int pair_mma_n(int remaining, int bn) {
+  return remaining >= bn ? bn : ((remaining + 31) & ~31);
+}
+
 template <int kGroupsT> struct PairCfg {
   static constexpr int BN = 256;
   static constexpr int kStageBytes = (BM + BN / 2) * BK * 2;  // 32 KB per CTA
@@ -802,7 +811,7 @@ template <typename T, int kGroups>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<kGroups>::kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_r,
-                    const TcParams p) {
+                    const __grid_constant__ CUtensorMap tmap_c2, const TcParams p) {
   using Cfg = PairCfg<kGroups>;
   constexpr int kBufs = Cfg::kBufs;
   constexpr int S = Cfg::kStages;
@@ -865,7 +874,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       bool ok = true;
       for (int t = pair; t < tiles && ok; t += pairs) {
         const int m0 = (t / n_tiles) * (2 * BM) + (int)rank * BM;
-        const int n0 = (t % n_tiles) * BN + (int)rank * (BN / 2);
+        // a narrower last tile is computed with a narrower MMA, of which each CTA supplies half the W rows
+        const int nt = (t % n_tiles) * BN;
+        const int n0 = nt + (int)rank * (pair_mma_n(p.N - nt, BN) / 2);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -883,8 +894,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   } else if (warp == 1) {
     // ---------------- MMA issuer (even CTA only) ----------------
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = (1u << 4) | (FmtCode<T>::v << 7) | (FmtCode<T>::v << 10) |
-                                 ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+      constexpr uint32_t idesc_base = (1u << 4) | (FmtCode<T>::v << 7) | (FmtCode<T>::v << 10) |
+                                      ((uint32_t)((2 * BM) >> 4) << 24);
       uint32_t it = 0, tile_it = 0;
       bool ok = true;
       for (int t = pair; t < tiles && ok; t += pairs, ++tile_it) {
@@ -893,6 +904,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tcgen05_fence_after();
         if (tile_it < 64) TRACE(512 + tile_it);
         const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t idesc = idesc_base | ((uint32_t)(pair_mma_n(p.N - (t % n_tiles) * BN, BN) >> 3) << 17);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -919,7 +931,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   } else if (warp == 2 || warp == 3) {
     // ---------------- store warps (both CTAs): TMA stores of the staged slabs, half of the groups each ----------
     if (lane == 0)
-      store_warp_loop<kGroups, kBufs>(p, &tmap_c, &tmap_r, epi_mem, stg_full, stg_free, res_bar,
+      store_warp_loop<kGroups, kBufs>(p, &tmap_c, &tmap_c2, &tmap_r, epi_mem, stg_full, stg_free, res_bar,
                                       (warp - 2) * (kGroups / 2), (warp - 1) * (kGroups / 2), pair, pairs, tiles, n_tiles,
                                       2 * BM, (int)rank * BM, BN, abort_flag);
   } else {
@@ -1048,6 +1060,7 @@ void fill_folded(TcParams& p, const GemmParams& g) {
   p.res_stats = g.res_stats; p.res_gamma = g.res_gamma; p.res_beta = g.res_beta;
   p.res_inv_c = g.res_inv_c; p.res_eps = g.res_eps;
   p.out_stats = g.out_stats;
+  p.n_split = 0;
 }
 
 // 4D map over a token-major activation [positions][8][8][channels]; box = 64 channels x 8 x 8 x 2 boards
@@ -1145,16 +1158,21 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   if (e != cudaSuccess) return e;
   e = get_map(g.W, g.ldw, g.N, g.K, Cfg::BN / 2, prec, &mw);
   if (e != cudaSuccess) return e;
-  e = get_map(g.C, g.ldc, g.M, g.N, BM, prec, &mc);
+  e = get_map(g.C, g.ldc, g.M, g.n_split > 0 ? g.n_split : g.N, BM, prec, &mc);
   if (e != cudaSuccess) return e;
-  CUtensorMap mr = mc;
+  CUtensorMap mr = mc, mc2 = mc;
   if (g.res) {
     if ((g.ldres % 8) != 0 || (reinterpret_cast<uintptr_t>(g.res) & 15) != 0) return cudaErrorInvalidValue;
     e = get_map(g.res, g.ldres, g.M, g.N, BM, prec, &mr);
     if (e != cudaSuccess) return e;
   }
+  if (g.n_split > 0) {
+    e = get_map(g.C2, g.ldc2, g.M, g.N - g.n_split, BM, prec, &mc2);
+    if (e != cudaSuccess) return e;
+  }
   TcParams p;
   fill_folded(p, g);
+  p.n_split = g.n_split;
   p.tma_store = 1;
   p.bias = g.bias; p.C = g.C; p.ldc = g.ldc;
   p.M = g.M; p.N = g.N; p.K = g.K; p.act = g.act; p.scale = g.scale; p.alpha = g.alpha;
@@ -1172,7 +1190,7 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   const int tiles = ceil_div(g.M, 2 * BM) * ceil_div(g.N, Cfg::BN);
   const int max_pairs = ((g.cta_limit > 0 && g.cta_limit < sm_count) ? g.cta_limit : sm_count) / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  gemm_tc_pair_kernel<T, kGroups><<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, p);
+  gemm_tc_pair_kernel<T, kGroups><<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, mc2, p);
   return cudaGetLastError();
 }
 
@@ -1198,18 +1216,31 @@ bool gemm_tc_supported(const GemmParams& p) {
          (p.ldw % 8) == 0 && al16(p.A) && al16(p.W);
 }
 
-template <typename T>
-cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaStream_t s) {
-  if (p.M <= 0 || p.N <= 0) return cudaSuccess;
-  if (!gemm_tc_supported(p) || p.skip) return cudaErrorInvalidValue;  // residuals go through `res`
-  // Large problems with 16-bit output go to the CTA-pair kernel (256x256 tiles).
+namespace {
+// Large problems with 16-bit output go to the CTA-pair kernel (256x256 tiles).
+bool pair_eligible(const GemmParams& p, int sm_count) {
   static const bool pair_enabled = [] {
     const char* e = getenv("B200_GEMM_PAIR");
     return !(e && e[0] == '0');
   }();
   const bool tma_store_ok = !p.out_f32 && (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
-  if (pair_enabled && tma_store_ok && p.conv_cin == 0 && p.M >= 512 && p.N > 128 &&
-      (long long)ceil_div(p.M, 2 * BM) * ceil_div(p.N, 256) >= sm_count / 4)
+  return pair_enabled && tma_store_ok && p.conv_cin == 0 && p.M >= 512 && p.N > 128 &&
+         (long long)ceil_div(p.M, 2 * BM) * ceil_div(p.N, 256) >= sm_count / 4;
+}
+}  // namespace
+
+bool gemm_tc_split_supported(const GemmParams& p, int sm_count) {
+  return gemm_tc_supported(p) && pair_eligible(p, sm_count) && p.n_split > 0 && (p.n_split % 256) == 0 &&
+         p.N > p.n_split && p.N - p.n_split <= 256 && p.C2 && (p.ldc2 % 8) == 0 &&
+         (reinterpret_cast<uintptr_t>(p.C2) & 15) == 0 && !p.res && !p.out_stats && !p.skip;
+}
+
+template <typename T>
+cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaStream_t s) {
+  if (p.M <= 0 || p.N <= 0) return cudaSuccess;
+  if (!gemm_tc_supported(p) || p.skip) return cudaErrorInvalidValue;  // residuals go through `res`
+  if (p.n_split > 0 && !gemm_tc_split_supported(p, sm_count)) return cudaErrorInvalidValue;
+  if (pair_eligible(p, sm_count))
   {
     // Four epilogue groups when a tile has few k-blocks (the epilogue then sets the pace), two otherwise (fewer
     // warps compete with the MMA issuer and the producer).  B200_PAIR_GROUPS=2|4 overrides.

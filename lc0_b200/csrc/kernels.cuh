@@ -40,6 +40,12 @@ struct GemmParams {
   // Upper bound on the CTAs (= SMs) the tensor-core kernel may occupy; 0 = all.  Lets a small product run beside a
   // large one on another stream.
   int cta_limit = 0;
+  // Second output of the CTA-pair kernel: columns [n_split, N) go to C2 (leading dimension ldc2, column n - n_split)
+  // instead of C.  n_split must be a multiple of 256 and the remainder at most 256 columns wide; the last tile is then
+  // computed with a narrower MMA.  Lets a narrow product share the operand traffic of a wide one (same A, same folded
+  // LayerNorm); no residual / statistics in this mode.
+  void* C2 = nullptr; long long ldc2 = 0;
+  int n_split = 0;
 };
 
 template <typename T> cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t s);
@@ -47,6 +53,8 @@ template <typename T> cudaError_t launch_gemm_simt(const GemmParams& p, cudaStre
 // `status` is a device int the kernel sets non-zero when a bounded wait gives up.
 template <typename T> cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaStream_t s);
 bool gemm_tc_supported(const GemmParams& p);
+// Whether launch_gemm_tc would run `p` (with C2 / n_split set) on the CTA-pair kernel, the only one that splits.
+bool gemm_tc_split_supported(const GemmParams& p, int sm_count);
 cudaError_t gemm_tc_init();  // resolves the driver entry point used to encode TMA descriptors
 
 template <typename T>

@@ -174,6 +174,7 @@ template <typename T> struct EncoderW {
   float *ln1g = nullptr, *ln1b = nullptr, *ln2g = nullptr, *ln2b = nullptr;
   bool smolgen = false;
   Dense<T> sg_compress, sg_d1, sg_d2;
+  int qkvc_out = 0;  // > 0: qkv.w holds this many rows, the smolgen compression's appended to Q, K, V's
   float *sg_ln1g = nullptr, *sg_ln1b = nullptr, *sg_ln2g = nullptr, *sg_ln2b = nullptr;
 };
 
@@ -339,6 +340,7 @@ struct Net : NetBase {
   bool use_tc = false;
   // LayerNorms of the encoder stack folded into the neighbouring tensor-core products (16-bit storage only).
   bool fold_ln = false;
+  bool merge_compress = true;  // B200_MERGE_COMPRESS=0: smolgen compression as a launch of its own
   int side_sms = 0;  // SMs left to the side stream while the QKV product runs (0: everything on one stream)
   bool fold_heads = false;  // the heads' first products fold the last LayerNorm too (else it is materialised)
   int* d_status = nullptr;
@@ -546,14 +548,27 @@ struct Net : NetBase {
       w.insert(w.end(), ww.begin(), ww.end());
       b.insert(b.end(), bb.begin(), bb.end());
     }
+    // The smolgen compression reads the same layer input as Q, K, V: its rows are appended to theirs so that one
+    // launch of the CTA-pair kernel can compute both (second output, narrow last tile); sg_compress below is a view
+    // of those rows for the cases that run it as a product of its own.
+    const size_t cw_size = size_of(p + ".mha.smolgen.compress");
+    const int hc_rows = cw_size ? (int)(cw_size / emb) : 0;
+    const bool merge = hc_rows > 0 && sizeof(T) == 2 && use_tc && (3 * dm) % 256 == 0 && hc_rows <= 256 && hc_rows % 8 == 0;
+    if (merge) {
+      const auto& cw = need(p + ".mha.smolgen.compress", (size_t)hc_rows * emb);
+      w.insert(w.end(), cw.begin(), cw.end());
+      b.resize((size_t)3 * dm + hc_rows, 0.f);
+    }
+    const int qkv_rows = 3 * dm + (merge ? hc_rows : 0);
     if (in_gamma) {
-      e.qkv = dense_folded(w, &b, 3 * dm, emb, *in_gamma, *in_beta);
+      e.qkv = dense_folded(w, &b, qkv_rows, emb, *in_gamma, *in_beta);
     } else {
-      e.qkv.out = 3 * dm;
       e.qkv.in = emb;
       e.qkv.w = up_T(w);
       e.qkv.b = up_f32(b);
     }
+    e.qkv.out = 3 * dm;
+    if (merge) e.qkvc_out = qkv_rows;
     e.proj = dense(p + ".mha.dense_w", p + ".mha.dense_b", emb, dm);
     const int dff = (int)size_of(p + ".ffn.dense1_b");
     if (fold_ln)
@@ -576,7 +591,15 @@ struct Net : NetBase {
       const int hc = (int)size_of(p + ".mha.smolgen.compress") / emb;
       const int hid = (int)size_of(p + ".mha.smolgen.dense1_b");
       const int gen = (int)size_of(p + ".mha.smolgen.dense2_b");
-      e.sg_compress = dense_maybe_folded(p + ".mha.smolgen.compress", "", hc, emb, in_gamma, in_beta);
+      if (e.qkvc_out) {
+        e.sg_compress.out = hc;
+        e.sg_compress.in = emb;
+        e.sg_compress.w = e.qkv.w + (size_t)3 * dm * emb;
+        e.sg_compress.b = e.qkv.b + 3 * dm;  // zeros, or beta . W^T of the folded LayerNorm
+        e.sg_compress.colsum = e.qkv.colsum ? e.qkv.colsum + 3 * dm : nullptr;
+      } else {
+        e.sg_compress = dense_maybe_folded(p + ".mha.smolgen.compress", "", hc, emb, in_gamma, in_beta);
+      }
       e.sg_d1 = dense(p + ".mha.smolgen.dense1_w", p + ".mha.smolgen.dense1_b", hid, 64 * hc);
       e.sg_d2 = dense(p + ".mha.smolgen.dense2_w", p + ".mha.smolgen.dense2_b", gen, hid);
       e.sg_ln1g = up_f32(p + ".mha.smolgen.ln1_gammas", hid);
@@ -634,6 +657,7 @@ struct Net : NetBase {
       CK(gemm_tc_init());
     }
     if (const char* v = getenv("B200_SIDE_SMS")) side_sms = atoi(v);
+    if (const char* v = getenv("B200_MERGE_COMPRESS")) merge_compress = v[0] != '0';
     fold_ln = use_tc && attn_body && !(getenv("B200_FOLD_LN") && getenv("B200_FOLD_LN")[0] == '0');
     // Folding needs every product that consumes or produces a folded LayerNorm to be eligible for the tensor-core
     // kernel's TMA epilogue: output widths that are multiples of 8.
@@ -946,9 +970,10 @@ struct Net : NetBase {
   // alpha * act(...) + LN(res) and optional accumulation of output row statistics.
   void gemm_ln(cudaStream_t st, const LNState& in, long long lda, const Dense<T>& d, T* Cout, long long ldc, int M,
                int act, const LNState* res = nullptr, float alpha_ = 1.f, float* out_stats = nullptr,
-               int cta_limit = 0) {
+               int cta_limit = 0, T* C2 = nullptr, long long ldc2 = 0, int n_split = 0) {
     GemmParams p;
     p.cta_limit = cta_limit;
+    p.C2 = C2; p.ldc2 = ldc2; p.n_split = n_split;
     p.A = in.u; p.lda = lda; p.W = d.w; p.ldw = d.in; p.bias = d.b;
     p.C = Cout; p.ldc = ldc; p.M = M; p.N = d.out; p.K = d.in; p.act = act;
     if (in.stats) {
@@ -1034,6 +1059,19 @@ struct Net : NetBase {
     // while the QKV product (which only needs the same layer input) runs on the others.  The per-kernel profiling
     // pass keeps everything on one stream so that each kernel is timed alone.
     const bool overlap = e.smolgen && side_sms > 0 && !profiling && use_tc && sizeof(T) == 2;
+    // One launch for Q, K, V and the smolgen compression when the CTA-pair kernel takes the product.
+    bool merged = false;
+    if (e.smolgen && e.qkvc_out && !overlap && merge_compress) {
+      GemmParams probe;
+      probe.A = in.u; probe.lda = E; probe.W = e.qkv.w; probe.ldw = E; probe.C = s.qkv; probe.ldc = 3 * E;
+      probe.M = R; probe.N = e.qkvc_out; probe.K = E; probe.C2 = s.sg_c; probe.ldc2 = sg_hc; probe.n_split = 3 * E;
+      merged = gemm_tc_split_supported(probe, sm_count);
+    }
+    if (merged) {
+      Dense<T> both = e.qkv;
+      both.out = e.qkvc_out;
+      gemm_ln(st, in, E, both, s.qkv, 3 * E, R, ACT_NONE, nullptr, 1.f, nullptr, 0, s.sg_c, sg_hc, 3 * E);
+    }
     if (e.smolgen) {  // network_blas.cc:300-339
       cudaStream_t ss = overlap ? s.side : st;
       const int lim = overlap ? side_sms : 0;
@@ -1042,7 +1080,7 @@ struct Net : NetBase {
         CK(cudaStreamWaitEvent(ss, s.ev_fork, 0));
         gemm_ln(st, in, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE, nullptr, 1.f, nullptr, sm_count - side_sms);
       }
-      gemm_ln(ss, in, E, e.sg_compress, s.sg_c, sg_hc, R, ACT_NONE, nullptr, 1.f, nullptr, lim);
+      if (!merged) gemm_ln(ss, in, E, e.sg_compress, s.sg_c, sg_hc, R, ACT_NONE, nullptr, 1.f, nullptr, lim);
       gemm(ss, s.sg_c, 64 * sg_hc, e.sg_d1, s.sg_h1, sg_hid, n, act_smolgen, nullptr, 0, 1.f, false, nullptr, lim);
       ln(ss, s.sg_h1, s.sg_h1, nullptr, e.sg_ln1g, e.sg_ln1b, n, sg_hid, 1.f, 1e-3f);
       gemm(ss, s.sg_h1, sg_hid, e.sg_d2, s.sg_h2, sg_gen, n, act_smolgen, nullptr, 0, 1.f, false, nullptr, lim);
@@ -1054,7 +1092,7 @@ struct Net : NetBase {
       gemm(st, s.sg_h2, sg_gen / H, smolgen_w, s.sg_bias, 4096, n * H, ACT_NONE);
       bias = s.sg_bias;
     }
-    if (!overlap) gemm_ln(st, in, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE);  // :341-350, :408-412
+    if (!overlap && !merged) gemm_ln(st, in, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE);  // :341-350, :408-412
     launches++;
     // algorithmic bytes: read Q, K, V (+ bias), write the head outputs
     span_begin(st, K_ATTENTION, (double)R * E * sizeof(T) * 4 + (bias ? (double)n * H * 4096 * sizeof(T) : 0.0));

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 
 from conftest import load_case
-from lc0_b200 import _lib, network, weights
+from lc0_b200 import _lib, mknet, network, weights
 from oracle import oracle
 
 pytestmark = pytest.mark.gpu
@@ -208,3 +208,24 @@ def test_concurrent_computations_on_two_slots():
     assert not errors, errors
     assert nw.device_status() == 0
     nw.close()
+
+
+def test_merged_qkv_and_smolgen_compression_launch_matches_separate_launches(monkeypatch):
+    """Q, K, V and the smolgen compression computed by one launch of the CTA-pair kernel (second output, narrow last
+    tile) against the same network with the compression as a product of its own."""
+    net = mknet.make_net("cfg4_2layer")
+    rng = np.random.default_rng(5)
+    n = 64
+    masks = rng.integers(0, 2 ** 63, size=(n, 112), dtype=np.int64).astype(np.uint64) & rng.integers(
+        0, 2 ** 63, size=(n, 112), dtype=np.int64).astype(np.uint64)
+    values = np.ones((n, 112), np.float32)
+    outs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("B200_MERGE_COMPRESS", flag)
+        nw = network.Network(net, "precision=fp16,max_batch=%d" % n)
+        outs.append(nw.evaluate(masks, values))
+        assert nw.device_status() == 0
+        nw.close()
+    scale = np.abs(outs[1]["policy"]).max()
+    assert np.abs(outs[0]["policy"] - outs[1]["policy"]).max() <= 2e-3 * scale
+    assert np.abs(outs[0]["q"] - outs[1]["q"]).max() <= 2e-3
