@@ -388,7 +388,11 @@ struct Net : NetBase {
     T *tokens = nullptr, *pre = nullptr, *pe = nullptr;
     T *x = nullptr, *x1 = nullptr, *y = nullptr, *qkv = nullptr, *att = nullptr, *ffn = nullptr;
     T *sg_c = nullptr, *sg_h1 = nullptr, *sg_h2 = nullptr, *sg_bias = nullptr;
-    float *stats1 = nullptr, *stats2 = nullptr;  // per-row (sum, sum of squares) of the folded LayerNorm inputs
+    // per-row (sum, sum of squares) of the folded LayerNorm inputs, laid out [stats2[0] | stats1 | stats2[1]] so that
+    // one memset at the start of a layer clears stats1 and the stats2 buffer that layer writes (layers alternate)
+    float *stats1 = nullptr, *stats2[2] = {nullptr, nullptr};
+    int stats_parity = 0;
+    size_t stats_stride = 0;  // floats between consecutive buffers of that block
     T *pemb = nullptr, *pq = nullptr, *pk = nullptr, *praw = nullptr;
     float* logits = nullptr;
     T *vtok = nullptr, *vhid = nullptr, *mtok = nullptr, *mhid = nullptr;
@@ -914,8 +918,11 @@ struct Net : NetBase {
         }
         s.qkv = A(R * 3 * E);
         if (fold_ln) {
-          s.stats1 = (float*)salloc.alloc(R * 2 * sizeof(float));
-          s.stats2 = (float*)salloc.alloc(R * 2 * sizeof(float));
+          float* blk = (float*)salloc.alloc(3 * R * 2 * sizeof(float));
+          s.stats2[0] = blk;
+          s.stats1 = blk + R * 2;
+          s.stats2[1] = blk + 2 * R * 2;
+          s.stats_stride = (size_t)R * 2;
         }
         s.att = A(R * E);
         s.ffn = A(R * std::max(max_dff, 8));
@@ -970,7 +977,7 @@ struct Net : NetBase {
   // alpha * act(...) + LN(res) and optional accumulation of output row statistics.
   void gemm_ln(cudaStream_t st, const LNState& in, long long lda, const Dense<T>& d, T* Cout, long long ldc, int M,
                int act, const LNState* res = nullptr, float alpha_ = 1.f, float* out_stats = nullptr,
-               int cta_limit = 0, T* C2 = nullptr, long long ldc2 = 0, int n_split = 0) {
+               int cta_limit = 0, T* C2 = nullptr, long long ldc2 = 0, int n_split = 0, bool zero_stats = true) {
     GemmParams p;
     p.cta_limit = cta_limit;
     p.C2 = C2; p.ldc2 = ldc2; p.n_split = n_split;
@@ -988,7 +995,7 @@ struct Net : NetBase {
       }
     }
     if (out_stats) {
-      CK(cudaMemsetAsync(out_stats, 0, (size_t)M * 2 * sizeof(float), st));
+      if (zero_stats) CK(cudaMemsetAsync(out_stats, 0, (size_t)M * 2 * sizeof(float), st));
       p.out_stats = out_stats;
     }
     run_gemm(st, p);
@@ -1055,6 +1062,15 @@ struct Net : NetBase {
     const int R = n * 64;
     const int depth = E / H;
     const T* bias = nullptr;
+    // The statistics this layer accumulates are cleared here, in one memset ahead of all its launches, so that no
+    // memset sits between two products.  The layer input may refer to the other stats2 buffer.
+    float* stats2 = nullptr;
+    if (fold_ln) {
+      const int par = s.stats_parity;
+      s.stats_parity ^= 1;
+      stats2 = s.stats2[par];
+      CK(cudaMemsetAsync(par == 0 ? s.stats2[0] : s.stats1, 0, (s.stats_stride + (size_t)R * 2) * sizeof(float), st));
+    }
     // With side_sms > 0 the small, latency-bound products of smolgen run on a second stream, confined to a few SMs,
     // while the QKV product (which only needs the same layer input) runs on the others.  The per-kernel profiling
     // pass keeps everything on one stream so that each kernel is timed alone.
@@ -1110,11 +1126,11 @@ struct Net : NetBase {
     span_end(st);
     if (fold_ln) {
       LNState att{s.att, nullptr, nullptr, nullptr}, ffn{s.ffn, nullptr, nullptr, nullptr};
-      gemm_ln(st, att, E, e.proj, x1, E, R, ACT_NONE, &in, alpha, s.stats1);      // u1 = alpha * proj + x
+      gemm_ln(st, att, E, e.proj, x1, E, R, ACT_NONE, &in, alpha, s.stats1, 0, nullptr, 0, 0, false);  // u1 = alpha * proj + x
       LNState mid{x1, s.stats1, e.ln1g, e.ln1b};
       gemm_ln(st, mid, E, e.ffn1, s.ffn, e.ffn1.out, R, act_ffn);                  // relu2(LN1(u1) W1 + b1)
-      gemm_ln(st, ffn, e.ffn1.out, e.ffn2, x, E, R, ACT_NONE, &mid, alpha, s.stats2);  // u2 = alpha * ffn + LN1(u1)
-      in = LNState{x, s.stats2, e.ln2g, e.ln2b};
+      gemm_ln(st, ffn, e.ffn1.out, e.ffn2, x, E, R, ACT_NONE, &mid, alpha, stats2, 0, nullptr, 0, 0, false);  // u2 = alpha * ffn + LN1(u1)
+      in = LNState{x, stats2, e.ln2g, e.ln2b};
       return;
     }
     gemm(st, s.att, E, e.proj, s.y, E, R, ACT_NONE);           // :441-445
@@ -1131,6 +1147,7 @@ struct Net : NetBase {
     T* flow = nullptr;  // output of the body, [R][body_ch]
     int body_ch = 0;
     LNState body_in;    // attention bodies: how the heads must read `flow` (folded LayerNorm or materialised)
+    s.stats_parity = 0;
     CK(cudaMemsetAsync(d_qdm, 0, (size_t)n * 3 * sizeof(float), st));
     if (!res.empty() || !attn_body) {  // network_blas.cc:564-601
       other(st, (double)R * 112 * sizeof(T), [&] {
