@@ -1,14 +1,16 @@
 // Tensor-core GEMM for sm_100a: C[M][N] = epilogue(A[M][K] . W[N][K]^T), 16-bit inputs, fp32 accumulation.
 //
-// Structure (one persistent CTA per SM, 192 threads):
-//   warp 0      TMA producer: cp.async.bulk.tensor 2D loads (no multicast) of a 128x64 A tile and a
-//               BNx64 W tile per k-block into a ring of 128B-swizzled shared-memory stages
-//   warp 1      MMA issuer: tcgen05.mma.cta_group::1.kind::f16, 128xBNx16 per instruction, accumulating in
-//               tensor memory (TMEM); two accumulators so the epilogue of tile i overlaps the MMAs of i+1
-//   warps 2..5  epilogue: tcgen05.ld TMEM -> registers, scale + bias + activation (+ alpha * v + skip),
-//               convert and store
-// Synchronisation is by mbarriers (full/empty per stage, full/empty per accumulator).  Every wait is
-// bounded by wall-clock time; a wait that gives up raises a status word and all roles leave the kernel.
+// Structure (one persistent CTA per SM, warp-specialised):
+//   TMA producer   cp.async.bulk.tensor 2D loads (no multicast) of a 128x64 A tile and a BNx64 W tile per k-block
+//                  into a ring of 128B-swizzled shared-memory stages
+//   MMA issuer     tcgen05.mma kind::f16, 128xBNx16 (cta_group::1) or 256xNx16 (cta_group::2) per instruction,
+//                  accumulating in tensor memory (TMEM); two accumulators so the epilogue of tile i overlaps the
+//                  MMAs of tile i+1
+//   epilogue       groups of four warps, one 64-column slab at a time: tcgen05.ld TMEM -> registers, scale, folded
+//                  LayerNorm, bias, activation, residual, row statistics, pack -> swizzled staging buffer
+//   store warp(s)  TMA stores of the staged slabs, hand-back of the staging buffers, prefetch of residual tiles
+// Synchronisation is by mbarriers (full/empty per stage, full/empty per accumulator, full/free per staging
+// buffer).  Every wait is bounded by wall-clock time; a wait that gives up raises a status word and all roles leave the kernel.
 //
 // It computes what the reference obtains from cuBLAS for every dense layer
 // (cublasXgemm call sites, src/neural/backends/cuda/layers.cc:1587-1605) fused with the bias/activation
@@ -101,6 +103,11 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
       : "memory");
+}
+// Brings a tensor map into the descriptor cache ahead of its first use (the first TMA store of a launch otherwise
+// waited about three microseconds for it).
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
@@ -524,6 +531,7 @@ __device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtenso
       const uint32_t s = count[g]++;
       const int idx = g * kBufs + (int)(s % kBufs);
       if (!mbar_wait(smem_u32(&stg_full[idx]), (s / kBufs) & 1, abort_flag, 7)) { ok = false; break; }
+      if (g_lo == 0) TRACE(3100);
       if (p.n_split > 0 && n0 >= p.n_split)
         tma_store_2d(tmap_c2, n0 + c0 - p.n_split, m0, smem_u32(epi_mem + idx * (BM * 128)));
       else
@@ -541,7 +549,9 @@ __device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtenso
       }
     }
   }
+  if (g_lo == 0) TRACE(3101);
   tma_store_wait_all();  // stores must complete before the CTA exits
+  if (g_lo == 0) TRACE(3102);
 }
 
 template <int BN> struct TileCfg {
@@ -578,10 +588,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   float* wvec = reinterpret_cast<float*>(bar_mem + 512) + ((threadIdx.x >> 5) & 7) * 256;  // per-warp scratch
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) TRACE(3000);
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
   const int tiles = m_tiles * n_tiles;
   const int k_blocks = p.conv_cblocks > 0 ? 9 * p.conv_cblocks : (p.K + BK - 1) / BK;
 
+  if (threadIdx.x == 32) {
+    tma_prefetch_map(&tmap_a);
+    tma_prefetch_map(&tmap_w);
+    tma_prefetch_map(&tmap_c);
+    if (p.res_mode) tma_prefetch_map(&tmap_r);
+  }
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
       mbar_init(smem_u32(&full_bar[i]), 1);
@@ -609,6 +626,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) TRACE(3001);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -679,6 +697,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint32_t tile_it = 0, slab_it = 0;
     ColRegs cr;
     int cr_nb = -1;  // first column of the slab whose vectors `cr` holds
+    if ((int)blockIdx.x < tiles && ((int)blockIdx.x % n_tiles) * BN + group * 64 < p.N) {
+      cr_nb = ((int)blockIdx.x % n_tiles) * BN + group * 64;  // first slab: fetched while the first tile is computed
+      load_col_regs(p, cr_nb, lane, cr);
+    }
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
       const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
       const int m0 = (t / n_tiles) * BM, n0 = (t % n_tiles) * BN;
@@ -760,9 +782,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   }
 
+  if (threadIdx.x == 0) TRACE(3002);
   __syncwarp();
   tcgen05_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TRACE(3003);
   if (*abort_flag) {
     // Give copies that may still be in flight time to land before the CTA's shared memory is released.
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
@@ -832,12 +856,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   float* wvec = reinterpret_cast<float*>(bar_mem + 512) + ((threadIdx.x >> 5) & 15) * 256;  // per-warp scratch
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) TRACE(3000);
   const uint32_t rank = cluster_ctarank();
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
   const int m_tiles = (p.M + 2 * BM - 1) / (2 * BM), n_tiles = (p.N + BN - 1) / BN;
   const int tiles = m_tiles * n_tiles;
   const int k_blocks = (p.K + BK - 1) / BK;
 
+  if (threadIdx.x == 64) {
+    tma_prefetch_map(&tmap_a);
+    tma_prefetch_map(&tmap_w);
+    tma_prefetch_map(&tmap_c);
+    if (p.res_mode) tma_prefetch_map(&tmap_r);
+    if (p.n_split > 0) tma_prefetch_map(&tmap_c2);
+  }
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
       mbar_init(smem_u32(&full_bar[i]), 1);
@@ -866,6 +898,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) TRACE(3001);
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
@@ -943,6 +976,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint32_t tile_it = 0, slab_it = 0;
     ColRegs cr;
     int cr_nb = -1;
+    if (pair < tiles && (pair % n_tiles) * BN + group * 64 < p.N) {
+      cr_nb = (pair % n_tiles) * BN + group * 64;  // first slab: fetched while the first tile is computed
+      load_col_regs(p, cr_nb, lane, cr);
+    }
     for (int t = pair; t < tiles; t += pairs, ++tile_it) {
       const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
       const int m0 = (t / n_tiles) * (2 * BM) + (int)rank * BM, n0 = (t % n_tiles) * BN;
@@ -983,9 +1020,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   }
 
+  if (threadIdx.x == 0) TRACE(3002);
   __syncwarp();
   tcgen05_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TRACE(3003);
   if (*abort_flag) {
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, 200 + *abort_flag);
@@ -1132,8 +1171,7 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
   p.out_f32 = g.out_f32 ? 1 : 0; p.status = status;
   p.conv_cblocks = g.conv_cin > 0 ? ceil_div(g.conv_cin, BK) : 0;
   const int tiles = ceil_div(g.M, BM) * ceil_div(g.N, BN);
-  const int ctas = (g.cta_limit > 0 && g.cta_limit < sm_count) ? g.cta_limit : sm_count;
-  const int grid = tiles < ctas ? tiles : ctas;
+  const int grid = tiles < sm_count ? tiles : sm_count;
   gemm_tc_kernel<T, BN><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, p);
   return cudaGetLastError();
 }
@@ -1188,7 +1226,7 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   }
 #endif
   const int tiles = ceil_div(g.M, 2 * BM) * ceil_div(g.N, Cfg::BN);
-  const int max_pairs = ((g.cta_limit > 0 && g.cta_limit < sm_count) ? g.cta_limit : sm_count) / 2;
+  const int max_pairs = sm_count / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   gemm_tc_pair_kernel<T, kGroups><<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, mc2, p);
   return cudaGetLastError();

@@ -37,9 +37,6 @@ struct GemmParams {
   // Per-row (sum, sum of squares) of the outputs, accumulated with atomic adds into out_stats[M][2]
   // (the caller zeroes it), so that the next product can fold the LayerNorm of this output.
   float* out_stats = nullptr;
-  // Upper bound on the CTAs (= SMs) the tensor-core kernel may occupy; 0 = all.  Lets a small product run beside a
-  // large one on another stream.
-  int cta_limit = 0;
   // Second output of the CTA-pair kernel: columns [n_split, N) go to C2 (leading dimension ldc2, column n - n_split)
   // instead of C.  n_split must be a multiple of 256 and the remainder at most 256 columns wide; the last tile is then
   // computed with a narrower MMA.  Lets a narrow product share the operand traffic of a wide one (same A, same folded

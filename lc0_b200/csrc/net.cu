@@ -340,8 +340,8 @@ struct Net : NetBase {
   bool use_tc = false;
   // LayerNorms of the encoder stack folded into the neighbouring tensor-core products (16-bit storage only).
   bool fold_ln = false;
+  bool fold_emb_ln = false;  // the embedding block's last LayerNorm is folded into the first encoder layer
   bool merge_compress = true;  // B200_MERGE_COMPRESS=0: smolgen compression as a launch of its own
-  int side_sms = 0;  // SMs left to the side stream while the QKV product runs (0: everything on one stream)
   bool fold_heads = false;  // the heads' first products fold the last LayerNorm too (else it is materialised)
   int* d_status = nullptr;
 
@@ -378,8 +378,6 @@ struct Net : NetBase {
   struct Slot {
     cudaStream_t stream = nullptr;
     cudaEvent_t compute_done = nullptr;  // recorded after the last kernel of an evaluation, before its result copies
-    cudaStream_t side = nullptr;         // smolgen's small products run here, beside the QKV product
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     uint64_t* d_masks = nullptr;
     float *d_values = nullptr, *d_policy = nullptr, *d_qdm = nullptr;
     unsigned short* d_move_ids = nullptr;
@@ -406,9 +404,6 @@ struct Net : NetBase {
     for (auto& s : slots) {
       if (s.stream) cudaStreamDestroy(s.stream);
       if (s.compute_done) cudaEventDestroy(s.compute_done);
-      if (s.side) cudaStreamDestroy(s.side);
-      if (s.ev_fork) cudaEventDestroy(s.ev_fork);
-      if (s.ev_join) cudaEventDestroy(s.ev_join);
     }
     free_host_sets();
     walloc.release();
@@ -660,7 +655,6 @@ struct Net : NetBase {
                                              std::to_string(prop.major) + std::to_string(prop.minor)};
       CK(gemm_tc_init());
     }
-    if (const char* v = getenv("B200_SIDE_SMS")) side_sms = atoi(v);
     if (const char* v = getenv("B200_MERGE_COMPRESS")) merge_compress = v[0] != '0';
     fold_ln = use_tc && attn_body && !(getenv("B200_FOLD_LN") && getenv("B200_FOLD_LN")[0] == '0');
     // Folding needs every product that consumes or produces a folded LayerNorm to be eligible for the tensor-core
@@ -777,6 +771,11 @@ struct Net : NetBase {
         if (fold_ln && i > 0) {
           g = &need("encoder." + std::to_string(i - 1) + ".ln2_gammas", E);
           bt = &need("encoder." + std::to_string(i - 1) + ".ln2_betas", E);
+        } else if (fold_ln && emb_fmt == EMB_PE_DENSE) {
+          // the LayerNorm that ends the embedding block is folded into the first layer the same way
+          fold_emb_ln = true;
+          g = &need("ip_emb_ffn_ln_gammas", E);
+          bt = &need("ip_emb_ffn_ln_betas", E);
         }
         enc.push_back(load_encoder("encoder." + std::to_string(i), E, H, g, bt));
         max_dff = std::max(max_dff, enc.back().ffn1.out);
@@ -888,9 +887,6 @@ struct Net : NetBase {
       Slot& s = slots[si];
       CK(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
       CK(cudaEventCreateWithFlags(&s.compute_done, cudaEventDisableTiming));
-      CK(cudaStreamCreateWithFlags(&s.side, cudaStreamNonBlocking));
-      CK(cudaEventCreateWithFlags(&s.ev_fork, cudaEventDisableTiming));
-      CK(cudaEventCreateWithFlags(&s.ev_join, cudaEventDisableTiming));
       s.d_masks = (uint64_t*)salloc.alloc(nb * 112 * 8);
       s.d_values = (float*)salloc.alloc(nb * 112 * 4);
       s.d_policy = (float*)salloc.alloc(nb * 1858 * 4);
@@ -957,9 +953,8 @@ struct Net : NetBase {
   // ---- launch helpers ----
   void gemm(cudaStream_t st, const T* A, long long lda, const Dense<T>& d, T* Cout, long long ldc, int M, int act,
             const T* skip = nullptr, long long ldskip = 0, float alpha_ = 1.f, bool out_f32 = false,
-            void* cf32 = nullptr, int cta_limit = 0) {
+            void* cf32 = nullptr) {
     GemmParams p;
-    p.cta_limit = cta_limit;
     p.A = A; p.lda = lda; p.W = d.w; p.ldw = d.in; p.bias = d.b;
     p.C = out_f32 ? cf32 : (void*)Cout; p.ldc = ldc; p.M = M; p.N = d.out; p.K = d.in; p.act = act;
     p.skip = skip; p.ldskip = ldskip; p.alpha = alpha_; p.out_f32 = out_f32;
@@ -977,9 +972,8 @@ struct Net : NetBase {
   // alpha * act(...) + LN(res) and optional accumulation of output row statistics.
   void gemm_ln(cudaStream_t st, const LNState& in, long long lda, const Dense<T>& d, T* Cout, long long ldc, int M,
                int act, const LNState* res = nullptr, float alpha_ = 1.f, float* out_stats = nullptr,
-               int cta_limit = 0, T* C2 = nullptr, long long ldc2 = 0, int n_split = 0, bool zero_stats = true) {
+               T* C2 = nullptr, long long ldc2 = 0, int n_split = 0, bool zero_stats = true) {
     GemmParams p;
-    p.cta_limit = cta_limit;
     p.C2 = C2; p.ldc2 = ldc2; p.n_split = n_split;
     p.A = in.u; p.lda = lda; p.W = d.w; p.ldw = d.in; p.bias = d.b;
     p.C = Cout; p.ldc = ldc; p.M = M; p.N = d.out; p.K = d.in; p.act = act;
@@ -1071,13 +1065,9 @@ struct Net : NetBase {
       stats2 = s.stats2[par];
       CK(cudaMemsetAsync(par == 0 ? s.stats2[0] : s.stats1, 0, (s.stats_stride + (size_t)R * 2) * sizeof(float), st));
     }
-    // With side_sms > 0 the small, latency-bound products of smolgen run on a second stream, confined to a few SMs,
-    // while the QKV product (which only needs the same layer input) runs on the others.  The per-kernel profiling
-    // pass keeps everything on one stream so that each kernel is timed alone.
-    const bool overlap = e.smolgen && side_sms > 0 && !profiling && use_tc && sizeof(T) == 2;
     // One launch for Q, K, V and the smolgen compression when the CTA-pair kernel takes the product.
     bool merged = false;
-    if (e.smolgen && e.qkvc_out && !overlap && merge_compress) {
+    if (e.smolgen && e.qkvc_out && merge_compress) {
       GemmParams probe;
       probe.A = in.u; probe.lda = E; probe.W = e.qkv.w; probe.ldw = E; probe.C = s.qkv; probe.ldc = 3 * E;
       probe.M = R; probe.N = e.qkvc_out; probe.K = E; probe.C2 = s.sg_c; probe.ldc2 = sg_hc; probe.n_split = 3 * E;
@@ -1086,29 +1076,19 @@ struct Net : NetBase {
     if (merged) {
       Dense<T> both = e.qkv;
       both.out = e.qkvc_out;
-      gemm_ln(st, in, E, both, s.qkv, 3 * E, R, ACT_NONE, nullptr, 1.f, nullptr, 0, s.sg_c, sg_hc, 3 * E);
+      gemm_ln(st, in, E, both, s.qkv, 3 * E, R, ACT_NONE, nullptr, 1.f, nullptr, s.sg_c, sg_hc, 3 * E);
+    } else {
+      gemm_ln(st, in, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE);  // :341-350, :408-412
     }
     if (e.smolgen) {  // network_blas.cc:300-339
-      cudaStream_t ss = overlap ? s.side : st;
-      const int lim = overlap ? side_sms : 0;
-      if (overlap) {
-        CK(cudaEventRecord(s.ev_fork, st));
-        CK(cudaStreamWaitEvent(ss, s.ev_fork, 0));
-        gemm_ln(st, in, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE, nullptr, 1.f, nullptr, sm_count - side_sms);
-      }
-      if (!merged) gemm_ln(ss, in, E, e.sg_compress, s.sg_c, sg_hc, R, ACT_NONE, nullptr, 1.f, nullptr, lim);
-      gemm(ss, s.sg_c, 64 * sg_hc, e.sg_d1, s.sg_h1, sg_hid, n, act_smolgen, nullptr, 0, 1.f, false, nullptr, lim);
-      ln(ss, s.sg_h1, s.sg_h1, nullptr, e.sg_ln1g, e.sg_ln1b, n, sg_hid, 1.f, 1e-3f);
-      gemm(ss, s.sg_h1, sg_hid, e.sg_d2, s.sg_h2, sg_gen, n, act_smolgen, nullptr, 0, 1.f, false, nullptr, lim);
-      ln(ss, s.sg_h2, s.sg_h2, nullptr, e.sg_ln2g, e.sg_ln2b, n, sg_gen, 1.f, 1e-3f);
-      if (overlap) {
-        CK(cudaEventRecord(s.ev_join, ss));
-        CK(cudaStreamWaitEvent(st, s.ev_join, 0));
-      }
+      if (!merged) gemm_ln(st, in, E, e.sg_compress, s.sg_c, sg_hc, R, ACT_NONE);
+      gemm(st, s.sg_c, 64 * sg_hc, e.sg_d1, s.sg_h1, sg_hid, n, act_smolgen);
+      ln(st, s.sg_h1, s.sg_h1, nullptr, e.sg_ln1g, e.sg_ln1b, n, sg_hid, 1.f, 1e-3f);
+      gemm(st, s.sg_h1, sg_hid, e.sg_d2, s.sg_h2, sg_gen, n, act_smolgen);
+      ln(st, s.sg_h2, s.sg_h2, nullptr, e.sg_ln2g, e.sg_ln2b, n, sg_gen, 1.f, 1e-3f);
       gemm(st, s.sg_h2, sg_gen / H, smolgen_w, s.sg_bias, 4096, n * H, ACT_NONE);
       bias = s.sg_bias;
     }
-    if (!overlap && !merged) gemm_ln(st, in, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE);  // :341-350, :408-412
     launches++;
     // algorithmic bytes: read Q, K, V (+ bias), write the head outputs
     span_begin(st, K_ATTENTION, (double)R * E * sizeof(T) * 4 + (bias ? (double)n * H * 4096 * sizeof(T) : 0.0));
@@ -1126,10 +1106,10 @@ struct Net : NetBase {
     span_end(st);
     if (fold_ln) {
       LNState att{s.att, nullptr, nullptr, nullptr}, ffn{s.ffn, nullptr, nullptr, nullptr};
-      gemm_ln(st, att, E, e.proj, x1, E, R, ACT_NONE, &in, alpha, s.stats1, 0, nullptr, 0, 0, false);  // u1 = alpha * proj + x
+      gemm_ln(st, att, E, e.proj, x1, E, R, ACT_NONE, &in, alpha, s.stats1, nullptr, 0, 0, false);  // u1 = alpha * proj + x
       LNState mid{x1, s.stats1, e.ln1g, e.ln1b};
       gemm_ln(st, mid, E, e.ffn1, s.ffn, e.ffn1.out, R, act_ffn);                  // relu2(LN1(u1) W1 + b1)
-      gemm_ln(st, ffn, e.ffn1.out, e.ffn2, x, E, R, ACT_NONE, &mid, alpha, stats2, 0, nullptr, 0, 0, false);  // u2 = alpha * ffn + LN1(u1)
+      gemm_ln(st, ffn, e.ffn1.out, e.ffn2, x, E, R, ACT_NONE, &mid, alpha, stats2, nullptr, 0, 0, false);  // u2 = alpha * ffn + LN1(u1)
       in = LNState{x, stats2, e.ln2g, e.ln2b};
       return;
     }
@@ -1186,13 +1166,24 @@ struct Net : NetBase {
       if (emb_fmt == EMB_PE_DENSE) {
         ln(st, x, x, nullptr, emb_lng, emb_lnb, R, E, 1.f, 1e-3f, gate_mult, gate_add);
         gemm(st, x, E, emb_ffn1, s.ffn, emb_dff, R, act_ffn);
-        gemm(st, s.ffn, emb_dff, emb_ffn2, s.y, E, R, ACT_NONE);
-        ln(st, x1, s.y, x, emb_ffn_lng, emb_ffn_lnb, R, E, alpha, 1e-3f);
-        std::swap(x, x1);
-      } else if (gate_mult) {
-        other(st, 2.0 * R * E * sizeof(T), [&] { return launch_gate<T>(x, gate_mult, gate_add, R, E, st); });
+        if (fold_emb_ln) {
+          // u = alpha * ffn2 + x with row statistics; the first layer reads LN(u) through its folded products.  The
+          // statistics live in the stats2 buffer that the first layer does not write.
+          LNState ffn{s.ffn, nullptr, nullptr, nullptr}, skip{x, nullptr, nullptr, nullptr};
+          gemm_ln(st, ffn, emb_dff, emb_ffn2, x1, E, R, ACT_NONE, &skip, alpha, s.stats2[1]);
+          std::swap(x, x1);
+          body_in = LNState{x, s.stats2[1], emb_ffn_lng, emb_ffn_lnb};
+        } else {
+          gemm(st, s.ffn, emb_dff, emb_ffn2, s.y, E, R, ACT_NONE);
+          ln(st, x1, s.y, x, emb_ffn_lng, emb_ffn_lnb, R, E, alpha, 1e-3f);
+          std::swap(x, x1);
+          body_in = LNState{x, nullptr, nullptr, nullptr};
+        }
+      } else {
+        if (gate_mult)
+          other(st, 2.0 * R * E * sizeof(T), [&] { return launch_gate<T>(x, gate_mult, gate_add, R, E, st); });
+        body_in = LNState{x, nullptr, nullptr, nullptr};
       }
-      body_in = LNState{x, nullptr, nullptr, nullptr};
       for (const auto& e : enc) encoder_layer(s, e, n, x, x1, body_in);
       if (body_in.stats && !fold_heads) {  // materialise the last LayerNorm for heads that cannot fold it
         ln(st, x1, x, nullptr, body_in.gamma, body_in.beta, R, E, 1.f, ln_eps);

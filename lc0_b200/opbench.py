@@ -17,7 +17,9 @@ def gemm_shapes(batch):
     return [("qkv", t, 3072, 1024), ("proj", t, 1024, 1024), ("ffn1", t, 1536, 1024), ("ffn2", t, 1024, 1536),
             ("smolgen_compress", t, 32, 1024), ("smolgen_dense1", batch, 256, 2048),
             ("smolgen_dense2", batch, 8192, 256), ("smolgen_global", batch * 32, 4096, 256),
-            ("embedding", t, 1024, 624), ("policy_emb", t, 1024, 1024)]
+            ("embedding", t, 1024, 624), ("policy_emb", t, 1024, 1024),
+            # one tile per CTA and one k-block: what a launch costs besides its work
+            ("fixed_cost", 128, 64, 64), ("fixed_cost_pair", 512, 9728, 64)]
 
 
 def main():

@@ -183,7 +183,8 @@ def test_concurrent_computations_on_two_slots():
     import threading
     net, pos, n, g = load_case("cfg4_mini")
     nw = network.Network(net, "precision=fp16,max_batch=32,slots=2")
-    want = nw.evaluate(pos["masks"][:n], pos["values"][:n])
+    masks, values = np.array(pos["masks"]), np.array(pos["values"])  # the lazy .npz reader is not thread-safe
+    want = nw.evaluate(masks[:n], values[:n])
     errors = []
 
     def worker(offset):
@@ -191,7 +192,7 @@ def test_concurrent_computations_on_two_slots():
             for it in range(12):
                 count = 5 + (it + offset) % 20
                 c = nw.new_computation()
-                c.add_inputs(pos["masks"][:count], pos["values"][:count])
+                c.add_inputs(masks[:count], values[:count])
                 c.compute_blocking()
                 got = np.stack([c.policy(i) for i in range(count)])
                 if np.abs(got - want["policy"][:count]).max() > HALF_ATOL:
