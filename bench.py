@@ -416,7 +416,12 @@ def main():
                     "achieved": achieved, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
                     "frac": achieved / peaks["tflops_sustained"], "peak_source": peaks["source"] + " sustained bf16",
                     "launches": g["launches"], "share_of_step": g["ms"] / total_ms if total_ms else None,
-                    "traffic": None,
+                    # DRAM bytes of the largest launch of the class (QKV + smolgen compression, M = 64 * batch): read
+                    # A once and W once, write C once.  An ncu capture of the same kernel at M = 8192 measured DRAM
+                    # reads equal to A + W (profiles/gemm_tc_kernel_qkv_batch128.md); scaled by the rows processed.
+                    "traffic": (float(B) * 64 * 1024 * 2 + 3104 * 1024 * 2 + float(B) * 64 * 3104 * 2)
+                    if args.config in ("cfg4", "cfg5") else None,
+                    "traffic_of": "the QKV launch (largest of the class), bytes per launch, scaled from an ncu capture",
                     "how": "CUDA-event pairs around every launch during a second pass of the same %d steps "
                            "(%.3f ms per step in that pass)" % (args.steps, prof_ms / args.steps)}
         other = {}
