@@ -156,6 +156,52 @@ int b200_net_device_status(b200_net* net);
 int b200_net_set_profiling(b200_net* net, int enabled);
 int b200_net_get_profile(b200_net* net, double* ms, double* work, long long* launches, int reset);
 
+/* ---- Position encoding on the device ------------------------------------------------------------------------
+ * What lc0 does on the host before AddInput: EncodePositionForNN (src/neural/encoder.cc:134-328) turns the game
+ * history into the 112 packed planes, with ChooseTransform (encoder.cc:50-104) for the canonical formats.  Here the
+ * caller passes the history itself, 88 bytes per position of the history instead of 1344 bytes of planes per evaluated
+ * position, and a kernel produces the planes where the network reads them.
+ *
+ * b200_board is one position of the history as Position::GetBoard() stores it (from the point of view of the side to
+ * move; bit i of a board = square i, a1 = 0, h8 = 63):
+ *   ours .. kings       ChessBoard::ours(), theirs(), pawns(), knights(), bishops(), rooks(), queens(), kings()
+ *   en_passant          ChessBoard::en_passant()
+ *   castling            ChessBoard::Castlings::as_int(): bit 0 we O-O, 1 we O-O-O, 2 they O-O, 3 they O-O-O
+ *   rook_files          our queenside, our kingside, their queenside, their kingside rook file (0 = a)
+ *   flags               bit 0 ChessBoard::flipped() (black to move), bit 1 the board equals ChessBoard::kStartposBoard
+ *   rule50, repetitions Position::GetRule50Ply(), GetRepetitions()
+ * A history is given oldest first with the position to encode last; `from_start` says that its first entry is the
+ * first position of the game history (the encoder may then repeat it to fill missing planes, as fill_empty_history
+ * asks).  A history that does not start there must hold at least 8 entries or, for the two V2 input formats, reach
+ * back to an entry with rule50 == 0; the walk stops at its beginning. */
+typedef struct b200_board {
+  uint64_t ours, theirs, pawns, knights, bishops, rooks, queens, kings, en_passant;
+  uint8_t castling;
+  uint8_t rook_files[4];
+  uint8_t flags;
+  uint16_t rule50;
+  uint8_t repetitions;
+  uint8_t reserved[7];
+} b200_board; /* 88 bytes */
+#define B200_FILL_NO 0        /* FillEmptyHistory::NO (src/neural/encoder.h:42) */
+#define B200_FILL_FEN_ONLY 1
+#define B200_FILL_ALWAYS 2
+/* Stand-alone operator: n positions; the history of position i is boards[offsets[i] .. offsets[i+1]) (offsets has
+ * n + 1 entries), from_start[i] as above.  Writes masks [n][112], values [n][112] and, when not NULL, transforms [n]
+ * (the value EncodePositionForNN returns through transform_out).  All pointers are device pointers. */
+int b200_op_encode_positions(const b200_board* d_boards, const int* d_offsets, const uint8_t* d_from_start, int n,
+                             int input_format, int fill_empty_history, uint64_t* d_masks, float* d_values,
+                             int* d_transforms, void* stream);
+/* Computation-level entry (instead of b200_comp_add_input): adds one position by its history (host memory, at most
+ * B200_MAX_HISTORY entries) and optionally the policy indices of its legal moves (n_moves < 0: none; see
+ * b200_comp_add_input_with_moves).  The planes are produced on the device at b200_comp_compute.  All positions of a
+ * computation must be added the same way.  b200_comp_set_encoding chooses the input format (default: the network's)
+ * and the fill policy (default B200_FILL_FEN_ONLY, lc0's default). */
+#define B200_MAX_HISTORY 128
+int b200_comp_set_encoding(b200_comp* c, int input_format, int fill_empty_history);
+int b200_comp_add_position(b200_comp* c, const b200_board* history, int count, int from_start,
+                           const uint16_t* move_ids, int n_moves);
+
 /* ---- Stand-alone operators (unit-test and profiling surface of the same kernels) --------------
  * All pointers are device pointers on the current device; `stream` is a cudaStream_t or NULL.
  * b200_op_expand_planes: 112 (mask,value) pairs per position -> dense [n][112][64] values of

@@ -4,6 +4,8 @@ There is no fallback: if the shared object is missing or a symbol cannot be
 resolved, importing fails loudly; if no CUDA device is usable, network creation fails.
 """
 import ctypes
+
+import numpy as np
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
@@ -68,6 +70,8 @@ SIGNATURES = {
     "b200_comp_add_inputs_with_moves": (_I, [_P, _P, _P, _P, _P, _I]),
     "b200_comp_set_policy_options": (_I, [_P, _F, _I]),
     "b200_comp_legal_policy": (_I, [_P, _I, ctypes.POINTER(ctypes.POINTER(_F)), ctypes.POINTER(_I)]),
+    "b200_comp_set_encoding": (_I, [_P, _I, _I]),
+    "b200_comp_add_position": (_I, [_P, _P, _I, _I, _P, _I]),
     "b200_net_eval_host": (_I, [_P, _P, _P, _I, _P, _P, _P, _P]),
     "b200_net_eval_device": (_I, [_P, _P, _P, _I, _P, _P]),
     "b200_net_enqueue_device": (_I, [_P, _P, _P, _I, _P, _P]),
@@ -78,11 +82,19 @@ SIGNATURES = {
     "b200_net_set_profiling": (_I, [_P, _I]),
     "b200_net_get_profile": (_I, [_P, _P, _P, _P, _I]),
     "b200_op_expand_planes": (_I, [_P, _P, _I, _P, _I, _P]),
+    "b200_op_encode_positions": (_I, [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P]),
     "b200_op_gemm": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "b200_op_policy_attention": (_I, [_P, _P, _P, _I, _I, _P, _P, _I, _P]),
     "b200_op_policy_attention_static": (_I, [_P, _P, _P, _I, _I, _P, _I, _P]),
     "b200_op_layer_norm": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _P]),
 }
+
+# struct b200_board (include/b200nn.h), 88 bytes
+BOARD_DTYPE = np.dtype([
+    ("ours", "<u8"), ("theirs", "<u8"), ("pawns", "<u8"), ("knights", "<u8"), ("bishops", "<u8"), ("rooks", "<u8"),
+    ("queens", "<u8"), ("kings", "<u8"), ("en_passant", "<u8"), ("castling", "u1"), ("rook_files", "u1", (4,)),
+    ("flags", "u1"), ("rule50", "<u2"), ("repetitions", "u1"), ("reserved", "u1", (7,))])
+FILL_NO, FILL_FEN_ONLY, FILL_ALWAYS = 0, 1, 2
 
 _lib = None
 

@@ -2,6 +2,8 @@
 #pragma once
 #include "common.cuh"
 
+struct b200_board;  // include/b200nn.h
+
 namespace b200 {
 
 struct GemmParams {
@@ -128,6 +130,14 @@ cudaError_t launch_se(const T* x, const float* conv_bias, const T* skip, const f
 template <typename T>
 cudaError_t launch_bias_skip_act(const T* x, const float* bias, const T* skip, T* y, int C, int rows, int act,
                                  cudaStream_t s);
+
+// Position encoding on the device (encoder.cu): game histories -> 112 packed planes per position, the work of the
+// reference's host-side EncodePositionForNN (src/neural/encoder.cc:134-328).  boards/offsets/from_start as in
+// b200_op_encode_positions (include/b200nn.h).
+bool encode_format_supported(int input_format);
+cudaError_t launch_encode_positions(const b200_board* boards, const int* offsets, const uint8_t* from_start, int n,
+                                    int input_format, int fill, uint64_t* masks, float* values, int* transforms,
+                                    cudaStream_t s);
 
 // Host copy of the 1858-entry attention-policy gather table (slot in the 64*64 + 8*24 raw vector per move).
 const short* attn_policy_src_table();

@@ -255,8 +255,31 @@ struct NetBase {
     unsigned short* move_ids = nullptr;
     int* n_moves = nullptr;
     float* probs = nullptr;
+    // device-side position encoding: the histories of the positions (allocated at the first b200_comp_add_position)
+    b200_board* boards = nullptr;
+    int* offsets = nullptr;
+    uint8_t* from_start = nullptr;
     int id = 0;
   };
+  // Board records a computation may stage: an average of kBoardsPerPosition per position of the largest batch.
+  static constexpr int kBoardsPerPosition = 16;
+  size_t board_capacity() const { return (size_t)opt.max_batch * kBoardsPerPosition; }
+  void ensure_board_staging(HostSet& h) {
+    if (h.boards) return;
+    const size_t nb = (size_t)opt.max_batch;
+    if (cudaSetDevice(opt.gpu) != cudaSuccess ||
+        cudaMallocHost(&h.boards, board_capacity() * sizeof(b200_board)) != cudaSuccess ||
+        cudaMallocHost(&h.offsets, (nb + 1) * sizeof(int)) != cudaSuccess ||
+        cudaMallocHost(&h.from_start, nb) != cudaSuccess) {
+      if (h.boards) cudaFreeHost(h.boards);
+      if (h.offsets) cudaFreeHost(h.offsets);
+      h.boards = nullptr;
+      h.offsets = nullptr;
+      cudaGetLastError();
+      throw Fail{B200_ERR_NOMEM, "cannot allocate pinned host staging for position histories"};
+    }
+    h.offsets[0] = 0;
+  }
   std::mutex host_mu;
   std::vector<HostSet*> host_free, host_all;
   HostSet* acquire_host() {
@@ -303,6 +326,9 @@ struct NetBase {
       cudaFreeHost(h->move_ids);
       cudaFreeHost(h->n_moves);
       cudaFreeHost(h->probs);
+      if (h->boards) cudaFreeHost(h->boards);
+      if (h->offsets) cudaFreeHost(h->offsets);
+      if (h->from_start) cudaFreeHost(h->from_start);
       delete h;
     }
     host_all.clear();
@@ -310,7 +336,9 @@ struct NetBase {
   }
   // policy_mode: 0 full 1858-logit policy, 1 full policy + legal-move probabilities, 2 legal-move probabilities
   // only (the 1858-logit vectors stay on the device).
-  virtual int eval_staged(int slot, HostSet& hs, int n, int policy_mode, float inv_temperature) = 0;
+  // enc_format > 0: the planes are produced on the device from hs.boards (n_boards records) in that input format
+  virtual int eval_staged(int slot, HostSet& hs, int n, int policy_mode, float inv_temperature, int enc_format = 0,
+                          int enc_fill = 0, int n_boards = 0) = 0;
   virtual cudaStream_t stream(int slot) = 0;
   virtual int device_status() = 0;
   // slot pool
@@ -383,6 +411,9 @@ struct Net : NetBase {
     unsigned short* d_move_ids = nullptr;
     int* d_n_moves = nullptr;
     float* d_probs = nullptr;
+    b200_board* d_boards = nullptr;  // histories for the device-side position encoding
+    int* d_offsets = nullptr;
+    uint8_t* d_from_start = nullptr;
     T *tokens = nullptr, *pre = nullptr, *pe = nullptr;
     T *x = nullptr, *x1 = nullptr, *y = nullptr, *qkv = nullptr, *att = nullptr, *ffn = nullptr;
     T *sg_c = nullptr, *sg_h1 = nullptr, *sg_h2 = nullptr, *sg_bias = nullptr;
@@ -894,6 +925,9 @@ struct Net : NetBase {
       s.d_move_ids = (unsigned short*)salloc.alloc(nb * kLegalStride * 2);
       s.d_n_moves = (int*)salloc.alloc(nb * 4);
       s.d_probs = (float*)salloc.alloc(nb * kLegalStride * 4);
+      s.d_boards = (b200_board*)salloc.alloc(board_capacity() * sizeof(b200_board));
+      s.d_offsets = (int*)salloc.alloc((nb + 1) * sizeof(int));
+      s.d_from_start = (uint8_t*)salloc.alloc(nb);
       const int body_ch = attn_body ? E : C;
       if (!res.empty() || !attn_body) {
         s.tokens = A(R * 112);
@@ -1265,9 +1299,17 @@ struct Net : NetBase {
   };
   std::vector<std::map<GraphKey, GraphEntry>> graph_cache;  // per slot
 
-  void enqueue_staged(Slot& s, HostSet& hs, int n, int policy_mode, float inv_t) {
-    CK(cudaMemcpyAsync(s.d_masks, hs.masks, (size_t)n * 112 * 8, cudaMemcpyHostToDevice, s.stream));
-    CK(cudaMemcpyAsync(s.d_values, hs.values, (size_t)n * 112 * 4, cudaMemcpyHostToDevice, s.stream));
+  void enqueue_staged(Slot& s, HostSet& hs, int n, int policy_mode, float inv_t, int enc_format, int enc_fill) {
+    if (enc_format > 0) {
+      // the histories were copied ahead of this (their size varies from call to call, a captured copy could not)
+      other(s.stream, (double)n * 112 * 12, [&] {
+        return launch_encode_positions(s.d_boards, s.d_offsets, s.d_from_start, n, enc_format, enc_fill, s.d_masks,
+                                       s.d_values, nullptr, s.stream);
+      });
+    } else {
+      CK(cudaMemcpyAsync(s.d_masks, hs.masks, (size_t)n * 112 * 8, cudaMemcpyHostToDevice, s.stream));
+      CK(cudaMemcpyAsync(s.d_values, hs.values, (size_t)n * 112 * 4, cudaMemcpyHostToDevice, s.stream));
+    }
     if (policy_mode) {
       CK(cudaMemcpyAsync(s.d_move_ids, hs.move_ids, (size_t)n * kLegalStride * 2, cudaMemcpyHostToDevice, s.stream));
       CK(cudaMemcpyAsync(s.d_n_moves, hs.n_moves, (size_t)n * 4, cudaMemcpyHostToDevice, s.stream));
@@ -1360,14 +1402,23 @@ struct Net : NetBase {
     if (sync) CK(cudaStreamSynchronize(s.stream));
     return B200_OK;
   }
-  int eval_staged(int slot, HostSet& hs, int n, int policy_mode, float inv_t) override {
+  int eval_staged(int slot, HostSet& hs, int n, int policy_mode, float inv_t, int enc_format, int enc_fill,
+                  int n_boards) override {
     Slot& s = slots[slot];
+    if (enc_format > 0) {
+      CK(cudaMemcpyAsync(s.d_boards, hs.boards, (size_t)n_boards * sizeof(b200_board), cudaMemcpyHostToDevice, s.stream));
+      CK(cudaMemcpyAsync(s.d_offsets, hs.offsets, (size_t)(n + 1) * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+      CK(cudaMemcpyAsync(s.d_from_start, hs.from_start, (size_t)n, cudaMemcpyHostToDevice, s.stream));
+    }
     // The captured copy nodes embed the host set's addresses and the softmax launch its temperature, so each
     // (host set, policy mode, temperature) gets its own graph; the temperature's bits ride in a pointer field.
     uint32_t tbits;
     memcpy(&tbits, &inv_t, 4);
-    run_or_replay(slot, GraphKey{n, hs.id * 4 + policy_mode, nullptr, nullptr, nullptr, (const void*)(uintptr_t)tbits},
-                  [&] { enqueue_staged(s, hs, n, policy_mode, inv_t); });
+    const int enc_code = enc_format > 0 ? enc_format * 4 + enc_fill : 0;  // below 1024
+    run_or_replay(slot,
+                  GraphKey{n, (hs.id * 4 + policy_mode) * 1024 + enc_code, nullptr, nullptr, nullptr,
+                           (const void*)(uintptr_t)tbits},
+                  [&] { enqueue_staged(s, hs, n, policy_mode, inv_t, enc_format, enc_fill); });
     CK(cudaStreamSynchronize(s.stream));
     return B200_OK;
   }
@@ -1397,6 +1448,11 @@ struct b200_comp {
   bool compact = false;  // return only legal-move probabilities (no 1858-logit vectors)
   float inv_temperature = 1.0f;
   bool computed = false;
+  // device-side position encoding
+  int positions = 0;     // inputs added by their history
+  int n_boards = 0;      // records staged
+  int enc_format = 0;    // 0: the network's input format
+  int enc_fill = B200_FILL_FEN_ONLY;
 };
 
 template <typename F>
@@ -1512,6 +1568,7 @@ int b200_comp_add_inputs(b200_comp* c, const uint64_t* masks, const float* value
     if (c->n + n > c->net->opt.max_batch)
       throw Fail{B200_ERR_INVALID, "computation exceeds max_batch=" + std::to_string(c->net->opt.max_batch)};
     if (n == 0) return (int)B200_OK;
+    if (c->positions) throw Fail{B200_ERR_INVALID, "a computation takes either planes or position histories, not both"};
     if (!c->hs) c->hs = c->net->acquire_host();
     memcpy(c->hs->masks + (size_t)c->n * 112, masks, (size_t)n * 112 * 8);
     memcpy(c->hs->values + (size_t)c->n * 112, values, (size_t)n * 112 * 4);
@@ -1534,7 +1591,12 @@ int b200_comp_compute(b200_comp* c) {
     int rc;
     try {
       const int mode = c->with_moves ? (c->compact ? 2 : 1) : 0;
-      rc = nb->eval_staged(slot, *c->hs, c->n, mode, c->inv_temperature);
+      if (c->positions) {
+        const int fmt = c->enc_format ? c->enc_format : nb->info.input_format;
+        rc = nb->eval_staged(slot, *c->hs, c->n, mode, c->inv_temperature, fmt, c->enc_fill, c->n_boards);
+      } else {
+        rc = nb->eval_staged(slot, *c->hs, c->n, mode, c->inv_temperature);
+      }
     } catch (...) {
       nb->release(slot);
       throw;
@@ -1578,6 +1640,58 @@ int b200_comp_add_inputs_with_moves(b200_comp* c, const uint64_t* masks, const f
     if (rc != B200_OK) return rc;
   }
   return B200_OK;
+}
+int b200_comp_set_encoding(b200_comp* c, int input_format, int fill_empty_history) {
+  if (!c || fill_empty_history < B200_FILL_NO || fill_empty_history > B200_FILL_ALWAYS ||
+      (input_format != 0 && !encode_format_supported(input_format))) {
+    set_error("b200_comp_set_encoding: unsupported input format or fill policy");
+    return B200_ERR_INVALID;
+  }
+  c->enc_format = input_format;
+  c->enc_fill = fill_empty_history;
+  return B200_OK;
+}
+int b200_comp_add_position(b200_comp* c, const b200_board* history, int count, int from_start,
+                           const uint16_t* move_ids, int n_moves) {
+  if (!c || !history || count < 1 || count > B200_MAX_HISTORY || n_moves > kLegalStride || (n_moves > 0 && !move_ids)) {
+    set_error("b200_comp_add_position: bad argument (1..128 history entries, at most 256 legal moves)");
+    return B200_ERR_INVALID;
+  }
+  for (int i = 0; i < n_moves; ++i)
+    if (move_ids[i] >= 1858) {
+      set_error("b200_comp_add_position: policy index out of range");
+      return B200_ERR_INVALID;
+    }
+  return guarded([&] {
+    NetBase* nb = c->net.get();
+    if (c->n != c->positions)
+      throw Fail{B200_ERR_INVALID, "a computation takes either planes or position histories, not both"};
+    if (c->n + 1 > nb->opt.max_batch)
+      throw Fail{B200_ERR_INVALID, "computation exceeds max_batch=" + std::to_string(nb->opt.max_batch)};
+    if (!encode_format_supported(c->enc_format ? c->enc_format : nb->info.input_format))
+      throw Fail{B200_ERR_UNSUPPORTED, "the network's input format has no device-side encoder"};
+    if (!c->hs) c->hs = nb->acquire_host();
+    nb->ensure_board_staging(*c->hs);
+    if ((size_t)c->n_boards + count > nb->board_capacity())
+      throw Fail{B200_ERR_INVALID, "position histories exceed the staging capacity of a computation (" +
+                                       std::to_string(nb->board_capacity()) + " boards); add planes instead"};
+    if (c->n == 0) c->hs->offsets[0] = 0;
+    memcpy(c->hs->boards + c->n_boards, history, (size_t)count * sizeof(b200_board));
+    c->n_boards += count;
+    c->hs->offsets[c->n + 1] = c->n_boards;
+    c->hs->from_start[c->n] = from_start ? 1 : 0;
+    if (n_moves >= 0) {
+      if (c->with_moves != c->n) throw Fail{B200_ERR_INVALID, "either every position of a computation has a move list or none"};
+      if (n_moves > 0) memcpy(c->hs->move_ids + (size_t)c->n * kLegalStride, move_ids, (size_t)n_moves * 2);
+      c->hs->n_moves[c->n] = n_moves;
+      c->with_moves++;
+    } else {
+      c->hs->n_moves[c->n] = 0;
+    }
+    c->n++;
+    c->positions++;
+    return (int)B200_OK;
+  });
 }
 int b200_comp_set_policy_options(b200_comp* c, float inv_temperature, int compact) {
   if (!c || !(inv_temperature > 0.f)) return B200_ERR_INVALID;
@@ -1740,6 +1854,23 @@ int b200_op_gemm(const void* A, const void* W, const float* bias, void* C, int M
   };
   return by_precision(precision, [&] { return run(float()); }, [&] { return run(__half()); },
                       [&] { return run(__nv_bfloat16()); });
+}
+
+int b200_op_encode_positions(const b200_board* d_boards, const int* d_offsets, const uint8_t* d_from_start, int n,
+                             int input_format, int fill_empty_history, uint64_t* d_masks, float* d_values,
+                             int* d_transforms, void* stream) {
+  if (n < 0 || (n > 0 && (!d_boards || !d_offsets || !d_from_start || !d_masks || !d_values)) ||
+      fill_empty_history < B200_FILL_NO || fill_empty_history > B200_FILL_ALWAYS) {
+    set_error("b200_op_encode_positions: bad argument");
+    return B200_ERR_INVALID;
+  }
+  if (!encode_format_supported(input_format)) {
+    set_error("Unsupported input plane encoding " + std::to_string(input_format));  // the reference's message
+    return B200_ERR_UNSUPPORTED;
+  }
+  B200_CUDA(launch_encode_positions(d_boards, d_offsets, d_from_start, n, input_format, fill_empty_history, d_masks,
+                                    d_values, d_transforms, (cudaStream_t)stream));
+  return B200_OK;
 }
 
 int b200_op_policy_attention(const void* q, const void* k, const float* w4, int dm, int n, float* scratch_logits,

@@ -81,6 +81,21 @@ class NetworkComputation:
         _lib.check(self._lib.b200_comp_add_inputs_with_moves(self._h, m.ctypes.data, v.ctypes.data, ids.ctypes.data,
                                                              cnt.ctypes.data, m.shape[0]))
 
+    def set_encoding(self, input_format=0, fill_empty_history=_lib.FILL_FEN_ONLY):
+        """Input format (0: the network's) and FillEmptyHistory policy of the device-side position encoder."""
+        _lib.check(self._lib.b200_comp_set_encoding(self._h, int(input_format), int(fill_empty_history)))
+
+    def add_position(self, history, from_start, move_ids=None):
+        """One position by its game history (records of _lib.BOARD_DTYPE, oldest first, the position itself last)
+        instead of its planes: EncodePositionForNN (src/neural/encoder.cc:134) runs on the device."""
+        h = np.ascontiguousarray(history, _lib.BOARD_DTYPE).reshape(-1)
+        if move_ids is None:
+            _lib.check(self._lib.b200_comp_add_position(self._h, h.ctypes.data, h.size, 1 if from_start else 0, None, -1))
+        else:
+            ids = np.ascontiguousarray(move_ids, np.uint16).reshape(-1)
+            _lib.check(self._lib.b200_comp_add_position(self._h, h.ctypes.data, h.size, 1 if from_start else 0,
+                                                        ids.ctypes.data, ids.size))
+
     def set_policy_options(self, temperature=1.0, compact=False):
         """Policy softmax temperature (the wrapper multiplies by 1/temperature) and compact return."""
         _lib.check(self._lib.b200_comp_set_policy_options(self._h, 1.0 / float(temperature), 1 if compact else 0))

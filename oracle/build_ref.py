@@ -7,6 +7,7 @@ small driver programs in this directory:
   oracle/_ref/ref_eval   run a registered reference backend (blas / eigen) on a
                          weights file + position file and dump raw outputs
   oracle/_ref/mkpos      seeded legal playouts -> packed input planes
+  oracle/_ref/mkenc      seeded game histories + the reference encoder's planes for every input format / fill policy
   oracle/_ref/lc0_ref    the reference's own `lc0` binary (backendbench, check ...)
 
 The recipe mirrors what the reference's meson build does (meson.build:60-124
@@ -140,7 +141,7 @@ def main():
     jobs = []
     for src in COMMON + ["src/main.cc"]:
         jobs.append((os.path.join(ref, src), os.path.join(obj, src.replace("/", "_") + ".o")))
-    for src in ("ref_eval.cc", "mkpos.cc"):
+    for src in ("ref_eval.cc", "mkpos.cc", "mkenc.cc"):
         jobs.append((os.path.join(HERE, src), os.path.join(obj, "oracle_" + src + ".o")))
     adapter_objs = []
     if args.adapter:
@@ -172,6 +173,7 @@ def main():
 
     run(["g++", "-o", os.path.join(OUT, "ref_eval")] + common_objs + adapter_objs + objof("ref_eval.cc") + link)
     run(["g++", "-o", os.path.join(OUT, "mkpos")] + common_objs + objof("mkpos.cc") + link)
+    run(["g++", "-o", os.path.join(OUT, "mkenc")] + common_objs + objof("mkenc.cc") + link)
     run(["g++", "-o", os.path.join(OUT, "lc0_ref")] + common_objs + adapter_objs + objof("src/main.cc") + link)
     if args.cuda:
         build_cuda_reference(ref, obj, flags, common_objs, objof("ref_eval.cc"), link, args.jobs)
