@@ -13,12 +13,15 @@
 // Options (parsed like the reference CUDA backend's, src/neural/backends/cuda/network_cuda.cc:210-254):
 //   gpu=<id>  max_batch=<n> (default 1024)  slots=<n> (concurrent computations, default 2)
 //   policy_head=<name>  value_head=<name>  mlh=<bool>  tensor_cores=<bool>  graph_capture=<bool>
+// "b200-native" only: precision=<fp16|bf16|fp32>  device_encode=<bool> (default true: the game history goes to the
+//   device and EncodePositionForNN's planes are produced there)
 #include <memory>
 #include <string>
 #include <vector>
 
 #include <mutex>
 
+#include "chess/position.h"
 #include "include/b200nn.h"
 #include "neural/backend.h"
 #include "neural/encoder.h"
@@ -268,8 +271,9 @@ FillEmptyHistory ParseHistoryFill(const std::string& s) {
 
 class B200Backend : public Backend {
  public:
-  B200Backend(std::unique_ptr<B200Network> network, const OptionsDict& options)
+  B200Backend(std::unique_ptr<B200Network> network, const OptionsDict& options, bool device_encode)
       : network_(std::move(network)),
+        device_encode_(device_encode),
         backend_opts_(options.Get<std::string>(SharedBackendParams::kBackendOptionsId)),
         weights_path_(options.Get<std::string>(SharedBackendParams::kWeightsId)) {
     UpdateConfiguration(options);
@@ -302,9 +306,35 @@ class B200Backend : public Backend {
   std::unique_ptr<B200Network> network_;
   const std::string backend_opts_;
   const std::string weights_path_;
+  const bool device_encode_;
   float inv_temperature_ = 1.0f;
   FillEmptyHistory history_fill_ = FillEmptyHistory::NO;
 };
+
+// One position of the history in the layout of include/b200nn.h.
+b200_board ToRecord(const Position& p) {
+  const ChessBoard& b = p.GetBoard();
+  b200_board r{};
+  r.ours = b.ours().as_int();
+  r.theirs = b.theirs().as_int();
+  r.pawns = b.pawns().as_int();
+  r.knights = b.knights().as_int();
+  r.bishops = b.bishops().as_int();
+  r.rooks = b.rooks().as_int();
+  r.queens = b.queens().as_int();
+  r.kings = b.kings().as_int();
+  r.en_passant = b.en_passant().as_int();
+  const auto& c = b.castlings();
+  r.castling = c.as_int();
+  r.rook_files[0] = c.our_queenside_rook.idx;
+  r.rook_files[1] = c.our_kingside_rook.idx;
+  r.rook_files[2] = c.their_queenside_rook.idx;
+  r.rook_files[3] = c.their_kingside_rook.idx;
+  r.flags = (b.flipped() ? 1 : 0) | (b == ChessBoard::kStartposBoard ? 2 : 0);
+  r.rule50 = static_cast<uint16_t>(p.GetRule50Ply());
+  r.repetitions = static_cast<uint8_t>(p.GetRepetitions());
+  return r;
+}
 
 class B200BackendComputation : public BackendComputation {
  public:
@@ -315,6 +345,7 @@ class B200BackendComputation : public BackendComputation {
         mlh_(backend->network_->info().has_mlh != 0) {
     Check(b200_comp_create(backend->network_->net(), &comp_));
     Check(b200_comp_set_policy_options(comp_, backend->inv_temperature_, /*compact=*/1));
+    Check(b200_comp_set_encoding(comp_, 0, static_cast<int>(backend->history_fill_)));
     results_.reserve(256);
   }
   ~B200BackendComputation() override { b200_comp_destroy(comp_); }
@@ -322,6 +353,12 @@ class B200BackendComputation : public BackendComputation {
   size_t UsedBatchSize() const override { return results_.size(); }
 
   AddInputResult AddInput(const EvalPosition& pos, EvalResultPtr result) override {
+    uint16_t ids[256];
+    int n_moves = 0;
+    const bool with_policy = !result.p.empty();
+    if (with_policy && (pos.legal_moves.size() > 256 || result.p.size() != pos.legal_moves.size()))
+      throw Exception("b200 backend: bad legal-move list");
+    if (by_history_allowed_ && AddByHistory(pos, result, with_policy, ids)) return ENQUEUED_FOR_EVAL;
     int transform;
     const InputPlanes planes =
         EncodePositionForNN(input_format_, pos.pos, 8, backend_->history_fill_, &transform);
@@ -331,18 +368,53 @@ class B200BackendComputation : public BackendComputation {
       masks[i] = planes[i].mask;
       values[i] = planes[i].value;
     }
-    uint16_t ids[256];
-    int n_moves = 0;
-    if (!result.p.empty()) {
-      if (pos.legal_moves.size() > 256 || result.p.size() != pos.legal_moves.size())
-        throw Exception("b200 backend: bad legal-move list");
+    if (with_policy)
       for (const Move& m : pos.legal_moves) ids[n_moves++] = MoveToNNIndex(m, transform);
-    }
     // The search may add inputs to one computation from several threads (the wrapper uses an atomic vector).
     std::lock_guard<std::mutex> lock(mutex_);
+    if (by_history_) throw Exception("b200 backend: mixed input kinds in one computation");
     Check(b200_comp_add_input_with_moves(comp_, masks, values, ids, n_moves));
     results_.push_back(result);
     return ENQUEUED_FOR_EVAL;
+  }
+
+  // Hands the history to the library instead of the planes.  The transform that maps the legal moves to policy
+  // indices is a few bit operations on the last board and stays on the host (TransformForPosition's rule,
+  // src/neural/encoder.cc:124-132).  Returns false when the history does not fit (the planes are then encoded here).
+  bool AddByHistory(const EvalPosition& pos, EvalResultPtr result, bool with_policy, uint16_t* ids) {
+    const auto& h = pos.pos;
+    // The encoder looks at most 8 positions back (the two V2 formats, which may walk back to the last irreversible
+    // move, keep the host encoder: their histories would not fit the per-computation staging in the worst case).
+    const size_t first = h.size() > 8 ? h.size() - 8 : 0;
+    const size_t count = h.size() - first;
+    if (count > B200_MAX_HISTORY) return false;
+    b200_board records[B200_MAX_HISTORY];
+    for (size_t i = 0; i < count; ++i) records[i] = ToRecord(h[first + i]);
+    int n_moves = -1;
+    if (with_policy) {
+      const int transform = IsCanonicalFormat(input_format_) ? TransformOf(h.back().GetBoard()) : 0;
+      n_moves = 0;
+      for (const Move& m : pos.legal_moves) ids[n_moves++] = MoveToNNIndex(m, transform);
+    }
+    std::lock_guard<std::mutex> lock(mutex_);
+    if (!results_.empty() && !by_history_) return false;
+    const int rc = b200_comp_add_position(comp_, records, static_cast<int>(count), first == 0 ? 1 : 0, ids,
+                                          with_policy ? n_moves : 0);
+    if (rc != B200_OK) {
+      if (results_.empty()) return false;  // e.g. staging capacity: fall back before anything was added this way
+      Check(rc);
+    }
+    by_history_ = true;
+    results_.push_back(result);
+    return true;
+  }
+
+  // ChooseTransform needs a PositionHistory in the reference's public API; EncodePositionForNN on the last position
+  // alone returns the same transform (it only looks at that board).
+  static int TransformOf(const ChessBoard& board) {
+    PositionHistory one;
+    one.Reset(board, 0, 1);
+    return TransformForPosition(pblczero::NetworkFormat::INPUT_112_WITH_CANONICALIZATION, one);
   }
 
   void ComputeBlocking() override {
@@ -369,6 +441,10 @@ class B200BackendComputation : public BackendComputation {
   b200_comp* comp_ = nullptr;
   std::mutex mutex_;
   std::vector<EvalResultPtr> results_;
+  bool by_history_ = false;
+  const bool by_history_allowed_ =
+      backend_->device_encode_ && input_format_ != pblczero::NetworkFormat::INPUT_112_WITH_CANONICALIZATION_V2 &&
+      input_format_ != pblczero::NetworkFormat::INPUT_112_WITH_CANONICALIZATION_V2_ARMAGEDDON;
 };
 
 std::unique_ptr<BackendComputation> B200Backend::CreateComputation() {
@@ -391,9 +467,10 @@ class B200BackendFactory : public BackendFactory {
     else if (prec == "bf16") precision = B200_PREC_BF16;
     else if (prec == "fp32") precision = B200_PREC_FP32;
     else throw Exception("b200 backend: unknown precision '" + prec + "'");
+    const bool device_encode = network_options.GetOrDefault<bool>("device_encode", true);
     auto network = std::make_unique<B200Network>(*weights, network_options, precision);
     network_options.CheckAllOptionsRead("b200-native");
-    return std::make_unique<B200Backend>(std::move(network), options);
+    return std::make_unique<B200Backend>(std::move(network), options, device_encode);
   }
 };
 

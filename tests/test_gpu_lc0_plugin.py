@@ -95,14 +95,17 @@ def _search(exe, npath, backend, opts, nodes=400, positions=3):
 
 @needs_plugin
 def test_native_backend_searches_like_the_wrapped_network(tmp_path):
-    """lc0's own single-threaded search over the native Backend ("b200-native": legal-move softmax on the device,
-    compact return) picks the same moves as over the Network adapter behind lc0's wrapper (host softmax)."""
+    """lc0's own single-threaded search over the native Backend ("b200-native": position encoding and legal-move
+    softmax on the device, compact return) picks the same moves as over the Network adapter behind lc0's wrapper
+    (host encoder, host softmax)."""
     npath = str(tmp_path / "n.pb.gz")
     mknet.write_net("cfg4_mini", npath)
     exe = os.path.join(REF, "lc0_ref")
     wrapped = _search(exe, npath, "b200", "")
-    native = _search(exe, npath, "b200-native", "")
+    native = _search(exe, npath, "b200-native", "")  # game histories go to the device, planes are produced there
     assert native == wrapped
+    host_encoded = _search(exe, npath, "b200-native", "device_encode=false")
+    assert host_encoded == wrapped
     native32 = _search(exe, npath, "b200-native", "precision=fp32")
     wrapped32 = _search(exe, npath, "b200-fp32", "")
     assert native32 == wrapped32
