@@ -202,6 +202,17 @@ int b200_comp_set_encoding(b200_comp* c, int input_format, int fill_empty_histor
 int b200_comp_add_position(b200_comp* c, const b200_board* history, int count, int from_start,
                            const uint16_t* move_ids, int n_moves);
 
+/* ---- Training-data records -> planes -------------------------------------------------------------------------
+ * PlanesFromTrainingData (src/trainingdata/reader.cc:32-118) for n packed V6TrainingData records
+ * (src/trainingdata/trainingdata_v6.h:36-87, 8356 bytes; V7 records start with the same fields) that lie
+ * `record_stride` bytes apart in device memory (4-byte aligned).  Writes masks [n][112] and values [n][112], the
+ * input of b200_net_eval_device / b200_op_expand_planes.  undo_transform = 0 gives the planes as a network is fed
+ * them (what EncodePositionForNN produced when the record was written); 1 takes the canonical formats' board transform
+ * back, which is what the reference function returns to the rescorer.  Records with an input format the reference
+ * rejects get empty planes and are counted in *d_unsupported (device int, may be NULL; the caller zeroes it). */
+int b200_op_planes_from_training_data(const void* d_records, int n, long long record_stride, int undo_transform,
+                                      uint64_t* d_masks, float* d_values, int* d_unsupported, void* stream);
+
 /* ---- Stand-alone operators (unit-test and profiling surface of the same kernels) --------------
  * All pointers are device pointers on the current device; `stream` is a cudaStream_t or NULL.
  * b200_op_expand_planes: 112 (mask,value) pairs per position -> dense [n][112][64] values of

@@ -83,6 +83,7 @@ SIGNATURES = {
     "b200_net_get_profile": (_I, [_P, _P, _P, _P, _I]),
     "b200_op_expand_planes": (_I, [_P, _P, _I, _P, _I, _P]),
     "b200_op_encode_positions": (_I, [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P]),
+    "b200_op_planes_from_training_data": (_I, [_P, _I, ctypes.c_longlong, _I, _P, _P, _P, _P]),
     "b200_op_gemm": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "b200_op_policy_attention": (_I, [_P, _P, _P, _I, _I, _P, _P, _I, _P]),
     "b200_op_policy_attention_static": (_I, [_P, _P, _P, _I, _I, _P, _I, _P]),

@@ -195,7 +195,70 @@ encode_positions_kernel(const b200_board* __restrict__ boards, const int* __rest
   }
 }
 
+// Training-data records -> planes: PlanesFromTrainingData (src/trainingdata/reader.cc:32-118).  One warp per packed
+// V6 record (src/trainingdata/trainingdata_v6.h:36-87), one plane per lane and step.  undo = 0 leaves the planes as
+// a network is fed them (what EncodePositionForNN produced when the record was written), undo = 1 takes the canonical
+// formats' board transform back as the reference function does for the rescorer.
+constexpr int kTdPlanes = 8 + 1858 * 4;        // byte offset of planes[104]
+constexpr int kTdBytes = kTdPlanes + 104 * 8;  // castling x4, side to move / en passant, rule50, invariance info
+
+__global__ void __launch_bounds__(128)
+planes_from_training_data_kernel(const uint8_t* __restrict__ records, int n, long long stride, int undo,
+                                 uint64_t* __restrict__ masks, float* __restrict__ values,
+                                 int* __restrict__ unsupported) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rec = blockIdx.x * 4 + warp;
+  if (rec >= n) return;
+  const uint8_t* r = records + (long long)rec * stride;
+  const int fmt = (int)*reinterpret_cast<const uint32_t*>(r + 4);  // records are 4-byte aligned (8356 = 4 * 2089)
+  const bool known = (fmt >= 1 && fmt <= 5) || fmt == 132 || fmt == 133;
+  if (!known && lane == 0 && unsupported) atomicAdd(unsupported, 1);
+  const uint64_t us_ooo = r[kTdBytes + 0], us_oo = r[kTdBytes + 1], them_ooo = r[kTdBytes + 2], them_oo = r[kTdBytes + 3];
+  const uint64_t stm_ep = r[kTdBytes + 4];
+  const int rule50 = r[kTdBytes + 5], inv = r[kTdBytes + 6];
+  for (int i = lane; i < 112; i += 32) {
+    uint64_t m = 0;
+    float v = 1.0f;
+    if (known) {
+      if (i < 104) {
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(r + kTdPlanes + i * 8);
+        m = reverse_bits_in_bytes((uint64_t)p[0] | ((uint64_t)p[1] << 32));
+      } else if (fmt == 1) {
+        if (i == 104) m = us_ooo ? kAll : 0;
+        else if (i == 105) m = us_oo ? kAll : 0;
+        else if (i == 106) m = them_ooo ? kAll : 0;
+        else if (i == 107) m = them_oo ? kAll : 0;
+      } else {
+        if (i == 104) m = us_ooo | (them_ooo << 56);
+        else if (i == 105) m = us_oo | (them_oo << 56);
+      }
+      if (i == 108) m = is_canonical(fmt) ? stm_ep << 56 : (stm_ep ? kAll : 0);
+      if (i == 109) {
+        m = kAll;
+        v = is_hectoplies(fmt) ? (float)rule50 / 100.0f : (float)rule50;
+      }
+      if (i == 110) m = (is_armageddon(fmt) && inv >= 128) ? kAll : 0;
+      if (i == 111) m = kAll;
+      if (undo && is_canonical(fmt) && inv != 0 && m != 0 && m != kAll) {
+        if (inv & 4) m = transpose_bits_in_bytes(m);
+        if (inv & 2) m = reverse_bytes_in_bytes(m);
+        if (inv & 1) m = reverse_bits_in_bytes(m);
+      }
+    }
+    masks[(long long)rec * 112 + i] = m;
+    values[(long long)rec * 112 + i] = v;
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_planes_from_training_data(const void* records, int n, long long stride, int undo, uint64_t* masks,
+                                             float* values, int* unsupported, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  planes_from_training_data_kernel<<<ceil_div(n, 4), 128, 0, s>>>(static_cast<const uint8_t*>(records), n, stride,
+                                                                   undo, masks, values, unsupported);
+  return cudaGetLastError();
+}
 
 bool encode_format_supported(int input_format) {
   return (input_format >= 1 && input_format <= 5) || input_format == 132 || input_format == 133;

@@ -139,6 +139,10 @@ cudaError_t launch_encode_positions(const b200_board* boards, const int* offsets
                                     int input_format, int fill, uint64_t* masks, float* values, int* transforms,
                                     cudaStream_t s);
 
+// Packed V6 training-data records -> 112 packed planes each (PlanesFromTrainingData, src/trainingdata/reader.cc:32-118).
+cudaError_t launch_planes_from_training_data(const void* records, int n, long long stride, int undo, uint64_t* masks,
+                                             float* values, int* unsupported, cudaStream_t s);
+
 // Host copy of the 1858-entry attention-policy gather table (slot in the 64*64 + 8*24 raw vector per move).
 const short* attn_policy_src_table();
 

@@ -1873,6 +1873,18 @@ int b200_op_encode_positions(const b200_board* d_boards, const int* d_offsets, c
   return B200_OK;
 }
 
+int b200_op_planes_from_training_data(const void* d_records, int n, long long record_stride, int undo_transform,
+                                      uint64_t* d_masks, float* d_values, int* d_unsupported, void* stream) {
+  if (n < 0 || (n > 0 && (!d_records || !d_masks || !d_values)) || record_stride < 8280 || (record_stride & 3) ||
+      (reinterpret_cast<uintptr_t>(d_records) & 3)) {
+    set_error("b200_op_planes_from_training_data: bad argument (records of at least 8280 bytes, 4-byte aligned)");
+    return B200_ERR_INVALID;
+  }
+  B200_CUDA(launch_planes_from_training_data(d_records, n, record_stride, undo_transform != 0, d_masks, d_values,
+                                             d_unsupported, (cudaStream_t)stream));
+  return B200_OK;
+}
+
 int b200_op_policy_attention(const void* q, const void* k, const float* w4, int dm, int n, float* scratch_logits,
                              float* policy, int precision, void* stream) {
   if (n < 0 || dm <= 0 || (n > 0 && (!q || !k || !w4 || !scratch_logits || !policy))) {

@@ -7,6 +7,7 @@ small driver programs in this directory:
   oracle/_ref/ref_eval   run a registered reference backend (blas / eigen) on a
                          weights file + position file and dump raw outputs
   oracle/_ref/mkpos      seeded legal playouts -> packed input planes
+  oracle/_ref/mktd       V6 training-data records for seeded histories + the planes the reference reads back from them
   oracle/_ref/mkenc      seeded game histories + the reference encoder's planes for every input format / fill policy
   oracle/_ref/lc0_ref    the reference's own `lc0` binary (backendbench, check ...)
 
@@ -141,7 +142,7 @@ def main():
     jobs = []
     for src in COMMON + ["src/main.cc"]:
         jobs.append((os.path.join(ref, src), os.path.join(obj, src.replace("/", "_") + ".o")))
-    for src in ("ref_eval.cc", "mkpos.cc", "mkenc.cc"):
+    for src in ("ref_eval.cc", "mkpos.cc", "mkenc.cc", "mktd.cc"):
         jobs.append((os.path.join(HERE, src), os.path.join(obj, "oracle_" + src + ".o")))
     adapter_objs = []
     if args.adapter:
@@ -174,6 +175,7 @@ def main():
     run(["g++", "-o", os.path.join(OUT, "ref_eval")] + common_objs + adapter_objs + objof("ref_eval.cc") + link)
     run(["g++", "-o", os.path.join(OUT, "mkpos")] + common_objs + objof("mkpos.cc") + link)
     run(["g++", "-o", os.path.join(OUT, "mkenc")] + common_objs + objof("mkenc.cc") + link)
+    run(["g++", "-o", os.path.join(OUT, "mktd")] + common_objs + objof("mktd.cc") + link)
     run(["g++", "-o", os.path.join(OUT, "lc0_ref")] + common_objs + adapter_objs + objof("src/main.cc") + link)
     if args.cuda:
         build_cuda_reference(ref, obj, flags, common_objs, objof("ref_eval.cc"), link, args.jobs)
