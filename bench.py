@@ -385,6 +385,42 @@ def main():
     tcs = sharding.gather_max(run_pipelined(step_compact, args.steps), dist if world > 1 else None)
     compact_value = world * B * args.steps / tcs
 
+    # ---- the same with game histories as input: position encoding (EncodePositionForNN) and legal-move softmax on the
+    # device; 88 bytes per history entry go up instead of 1344 bytes of planes per position ----
+    enc_value = None
+    enc_h2d = 0
+    enc_path = os.path.join(ROOT, "tests", "golden", "encoder_golden.npz")
+    if os.path.exists(enc_path) and info.input_format in (1, 2, 3, 4, 132):
+        eg = np.load(enc_path)
+        offs = eg["offsets"]
+        # the last (at most 8) entries of each fixture history, tiled to the batch
+        hists = []
+        for s_ in range(len(eg["from_start"])):
+            a, b = int(offs[s_]), int(offs[s_ + 1])
+            first = max(a, b - 8)
+            hists.append((np.ascontiguousarray(eg["boards"][first:b]), bool(eg["from_start"][s_]) and first == a))
+        order = [(i + 17 * rank) % len(hists) for i in range(B)]
+        h_boards = np.concatenate([hists[i][0] for i in order])
+        h_offsets = np.concatenate([[0], np.cumsum([len(hists[i][0]) for i in order])]).astype(np.int32)
+        h_from_start = np.array([hists[i][1] for i in order], np.uint8)
+        enc_h2d = int(len(h_boards) * 88 + B * (256 * 2 + 4 + 4 + 1))
+
+        def step_history():
+            c = nw.new_computation()
+            c.set_policy_options(1.0, compact=True)
+            c.add_positions(h_boards, h_offsets, h_from_start, legal, n_legal)
+            c.compute_blocking()
+            q = c.get_q_val(0)
+            c.close()
+            return q
+
+        for _ in range(2):
+            step_history()
+        barrier()
+        tenc = sharding.gather_max(run_pipelined(step_history, max(2, args.steps // 2)),
+                                   dist if world > 1 else None)
+        enc_value = world * B * max(2, args.steps // 2) / tenc
+
     # ---- latency of one batch-256 computation through the same API (p50 / p99 over 40 calls) ----
     lat = None
     if B >= 256:
@@ -453,6 +489,11 @@ def main():
                                    "d2h_bytes_per_step": int(B * (256 * 4 + 12)),
                                    "what": "legal-move policy softmax on the device, only per-move probabilities "
                                            "returned; two computations in flight"},
+            "e2e_history_input": None if enc_value is None else {
+                "value": enc_value, "unit": UNIT, "h2d_bytes_per_step": enc_h2d,
+                "d2h_bytes_per_step": int(B * (256 * 4 + 12)),
+                "what": "positions given as game histories (last 8 boards), planes and legal-move softmax produced on "
+                        "the device; two computations in flight"},
             "gpu_launches": int(launches),
             "roofline": roofline,
             "kernel_classes": other,

@@ -201,6 +201,10 @@ int b200_op_encode_positions(const b200_board* d_boards, const int* d_offsets, c
 int b200_comp_set_encoding(b200_comp* c, int input_format, int fill_empty_history);
 int b200_comp_add_position(b200_comp* c, const b200_board* history, int count, int from_start,
                            const uint16_t* move_ids, int n_moves);
+/* n positions at once: histories concatenated in `boards` with n + 1 `offsets` (as in b200_op_encode_positions, host
+ * memory), from_start [n]; move_ids [n][256] (rows padded) and n_moves [n], or both NULL for no move lists. */
+int b200_comp_add_positions(b200_comp* c, const b200_board* boards, const int* offsets, const uint8_t* from_start,
+                            const uint16_t* move_ids, const int* n_moves, int n);
 
 /* ---- Training-data records -> planes -------------------------------------------------------------------------
  * PlanesFromTrainingData (src/trainingdata/reader.cc:32-118) for n packed V6TrainingData records

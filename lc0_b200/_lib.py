@@ -72,6 +72,7 @@ SIGNATURES = {
     "b200_comp_legal_policy": (_I, [_P, _I, ctypes.POINTER(ctypes.POINTER(_F)), ctypes.POINTER(_I)]),
     "b200_comp_set_encoding": (_I, [_P, _I, _I]),
     "b200_comp_add_position": (_I, [_P, _P, _I, _I, _P, _I]),
+    "b200_comp_add_positions": (_I, [_P, _P, _P, _P, _P, _P, _I]),
     "b200_net_eval_host": (_I, [_P, _P, _P, _I, _P, _P, _P, _P]),
     "b200_net_eval_device": (_I, [_P, _P, _P, _I, _P, _P]),
     "b200_net_enqueue_device": (_I, [_P, _P, _P, _I, _P, _P]),

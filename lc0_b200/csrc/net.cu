@@ -1693,6 +1693,20 @@ int b200_comp_add_position(b200_comp* c, const b200_board* history, int count, i
     return (int)B200_OK;
   });
 }
+int b200_comp_add_positions(b200_comp* c, const b200_board* boards, const int* offsets, const uint8_t* from_start,
+                            const uint16_t* move_ids, const int* n_moves, int n) {
+  if (!c || n < 0 || (n > 0 && (!boards || !offsets || !from_start)) || ((move_ids == nullptr) != (n_moves == nullptr))) {
+    set_error("b200_comp_add_positions: bad argument");
+    return B200_ERR_INVALID;
+  }
+  for (int i = 0; i < n; ++i) {
+    const int rc = b200_comp_add_position(c, boards + offsets[i], offsets[i + 1] - offsets[i], from_start[i],
+                                          move_ids ? move_ids + (size_t)i * kLegalStride : nullptr,
+                                          n_moves ? n_moves[i] : -1);
+    if (rc != B200_OK) return rc;
+  }
+  return B200_OK;
+}
 int b200_comp_set_policy_options(b200_comp* c, float inv_temperature, int compact) {
   if (!c || !(inv_temperature > 0.f)) return B200_ERR_INVALID;
   c->inv_temperature = inv_temperature;

@@ -96,6 +96,22 @@ class NetworkComputation:
             _lib.check(self._lib.b200_comp_add_position(self._h, h.ctypes.data, h.size, 1 if from_start else 0,
                                                         ids.ctypes.data, ids.size))
 
+    def add_positions(self, boards, offsets, from_start, move_ids=None, n_moves=None):
+        """Batch form of add_position: concatenated histories with n + 1 offsets; move_ids [n][256], n_moves [n]."""
+        b = np.ascontiguousarray(boards, _lib.BOARD_DTYPE).reshape(-1)
+        o = np.ascontiguousarray(offsets, np.int32).reshape(-1)
+        f = np.ascontiguousarray(from_start, np.uint8).reshape(-1)
+        n = f.size
+        if o.size != n + 1:
+            raise ValueError("offsets must have one entry more than from_start")
+        if move_ids is None:
+            _lib.check(self._lib.b200_comp_add_positions(self._h, b.ctypes.data, o.ctypes.data, f.ctypes.data, None, None, n))
+        else:
+            ids = np.ascontiguousarray(move_ids, np.uint16).reshape(n, 256)
+            cnt = np.ascontiguousarray(n_moves, np.int32).reshape(n)
+            _lib.check(self._lib.b200_comp_add_positions(self._h, b.ctypes.data, o.ctypes.data, f.ctypes.data,
+                                                         ids.ctypes.data, cnt.ctypes.data, n))
+
     def set_policy_options(self, temperature=1.0, compact=False):
         """Policy softmax temperature (the wrapper multiplies by 1/temperature) and compact return."""
         _lib.check(self._lib.b200_comp_set_policy_options(self._h, 1.0 / float(temperature), 1 if compact else 0))

@@ -108,6 +108,13 @@ def test_positions_added_by_history_evaluate_like_their_planes(golden):
             assert np.array_equal(p.legal_policy(s), q.legal_policy(s))
         p.close()
         q.close()
+    # batch form
+    r = nw.new_computation()
+    r.add_positions(golden["boards"][:offsets[count]], offsets[:count + 1], golden["from_start"][:count])
+    r.compute_blocking()
+    for s in range(count):
+        assert np.array_equal(a.policy(s), r.policy(s))
+    r.close()
     # mixing the two ways of adding inputs is an error
     with pytest.raises(_lib.B200Error):
         b.add_inputs(golden["masks"][:1, c_fmt], golden["values"][:1, c_fmt])
