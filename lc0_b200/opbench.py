@@ -2,6 +2,7 @@
 stand-alone operator entry points, on the matrix shapes of the BT4-class network.
 
     python -m lc0_b200.opbench gemm [--batch 1024] [--precision fp16] [--reps 5] [--only NAME]
+    python -m lc0_b200.opbench encode [--batch 65536] [--reps 5]     (device-side position encoder)
 
 Prints one line per shape with the CUDA-event time and achieved TFLOP/s.  Small enough to run under
 `ncu -k regex:gemm_tc --set full` (use --batch 64..256 and --reps 1 for a capture).
@@ -22,9 +23,46 @@ def gemm_shapes(batch):
             ("fixed_cost", 128, 64, 64), ("fixed_cost_pair", 512, 9728, 64)]
 
 
+def encode_bench(lib, args):
+    """Times b200_op_encode_positions on the fixture histories of tests/golden/encoder_golden.npz tiled to --batch
+    positions (last 8 boards each), input format 2, fill policy FEN_ONLY."""
+    import os
+    import torch
+    from . import _lib
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    g = np.load(os.path.join(root, "tests", "golden", "encoder_golden.npz"))
+    offs = g["offsets"]
+    hists = [g["boards"][max(int(offs[i]), int(offs[i + 1]) - 8):int(offs[i + 1])] for i in range(len(offs) - 1)]
+    fs = [bool(g["from_start"][i]) and int(offs[i + 1]) - int(offs[i]) <= 8 for i in range(len(offs) - 1)]
+    n = args.batch
+    order = [i % len(hists) for i in range(n)]
+    boards = np.concatenate([hists[i] for i in order])
+    offsets = np.concatenate([[0], np.cumsum([len(hists[i]) for i in order])]).astype(np.int32)
+    d_boards = torch.from_numpy(boards.view(np.uint8).reshape(-1, 88).copy()).cuda()
+    d_offsets = torch.from_numpy(offsets).cuda()
+    d_fs = torch.from_numpy(np.array([fs[i] for i in order], np.uint8)).cuda()
+    masks = torch.zeros(n, 112, dtype=torch.int64, device="cuda")
+    values = torch.zeros(n, 112, dtype=torch.float32, device="cuda")
+    times = []
+    for r in range(args.reps + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        _lib.check(lib.b200_op_encode_positions(d_boards.data_ptr(), d_offsets.data_ptr(), d_fs.data_ptr(), n, 2, 1,
+                                                masks.data_ptr(), values.data_ptr(), None, None))
+        e1.record()
+        torch.cuda.synchronize()
+        if r > 0 or args.reps == 0:
+            times.append(e0.elapsed_time(e1))
+    ms = float(np.median(times))
+    nbytes = boards.nbytes + offsets.nbytes + n + n * 112 * 12
+    print("encode_positions   n=%-7d boards=%-8d %8.3f ms  %8.1f GB/s (%d bytes read + written)  %.1f M positions/s"
+          % (n, len(boards), ms, nbytes / ms / 1e6, nbytes, n / ms / 1e3), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm"])
+    ap.add_argument("what", choices=["gemm", "encode"])
     ap.add_argument("--batch", type=int, default=1024)
     ap.add_argument("--precision", default="fp16")
     ap.add_argument("--reps", type=int, default=5)
@@ -36,6 +74,8 @@ def main():
     lib = _lib.load()
     prec = _lib.PRECISIONS[args.precision]
     dt = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}[prec]
+    if args.what == "encode":
+        return encode_bench(lib, args)
     for name, M, N, K in gemm_shapes(args.batch):
         if args.only and args.only != name:
             continue
