@@ -156,6 +156,20 @@ int b200_net_device_status(b200_net* net);
 int b200_net_set_profiling(b200_net* net, int enabled);
 int b200_net_get_profile(b200_net* net, double* ms, double* work, long long* launches, int reset);
 
+/* ---- Batch aggregation across caller threads ------------------------------------------------------------------
+ * Many threads with a few positions each, one GPU batch: the role of the reference's `multiplexing` decorator
+ * (MuxingNetwork::Worker, src/neural/backends/network_mux.cc:169-205).  b200_mux_eval blocks until its positions
+ * have been evaluated together with whatever other callers queued meanwhile; two worker threads alternate, a worker
+ * that finds fewer than max_batch positions queued waits up to wait_us microseconds for more.  Outputs as in
+ * b200_net_eval_host (any may be NULL).  The network must outlive the aggregator; destroying the aggregator fails the
+ * requests still queued. */
+typedef struct b200_mux b200_mux;
+int b200_mux_create(b200_net* net, int max_batch, int wait_us, b200_mux** out);
+int b200_mux_eval(b200_mux* mux, const uint64_t* masks, const float* values, int n, float* policy, float* q, float* d,
+                  float* m);
+int b200_mux_stats(b200_mux* mux, long long* requests, long long* batches, long long* positions);
+void b200_mux_destroy(b200_mux* mux);
+
 /* ---- Position encoding on the device ------------------------------------------------------------------------
  * What lc0 does on the host before AddInput: EncodePositionForNN (src/neural/encoder.cc:134-328) turns the game
  * history into the 112 packed planes, with ChooseTransform (encoder.cc:50-104) for the canonical formats.  Here the

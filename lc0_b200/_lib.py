@@ -73,6 +73,11 @@ SIGNATURES = {
     "b200_comp_set_encoding": (_I, [_P, _I, _I]),
     "b200_comp_add_position": (_I, [_P, _P, _I, _I, _P, _I]),
     "b200_comp_add_positions": (_I, [_P, _P, _P, _P, _P, _P, _I]),
+    "b200_mux_create": (_I, [_P, _I, _I, ctypes.POINTER(_P)]),
+    "b200_mux_eval": (_I, [_P, _P, _P, _I, _P, _P, _P, _P]),
+    "b200_mux_stats": (_I, [_P, ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong),
+                            ctypes.POINTER(ctypes.c_longlong)]),
+    "b200_mux_destroy": (None, [_P]),
     "b200_net_eval_host": (_I, [_P, _P, _P, _I, _P, _P, _P, _P]),
     "b200_net_eval_device": (_I, [_P, _P, _P, _I, _P, _P]),
     "b200_net_enqueue_device": (_I, [_P, _P, _P, _I, _P, _P]),

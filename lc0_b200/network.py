@@ -244,6 +244,10 @@ class Network:
                                                 out["d"].ctypes.data, out["m"].ctypes.data))
         return out
 
+    def new_mux(self, max_batch=None, wait_us=200):
+        """Batch aggregator over this network: see Mux."""
+        return Mux(self, max_batch or self.info.max_batch, wait_us)
+
     def enqueue_device(self, d_masks, d_values, n, d_policy, d_qdm):
         _lib.check(self._lib.b200_net_enqueue_device(self._handle, d_masks, d_values, n, d_policy, d_qdm))
 
@@ -293,3 +297,41 @@ def create_network(weights_path_or_net, options=None):
     if not isinstance(net, dict):
         net = netproto.load_net(net)
     return Network(net, options)
+
+
+class Mux:
+    """Many caller threads, one GPU batch: blocking `evaluate` calls from different threads are merged (the role of
+    lc0's `multiplexing` backend, src/neural/backends/network_mux.cc:169-205)."""
+
+    def __init__(self, network, max_batch, wait_us):
+        self._lib = _lib.load()
+        self._network = network  # keeps the network alive
+        h = ctypes.c_void_p()
+        _lib.check(self._lib.b200_mux_create(network._handle, int(max_batch), int(wait_us), ctypes.byref(h)))
+        self._h = h
+
+    def evaluate(self, masks, values):
+        m = np.ascontiguousarray(masks, np.uint64).reshape(-1, 112)
+        v = np.ascontiguousarray(values, np.float32).reshape(-1, 112)
+        n = m.shape[0]
+        out = dict(policy=np.empty((n, 1858), np.float32), q=np.empty(n, np.float32),
+                   d=np.empty(n, np.float32), m=np.empty(n, np.float32))
+        _lib.check(self._lib.b200_mux_eval(self._h, m.ctypes.data, v.ctypes.data, n, out["policy"].ctypes.data,
+                                           out["q"].ctypes.data, out["d"].ctypes.data, out["m"].ctypes.data))
+        return out
+
+    def stats(self):
+        r, b, p = ctypes.c_longlong(), ctypes.c_longlong(), ctypes.c_longlong()
+        _lib.check(self._lib.b200_mux_stats(self._h, ctypes.byref(r), ctypes.byref(b), ctypes.byref(p)))
+        return dict(requests=r.value, batches=b.value, positions=p.value)
+
+    def close(self):
+        if self._h:
+            self._lib.b200_mux_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass

@@ -3,6 +3,7 @@ stand-alone operator entry points, on the matrix shapes of the BT4-class network
 
     python -m lc0_b200.opbench gemm [--batch 1024] [--precision fp16] [--reps 5] [--only NAME]
     python -m lc0_b200.opbench encode [--batch 65536] [--reps 5]     (device-side position encoder)
+    python -m lc0_b200.opbench mux [--threads 64] [--request 16] [--config cfg4]   (batch aggregation across threads)
 
 Prints one line per shape with the CUDA-event time and achieved TFLOP/s.  Small enough to run under
 `ncu -k regex:gemm_tc --set full` (use --batch 64..256 and --reps 1 for a capture).
@@ -60,9 +61,51 @@ def encode_bench(lib, args):
     return 0
 
 
+def mux_bench(args):
+    """Caller threads with small requests, through the aggregator and straight to the network."""
+    import threading
+    import time
+    from . import mknet, network
+    net = mknet.make_net(args.config)
+    nw = network.Network(net, dict(max_batch=1024, precision=args.precision, slots=2))
+    rng = np.random.default_rng(0)
+    masks = rng.integers(0, 2 ** 62, size=(args.request, 112), dtype=np.int64).astype(np.uint64)
+    values = np.ones((args.request, 112), np.float32)
+    per_thread = 24
+
+    def run(fn):
+        def worker():
+            for _ in range(per_thread):
+                fn(masks, values)
+        ths = [threading.Thread(target=worker) for _ in range(args.threads)]
+        t0 = time.time()
+        for t in ths:
+            t.start()
+        for t in ths:
+            t.join()
+        return args.threads * per_thread * args.request / (time.time() - t0)
+
+    mux = nw.new_mux(max_batch=1024, wait_us=300)
+    run(mux.evaluate)  # warm-up (graphs of the batch sizes that occur)
+    before = mux.stats()
+    merged = run(mux.evaluate)
+    st = mux.stats()
+    launches = st["batches"] - before["batches"]
+    print("mux: %d threads x %d-position requests: %.0f evals/s, %.0f positions per launch"
+          % (args.threads, args.request, merged, (st["positions"] - before["positions"]) / max(1, launches)), flush=True)
+    mux.close()
+    direct = run(nw.evaluate)
+    print("direct: the same requests one computation each: %.0f evals/s" % direct, flush=True)
+    nw.close()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "encode"])
+    ap.add_argument("what", choices=["gemm", "encode", "mux"])
+    ap.add_argument("--threads", type=int, default=64)
+    ap.add_argument("--request", type=int, default=16, help="positions per request (mux)")
+    ap.add_argument("--config", default="cfg4")
     ap.add_argument("--batch", type=int, default=1024)
     ap.add_argument("--precision", default="fp16")
     ap.add_argument("--reps", type=int, default=5)
@@ -76,6 +119,8 @@ def main():
     dt = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}[prec]
     if args.what == "encode":
         return encode_bench(lib, args)
+    if args.what == "mux":
+        return mux_bench(args)
     for name, M, N, K in gemm_shapes(args.batch):
         if args.only and args.only != name:
             continue
