@@ -106,7 +106,8 @@ def build_cuda_reference(ref, obj, flags, common_objs, main_objs, link, jobs):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get(
+        "LC0_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference")), help="root of the lc0 source tree")
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 4)
     ap.add_argument("--opt", default="-O2")
     ap.add_argument("--cuda", action="store_true",

@@ -7,7 +7,8 @@ import pytest
 
 from oracle import tables
 
-REF = "/root/reference/src/neural"
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(os.environ.get("LC0_REFERENCE", os.path.join(os.path.dirname(_ROOT), "reference")), "src", "neural")
 
 
 def test_table_shapes_and_bijection():
