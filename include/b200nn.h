@@ -244,6 +244,18 @@ int b200_op_expand_planes(const void* d_masks, const void* d_values, int n, void
                           int precision, void* stream);
 int b200_op_gemm(const void* A, const void* W, const float* bias, void* C, int M, int N, int K,
                  int activation, int precision, int use_tc, void* stream);
+/* b200_op_attention: out = softmax(Q K^T / sqrt(depth) + bias) V for every (position, head) of n positions of 64
+ *   tokens (BlasComputation::ForwardEncoderLayer, network_blas.cc:352-439).  q, k, v: [n*64] rows with leading
+ *   dimension ld (elements), head h in columns [h*depth, (h+1)*depth); bias: [n][heads][64][64] or NULL; out:
+ *   [n*64] rows with leading dimension ldo.  variant 0: FMA kernel (any precision); 1: cp.async + mma.sync kernel;
+ *   2: persistent TMA kernel (the one the network uses).  1 and 2 take fp16 / bf16 and depth 32 or 64. */
+int b200_op_attention(const void* q, const void* k, const void* v, long long ld, const void* bias, void* out,
+                      long long ldo, int n, int heads, int depth, int precision, int variant, void* stream);
+/* b200_op_gemm_timed: the tensor-core product of b200_op_gemm queued `launches` times back to back on `stream`
+ *   between two CUDA events; *ms_per_launch = elapsed / launches.  With enough launches the host's launch latency
+ *   drops out, which is what a launch costs inside a replayed graph (profiling surface only). */
+int b200_op_gemm_timed(const void* A, const void* W, const float* bias, void* C, int M, int N, int K,
+                       int activation, int precision, int launches, float* ms_per_launch, void* stream);
 /* b200_op_policy_attention: tail of the attention policy head for n positions: logits = Q K^T / sqrt(dm)
  *   per position (64x64), promotion offsets from the rank-8 keys and `w4` ([4][dm], fp32), and the gather of
  *   the 1858 move logits (network_blas.cc:850-914).  q, k: [n*64][dm] in `precision`; scratch_logits: n*4096

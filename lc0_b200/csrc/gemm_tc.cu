@@ -1246,6 +1246,27 @@ cudaError_t gemm_tc_init() {
   return cudaSuccess;
 }
 
+cudaError_t tma_encode_2d(const void* ptr, long long ld, long long rows, int cols, int box_cols, int box_rows,
+                          int swizzle_bytes, int prec, void* out) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_encode) return cudaErrorNotReady;
+  if (box_cols * 2 != swizzle_bytes || (swizzle_bytes != 64 && swizzle_bytes != 128)) return cudaErrorInvalidValue;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(reinterpret_cast<CUtensorMap*>(out),
+                        prec == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                        const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
+    return cudaErrorInvalidValue;
+  }
+  return cudaSuccess;
+}
+
 bool gemm_tc_supported(const GemmParams& p) {
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   if (p.conv_cin > 0)

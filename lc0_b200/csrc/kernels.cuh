@@ -55,6 +55,11 @@ bool gemm_tc_supported(const GemmParams& p);
 // Whether launch_gemm_tc would run `p` (with C2 / n_split set) on the CTA-pair kernel, the only one that splits.
 bool gemm_tc_split_supported(const GemmParams& p, int sm_count);
 cudaError_t gemm_tc_init();  // resolves the driver entry point used to encode TMA descriptors
+// TMA descriptor over a row-major 16-bit matrix [rows][cols] with leading dimension ld (elements), box
+// box_cols x box_rows, shared-memory swizzle of 64 or 128 bytes (= box_cols * 2); `out` is a CUtensorMap.
+// prec: 1 = fp16, 2 = bf16.  Needs gemm_tc_init().
+cudaError_t tma_encode_2d(const void* ptr, long long ld, long long rows, int cols, int box_cols, int box_rows,
+                          int swizzle_bytes, int prec, void* out);
 
 template <typename T>
 cudaError_t launch_expand_planes(const uint64_t* masks, const float* values, int n, T* out, cudaStream_t s);
@@ -88,6 +93,12 @@ bool attention_tc_supported(long long ld, long long ldo, int depth, const void* 
 template <typename T>
 cudaError_t launch_attention_tc(const T* q, const T* k, const T* v, long long ld, const T* bias, T* out,
                                 long long ldo, int n, int heads, int depth, float scale, cudaStream_t s);
+// Persistent variant of the same operator: TMA loads into a ring of swizzled shared-memory stages, TMA stores of
+// the result; `status` receives 300 + code if a bounded device-side wait gives up.  Same support conditions.
+template <typename T>
+cudaError_t launch_attention_tma(const T* q, const T* k, const T* v, long long ld, const T* bias, T* out,
+                                 long long ldo, int n, int heads, int depth, float scale, int* status, int sm_count,
+                                 cudaStream_t s);
 
 // Attention policy: promotion logits + gather to 1858 (network_blas.cc:873-914).
 // logits: fp32 [n][64*64] (already scaled), kp: [n*64][dm] keys, w4: fp32 [4][dm].

@@ -1129,8 +1129,14 @@ struct Net : NetBase {
     bool done = false;
     if constexpr (sizeof(T) == 2) {
       if (use_tc && attention_tc_supported(3 * E, E, depth, s.qkv, s.qkv + E, s.qkv + 2 * E, bias, s.att)) {
-        CK(launch_attention_tc<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
-                                  1.0f / sqrtf((float)depth), st));  // :352-439
+        // :352-439.  The persistent TMA kernel unless B200_ATTN_TMA=0 asks for the cp.async one (kept for comparison).
+        static const bool tma = !(getenv("B200_ATTN_TMA") && getenv("B200_ATTN_TMA")[0] == '0');
+        if (tma)
+          CK(launch_attention_tma<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
+                                     1.0f / sqrtf((float)depth), d_status, sm_count, st));
+        else
+          CK(launch_attention_tc<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
+                                    1.0f / sqrtf((float)depth), st));
         done = true;
       }
     }
@@ -1870,6 +1876,52 @@ int b200_op_gemm(const void* A, const void* W, const float* bias, void* C, int M
                       [&] { return run(__nv_bfloat16()); });
 }
 
+int b200_op_gemm_timed(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int activation,
+                       int precision, int launches, float* ms_per_launch, void* stream) {
+  GemmParams p;
+  p.A = A; p.lda = K; p.W = W; p.ldw = K; p.bias = bias; p.C = C; p.ldc = N;
+  p.M = M; p.N = N; p.K = K; p.act = activation;
+  if (launches < 1 || !ms_per_launch) {
+    set_error("b200_op_gemm_timed: bad argument");
+    return B200_ERR_INVALID;
+  }
+  if (precision == B200_PREC_FP32 || !gemm_tc_supported(p)) {
+    set_error("b200_op_gemm_timed: shape or precision not supported by the tensor-core kernel");
+    return B200_ERR_UNSUPPORTED;
+  }
+  B200_CUDA(gemm_tc_init());
+  int dev = 0, sms = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  B200_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  int* status = nullptr;
+  B200_CUDA(cudaMalloc(&status, sizeof(int)));
+  B200_CUDA(cudaMemset(status, 0, sizeof(int)));
+  cudaEvent_t e0, e1;
+  B200_CUDA(cudaEventCreate(&e0));
+  B200_CUDA(cudaEventCreate(&e1));
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t err = cudaEventRecord(e0, s);
+  for (int i = 0; i < launches && err == cudaSuccess; ++i)
+    err = precision == B200_PREC_FP16 ? launch_gemm_tc<__half>(p, status, sms, s)
+                                      : launch_gemm_tc<__nv_bfloat16>(p, status, sms, s);
+  if (err == cudaSuccess) err = cudaEventRecord(e1, s);
+  if (err == cudaSuccess) err = cudaEventSynchronize(e1);
+  float ms = 0.f;
+  if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, e0, e1);
+  int st = 0;
+  if (err == cudaSuccess) err = cudaMemcpy(&st, status, sizeof(int), cudaMemcpyDeviceToHost);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(status);
+  B200_CUDA(err);
+  if (st) {
+    set_error("tensor-core GEMM: a bounded device-side wait gave up, status " + std::to_string(st));
+    return B200_ERR_TIMEOUT;
+  }
+  *ms_per_launch = ms / launches;
+  return B200_OK;
+}
+
 int b200_op_encode_positions(const b200_board* d_boards, const int* d_offsets, const uint8_t* d_from_start, int n,
                              int input_format, int fill_empty_history, uint64_t* d_masks, float* d_values,
                              int* d_transforms, void* stream) {
@@ -1941,6 +1993,59 @@ int b200_op_layer_norm(void* out, const void* x, const void* skip, const float* 
     B200_CUDA(launch_layer_norm<T>((T*)out, (const T*)x, (const T*)skip, gamma, beta, nullptr, nullptr, rows, C,
                                    alpha, eps, (cudaStream_t)stream));
     return B200_OK;
+  };
+  return by_precision(precision, [&] { return run(float()); }, [&] { return run(__half()); },
+                      [&] { return run(__nv_bfloat16()); });
+}
+
+int b200_op_attention(const void* q, const void* k, const void* v, long long ld, const void* bias, void* out,
+                      long long ldo, int n, int heads, int depth, int precision, int variant, void* stream) {
+  if (n < 0 || heads < 1 || depth < 1 || (n > 0 && (!q || !k || !v || !out)) || variant < 0 || variant > 2) {
+    set_error("b200_op_attention: bad argument");
+    return B200_ERR_INVALID;
+  }
+  const float scale = 1.0f / sqrtf((float)depth);
+  cudaStream_t st = (cudaStream_t)stream;
+  auto run = [&](auto tag) -> int {
+    using T = decltype(tag);
+    if (variant == 0) {
+      B200_CUDA(launch_attention<T>((const T*)q, (const T*)k, (const T*)v, ld, (const T*)bias, (T*)out, ldo, n, heads,
+                                    depth, scale, st));
+      return B200_OK;
+    }
+    if constexpr (sizeof(T) == 2) {
+      if (!attention_tc_supported(ld, ldo, depth, q, k, v, bias, out)) {
+        set_error("b200_op_attention: layout not supported by the tensor-core kernels");
+        return B200_ERR_UNSUPPORTED;
+      }
+      if (variant == 1) {
+        B200_CUDA(launch_attention_tc<T>((const T*)q, (const T*)k, (const T*)v, ld, (const T*)bias, (T*)out, ldo, n,
+                                         heads, depth, scale, st));
+        return B200_OK;
+      }
+      B200_CUDA(gemm_tc_init());
+      int dev = 0, sms = 0;
+      B200_CUDA(cudaGetDevice(&dev));
+      B200_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+      int* status = nullptr;
+      B200_CUDA(cudaMalloc(&status, sizeof(int)));
+      B200_CUDA(cudaMemset(status, 0, sizeof(int)));
+      cudaError_t err = launch_attention_tma<T>((const T*)q, (const T*)k, (const T*)v, ld, (const T*)bias, (T*)out,
+                                                ldo, n, heads, depth, scale, status, sms, st);
+      if (err == cudaSuccess) err = cudaStreamSynchronize(st);
+      int code = 0;
+      if (err == cudaSuccess) err = cudaMemcpy(&code, status, sizeof(int), cudaMemcpyDeviceToHost);
+      cudaFree(status);
+      B200_CUDA(err);
+      if (code) {
+        set_error("attention: a bounded device-side wait gave up, status " + std::to_string(code));
+        return B200_ERR_TIMEOUT;
+      }
+      return B200_OK;
+    } else {
+      set_error("b200_op_attention: the tensor-core kernels take fp16 or bf16");
+      return B200_ERR_UNSUPPORTED;
+    }
   };
   return by_precision(precision, [&] { return run(float()); }, [&] { return run(__half()); },
                       [&] { return run(__nv_bfloat16()); });

@@ -9,6 +9,7 @@ Prints one line per shape with the CUDA-event time and achieved TFLOP/s.  Small 
 `ncu -k regex:gemm_tc --set full` (use --batch 64..256 and --reps 1 for a capture).
 """
 import argparse
+import ctypes
 import sys
 
 import numpy as np
@@ -111,6 +112,9 @@ def main():
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--only", default="")
     ap.add_argument("--fma", action="store_true", help="time the FMA kernel instead of the tensor-core kernel")
+    ap.add_argument("--chain", type=int, default=1,
+                    help="launches queued back to back between the two events (gemm): the time per launch then excludes "
+                         "the host's launch latency, as in a graph replay")
     args = ap.parse_args()
     import torch
     from . import _lib
@@ -131,6 +135,13 @@ def main():
         times = []
         for r in range(args.reps + 1):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if args.chain > 1:
+                ms = ctypes.c_float(0)
+                _lib.check(lib.b200_op_gemm_timed(A.data_ptr(), W.data_ptr(), b.data_ptr(), C.data_ptr(), M, N, K, 3,
+                                                  prec, args.chain, ctypes.byref(ms), None))
+                if r > 0 or args.reps == 0:
+                    times.append(ms.value)
+                continue
             e0.record()
             _lib.check(lib.b200_op_gemm(A.data_ptr(), W.data_ptr(), b.data_ptr(), C.data_ptr(), M, N, K, 3, prec,
                                         0 if args.fma else 1, None))

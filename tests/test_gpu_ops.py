@@ -119,3 +119,58 @@ def test_policy_attention_op(lib, prec, n, dm):
     torch.cuda.synchronize()
     want = _policy_reference(q.float().cpu().numpy(), k.float().cpu().numpy(), w4.cpu().numpy())
     assert np.abs(pol.cpu().numpy() - want).max() <= 2e-4 * max(1.0, np.abs(want).max())
+
+
+def _attention_reference(qkv, bias, n, heads, depth):
+    """softmax(Q K^T / sqrt(depth) + bias) V per (position, head) in fp32 (network_blas.cc:352-439)."""
+    e = heads * depth
+    x = qkv.float().reshape(n, 64, 3, heads, depth)
+    q, k, v = (x[:, :, i].permute(0, 2, 1, 3) for i in range(3))  # [n][heads][64][depth]
+    s = torch.matmul(q, k.transpose(-1, -2)) / depth ** 0.5
+    if bias is not None:
+        s = s + bias.float().reshape(n, heads, 64, 64)
+    p = torch.softmax(s, dim=-1)
+    return torch.matmul(p, v).permute(0, 2, 1, 3).reshape(n * 64, e)
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("prec", [1, 2])
+@pytest.mark.parametrize("n,heads,depth,with_bias", [(1, 4, 32, True), (7, 32, 32, True), (3, 8, 64, False),
+                                                     (150, 8, 32, True), (40, 6, 64, True), (2, 1, 32, False)])
+def test_attention_op(lib, variant, prec, n, heads, depth, with_bias):
+    """The three attention kernels against an fp32 reference on the fused Q|K|V layout the network uses; the
+    persistent TMA kernel (variant 2) walks several items per CTA at the larger sizes."""
+    torch.manual_seed(n * heads + depth)
+    e = heads * depth
+    qkv = torch.randn(n * 64, 3 * e, device="cuda").to(DT[prec])
+    bias = (torch.randn(n, heads, 64, 64, device="cuda") * 2).to(DT[prec]) if with_bias else None
+    out = torch.zeros(n * 64, e, device="cuda", dtype=DT[prec])
+    esz = 2
+    _lib.check(lib.b200_op_attention(qkv.data_ptr(), qkv.data_ptr() + e * esz, qkv.data_ptr() + 2 * e * esz, 3 * e,
+                                     bias.data_ptr() if with_bias else None, out.data_ptr(), e, n, heads, depth, prec,
+                                     variant, None))
+    torch.cuda.synchronize()
+    want = _attention_reference(qkv, bias, n, heads, depth)
+    tol = 4e-3 if prec == 1 else 3e-2  # probabilities and outputs are rounded to 16 bits (11 / 8 significant bits)
+    assert (out.float() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
+
+
+def test_attention_op_variants_agree(lib):
+    """The persistent TMA kernel and the cp.async kernel differ only in how exp is evaluated."""
+    torch.manual_seed(5)
+    n, heads, depth = 64, 32, 32
+    e = heads * depth
+    qkv = torch.randn(n * 64, 3 * e, device="cuda").half()
+    bias = torch.randn(n, heads, 64, 64, device="cuda").half()
+    outs = []
+    for variant in (1, 2):
+        out = torch.zeros(n * 64, e, device="cuda", dtype=torch.float16)
+        _lib.check(lib.b200_op_attention(qkv.data_ptr(), qkv.data_ptr() + e * 2, qkv.data_ptr() + 4 * e, 3 * e,
+                                         bias.data_ptr(), out.data_ptr(), e, n, heads, depth, 1, variant, None))
+        outs.append(out.float())
+    torch.cuda.synchronize()
+    assert (outs[0] - outs[1]).abs().max().item() <= 2e-3
+
+
+def test_attention_op_rejects_fp32_tensor_core_variants(lib):
+    assert lib.b200_op_attention(None, None, None, 96, None, None, 32, 0, 1, 32, 0, 2, None) == _lib.ERR_UNSUPPORTED
