@@ -258,6 +258,86 @@ REGISTER_NETWORK("b200-bf16", MakeB200Network<B200_PREC_BF16>, 89)
 REGISTER_NETWORK("b200-fp32", MakeB200Network<B200_PREC_FP32>, 88)
 
 
+// ---- batch aggregation inside the plug-in -----------------------------------------------------------------------
+// "b200-mux": what `multiplexing` over `b200` gives (MuxingNetwork, src/neural/backends/network_mux.cc:40-205), with
+// the merging done by the library's aggregator (b200_mux_*): every computation keeps its inputs and results in host
+// vectors of its own, ComputeBlocking() queues them and blocks until a worker has evaluated them together with the
+// requests of the other search threads or games.  For selfplay with many games of small batches.
+// Options: the ones of `b200` plus precision=fp16|bf16|fp32 and mux_wait_us (how long a worker that finds fewer than
+// max_batch positions waits for more; default 200).
+class B200MuxComputation : public NetworkComputation {
+ public:
+  B200MuxComputation(b200_mux* mux, bool wdl, bool mlh) : mux_(mux), wdl_(wdl), mlh_(mlh) {}
+  void AddInput(InputPlanes&& input) override {
+    if (input.size() != static_cast<size_t>(kInputPlanes)) throw Exception("b200 backend: expected 112 input planes");
+    for (int i = 0; i < kInputPlanes; ++i) {
+      masks_.push_back(input[i].mask);
+      values_.push_back(input[i].value);
+    }
+    ++n_;
+  }
+  void ComputeBlocking() override {
+    if (n_ == 0) return;
+    policy_.resize(static_cast<size_t>(n_) * kPolicySize);
+    q_.resize(n_);
+    d_.resize(n_);
+    m_.resize(n_);
+    Check(b200_mux_eval(mux_, masks_.data(), values_.data(), n_, policy_.data(), q_.data(), d_.data(), m_.data()));
+  }
+  int GetBatchSize() const override { return n_; }
+  float GetQVal(int sample) const override { return q_[sample]; }
+  float GetDVal(int sample) const override { return wdl_ ? d_[sample] : 0.0f; }
+  float GetMVal(int sample) const override { return mlh_ ? m_[sample] : 0.0f; }
+  float GetPVal(int sample, int move_id) const override {
+    return policy_[static_cast<size_t>(sample) * kPolicySize + move_id];
+  }
+
+ private:
+  static constexpr int kPolicySize = 1858;
+  b200_mux* mux_;
+  bool wdl_, mlh_;
+  int n_ = 0;
+  std::vector<uint64_t> masks_;
+  std::vector<float> values_, policy_, q_, d_, m_;
+};
+
+class B200MuxNetwork : public Network {
+ public:
+  B200MuxNetwork(const WeightsFile& file, const OptionsDict& options)
+      : net_(file, options, PrecisionOption(options)) {
+    Check(b200_mux_create(net_.net(), options.GetOrDefault<int>("max_batch", 1024),
+                          options.GetOrDefault<int>("mux_wait_us", 200), &mux_));
+  }
+  ~B200MuxNetwork() override { b200_mux_destroy(mux_); }  // before net_, which the aggregator uses
+
+  const NetworkCapabilities& GetCapabilities() const override { return net_.GetCapabilities(); }
+  std::unique_ptr<NetworkComputation> NewComputation() override {
+    return std::make_unique<B200MuxComputation>(mux_, net_.info().wdl != 0, net_.info().has_mlh != 0);
+  }
+  int GetThreads() const override { return 8; }  // callers only queue and wait; the aggregator owns the GPU
+  bool IsCpu() const override { return false; }
+  int GetMiniBatchSize() const override { return 32; }
+  int GetPreferredBatchStep() const override { return 1; }
+
+ private:
+  static int PrecisionOption(const OptionsDict& options) {
+    const std::string p = options.GetOrDefault<std::string>("precision", "fp16");
+    if (p == "fp16") return B200_PREC_FP16;
+    if (p == "bf16") return B200_PREC_BF16;
+    if (p == "fp32") return B200_PREC_FP32;
+    throw Exception("b200-mux: precision must be fp16, bf16 or fp32");
+  }
+  B200Network net_;
+  b200_mux* mux_ = nullptr;
+};
+
+std::unique_ptr<Network> MakeB200MuxNetwork(const std::optional<WeightsFile>& w, const OptionsDict& options) {
+  if (!w) throw Exception("The b200-mux backend requires a network file.");
+  return std::make_unique<B200MuxNetwork>(*w, options);
+}
+REGISTER_NETWORK("b200-mux", MakeB200MuxNetwork, 86)
+
+
 // ---- native Backend ---------------------------------------------------------------------------------------------
 // Same contract as NetworkAsBackend (src/neural/wrapper.cc:48-101) with two differences: the batch limit is the
 // network's max_batch option instead of the wrapper's fixed 1024, and EvalResultPtr::p is filled from the device's

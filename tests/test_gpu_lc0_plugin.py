@@ -80,9 +80,9 @@ def test_lc0_backendbench_and_check_decorator(tmp_path):
     assert "Check passed" in out or "passed" in out.lower(), out[-2000:]
 
 
-def _search(exe, npath, backend, opts, nodes=400, positions=3):
+def _search(exe, npath, backend, opts, nodes=400, positions=3, extra=()):
     cmd = [exe, "benchmark", "--weights=" + npath, "--backend=" + backend, "--nodes=%d" % nodes, "--threads=1",
-           "--num-positions=%d" % positions]
+           "--num-positions=%d" % positions] + list(extra)
     if opts:
         cmd.append("--backend-opts=" + opts)
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
@@ -124,3 +124,32 @@ def test_native_backend_backendbench_and_options(tmp_path):
     r = subprocess.run([exe, "backendbench", "--weights=" + npath, "--backend=b200-native",
                         "--backend-opts=precision=fp64", "--batches=1"], capture_output=True, text=True, timeout=300)
     assert "unknown precision" in r.stdout + r.stderr
+
+
+@needs_plugin
+def test_mux_backend_matches_the_reference_outputs_and_searches_like_b200(tmp_path):
+    """"b200-mux" (every computation goes through the library's batch aggregator): the recorded reference outputs in
+    fp32, the same moves as "b200" in lc0's single-threaded search, and lc0's multi-threaded search runs over it."""
+    net, pos, n, g = load_case("cfg4_mini")
+    npath, ppath, opath = str(tmp_path / "n.pb.gz"), str(tmp_path / "p.pos"), str(tmp_path / "o.bin")
+    mknet.write_net("cfg4_mini", npath)
+    _write_pos(ppath, pos, n)
+    r = subprocess.run([os.path.join(REF, "ref_eval"), "b200-mux", npath, ppath, opath, "max_batch=64,precision=fp32"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    raw = np.fromfile(opath, "<f4", offset=12)
+    pol = raw[:n * 1858].reshape(n, 1858)
+    q = raw[n * 1858:n * 1859]
+    assert np.abs(pol - g["policy"]).max() <= 1e-5 * np.abs(g["policy"]).max()
+    assert np.abs(q - g["q"]).max() <= 1e-5
+    exe = os.path.join(REF, "lc0_ref")
+    # the same minibatch size for both: lc0 otherwise takes each backend's own recommendation, which shapes the search
+    mb = ["--minibatch-size=32"]
+    assert _search(exe, npath, "b200-mux", "", extra=mb) == _search(exe, npath, "b200", "", extra=mb)
+    r = subprocess.run([exe, "benchmark", "--weights=" + npath, "--backend=b200-mux", "--backend-opts=mux_wait_us=100",
+                        "--nodes=2000", "--threads=4", "--num-positions=2"], capture_output=True, text=True, timeout=600)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0 and out.count("bestmove") == 2, out[-2000:]
+    r = subprocess.run([exe, "backendbench", "--weights=" + npath, "--backend=b200-mux",
+                        "--backend-opts=precision=fp64", "--batches=1"], capture_output=True, text=True, timeout=300)
+    assert "precision must be" in r.stdout + r.stderr
