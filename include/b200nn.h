@@ -170,6 +170,23 @@ int b200_mux_eval(b200_mux* mux, const uint64_t* masks, const float* values, int
 int b200_mux_stats(b200_mux* mux, long long* requests, long long* batches, long long* positions);
 void b200_mux_destroy(b200_mux* mux);
 
+/* ---- One batch over several GPUs of the box ---------------------------------------------------------------------
+ * Positions are independent: the batch is cut into contiguous slices whose sizes differ by at most one (b200_multi_slice),
+ * one per GPU, the weights are replicated, nothing is exchanged.  The role of the reference's `demux` decorator
+ * (DemuxingComputation::ComputeBlocking, src/neural/backends/network_demux.cc:268-330) without its per-slice
+ * computations: one persistent host thread per GPU evaluates its slice with b200_net_eval_host and writes the results
+ * into the caller's arrays at the slice's offset.  `opt->gpu` is ignored, `opt->max_batch` is per GPU; the same GPU may
+ * be listed more than once.  Calls are serialised. */
+typedef struct b200_multi b200_multi;
+void b200_multi_slice(int n, int parts, int part, int* begin, int* count);
+int b200_multi_create(const b200_builder* b, const b200_net_options* opt, const int* gpus, int n_gpus,
+                      b200_multi** out);
+int b200_multi_gpu_count(const b200_multi* mg);
+b200_net* b200_multi_net(b200_multi* mg, int i);
+int b200_multi_eval_host(b200_multi* mg, const uint64_t* masks, const float* values, int n, float* policy, float* q,
+                         float* d, float* m);
+void b200_multi_destroy(b200_multi* mg);
+
 /* ---- Position encoding on the device ------------------------------------------------------------------------
  * What lc0 does on the host before AddInput: EncodePositionForNN (src/neural/encoder.cc:134-328) turns the game
  * history into the 112 packed planes, with ChooseTransform (encoder.cc:50-104) for the canonical formats.  Here the

@@ -78,6 +78,12 @@ SIGNATURES = {
     "b200_mux_stats": (_I, [_P, ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong),
                             ctypes.POINTER(ctypes.c_longlong)]),
     "b200_mux_destroy": (None, [_P]),
+    "b200_multi_slice": (None, [_I, _I, _I, ctypes.POINTER(_I), ctypes.POINTER(_I)]),
+    "b200_multi_create": (_I, [_P, _P, ctypes.POINTER(_I), _I, ctypes.POINTER(_P)]),
+    "b200_multi_gpu_count": (_I, [_P]),
+    "b200_multi_net": (_P, [_P, _I]),
+    "b200_multi_eval_host": (_I, [_P, _P, _P, _I, _P, _P, _P, _P]),
+    "b200_multi_destroy": (None, [_P]),
     "b200_net_eval_host": (_I, [_P, _P, _P, _I, _P, _P, _P, _P]),
     "b200_net_eval_device": (_I, [_P, _P, _P, _I, _P, _P]),
     "b200_net_enqueue_device": (_I, [_P, _P, _P, _I, _P, _P]),

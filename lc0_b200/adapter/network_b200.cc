@@ -119,113 +119,123 @@ class Builder {
   b200_builder* b_ = nullptr;
 };
 
+// Describes the network of `file` to the library: format integers and every weight tensor by name.
+void FillBuilder(const WeightsFile& file, const OptionsDict& options, Builder& b) {
+  const auto nf = file.format().network_format();
+  using NF = pblczero::NetworkFormat;
+  const MultiHeadWeights weights(file.weights());
+
+  const std::string policy_head = options.GetOrDefault<std::string>("policy_head", "vanilla");
+  if (weights.policy_heads.count(policy_head) == 0)
+    throw Exception("The policy head you specified '" + policy_head + "' does not exist in this net.");
+  const std::string value_head = options.GetOrDefault<std::string>("value_head", "winner");
+  if (weights.value_heads.count(value_head) == 0)
+    throw Exception("The value head you specified '" + value_head + "' does not exist in this net.");
+  const auto& ph = weights.policy_heads.at(policy_head);
+  const auto& vh = weights.value_heads.at(value_head);
+
+  // Activation resolution as in the reference backends (network_blas.cc:1010-1028).
+  const int default_act =
+      nf.default_activation() == NF::DEFAULT_ACTIVATION_MISH ? ACTIVATION_MISH : ACTIVATION_RELU;
+  const int smolgen_act =
+      nf.smolgen_activation() == NF::ACTIVATION_DEFAULT ? default_act : static_cast<int>(nf.smolgen_activation());
+  const int ffn_act =
+      nf.ffn_activation() == NF::ACTIVATION_DEFAULT ? default_act : static_cast<int>(nf.ffn_activation());
+
+  b.Int("input_format", nf.input());
+  b.Int("output_format", nf.output());
+  b.Int("network", nf.network());
+  b.Int("policy", nf.policy());
+  b.Int("value", nf.value());
+  b.Int("moves_left", nf.moves_left());
+  b.Int("input_embedding", nf.input_embedding());
+  b.Int("default_activation", default_act);
+  b.Int("smolgen_activation", smolgen_act);
+  b.Int("ffn_activation", ffn_act);
+  b.Int("headcount", weights.encoder_head_count);
+  b.Int("pol_headcount", ph.pol_encoder_head_count);
+
+  b.Conv("input", weights.input);
+  for (size_t i = 0; i < weights.residual.size(); ++i) {
+    const auto& r = weights.residual[i];
+    const std::string p = "residual." + std::to_string(i);
+    b.Conv(p + ".conv1", r.conv1);
+    b.Conv(p + ".conv2", r.conv2);
+    if (r.has_se) {
+      b.Tensor(p + ".se.w1", r.se.w1);
+      b.Tensor(p + ".se.b1", r.se.b1);
+      b.Tensor(p + ".se.w2", r.se.w2);
+      b.Tensor(p + ".se.b2", r.se.b2);
+    }
+  }
+  b.Tensor("ip_emb_preproc_w", weights.ip_emb_preproc_w);
+  b.Tensor("ip_emb_preproc_b", weights.ip_emb_preproc_b);
+  b.Tensor("ip_emb_w", weights.ip_emb_w);
+  b.Tensor("ip_emb_b", weights.ip_emb_b);
+  b.Tensor("ip_emb_ln_gammas", weights.ip_emb_ln_gammas);
+  b.Tensor("ip_emb_ln_betas", weights.ip_emb_ln_betas);
+  b.Tensor("ip_mult_gate", weights.ip_mult_gate);
+  b.Tensor("ip_add_gate", weights.ip_add_gate);
+  b.Tensor("ip_emb_ffn.dense1_w", weights.ip_emb_ffn.dense1_w);
+  b.Tensor("ip_emb_ffn.dense1_b", weights.ip_emb_ffn.dense1_b);
+  b.Tensor("ip_emb_ffn.dense2_w", weights.ip_emb_ffn.dense2_w);
+  b.Tensor("ip_emb_ffn.dense2_b", weights.ip_emb_ffn.dense2_b);
+  b.Tensor("ip_emb_ffn_ln_gammas", weights.ip_emb_ffn_ln_gammas);
+  b.Tensor("ip_emb_ffn_ln_betas", weights.ip_emb_ffn_ln_betas);
+  for (size_t i = 0; i < weights.encoder.size(); ++i) b.Encoder("encoder." + std::to_string(i), weights.encoder[i]);
+  b.Tensor("smolgen_w", weights.smolgen_w);
+  b.Conv("moves_left", weights.moves_left);
+  b.Tensor("ip_mov_w", weights.ip_mov_w);
+  b.Tensor("ip_mov_b", weights.ip_mov_b);
+  b.Tensor("ip1_mov_w", weights.ip1_mov_w);
+  b.Tensor("ip1_mov_b", weights.ip1_mov_b);
+  b.Tensor("ip2_mov_w", weights.ip2_mov_w);
+  b.Tensor("ip2_mov_b", weights.ip2_mov_b);
+
+  b.Tensor("policy.ip_pol_w", ph.ip_pol_w);
+  b.Tensor("policy.ip_pol_b", ph.ip_pol_b);
+  b.Tensor("policy.ip2_pol_w", ph.ip2_pol_w);
+  b.Tensor("policy.ip2_pol_b", ph.ip2_pol_b);
+  b.Tensor("policy.ip3_pol_w", ph.ip3_pol_w);
+  b.Tensor("policy.ip3_pol_b", ph.ip3_pol_b);
+  b.Tensor("policy.ip4_pol_w", ph.ip4_pol_w);
+  b.Conv("policy.policy1", ph.policy1);
+  b.Conv("policy.policy", ph.policy);
+  for (size_t i = 0; i < ph.pol_encoder.size(); ++i)
+    b.Encoder("policy.pol_encoder." + std::to_string(i), ph.pol_encoder[i]);
+  b.Conv("value.value", vh.value);
+  b.Tensor("value.ip_val_w", vh.ip_val_w);
+  b.Tensor("value.ip_val_b", vh.ip_val_b);
+  b.Tensor("value.ip1_val_w", vh.ip1_val_w);
+  b.Tensor("value.ip1_val_b", vh.ip1_val_b);
+  b.Tensor("value.ip2_val_w", vh.ip2_val_w);
+  b.Tensor("value.ip2_val_b", vh.ip2_val_b);
+
+}
+
+b200_net_options MakeNetOptions(const OptionsDict& options, int precision) {
+  b200_net_options opt{};
+  opt.gpu = options.GetOrDefault<int>("gpu", 0);
+  opt.max_batch = options.GetOrDefault<int>("max_batch", 1024);
+  opt.slots = options.GetOrDefault<int>("slots", 2);
+  opt.precision = precision;
+  opt.mlh = options.GetOrDefault<bool>("mlh", true) ? 1 : 0;
+  opt.flags = (options.GetOrDefault<bool>("tensor_cores", true) ? 0 : B200_FLAG_NO_TENSOR_CORES) |
+              (options.GetOrDefault<bool>("graph_capture", true) ? 0 : B200_FLAG_NO_GRAPHS);
+  return opt;
+}
+
 class B200Network : public Network {
  public:
   B200Network(const WeightsFile& file, const OptionsDict& options, int precision)
       : capabilities_{file.format().network_format().input(), file.format().network_format().output(),
                       file.format().network_format().moves_left()} {
-    const auto nf = file.format().network_format();
-    using NF = pblczero::NetworkFormat;
-    const MultiHeadWeights weights(file.weights());
-
-    const std::string policy_head = options.GetOrDefault<std::string>("policy_head", "vanilla");
-    if (weights.policy_heads.count(policy_head) == 0)
-      throw Exception("The policy head you specified '" + policy_head + "' does not exist in this net.");
-    const std::string value_head = options.GetOrDefault<std::string>("value_head", "winner");
-    if (weights.value_heads.count(value_head) == 0)
-      throw Exception("The value head you specified '" + value_head + "' does not exist in this net.");
-    const auto& ph = weights.policy_heads.at(policy_head);
-    const auto& vh = weights.value_heads.at(value_head);
-
-    // Activation resolution as in the reference backends (network_blas.cc:1010-1028).
-    const int default_act =
-        nf.default_activation() == NF::DEFAULT_ACTIVATION_MISH ? ACTIVATION_MISH : ACTIVATION_RELU;
-    const int smolgen_act =
-        nf.smolgen_activation() == NF::ACTIVATION_DEFAULT ? default_act : static_cast<int>(nf.smolgen_activation());
-    const int ffn_act =
-        nf.ffn_activation() == NF::ACTIVATION_DEFAULT ? default_act : static_cast<int>(nf.ffn_activation());
-
     Builder b;
-    b.Int("input_format", nf.input());
-    b.Int("output_format", nf.output());
-    b.Int("network", nf.network());
-    b.Int("policy", nf.policy());
-    b.Int("value", nf.value());
-    b.Int("moves_left", nf.moves_left());
-    b.Int("input_embedding", nf.input_embedding());
-    b.Int("default_activation", default_act);
-    b.Int("smolgen_activation", smolgen_act);
-    b.Int("ffn_activation", ffn_act);
-    b.Int("headcount", weights.encoder_head_count);
-    b.Int("pol_headcount", ph.pol_encoder_head_count);
-
-    b.Conv("input", weights.input);
-    for (size_t i = 0; i < weights.residual.size(); ++i) {
-      const auto& r = weights.residual[i];
-      const std::string p = "residual." + std::to_string(i);
-      b.Conv(p + ".conv1", r.conv1);
-      b.Conv(p + ".conv2", r.conv2);
-      if (r.has_se) {
-        b.Tensor(p + ".se.w1", r.se.w1);
-        b.Tensor(p + ".se.b1", r.se.b1);
-        b.Tensor(p + ".se.w2", r.se.w2);
-        b.Tensor(p + ".se.b2", r.se.b2);
-      }
-    }
-    b.Tensor("ip_emb_preproc_w", weights.ip_emb_preproc_w);
-    b.Tensor("ip_emb_preproc_b", weights.ip_emb_preproc_b);
-    b.Tensor("ip_emb_w", weights.ip_emb_w);
-    b.Tensor("ip_emb_b", weights.ip_emb_b);
-    b.Tensor("ip_emb_ln_gammas", weights.ip_emb_ln_gammas);
-    b.Tensor("ip_emb_ln_betas", weights.ip_emb_ln_betas);
-    b.Tensor("ip_mult_gate", weights.ip_mult_gate);
-    b.Tensor("ip_add_gate", weights.ip_add_gate);
-    b.Tensor("ip_emb_ffn.dense1_w", weights.ip_emb_ffn.dense1_w);
-    b.Tensor("ip_emb_ffn.dense1_b", weights.ip_emb_ffn.dense1_b);
-    b.Tensor("ip_emb_ffn.dense2_w", weights.ip_emb_ffn.dense2_w);
-    b.Tensor("ip_emb_ffn.dense2_b", weights.ip_emb_ffn.dense2_b);
-    b.Tensor("ip_emb_ffn_ln_gammas", weights.ip_emb_ffn_ln_gammas);
-    b.Tensor("ip_emb_ffn_ln_betas", weights.ip_emb_ffn_ln_betas);
-    for (size_t i = 0; i < weights.encoder.size(); ++i) b.Encoder("encoder." + std::to_string(i), weights.encoder[i]);
-    b.Tensor("smolgen_w", weights.smolgen_w);
-    b.Conv("moves_left", weights.moves_left);
-    b.Tensor("ip_mov_w", weights.ip_mov_w);
-    b.Tensor("ip_mov_b", weights.ip_mov_b);
-    b.Tensor("ip1_mov_w", weights.ip1_mov_w);
-    b.Tensor("ip1_mov_b", weights.ip1_mov_b);
-    b.Tensor("ip2_mov_w", weights.ip2_mov_w);
-    b.Tensor("ip2_mov_b", weights.ip2_mov_b);
-
-    b.Tensor("policy.ip_pol_w", ph.ip_pol_w);
-    b.Tensor("policy.ip_pol_b", ph.ip_pol_b);
-    b.Tensor("policy.ip2_pol_w", ph.ip2_pol_w);
-    b.Tensor("policy.ip2_pol_b", ph.ip2_pol_b);
-    b.Tensor("policy.ip3_pol_w", ph.ip3_pol_w);
-    b.Tensor("policy.ip3_pol_b", ph.ip3_pol_b);
-    b.Tensor("policy.ip4_pol_w", ph.ip4_pol_w);
-    b.Conv("policy.policy1", ph.policy1);
-    b.Conv("policy.policy", ph.policy);
-    for (size_t i = 0; i < ph.pol_encoder.size(); ++i)
-      b.Encoder("policy.pol_encoder." + std::to_string(i), ph.pol_encoder[i]);
-    b.Conv("value.value", vh.value);
-    b.Tensor("value.ip_val_w", vh.ip_val_w);
-    b.Tensor("value.ip_val_b", vh.ip_val_b);
-    b.Tensor("value.ip1_val_w", vh.ip1_val_w);
-    b.Tensor("value.ip1_val_b", vh.ip1_val_b);
-    b.Tensor("value.ip2_val_w", vh.ip2_val_w);
-    b.Tensor("value.ip2_val_b", vh.ip2_val_b);
-
-    b200_net_options opt{};
-    opt.gpu = options.GetOrDefault<int>("gpu", 0);
-    opt.max_batch = options.GetOrDefault<int>("max_batch", 1024);
-    opt.slots = options.GetOrDefault<int>("slots", 2);
-    opt.precision = precision;
-    opt.mlh = options.GetOrDefault<bool>("mlh", true) ? 1 : 0;
-    opt.flags = (options.GetOrDefault<bool>("tensor_cores", true) ? 0 : B200_FLAG_NO_TENSOR_CORES) |
-                (options.GetOrDefault<bool>("graph_capture", true) ? 0 : B200_FLAG_NO_GRAPHS);
+    FillBuilder(file, options, b);
+    const b200_net_options opt = MakeNetOptions(options, precision);
     Check(b200_net_create(b.get(), &opt, &net_));
     Check(b200_net_get_info(net_, &info_));
-    if (!info_.has_mlh) capabilities_.moves_left = NF::MOVES_LEFT_NONE;
+    if (!info_.has_mlh) capabilities_.moves_left = pblczero::NetworkFormat::MOVES_LEFT_NONE;
   }
   ~B200Network() override { b200_net_destroy(net_); }
 
@@ -336,6 +346,100 @@ std::unique_ptr<Network> MakeB200MuxNetwork(const std::optional<WeightsFile>& w,
   return std::make_unique<B200MuxNetwork>(*w, options);
 }
 REGISTER_NETWORK("b200-mux", MakeB200MuxNetwork, 86)
+
+
+// ---- one batch over several GPUs ----------------------------------------------------------------------------------
+// "b200-multi": what `demux` over per-GPU `b200` backends gives (DemuxingNetwork, src/neural/backends/network_demux.cc),
+// with the split done by the library (b200_multi_*): a computation keeps its planes and results in host vectors and
+// ComputeBlocking() hands the whole batch to b200_multi_eval_host, which cuts it into one contiguous slice per GPU.
+// Options: the ones of `b200` plus precision=fp16|bf16|fp32, gpus=<count> (default 2) and first_gpu (default 0);
+// max_batch is per GPU.
+class B200MultiComputation : public NetworkComputation {
+ public:
+  B200MultiComputation(b200_multi* multi, bool wdl, bool mlh) : multi_(multi), wdl_(wdl), mlh_(mlh) {}
+  void AddInput(InputPlanes&& input) override {
+    if (input.size() != static_cast<size_t>(kInputPlanes)) throw Exception("b200 backend: expected 112 input planes");
+    for (int i = 0; i < kInputPlanes; ++i) {
+      masks_.push_back(input[i].mask);
+      values_.push_back(input[i].value);
+    }
+    ++n_;
+  }
+  void ComputeBlocking() override {
+    if (n_ == 0) return;
+    policy_.resize(static_cast<size_t>(n_) * kPolicySize);
+    q_.resize(n_);
+    d_.resize(n_);
+    m_.resize(n_);
+    Check(b200_multi_eval_host(multi_, masks_.data(), values_.data(), n_, policy_.data(), q_.data(), d_.data(),
+                               m_.data()));
+  }
+  int GetBatchSize() const override { return n_; }
+  float GetQVal(int sample) const override { return q_[sample]; }
+  float GetDVal(int sample) const override { return wdl_ ? d_[sample] : 0.0f; }
+  float GetMVal(int sample) const override { return mlh_ ? m_[sample] : 0.0f; }
+  float GetPVal(int sample, int move_id) const override {
+    return policy_[static_cast<size_t>(sample) * kPolicySize + move_id];
+  }
+
+ private:
+  static constexpr int kPolicySize = 1858;
+  b200_multi* multi_;
+  bool wdl_, mlh_;
+  int n_ = 0;
+  std::vector<uint64_t> masks_;
+  std::vector<float> values_, policy_, q_, d_, m_;
+};
+
+int PrecisionByName(const OptionsDict& options, const char* backend) {
+  const std::string p = options.GetOrDefault<std::string>("precision", "fp16");
+  if (p == "fp16") return B200_PREC_FP16;
+  if (p == "bf16") return B200_PREC_BF16;
+  if (p == "fp32") return B200_PREC_FP32;
+  throw Exception(std::string(backend) + ": precision must be fp16, bf16 or fp32");
+}
+
+class B200MultiNetwork : public Network {
+ public:
+  B200MultiNetwork(const WeightsFile& file, const OptionsDict& options)
+      : capabilities_{file.format().network_format().input(), file.format().network_format().output(),
+                      file.format().network_format().moves_left()} {
+    Builder b;
+    FillBuilder(file, options, b);
+    const b200_net_options opt = MakeNetOptions(options, PrecisionByName(options, "b200-multi"));
+    const int count = options.GetOrDefault<int>("gpus", 2);
+    const int first = options.GetOrDefault<int>("first_gpu", 0);
+    if (count < 1 || count > 64) throw Exception("b200-multi: gpus must be between 1 and 64");
+    std::vector<int> ids;
+    for (int i = 0; i < count; ++i) ids.push_back(first + i);
+    Check(b200_multi_create(b.get(), &opt, ids.data(), count, &multi_));
+    Check(b200_net_get_info(b200_multi_net(multi_, 0), &info_));
+    if (!info_.has_mlh) capabilities_.moves_left = pblczero::NetworkFormat::MOVES_LEFT_NONE;
+    gpus_ = count;
+  }
+  ~B200MultiNetwork() override { b200_multi_destroy(multi_); }
+
+  const NetworkCapabilities& GetCapabilities() const override { return capabilities_; }
+  std::unique_ptr<NetworkComputation> NewComputation() override {
+    return std::make_unique<B200MultiComputation>(multi_, info_.wdl != 0, info_.has_mlh != 0);
+  }
+  int GetThreads() const override { return 2; }
+  bool IsCpu() const override { return false; }
+  int GetMiniBatchSize() const override { return 2 * info_.sm_count * gpus_; }
+  int GetPreferredBatchStep() const override { return gpus_; }
+
+ private:
+  NetworkCapabilities capabilities_;
+  b200_multi* multi_ = nullptr;
+  b200_net_info info_{};
+  int gpus_ = 1;
+};
+
+std::unique_ptr<Network> MakeB200MultiNetwork(const std::optional<WeightsFile>& w, const OptionsDict& options) {
+  if (!w) throw Exception("The b200-multi backend requires a network file.");
+  return std::make_unique<B200MultiNetwork>(*w, options);
+}
+REGISTER_NETWORK("b200-multi", MakeB200MultiNetwork, 85)
 
 
 // ---- native Backend ---------------------------------------------------------------------------------------------

@@ -335,3 +335,62 @@ class Mux:
             self.close()
         except Exception:  # noqa: BLE001 - interpreter shutdown
             pass
+
+
+class MultiGpuNetwork:
+    """One batch over several GPUs of the box: contiguous slices, replicated weights, no exchange (the role of lc0's
+    `demux` backend, src/neural/backends/network_demux.cc:268-330).  `options` as for Network plus
+    `gpus=0+1+2` (or a list); `max_batch` is per GPU."""
+
+    def __init__(self, net, options=None, gpus=None):
+        opts = parse_options(options)
+        lib = _lib.load()
+        self._lib = lib
+        self._h = None
+        if gpus is None:
+            gpus = [int(g) for g in str(opts.get("gpus", "0")).replace("+", " ").split()]
+        prec = str(opts.get("precision", "fp16")).lower()
+        if prec not in _lib.PRECISIONS:
+            raise ValueError("Unknown precision '%s'" % prec)
+        meta, tensors = _weights.flatten(net, policy_head=opts.get("policy_head", "vanilla"),
+                                         value_head=opts.get("value_head", "winner"))
+        b = ctypes.c_void_p()
+        _lib.check(lib.b200_builder_create(ctypes.byref(b)))
+        try:
+            for k, v in meta.items():
+                _lib.check(lib.b200_builder_set_int(b, k.encode(), int(v)))
+            for name, arr in tensors.items():
+                a = np.ascontiguousarray(arr, np.float32)
+                _lib.check(lib.b200_builder_add_tensor(b, name.encode(), a.ctypes.data, a.size))
+            o = _lib.NetOptions(gpu=0, max_batch=int(opts.get("max_batch", 1024)), precision=_lib.PRECISIONS[prec],
+                                slots=int(opts.get("slots", 1)), mlh=1 if _as_bool(opts.get("mlh", True)) else 0,
+                                flags=(0 if _as_bool(opts.get("tensor_cores", True)) else _lib.FLAG_NO_TENSOR_CORES) |
+                                      (0 if _as_bool(opts.get("graph_capture", True)) else _lib.FLAG_NO_GRAPHS))
+            ids = (ctypes.c_int * len(gpus))(*gpus)
+            h = ctypes.c_void_p()
+            _lib.check(lib.b200_multi_create(b, ctypes.byref(o), ids, len(gpus), ctypes.byref(h)))
+            self._h = h
+        finally:
+            lib.b200_builder_destroy(b)
+        self.gpus = list(gpus)
+
+    def evaluate(self, masks, values):
+        m = np.ascontiguousarray(masks, np.uint64).reshape(-1, 112)
+        v = np.ascontiguousarray(values, np.float32).reshape(-1, 112)
+        n = m.shape[0]
+        out = dict(policy=np.empty((n, 1858), np.float32), q=np.empty(n, np.float32),
+                   d=np.empty(n, np.float32), m=np.empty(n, np.float32))
+        _lib.check(self._lib.b200_multi_eval_host(self._h, m.ctypes.data, v.ctypes.data, n, out["policy"].ctypes.data,
+                                                  out["q"].ctypes.data, out["d"].ctypes.data, out["m"].ctypes.data))
+        return out
+
+    def close(self):
+        if self._h:
+            self._lib.b200_multi_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass

@@ -153,3 +153,23 @@ def test_mux_backend_matches_the_reference_outputs_and_searches_like_b200(tmp_pa
     r = subprocess.run([exe, "backendbench", "--weights=" + npath, "--backend=b200-mux",
                         "--backend-opts=precision=fp64", "--batches=1"], capture_output=True, text=True, timeout=300)
     assert "precision must be" in r.stdout + r.stderr
+
+
+@needs_plugin
+def test_multi_gpu_backend_matches_the_reference_outputs(tmp_path):
+    """"b200-multi" (the batch cut into one slice per GPU by the library); with one GPU in the box both slices run on
+    it (gpus=1 is the degenerate case, two networks on GPU 0 are covered by tests/test_gpu_multi.py)."""
+    import torch
+    count = min(2, torch.cuda.device_count())
+    net, pos, n, g = load_case("cfg4_mini")
+    npath, ppath, opath = str(tmp_path / "n.pb.gz"), str(tmp_path / "p.pos"), str(tmp_path / "o.bin")
+    mknet.write_net("cfg4_mini", npath)
+    _write_pos(ppath, pos, n)
+    r = subprocess.run([os.path.join(REF, "ref_eval"), "b200-multi", npath, ppath, opath,
+                        "max_batch=64,precision=fp32,gpus=%d" % count], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    raw = np.fromfile(opath, "<f4", offset=12)
+    pol = raw[:n * 1858].reshape(n, 1858)
+    q = raw[n * 1858:n * 1859]
+    assert np.abs(pol - g["policy"]).max() <= 1e-5 * np.abs(g["policy"]).max()
+    assert np.abs(q - g["q"]).max() <= 1e-5

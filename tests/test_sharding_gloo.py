@@ -53,3 +53,18 @@ def test_two_rank_gloo_group(tmp_path):
     assert float(line[1]) == float(np.arange(1000).sum())  # the two slices cover the batch exactly once
     assert float(line[2]) == 1.5                            # max over ranks
     assert int(line[3]) == 504
+
+
+def test_library_slices_agree_with_split_batch():
+    """The multi-GPU dispatcher of the library (b200_multi_slice, host code) cuts a batch exactly as split_batch."""
+    import ctypes
+    from lc0_b200 import _lib
+    lib = _lib.load()
+    for total, parts in ((10, 4), (8192, 8), (3, 8), (0, 2), (1025, 2), (1, 1), (4097, 3)):
+        want = sharding.split_batch(total, parts)
+        got = []
+        for i in range(parts):
+            b, c = ctypes.c_int(), ctypes.c_int()
+            lib.b200_multi_slice(total, parts, i, ctypes.byref(b), ctypes.byref(c))
+            got.append((b.value, b.value + c.value))
+        assert got == want
