@@ -7,7 +7,7 @@
 // It also registers "b200-native", a direct lczero::Backend (src/neural/backend.h:64-133) that skips the
 // Network-to-Backend wrapper of src/neural/wrapper.cc: the legal-move policy softmax of that wrapper runs on the
 // device and only the legal moves' probabilities come back to the host.
-// Build: add this file to lc0's source list and link libb200nn.so (see INTEGRATION.md); this file is GPL-3
+// Build: add this file to lc0's source list and link libb200nn.so; this file is GPL-3
 // like lc0 because it includes lc0 headers, the library behind the C ABI contains no lc0 code.
 //
 // Options (parsed like the reference CUDA backend's, src/neural/backends/cuda/network_cuda.cc:210-254):
