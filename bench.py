@@ -257,7 +257,9 @@ def main():
     if not args.batch:
         args.batch = cfg_batch // world if args.config == "cfg5" else cfg_batch
     net = mknet.make_net(net_name)
-    nw = network.Network(net, dict(gpu=local_rank, max_batch=args.batch, precision=args.precision))
+    # two workspace slots, as the lc0 plug-in creates the network: a second computation can stage its inputs and have
+    # its graph queued while the first one's kernels run (the phases with two computations in flight need it)
+    nw = network.Network(net, dict(gpu=local_rank, max_batch=args.batch, precision=args.precision, slots=2))
     del net
     info = nw.info
     B = args.batch
