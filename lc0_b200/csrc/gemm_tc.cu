@@ -275,6 +275,9 @@ struct TcParams {
   int out_f32;
   int* status;
   int tma_store;  // 1: 16-bit output staged in shared memory and written with TMA stores
+  // CTA-pair kernel: the tiles from split_from on are computed as two half-width tiles each (tiles_v virtual tiles in
+  // all), so that a last, less than half filled wave spreads over all pairs; split_from >= tiles_v means no split
+  int split_from, tiles_v;
   int conv_cblocks;  // > 0: 3x3 convolution, number of 64-channel blocks of the input (k_blocks = 9 * conv_cblocks)
   // folded LayerNorm (see GemmParams)
   const float* a_stats; const float* colsum; float a_inv_c, a_eps;
@@ -469,12 +472,17 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, uint8_t* buf, u
 struct SlabWalk {
   const TcParams& p;
   int first_tile, tile_step, tiles, n_tiles, tile_rows, row_offset, bn, groups;
-  __device__ __forceinline__ int n0(int t) const { return (t % n_tiles) * bn; }
-  __device__ __forceinline__ int m0(int t) const { return (t / n_tiles) * tile_rows + row_offset; }
+  int split_from;  // virtual tiles from here on are half-width halves of the tiles split_from, split_from + 1, ...
+  __device__ __forceinline__ int tile(int t) const { return t < split_from ? t : split_from + ((t - split_from) >> 1); }
+  __device__ __forceinline__ int width(int t) const { return t < split_from ? bn : bn / 2; }
+  __device__ __forceinline__ int n0(int t) const {
+    return (tile(t) % n_tiles) * bn + (t < split_from ? 0 : ((t - split_from) & 1) * (bn / 2));
+  }
+  __device__ __forceinline__ int m0(int t) const { return (tile(t) / n_tiles) * tile_rows + row_offset; }
   // cursor over the slabs of one epilogue group (columns g*64, (g + groups)*64, ... of each tile)
   struct Cursor { int t, c0; };
   __device__ __forceinline__ void settle(Cursor& c, int g) const {
-    while (c.t < tiles && (c.c0 >= bn || n0(c.t) + c.c0 >= p.N)) { c.t += tile_step; c.c0 = g * 64; }
+    while (c.t < tiles && (c.c0 >= width(c.t) || n0(c.t) + c.c0 >= p.N)) { c.t += tile_step; c.c0 = g * 64; }
   }
   __device__ __forceinline__ Cursor begin(int g) const {
     Cursor c{first_tile, g * 64};
@@ -483,7 +491,7 @@ struct SlabWalk {
   }
   __device__ __forceinline__ void next(Cursor& c, int g) const {
     c.c0 += 64 * groups;
-    if (c.c0 >= bn || n0(c.t) + c.c0 >= p.N) { c.t += tile_step; c.c0 = g * 64; }
+    if (c.c0 >= width(c.t) || n0(c.t) + c.c0 >= p.N) { c.t += tile_step; c.c0 = g * 64; }
     settle(c, g);
   }
 };
@@ -493,8 +501,8 @@ __device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtenso
                                                 const CUtensorMap* tmap_r, uint8_t* epi_mem, uint64_t* stg_full, uint64_t* stg_free,
                                                 uint64_t* res_bar, int g_lo, int g_hi, int first_tile, int tile_step,
                                                 int tiles, int n_tiles, int tile_rows, int row_offset, int bn,
-                                                volatile int* abort_flag) {
-  const SlabWalk w{p, first_tile, tile_step, tiles, n_tiles, tile_rows, row_offset, bn, kGroups};
+                                                int split_from, volatile int* abort_flag) {
+  const SlabWalk w{p, first_tile, tile_step, tiles, n_tiles, tile_rows, row_offset, bn, kGroups, split_from};
   SlabWalk::Cursor pf[kGroups];
   uint32_t pf_count[kGroups], count[kGroups];
 #pragma unroll
@@ -523,8 +531,8 @@ __device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtenso
   int prev = -1;
   bool ok = true;
   for (int t = first_tile; t < tiles && ok; t += tile_step) {
-    const int m0 = w.m0(t), n0 = w.n0(t);
-    for (int c0 = 0; c0 < bn; c0 += 64) {
+    const int m0 = w.m0(t), n0 = w.n0(t), width = w.width(t);
+    for (int c0 = 0; c0 < width; c0 += 64) {
       if (n0 + c0 >= p.N) break;
       const int g = (c0 >> 6) % kGroups;
       if (g < g_lo || g >= g_hi) continue;
@@ -687,7 +695,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ---------------- store warp: TMA stores of the staged slabs ----------------
     if (lane == 0 && p.tma_store)
       store_warp_loop<2, 2>(p, &tmap_c, &tmap_c, &tmap_r, epi_mem, stg_full, stg_free, res_bar, 0, 2, blockIdx.x, gridDim.x,
-                            tiles, n_tiles, BM, 0, BN, abort_flag);
+                            tiles, n_tiles, BM, 0, BN, 0x7fffffff, abort_flag);
   } else {
     // ---------------- epilogue (warps 2..9: two groups of four warps, alternating 64-column slabs) ----------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
@@ -860,7 +868,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const uint32_t rank = cluster_ctarank();
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
   const int m_tiles = (p.M + 2 * BM - 1) / (2 * BM), n_tiles = (p.N + BN - 1) / BN;
-  const int tiles = m_tiles * n_tiles;
+  // virtual tiles: the tiles from split_from on count twice, as a left and a right half of 128 columns
+  const int split_from = p.split_from < m_tiles * n_tiles ? p.split_from : 0x7fffffff;
+  const int tiles = split_from < m_tiles * n_tiles ? p.tiles_v : m_tiles * n_tiles;
+  auto tile_of = [&](int t) { return t < split_from ? t : split_from + ((t - split_from) >> 1); };
+  auto col_of = [&](int t) {
+    return (tile_of(t) % n_tiles) * BN + (t < split_from ? 0 : ((t - split_from) & 1) * (BN / 2));
+  };
+  auto width_of = [&](int t) { return t < split_from ? BN : BN / 2; };
+  // N of the MMA that computes virtual tile t: the tile's width, or what is left of N rounded up to 32
+  auto mma_n_of = [&](int t) { return pair_mma_n(p.N - col_of(t), width_of(t)); };
   const int k_blocks = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 64) {
@@ -906,10 +923,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t it = 0;
       bool ok = true;
       for (int t = pair; t < tiles && ok; t += pairs) {
-        const int m0 = (t / n_tiles) * (2 * BM) + (int)rank * BM;
-        // a narrower last tile is computed with a narrower MMA, of which each CTA supplies half the W rows
-        const int nt = (t % n_tiles) * BN;
-        const int n0 = nt + (int)rank * (pair_mma_n(p.N - nt, BN) / 2);
+        const int m0 = (tile_of(t) / n_tiles) * (2 * BM) + (int)rank * BM;
+        // a narrower tile is computed with a narrower MMA, of which each CTA supplies half the W rows
+        const int n0 = col_of(t) + (int)rank * (mma_n_of(t) / 2);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -937,7 +953,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tcgen05_fence_after();
         if (tile_it < 64) TRACE(512 + tile_it);
         const uint32_t d_tmem = tmem_base + acc * BN;
-        const uint32_t idesc = idesc_base | ((uint32_t)(pair_mma_n(p.N - (t % n_tiles) * BN, BN) >> 3) << 17);
+        const uint32_t idesc = idesc_base | ((uint32_t)(mma_n_of(t) >> 3) << 17);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -966,7 +982,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (lane == 0)
       store_warp_loop<kGroups, kBufs>(p, &tmap_c, &tmap_c2, &tmap_r, epi_mem, stg_full, stg_free, res_bar,
                                       (warp - 2) * (kGroups / 2), (warp - 1) * (kGroups / 2), pair, pairs, tiles, n_tiles,
-                                      2 * BM, (int)rank * BM, BN, abort_flag);
+                                      2 * BM, (int)rank * BM, BN, split_from, abort_flag);
   } else {
     // ---------------- epilogue (warps 4.. of both CTAs): group g handles the 64-column slabs g, g + kGroups, ... of
     // every tile ----------------
@@ -976,13 +992,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint32_t tile_it = 0, slab_it = 0;
     ColRegs cr;
     int cr_nb = -1;
-    if (pair < tiles && (pair % n_tiles) * BN + group * 64 < p.N) {
-      cr_nb = (pair % n_tiles) * BN + group * 64;  // first slab: fetched while the first tile is computed
+    if (pair < tiles && group * 64 < width_of(pair) && col_of(pair) + group * 64 < p.N) {
+      cr_nb = col_of(pair) + group * 64;  // first slab: fetched while the first tile is computed
       load_col_regs(p, cr_nb, lane, cr);
     }
     for (int t = pair; t < tiles; t += pairs, ++tile_it) {
       const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
-      const int m0 = (t / n_tiles) * (2 * BM) + (int)rank * BM, n0 = (t % n_tiles) * BN;
+      const int m0 = (tile_of(t) / n_tiles) * (2 * BM) + (int)rank * BM, n0 = col_of(t), width = width_of(t);
       if (leader && tile_it < 32) TRACE(2100 + (group * 32 + (int)tile_it) * 4 + 0);
       if (!mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4)) break;
       tcgen05_fence_after();
@@ -992,16 +1008,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       RowCtx rc;
       load_row_ctx(p, m, rc);
 #pragma unroll 1
-      for (int c0 = group * 64; c0 < BN; c0 += 64 * kGroups) {
+      for (int c0 = group * 64; c0 < width; c0 += 64 * kGroups) {
         if (n0 + c0 >= p.N) break;  // uniform over the group
         const int idx = group * kBufs + (int)(slab_it % kBufs);
         if (cr_nb != n0 + c0) load_col_regs(p, n0 + c0, lane, cr);
         // the slab this group handles next: further right in this tile, else the first one of its next tile
         int next_nb = -1;
-        if (c0 + 64 * kGroups < BN && n0 + c0 + 64 * kGroups < p.N) {
+        if (c0 + 64 * kGroups < width && n0 + c0 + 64 * kGroups < p.N) {
           next_nb = n0 + c0 + 64 * kGroups;
-        } else if (t + pairs < tiles) {
-          const int nn = ((t + pairs) % n_tiles) * BN + group * 64;
+        } else if (t + pairs < tiles && group * 64 < width_of(t + pairs)) {
+          const int nn = col_of(t + pairs) + group * 64;
           if (nn < p.N) next_nb = nn;
         }
         cr_nb = next_nb;
@@ -1166,6 +1182,7 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
   TcParams p;
   fill_folded(p, g);
   p.tma_store = tma_store ? 1 : 0;
+  p.split_from = 0x7fffffff; p.tiles_v = 0;
   p.bias = g.bias; p.C = g.C; p.ldc = g.ldc;
   p.M = g.M; p.N = g.N; p.K = g.K; p.act = g.act; p.scale = g.scale; p.alpha = g.alpha;
   p.out_f32 = g.out_f32 ? 1 : 0; p.status = status;
@@ -1228,6 +1245,20 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   const int tiles = ceil_div(g.M, 2 * BM) * ceil_div(g.N, Cfg::BN);
   const int max_pairs = sm_count / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  // A last wave that fills at most half of the pairs is computed as half-width tiles (twice as many, half as long), so
+  // that it costs about half a tile time instead of a whole one: 13-16 % of a product of three to six waves.
+  // Full-width tiles only; B200_SPLIT_LAST_WAVE=0 switches it off.
+  static const bool split_enabled = [] {
+    const char* e = getenv("B200_SPLIT_LAST_WAVE");
+    return !(e && e[0] == '0');
+  }();
+  const int rem = tiles % pairs;
+  p.split_from = 0x7fffffff;
+  p.tiles_v = tiles;
+  if (split_enabled && g.n_split == 0 && (g.N % Cfg::BN) == 0 && tiles > pairs && rem > 0 && 2 * rem <= pairs) {
+    p.split_from = tiles - rem;
+    p.tiles_v = tiles + rem;
+  }
   gemm_tc_pair_kernel<T, kGroups><<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, mc2, p);
   return cudaGetLastError();
 }

@@ -35,7 +35,9 @@ def test_expand_planes_empty(lib):
                                    (8192, 3072, 1024), (4096, 1024, 1536), (130, 4096, 256), (2048, 32, 1024),
                                    # CTA-pair kernel with row / column tails (narrow last MMA tile) and few k-blocks
                                    # (four epilogue groups)
-                                   (5000, 1312, 256), (3000, 2000, 1024), (2560, 1096, 320)])
+                                   (5000, 1312, 256), (3000, 2000, 1024), (2560, 1096, 320),
+                                   # a last wave of at most half the CTA pairs: computed as half-width tiles
+                                   (16384, 1024, 1024), (19200, 512, 256), (9600, 1024, 576)])
 @pytest.mark.parametrize("act", [oracle.ACT_NONE, oracle.ACT_RELU_2, oracle.ACT_MISH])
 def test_tensor_core_gemm(lib, prec, shape, act):
     M, N, K = shape

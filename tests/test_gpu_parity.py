@@ -230,3 +230,26 @@ def test_merged_qkv_and_smolgen_compression_launch_matches_separate_launches(mon
     scale = np.abs(outs[1]["policy"]).max()
     assert np.abs(outs[0]["policy"] - outs[1]["policy"]).max() <= 2e-3 * scale
     assert np.abs(outs[0]["q"] - outs[1]["q"]).max() <= 2e-3
+
+
+def test_split_last_wave_matches_whole_tiles(monkeypatch):
+    """Products whose last wave of 256x256 tiles fills at most half of the CTA pairs compute that wave as half-width
+    tiles (out-projection and FFN2 here, both with residual input and row statistics): same results as whole tiles."""
+    net = mknet.make_net("cfg4_2layer")
+    rng = np.random.default_rng(17)
+    n = 96  # 96 tiles per 1024-wide product on 74 pairs: 22 tiles in the last wave
+    masks = rng.integers(0, 2 ** 63, size=(n, 112), dtype=np.int64).astype(np.uint64) & rng.integers(
+        0, 2 ** 63, size=(n, 112), dtype=np.int64).astype(np.uint64)
+    values = np.ones((n, 112), np.float32)
+    outs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("B200_SPLIT_LAST_WAVE", flag)
+        nw = network.Network(net, "precision=fp16,max_batch=%d" % n)
+        outs.append(nw.evaluate(masks, values))
+        assert nw.device_status() == 0
+        nw.close()
+    # the same MMAs on the same operands, in a different order over the CTA pairs: identical up to the atomics'
+    # summation order in the row statistics
+    scale = np.abs(outs[1]["policy"]).max()
+    assert np.abs(outs[0]["policy"] - outs[1]["policy"]).max() <= 1e-3 * scale
+    assert np.abs(outs[0]["q"] - outs[1]["q"]).max() <= 1e-3
