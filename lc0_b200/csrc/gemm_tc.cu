@@ -843,7 +843,8 @@ template <typename T, int kGroups>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<kGroups>::kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_r,
-                    const __grid_constant__ CUtensorMap tmap_c2, const TcParams p) {
+                    const __grid_constant__ CUtensorMap tmap_c2, const __grid_constant__ CUtensorMap tmap_wh,
+                    const TcParams p) {
   using Cfg = PairCfg<kGroups>;
   constexpr int kBufs = Cfg::kBufs;
   constexpr int S = Cfg::kStages;
@@ -886,6 +887,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tma_prefetch_map(&tmap_c);
     if (p.res_mode) tma_prefetch_map(&tmap_r);
     if (p.n_split > 0) tma_prefetch_map(&tmap_c2);
+    if (p.split_from < p.tiles_v) tma_prefetch_map(&tmap_wh);
   }
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -926,17 +928,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int m0 = (tile_of(t) / n_tiles) * (2 * BM) + (int)rank * BM;
         // a narrower tile is computed with a narrower MMA, of which each CTA supplies half the W rows
         const int n0 = col_of(t) + (int)rank * (mma_n_of(t) / 2);
+        const bool half = t >= split_from;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, 1)) { ok = false; break; }
           const uint32_t fb_local = smem_u32(&full_bar[s]);
-          if (rank == 0) mbar_expect_tx(fb_local, 2 * Cfg::kStageBytes);  // both CTAs' bytes land on this barrier
+          // both CTAs' bytes land on this barrier; a half-width tile takes 64 W rows per CTA instead of 128
+          if (rank == 0) mbar_expect_tx(fb_local, half ? 2 * (BM + BN / 4) * BK * 2 : 2 * Cfg::kStageBytes);
           const uint32_t fb = mapa(fb_local, 0);
           const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
           if (it < 256) TRACE(it);
           tma_load_2d_pair(sa, &tmap_a, kb * BK, m0, fb);
-          tma_load_2d_pair(sa + BM * BK * 2, &tmap_w, kb * BK, n0, fb);
+          tma_load_2d_pair(sa + BM * BK * 2, half ? &tmap_wh : &tmap_w, kb * BK, n0, fb);
         }
       }
     }
@@ -1259,7 +1263,12 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
     p.split_from = tiles - rem;
     p.tiles_v = tiles + rem;
   }
-  gemm_tc_pair_kernel<T, kGroups><<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, mc2, p);
+  CUtensorMap mwh = mw;  // W in boxes of 64 rows, for the half-width tiles
+  if (p.split_from < p.tiles_v) {
+    e = get_map(g.W, g.ldw, g.N, g.K, Cfg::BN / 4, prec, &mwh);
+    if (e != cudaSuccess) return e;
+  }
+  gemm_tc_pair_kernel<T, kGroups><<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, mc2, mwh, p);
   return cudaGetLastError();
 }
 
