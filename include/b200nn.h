@@ -173,7 +173,7 @@ void b200_mux_destroy(b200_mux* mux);
 /* ---- One batch over several GPUs of the box ---------------------------------------------------------------------
  * Positions are independent: the batch is cut into contiguous slices whose sizes differ by at most one (b200_multi_slice),
  * one per GPU, the weights are replicated, nothing is exchanged.  The role of the reference's `demux` decorator
- * (DemuxingComputation::ComputeBlocking, src/neural/backends/network_demux.cc:268-330) without its per-slice
+ * (DemuxingComputation::ComputeBlocking, src/neural/backends/network_demux.cc:279-334) without its per-slice
  * computations: one persistent host thread per GPU evaluates its slice with b200_net_eval_host and writes the results
  * into the caller's arrays at the slice's offset.  `opt->gpu` is ignored, `opt->max_batch` is per GPU; the same GPU may
  * be listed more than once.  Calls are serialised. */

@@ -2,7 +2,7 @@
 // equal slices (sizes differ by at most one), one per GPU, with the weights replicated and no exchange step.
 //
 // What the reference's `demux` decorator does around per-GPU backends (DemuxingComputation::ComputeBlocking,
-// src/neural/backends/network_demux.cc:268-330: the batch is split into work items that the backends' worker threads
+// src/neural/backends/network_demux.cc:279-334: the batch is split into work items that the backends' worker threads
 // evaluate through their own computations), without the decorator's per-slice NewComputation and plane moves: one
 // persistent host thread per GPU calls b200_net_eval_host on its slice and writes the results straight into the
 // caller's arrays at the slice's offset.  Host code only; it drives the C ABI of include/b200nn.h.

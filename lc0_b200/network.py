@@ -339,7 +339,7 @@ class Mux:
 
 class MultiGpuNetwork:
     """One batch over several GPUs of the box: contiguous slices, replicated weights, no exchange (the role of lc0's
-    `demux` backend, src/neural/backends/network_demux.cc:268-330).  `options` as for Network plus
+    `demux` backend, src/neural/backends/network_demux.cc:279-334).  `options` as for Network plus
     `gpus=0+1+2` (or a list); `max_batch` is per GPU."""
 
     def __init__(self, net, options=None, gpus=None):
