@@ -269,7 +269,7 @@ REGISTER_NETWORK("b200-fp32", MakeB200Network<B200_PREC_FP32>, 88)
 
 
 // ---- batch aggregation inside the plug-in -----------------------------------------------------------------------
-// "b200-mux": what `multiplexing` over `b200` gives (MuxingNetwork, src/neural/backends/network_mux.cc:40-205), with
+// "b200-mux": what `multiplexing` over `b200` gives (MuxingComputation and MuxingNetwork, src/neural/backends/network_mux.cc:39-245), with
 // the merging done by the library's aggregator (b200_mux_*): every computation keeps its inputs and results in host
 // vectors of its own, ComputeBlocking() queues them and blocks until a worker has evaluated them together with the
 // requests of the other search threads or games.  For selfplay with many games of small batches.
