@@ -830,7 +830,7 @@ template <int kGroupsT> struct PairCfg {
   static constexpr int kTmemCols = 512;
   // warp 0 TMA, warp 1 MMA, warps 2 and 3 stores (half of the epilogue groups each), then kGroups epilogue groups of
   // four warps.  The 64 KB of staging are four buffers of 128 rows x 128 bytes: two groups with two buffers each
-  // (168 registers per thread; best when the main loop dominates) or four groups with one buffer each (96
+  // (138 registers per thread; best when the main loop dominates) or four groups with one buffer each (96
   // registers; twice the epilogue throughput, for products with few k-blocks per tile).
   static constexpr int kGroups = kGroupsT;
   static constexpr int kBufs = 4 / kGroupsT;
