@@ -75,7 +75,13 @@ typedef struct b200_net_options {
 
 enum {
   B200_FLAG_NO_TENSOR_CORES = 1, /* force the plain FMA matrix kernels in fp16/bf16 mode */
-  B200_FLAG_NO_GRAPHS = 2        /* launch kernels one by one instead of replaying captured CUDA graphs */
+  B200_FLAG_NO_GRAPHS = 2,       /* launch kernels one by one instead of replaying captured CUDA graphs */
+  /* Verification switches: each turns one fusion of the 16-bit tensor-core schedule off, so that a test can compare
+   * the fused schedule with the plain one on the same network (results agree to rounding). */
+  B200_FLAG_NO_LN_FOLD = 4,          /* run the encoder LayerNorms as kernels instead of folding them into the products */
+  B200_FLAG_NO_MERGED_COMPRESS = 8,  /* smolgen compression as a product of its own instead of riding on the QKV launch */
+  B200_FLAG_NO_SPLIT_LAST_WAVE = 16, /* whole 256x256 tiles in the last wave of the CTA-pair kernel */
+  B200_FLAG_NO_FUSED_SMOLGEN = 32    /* smolgen bias written by a product of its own and read back by the attention kernel */
 };
 
 typedef struct b200_net_info {
@@ -143,8 +149,13 @@ void* b200_net_stream(b200_net* net); /* cudaStream_t of slot 0 */
 
 /* Number of kernels this library launched on behalf of `net` since creation. */
 long long b200_net_launch_count(const b200_net* net);
-/* Device status word written by kernels whose bounded waits gave up (0 = none). */
+/* Device status word written by kernels whose bounded waits gave up (0 = none).  Every evaluation call reads its own
+ * slot's word with its results and returns B200_ERR_TIMEOUT (and clears the word) when it is set; this accessor is for
+ * diagnostics. */
 int b200_net_device_status(b200_net* net);
+/* Failure-injection hook for tests of that error path: writes `code` into the status words from the host, as a kernel
+ * that gave up would; the next evaluation of each slot then fails with B200_ERR_TIMEOUT.  No kernel is disturbed. */
+int b200_net_inject_device_status(b200_net* net, int code);
 
 /* Per-kernel-class timing with CUDA events recorded on the evaluation stream around every launch
  * (off by default).  Classes: 0 tensor-core GEMM, 1 FMA GEMM, 2 attention, 3 LayerNorm, 4 other.
@@ -155,6 +166,12 @@ int b200_net_device_status(b200_net* net);
 #define B200_PROFILE_CLASSES 5
 int b200_net_set_profiling(b200_net* net, int enabled);
 int b200_net_get_profile(b200_net* net, double* ms, double* work, long long* launches, int reset);
+/* The same sums by tag, for the launches that carry one (arrays of B200_PROFILE_TAGS entries): 1 QKV (+ smolgen
+ * compression), 2 attention output projection, 3 FFN dense 1, 4 FFN dense 2, 5 smolgen dense layers, 6 smolgen bias
+ * product, 7 attention, 8 embedding block, 9 heads; the products of ForwardEncoderLayer
+ * (src/neural/backends/blas/network_blas.cc:271-471) one by one. */
+#define B200_PROFILE_TAGS 16
+int b200_net_get_profile_tagged(b200_net* net, double* ms, double* work, long long* launches, int reset);
 
 /* ---- Batch aggregation across caller threads ------------------------------------------------------------------
  * Many threads with a few positions each, one GPU batch: the role of the reference's `multiplexing` decorator
@@ -261,11 +278,36 @@ int b200_op_expand_planes(const void* d_masks, const void* d_values, int n, void
                           int precision, void* stream);
 int b200_op_gemm(const void* A, const void* W, const float* bias, void* C, int M, int N, int K,
                  int activation, int precision, int use_tc, void* stream);
+/* b200_op_gemm_ex: the tensor-core product with every epilogue the network's schedule uses, for tests of those
+ *   epilogues on their own.  out = alpha * act(rstd_a * (scale * A . W^T - mean_a * colsum) + bias) + residual, where
+ *   - a_stats [M][2] (per-row sum and sum of squares of A's rows over K columns, with a_inv_c = 1/K and a_eps) and
+ *     colsum [N] describe a LayerNorm of A folded into the product (W then holds W * gamma, bias holds
+ *     beta . W^T + b): LayerNorm2DWithSkipConnection followed by Forward1D (backends/blas/encoder.h:29-78,
+ *     fully_connected_layer.cc:50-106) in one launch; NULL: plain product;
+ *   - res [M][N] is added after the activation, normalised on the fly with res_stats / res_gamma / res_beta
+ *     (res_inv_c = 1/N, res_eps) when those are given;
+ *   - out_stats [M][2] accumulates the per-row sum and sum of squares of the outputs (the caller zeroes it);
+ *   - columns [n_split, N) go to C2 (leading dimension ldc2) instead of C when n_split > 0.
+ *   Leading dimensions of 0 mean dense.  fp16 / bf16 only; synchronises the stream before returning. */
+typedef struct b200_gemm_desc {
+  const void* A; const void* W; const float* bias; void* C;
+  int M, N, K;
+  long long lda, ldw, ldc;
+  int activation, precision;
+  float scale, alpha;
+  const float* a_stats; const float* colsum; float a_inv_c, a_eps;
+  const void* res; long long ldres;
+  const float* res_stats; const float* res_gamma; const float* res_beta; float res_inv_c, res_eps;
+  float* out_stats;
+  void* C2; long long ldc2; int n_split;
+  int whole_tiles;
+} b200_gemm_desc;
+int b200_op_gemm_ex(const b200_gemm_desc* d, void* stream);
 /* b200_op_attention: out = softmax(Q K^T / sqrt(depth) + bias) V for every (position, head) of n positions of 64
  *   tokens (BlasComputation::ForwardEncoderLayer, network_blas.cc:352-439).  q, k, v: [n*64] rows with leading
  *   dimension ld (elements), head h in columns [h*depth, (h+1)*depth); bias: [n][heads][64][64] or NULL; out:
- *   [n*64] rows with leading dimension ldo.  variant 0: FMA kernel (any precision); 1: cp.async + mma.sync kernel;
- *   2: persistent TMA kernel (the one the network uses).  1 and 2 take fp16 / bf16 and depth 32 or 64. */
+ *   [n*64] rows with leading dimension ldo.  variant 0: FMA kernel (any precision); 1: persistent TMA +
+ *   tensor-core kernel (the one the network uses; fp16 / bf16, depth 32 or 64). */
 int b200_op_attention(const void* q, const void* k, const void* v, long long ld, const void* bias, void* out,
                       long long ldo, int n, int heads, int depth, int precision, int variant, void* stream);
 /* b200_op_gemm_timed: the tensor-core product of b200_op_gemm queued `launches` times back to back on `stream`

@@ -16,6 +16,10 @@ PREC_FP32, PREC_FP16, PREC_BF16 = 0, 1, 2
 PRECISIONS = {"fp32": PREC_FP32, "fp16": PREC_FP16, "bf16": PREC_BF16}
 FLAG_NO_TENSOR_CORES = 1
 FLAG_NO_GRAPHS = 2
+FLAG_NO_LN_FOLD = 4
+FLAG_NO_MERGED_COMPRESS = 8
+FLAG_NO_SPLIT_LAST_WAVE = 16
+FLAG_NO_FUSED_SMOLGEN = 32
 POLICY_SIZE = 1858
 INPUT_PLANES = 112
 
@@ -29,6 +33,23 @@ class B200Error(RuntimeError):
 class NetOptions(ctypes.Structure):
     _fields_ = [("gpu", ctypes.c_int), ("max_batch", ctypes.c_int), ("precision", ctypes.c_int),
                 ("slots", ctypes.c_int), ("mlh", ctypes.c_int), ("flags", ctypes.c_int)]
+
+
+class GemmDesc(ctypes.Structure):
+    """b200_gemm_desc (include/b200nn.h)."""
+    _fields_ = [("A", ctypes.c_void_p), ("W", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("C", ctypes.c_void_p),
+                ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
+                ("lda", ctypes.c_longlong), ("ldw", ctypes.c_longlong), ("ldc", ctypes.c_longlong),
+                ("activation", ctypes.c_int), ("precision", ctypes.c_int),
+                ("scale", ctypes.c_float), ("alpha", ctypes.c_float),
+                ("a_stats", ctypes.c_void_p), ("colsum", ctypes.c_void_p),
+                ("a_inv_c", ctypes.c_float), ("a_eps", ctypes.c_float),
+                ("res", ctypes.c_void_p), ("ldres", ctypes.c_longlong),
+                ("res_stats", ctypes.c_void_p), ("res_gamma", ctypes.c_void_p), ("res_beta", ctypes.c_void_p),
+                ("res_inv_c", ctypes.c_float), ("res_eps", ctypes.c_float),
+                ("out_stats", ctypes.c_void_p),
+                ("C2", ctypes.c_void_p), ("ldc2", ctypes.c_longlong), ("n_split", ctypes.c_int),
+                ("whole_tiles", ctypes.c_int)]
 
 
 class NetInfo(ctypes.Structure):
@@ -91,12 +112,15 @@ SIGNATURES = {
     "b200_net_stream": (_P, [_P]),
     "b200_net_launch_count": (ctypes.c_longlong, [_P]),
     "b200_net_device_status": (_I, [_P]),
+    "b200_net_inject_device_status": (_I, [_P, _I]),
+    "b200_net_get_profile_tagged": (_I, [_P, _P, _P, _P, _I]),
     "b200_net_set_profiling": (_I, [_P, _I]),
     "b200_net_get_profile": (_I, [_P, _P, _P, _P, _I]),
     "b200_op_expand_planes": (_I, [_P, _P, _I, _P, _I, _P]),
     "b200_op_encode_positions": (_I, [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P]),
     "b200_op_planes_from_training_data": (_I, [_P, _I, ctypes.c_longlong, _I, _P, _P, _P, _P]),
     "b200_op_gemm": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "b200_op_gemm_ex": (_I, [ctypes.POINTER(GemmDesc), _P]),
     "b200_op_attention": (_I, [_P, _P, _P, ctypes.c_longlong, _P, _P, ctypes.c_longlong, _I, _I, _I, _I, _I, _P]),
     "b200_op_gemm_timed": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.POINTER(ctypes.c_float), _P]),
     "b200_op_policy_attention": (_I, [_P, _P, _P, _I, _I, _P, _P, _I, _P]),

@@ -221,7 +221,11 @@ b200_net_options MakeNetOptions(const OptionsDict& options, int precision) {
   opt.precision = precision;
   opt.mlh = options.GetOrDefault<bool>("mlh", true) ? 1 : 0;
   opt.flags = (options.GetOrDefault<bool>("tensor_cores", true) ? 0 : B200_FLAG_NO_TENSOR_CORES) |
-              (options.GetOrDefault<bool>("graph_capture", true) ? 0 : B200_FLAG_NO_GRAPHS);
+              (options.GetOrDefault<bool>("graph_capture", true) ? 0 : B200_FLAG_NO_GRAPHS) |
+              (options.GetOrDefault<bool>("fold_ln", true) ? 0 : B200_FLAG_NO_LN_FOLD) |
+              (options.GetOrDefault<bool>("merge_compress", true) ? 0 : B200_FLAG_NO_MERGED_COMPRESS) |
+              (options.GetOrDefault<bool>("split_last_wave", true) ? 0 : B200_FLAG_NO_SPLIT_LAST_WAVE) |
+              (options.GetOrDefault<bool>("fused_smolgen", true) ? 0 : B200_FLAG_NO_FUSED_SMOLGEN);
   return opt;
 }
 

@@ -4,16 +4,13 @@
 //   P = softmax_rows(S)
 //   O = P V
 //
-// Two kernels with the same arithmetic.  In both, a warp owns 16 query rows, computes its 16x64 slab of S with
-// m16n8k16 tensor-core MMAs (fp32 accumulation), does the softmax in registers (row reductions by quad shuffles)
-// and reuses the probabilities as the A operand of the second product.  The problem is 64x64x32 per head, far
-// below one tcgen05 tile, and the operator is bound by the HBM traffic of Q/K/V/bias, so the warp-level MMA shape
-// is the right granularity here.
-//   attention_tma_kernel  persistent CTAs; a producer lane streams the tiles of successive (position, head) items
-//                         into a ring of swizzled shared-memory stages with TMA loads, the compute warps only touch
-//                         shared memory and hand their slab of O to a TMA store.  The one the network uses.
-//   attention_tc_kernel   one CTA per item, 16-byte cp.async copies into padded shared memory, 16-byte global
-//                         stores.  Limited by instruction issue (its time follows the SM clock); kept for comparison.
+// A warp owns 16 query rows, computes its 16x64 slab of S with m16n8k16 tensor-core MMAs (fp32 accumulation), does
+// the softmax in registers (row reductions by quad shuffles) and reuses the probabilities as the A operand of the
+// second product.  The problem is 64x64x32 per head, far below one tcgen05 tile, and the operator is bound by the
+// HBM traffic of Q/K/V/bias, so the warp-level MMA shape is the right granularity here.
+// attention_tma_kernel: persistent CTAs; a producer lane streams the tiles of successive (position, head) items
+// into a ring of swizzled shared-memory stages with TMA loads, the compute warps only touch shared memory and hand
+// their slab of O to a TMA store.
 //
 // Reference: BlasComputation::ForwardEncoderLayer, src/neural/backends/blas/network_blas.cc:352-439
 // (per-head sgemm, SoftmaxActivation, sgemm); the reference CUDA backend does this with two batched
@@ -35,145 +32,15 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
-// Shared-memory rows are padded by 16 bytes so that the eight 16-byte rows an ldmatrix phase (or a quad-row
-// bias read) touches fall into distinct bank groups.
-template <int D> struct AttnSmem {
-  static constexpr int kRow = D * 2 + 16;       // bytes per Q/K/V row
-  static constexpr int kBiasRow = 64 * 2 + 16;  // bytes per bias row
-  static constexpr int kBytes = 3 * 64 * kRow + 64 * kBiasRow;
-};
-
-template <typename T, int D>
-__global__ void __launch_bounds__(128)
-attention_tc_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long long ld,
-                    const T* __restrict__ bias, T* __restrict__ out, long long ldo, int heads, float scale) {
-  using L = AttnSmem<D>;
-  extern __shared__ __align__(16) uint8_t sm[];
-  uint8_t* sq = sm;
-  uint8_t* sk = sq + 64 * L::kRow;
-  uint8_t* sv = sk + 64 * L::kRow;
-  uint8_t* sb = sv + 64 * L::kRow;
-  const int n = blockIdx.x / heads, h = blockIdx.x - n * heads;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const long long base = (long long)n * 64 * ld + (long long)h * D;
-  constexpr int kChunks = D / 8;  // 16-byte chunks per row
-  for (int i = tid; i < 64 * kChunks; i += 128) {
-    const int r = i / kChunks, c = i - r * kChunks;
-    const long long g = base + r * ld + c * 8;
-    cp_async16(sq + r * L::kRow + c * 16, q + g);
-    cp_async16(sk + r * L::kRow + c * 16, k + g);
-    cp_async16(sv + r * L::kRow + c * 16, v + g);
-  }
-  if (bias) {
-    const T* bsrc = bias + ((long long)n * heads + h) * 4096;
-    for (int i = tid; i < 64 * 8; i += 128) {
-      const int r = i >> 3, c = i & 7;
-      cp_async16(sb + r * L::kBiasRow + c * 16, bsrc + r * 64 + c * 8);
-    }
-  }
-  cp_async_wait_all();
-  __syncthreads();
-
-  const int m0 = warp * 16;
-  const int g = lane >> 2, t = lane & 3;
-  // ---- S = Q K^T : 8 key tiles of 8, fp32 accumulators ----
-  float s[8][4];
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
-#pragma unroll
-  for (int ks = 0; ks < D / 16; ++ks) {
-    uint32_t a[4];
-    ldmatrix_x4(a, sq + (m0 + (lane & 15)) * L::kRow + (ks * 16 + (lane >> 4) * 8) * 2);
-#pragma unroll
-    for (int np = 0; np < 4; ++np) {
-      uint32_t b[4];
-      ldmatrix_x4(b, sk + (np * 16 + (lane & 7) + (lane >> 4) * 8) * L::kRow + (ks * 16 + ((lane >> 3) & 1) * 8) * 2);
-      mma16816<T>(s[2 * np], a, b[0], b[1]);
-      mma16816<T>(s[2 * np + 1], a, b[2], b[3]);
-    }
-  }
-  // ---- scale, bias, row softmax (rows g and g+8 of this warp's slab) ----
-  float mx0 = -3.0e38f, mx1 = -3.0e38f;
-#pragma unroll
-  for (int nt = 0; nt < 8; ++nt) {
-    float2 b0 = make_float2(0.f, 0.f), b1 = make_float2(0.f, 0.f);
-    if (bias) {
-      b0 = unpack2<T>(*reinterpret_cast<const uint32_t*>(sb + (m0 + g) * L::kBiasRow + (nt * 8 + 2 * t) * 2));
-      b1 = unpack2<T>(*reinterpret_cast<const uint32_t*>(sb + (m0 + g + 8) * L::kBiasRow + (nt * 8 + 2 * t) * 2));
-    }
-    s[nt][0] = fmaf(s[nt][0], scale, b0.x);
-    s[nt][1] = fmaf(s[nt][1], scale, b0.y);
-    s[nt][2] = fmaf(s[nt][2], scale, b1.x);
-    s[nt][3] = fmaf(s[nt][3], scale, b1.y);
-    mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
-    mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
-  }
-  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-  float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-  for (int nt = 0; nt < 8; ++nt) {
-    s[nt][0] = __expf(s[nt][0] - mx0);
-    s[nt][1] = __expf(s[nt][1] - mx0);
-    s[nt][2] = __expf(s[nt][2] - mx1);
-    s[nt][3] = __expf(s[nt][3] - mx1);
-    sum0 += s[nt][0] + s[nt][1];
-    sum1 += s[nt][2] + s[nt][3];
-  }
-  sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
-  sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
-  sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
-  sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
-  const float inv0 = 1.0f / sum0, inv1 = 1.0f / sum1;
-  // ---- O = P V : probabilities become the A operand (normalised first, like the reference) ----
-  float o[D / 8][4];
-#pragma unroll
-  for (int i = 0; i < D / 8; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {  // 16 keys per step
-    uint32_t a[4];
-    a[0] = pack2<T>(s[2 * j][0] * inv0, s[2 * j][1] * inv0);
-    a[1] = pack2<T>(s[2 * j][2] * inv1, s[2 * j][3] * inv1);
-    a[2] = pack2<T>(s[2 * j + 1][0] * inv0, s[2 * j + 1][1] * inv0);
-    a[3] = pack2<T>(s[2 * j + 1][2] * inv1, s[2 * j + 1][3] * inv1);
-#pragma unroll
-    for (int np = 0; np < D / 16; ++np) {
-      uint32_t b[4];
-      ldmatrix_x4_trans(b, sv + (j * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * L::kRow + (np * 16 + (lane >> 4) * 8) * 2);
-      mma16816<T>(o[2 * np], a, b[0], b[1]);
-      mma16816<T>(o[2 * np + 1], a, b[2], b[3]);
-    }
-  }
-  // ---- write the 16 x D slab through this warp's (now unused) Q rows ----
-  __syncwarp();
-#pragma unroll
-  for (int nt = 0; nt < D / 8; ++nt) {
-    *reinterpret_cast<uint32_t*>(sq + (m0 + g) * L::kRow + (nt * 8 + 2 * t) * 2) = pack2<T>(o[nt][0], o[nt][1]);
-    *reinterpret_cast<uint32_t*>(sq + (m0 + g + 8) * L::kRow + (nt * 8 + 2 * t) * 2) = pack2<T>(o[nt][2], o[nt][3]);
-  }
-  __syncwarp();
-  for (int i = lane; i < 16 * kChunks; i += 32) {
-    const int r = i / kChunks, c = i - r * kChunks;
-    const uint4 val = *reinterpret_cast<const uint4*>(sq + (m0 + r) * L::kRow + c * 16);
-    *reinterpret_cast<uint4*>(out + ((long long)n * 64 + m0 + r) * ldo + (long long)h * D + c * 8) = val;
-  }
-}
-
 // ------------------------------------------------------------------------------------------------
-// Persistent variant.  A CTA is four compute warps and one producer warp and walks over (position, head) items
+// A CTA is four compute warps and one producer warp and walks over (position, head) items
 // blockIdx.x, blockIdx.x + gridDim.x, ...  The producer's elected lane brings the bias tile (64 x 64) and the Q, K, V
 // tiles (64 x D) of an item into one stage of a shared-memory ring with four TMA loads (swizzled: 128-byte rows for
 // the bias, D*2-byte rows for Q, K, V) that complete on the stage's `full` mbarrier; each compute warp owns 16 query
-// rows exactly as in the kernel above, releases the stage with an arrival on its `empty` mbarrier after its last
-// read, and writes its 16 x D slab of O with a TMA store of its own from one of two swizzled staging slabs.  The
-// compute warps never issue a global-memory instruction, which is what this kernel is about: the one above is
-// limited by instruction issue (its time follows the SM clock), not by HBM.
+// rows, releases the stage with an arrival on its `empty` mbarrier after its last read, and writes its 16 x D slab
+// of O with a TMA store of its own from one of two swizzled staging slabs.  The compute warps never issue a
+// global-memory instruction: a version whose compute warps did their own loads and stores was limited by
+// instruction issue (its time followed the SM clock), not by HBM.
 // Every mbarrier wait is bounded; a wait that gives up raises the CTA's abort flag and the status word.
 // ------------------------------------------------------------------------------------------------
 template <int D, int NS> struct AttnTma {
@@ -466,20 +333,6 @@ bool attention_tc_supported(long long ld, long long ldo, int depth, const void* 
          al(out);
 }
 
-template <typename T>
-cudaError_t launch_attention_tc(const T* q, const T* k, const T* v, long long ld, const T* bias, T* out,
-                                long long ldo, int n, int heads, int depth, float scale, cudaStream_t s) {
-  if (n <= 0) return cudaSuccess;
-  if (depth == 32) {
-    attention_tc_kernel<T, 32><<<n * heads, 128, AttnSmem<32>::kBytes, s>>>(q, k, v, ld, bias, out, ldo, heads, scale);
-  } else if (depth == 64) {
-    attention_tc_kernel<T, 64><<<n * heads, 128, AttnSmem<64>::kBytes, s>>>(q, k, v, ld, bias, out, ldo, heads, scale);
-  } else {
-    return cudaErrorInvalidValue;
-  }
-  return cudaGetLastError();
-}
-
 template <typename T, int D, int NS>
 static cudaError_t launch_attention_tma_cfg(const T* q, const T* k, const T* v, long long ld, const T* bias, T* out,
                                             long long ldo, int n, int heads, float scale, int* status, int sm_count,
@@ -531,14 +384,6 @@ template cudaError_t launch_attention_tma<__nv_bfloat16>(const __nv_bfloat16*, c
                                                          const __nv_bfloat16*, long long, const __nv_bfloat16*,
                                                          __nv_bfloat16*, long long, int, int, int, float, int*, int,
                                                          cudaStream_t);
-
-template cudaError_t launch_attention_tc<__half>(const __half*, const __half*, const __half*, long long,
-                                                 const __half*, __half*, long long, int, int, int, float,
-                                                 cudaStream_t);
-template cudaError_t launch_attention_tc<__nv_bfloat16>(const __nv_bfloat16*, const __nv_bfloat16*,
-                                                        const __nv_bfloat16*, long long, const __nv_bfloat16*,
-                                                        __nv_bfloat16*, long long, int, int, int, float,
-                                                        cudaStream_t);
 
 }  // namespace b200
 

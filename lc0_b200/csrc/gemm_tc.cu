@@ -256,15 +256,6 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
          ((uint32_t)(BM >> 4) << 24);
 }
 
-#ifdef B200_TRACE
-// Development aid (not compiled into the library): clock64() checkpoints of CTA 0 of the pair kernel.
-__device__ long long g_trace[4096];
-__device__ int g_trace_on;
-#define TRACE(idx) do { if (blockIdx.x == 0 && g_trace_on && (idx) < 4096) g_trace[(idx)] = clock64(); } while (0)
-#else
-#define TRACE(idx) do { } while (0)
-#endif
-
 struct TcParams {
   const float* bias;
   void* C;
@@ -350,9 +341,7 @@ template <typename T>
 __device__ __forceinline__ void epilogue_slab(const TcParams& p, uint8_t* buf, uint32_t res_bar, uint32_t free_bar,
                                               uint32_t full_bar, uint32_t use, bool leader, uint32_t taddr, int row,
                                               int lane, int nb, int next_nb, ColRegs& cr, float* wvec, RowCtx& rc,
-                                              volatile int* abort_flag, int tr = -1) {
-#define ET(k) do { if (leader && tr >= 0) TRACE(tr + (k)); } while (0)
-  ET(0);
+                                              volatile int* abort_flag) {
   __syncwarp();  // the previous slab's reads of wvec are done
   if (p.bias) { wvec[lane] = cr.bias0; wvec[32 + lane] = cr.bias1; }
   if (p.a_stats) { wvec[64 + lane] = cr.cs0; wvec[96 + lane] = cr.cs1; }
@@ -362,7 +351,6 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, uint8_t* buf, u
   }
   __syncwarp();
   if (next_nb >= 0) load_col_regs(p, next_nb, lane, cr);  // in flight during the arithmetic below
-  ET(1);
   uint8_t* srow = buf + row * 128;
   // The slab is processed as two halves of 32 columns (keeps the register footprint of an epilogue thread small
   // enough for sixteen epilogue warps per CTA).
@@ -398,13 +386,11 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, uint8_t* buf, u
     }
     apply_activation(v, p.act);
     if (h == 0) {
-      ET(2);
       // Every thread does its own bounded wait (after a failed wait the result is meaningless and the status word
       // says so): for the residual tile, which the store warp fetched into `buf` once the buffer was free, or
       // for the buffer itself.
       if (p.res_mode) mbar_wait(res_bar, use & 1, abort_flag, 5);
       else mbar_wait(free_bar, (use & 1) ^ 1, abort_flag, 6);
-      ET(3);
     }
     if (p.res_mode) {
 #pragma unroll
@@ -455,12 +441,9 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, uint8_t* buf, u
       *reinterpret_cast<uint4*>(srow + ((cc ^ (row & 7)) << 4)) = o;
     }
   }
-  ET(6);
   fence_async_smem();  // this thread's writes are visible to the TMA store the store warp will issue
   __syncwarp();
   if (lane == 0) mbar_arrive(full_bar);
-  ET(7);
-#undef ET
 }
 
 // A store thread's side of the fast path: for every slab of this CTA's tiles that belongs to the epilogue groups
@@ -539,7 +522,6 @@ __device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtenso
       const uint32_t s = count[g]++;
       const int idx = g * kBufs + (int)(s % kBufs);
       if (!mbar_wait(smem_u32(&stg_full[idx]), (s / kBufs) & 1, abort_flag, 7)) { ok = false; break; }
-      if (g_lo == 0) TRACE(3100);
       if (p.n_split > 0 && n0 >= p.n_split)
         tma_store_2d(tmap_c2, n0 + c0 - p.n_split, m0, smem_u32(epi_mem + idx * (BM * 128)));
       else
@@ -557,9 +539,7 @@ __device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtenso
       }
     }
   }
-  if (g_lo == 0) TRACE(3101);
   tma_store_wait_all();  // stores must complete before the CTA exits
-  if (g_lo == 0) TRACE(3102);
 }
 
 template <int BN> struct TileCfg {
@@ -596,7 +576,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   float* wvec = reinterpret_cast<float*>(bar_mem + 512) + ((threadIdx.x >> 5) & 7) * 256;  // per-warp scratch
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) TRACE(3000);
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
   const int tiles = m_tiles * n_tiles;
   const int k_blocks = p.conv_cblocks > 0 ? 9 * p.conv_cblocks : (p.K + BK - 1) / BK;
@@ -634,7 +613,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) TRACE(3001);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -790,11 +768,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   }
 
-  if (threadIdx.x == 0) TRACE(3002);
   __syncwarp();
   tcgen05_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) TRACE(3003);
   if (*abort_flag) {
     // Give copies that may still be in flight time to land before the CTA's shared memory is released.
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
@@ -865,7 +841,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   float* wvec = reinterpret_cast<float*>(bar_mem + 512) + ((threadIdx.x >> 5) & 15) * 256;  // per-warp scratch
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) TRACE(3000);
   const uint32_t rank = cluster_ctarank();
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
   const int m_tiles = (p.M + 2 * BM - 1) / (2 * BM), n_tiles = (p.N + BN - 1) / BN;
@@ -917,7 +892,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) TRACE(3001);
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
@@ -938,7 +912,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (rank == 0) mbar_expect_tx(fb_local, half ? 2 * (BM + BN / 4) * BK * 2 : 2 * Cfg::kStageBytes);
           const uint32_t fb = mapa(fb_local, 0);
           const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
-          if (it < 256) TRACE(it);
           tma_load_2d_pair(sa, &tmap_a, kb * BK, m0, fb);
           tma_load_2d_pair(sa + BM * BK * 2, half ? &tmap_wh : &tmap_w, kb * BK, n0, fb);
         }
@@ -955,7 +928,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
         if (!mbar_wait(smem_u32(&tempty_bar[acc]), aph ^ 1, abort_flag, 2)) break;
         tcgen05_fence_after();
-        if (tile_it < 64) TRACE(512 + tile_it);
         const uint32_t d_tmem = tmem_base + acc * BN;
         const uint32_t idesc = idesc_base | ((uint32_t)(mma_n_of(t) >> 3) << 17);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -963,7 +935,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           const uint32_t ph = (it / S) & 1;
           if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, 3)) { ok = false; break; }
           tcgen05_fence_after();
-          if (it < 256) TRACE(256 + it);
           const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
           const uint64_t adesc = make_smem_desc(sa);
           const uint64_t bdesc = make_smem_desc(sa + BM * BK * 2);
@@ -1003,10 +974,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     for (int t = pair; t < tiles; t += pairs, ++tile_it) {
       const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
       const int m0 = (tile_of(t) / n_tiles) * (2 * BM) + (int)rank * BM, n0 = col_of(t), width = width_of(t);
-      if (leader && tile_it < 32) TRACE(2100 + (group * 32 + (int)tile_it) * 4 + 0);
       if (!mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4)) break;
       tcgen05_fence_after();
-      if (leader && tile_it < 32) TRACE(2100 + (group * 32 + (int)tile_it) * 4 + 1);
       const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       const int m = m0 + quarter * 32 + lane;
       RowCtx rc;
@@ -1027,24 +996,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         cr_nb = next_nb;
         epilogue_slab<T>(p, epi_mem + idx * (BM * 128), smem_u32(&res_bar[idx]), smem_u32(&stg_free[idx]),
                          smem_u32(&stg_full[idx]), slab_it / kBufs, leader, trow + c0, quarter * 32 + lane, lane,
-                         n0 + c0, next_nb, cr, wvec, rc, abort_flag,
-                         slab_it < 32 ? 1024 + (group * 32 + (int)slab_it) * 8 : -1);
+                         n0 + c0, next_nb, cr, wvec, rc, abort_flag);
         ++slab_it;
       }
       flush_row_ctx(p, m, rc);
       tcgen05_fence_before();
       __syncwarp();
-      if (leader && tile_it < 32) TRACE(2100 + (group * 32 + (int)tile_it) * 4 + 2);
       if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&tempty_bar[acc]), 0));
-      if (leader && tile_it < 32) TRACE(2100 + (group * 32 + (int)tile_it) * 4 + 3);
     }
   }
 
-  if (threadIdx.x == 0) TRACE(3002);
   __syncwarp();
   tcgen05_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) TRACE(3003);
   if (*abort_flag) {
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, 200 + *abort_flag);
@@ -1237,25 +1201,13 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   p.M = g.M; p.N = g.N; p.K = g.K; p.act = g.act; p.scale = g.scale; p.alpha = g.alpha;
   p.out_f32 = 0; p.status = status;
   p.conv_cblocks = 0;
-#ifdef B200_TRACE
-  {  // development aid: B200_TRACE_LAUNCH=<k> records the k-th launch of this kernel (default: every launch)
-    static std::atomic<int> counter{0};
-    const char* sel = getenv("B200_TRACE_LAUNCH");
-    const int on = (!sel || atoi(sel) == counter.load()) ? 1 : 0;
-    counter++;
-    cudaMemcpyToSymbolAsync(g_trace_on, &on, sizeof(int), 0, cudaMemcpyHostToDevice, s);
-  }
-#endif
   const int tiles = ceil_div(g.M, 2 * BM) * ceil_div(g.N, Cfg::BN);
   const int max_pairs = sm_count / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   // A last wave that fills at most half of the pairs is computed as half-width tiles (twice as many, half as long), so
   // that it costs about half a tile time instead of a whole one: 13-16 % of a product of three to six waves.
-  // Full-width tiles only; B200_SPLIT_LAST_WAVE=0 switches it off.
-  static const bool split_enabled = [] {
-    const char* e = getenv("B200_SPLIT_LAST_WAVE");
-    return !(e && e[0] == '0');
-  }();
+  // Full-width tiles only; GemmParams::whole_tiles switches it off.
+  const bool split_enabled = !g.whole_tiles;
   const int rem = tiles % pairs;
   p.split_from = 0x7fffffff;
   p.tiles_v = tiles;
@@ -1318,12 +1270,8 @@ bool gemm_tc_supported(const GemmParams& p) {
 namespace {
 // Large problems with 16-bit output go to the CTA-pair kernel (256x256 tiles).
 bool pair_eligible(const GemmParams& p, int sm_count) {
-  static const bool pair_enabled = [] {
-    const char* e = getenv("B200_GEMM_PAIR");
-    return !(e && e[0] == '0');
-  }();
   const bool tma_store_ok = !p.out_f32 && (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
-  return pair_enabled && tma_store_ok && p.conv_cin == 0 && p.M >= 512 && p.N > 128 &&
+  return tma_store_ok && p.conv_cin == 0 && p.M >= 512 && p.N > 128 &&
          (long long)ceil_div(p.M, 2 * BM) * ceil_div(p.N, 256) >= sm_count / 4;
 }
 }  // namespace
@@ -1342,12 +1290,8 @@ cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaS
   if (pair_eligible(p, sm_count))
   {
     // Four epilogue groups when a tile has few k-blocks (the epilogue then sets the pace), two otherwise (fewer
-    // warps compete with the MMA issuer and the producer).  B200_PAIR_GROUPS=2|4 overrides.
-    static const int forced = [] {
-      const char* e = getenv("B200_PAIR_GROUPS");
-      return e ? atoi(e) : 0;
-    }();
-    const bool four = forced ? forced == 4 : p.K <= 8 * BK;
+    // warps compete with the MMA issuer and the producer).
+    const bool four = p.K <= 8 * BK;
     return four ? launch_pair<T, 4>(p, status, sm_count, s) : launch_pair<T, 2>(p, status, sm_count, s);
   }
   // Wide tiles amortise the A-tile loads; narrow problems take the smallest tile that covers N, and skinny
@@ -1363,9 +1307,3 @@ template cudaError_t launch_gemm_tc<__half>(const GemmParams&, int*, int, cudaSt
 template cudaError_t launch_gemm_tc<__nv_bfloat16>(const GemmParams&, int*, int, cudaStream_t);
 
 }  // namespace b200
-
-#ifdef B200_TRACE
-extern "C" int b200_trace_read(long long* out, int n) {
-  return (int)cudaMemcpyFromSymbol(out, b200::g_trace, sizeof(long long) * n);
-}
-#endif

@@ -45,6 +45,9 @@ struct GemmParams {
   // LayerNorm); no residual / statistics in this mode.
   void* C2 = nullptr; long long ldc2 = 0;
   int n_split = 0;
+  // CTA-pair kernel: compute a sparsely filled last wave as whole 256x256 tiles instead of half-width ones
+  // (verification switch; the split is on by default).
+  bool whole_tiles = false;
 };
 
 template <typename T> cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t s);
@@ -90,11 +93,8 @@ cudaError_t launch_attention(const T* q, const T* k, const T* v, long long ld, c
 // Tensor-core version of the same operator for 16-bit storage and depth 32 or 64 (attention_tc.cu).
 bool attention_tc_supported(long long ld, long long ldo, int depth, const void* q, const void* k, const void* v,
                             const void* bias, const void* out);
-template <typename T>
-cudaError_t launch_attention_tc(const T* q, const T* k, const T* v, long long ld, const T* bias, T* out,
-                                long long ldo, int n, int heads, int depth, float scale, cudaStream_t s);
-// Persistent variant of the same operator: TMA loads into a ring of swizzled shared-memory stages, TMA stores of
-// the result; `status` receives 300 + code if a bounded device-side wait gives up.  Same support conditions.
+// Persistent kernel: TMA loads into a ring of swizzled shared-memory stages, TMA stores of the result; `status`
+// receives 300 + code if a bounded device-side wait gives up.
 template <typename T>
 cudaError_t launch_attention_tma(const T* q, const T* k, const T* v, long long ld, const T* bias, T* out,
                                  long long ldo, int n, int heads, int depth, float scale, int* status, int sm_count,

@@ -38,9 +38,10 @@ struct b200_mux {
   int max_batch = 0;
   int wait_us = 0;
   std::mutex mu;
-  std::condition_variable cv_work, cv_done;
+  std::condition_variable cv_work, cv_done, cv_idle;
   std::deque<Request*> queue;
   int queued_positions = 0;
+  int inside = 0;  // callers blocked in b200_mux_eval
   bool abort = false;
   long long batches = 0, positions = 0, requests = 0;
   std::vector<std::thread> workers;
@@ -147,8 +148,11 @@ int b200_mux_eval(b200_mux* mux, const uint64_t* masks, const float* values, int
     mux->queue.push_back(&r);
     mux->queued_positions += n;
     mux->requests++;
+    mux->inside++;
     mux->cv_work.notify_all();
     mux->cv_done.wait(lock, [&] { return r.done; });
+    // b200_mux_destroy waits for this count to reach zero before it frees the mutex this thread still holds
+    if (--mux->inside == 0) mux->cv_idle.notify_all();
   }
   if (r.rc != B200_OK) b200::set_error(r.error);
   return r.rc;
@@ -179,6 +183,11 @@ void b200_mux_destroy(b200_mux* mux) {
   mux->cv_work.notify_all();
   mux->cv_done.notify_all();
   for (auto& t : mux->workers) t.join();
+  {
+    // callers that were woken above are still inside b200_mux_eval until they have re-acquired and released the mutex
+    std::unique_lock<std::mutex> lock(mux->mu);
+    mux->cv_idle.wait(lock, [&] { return mux->inside == 0; });
+  }
   delete mux;
 }
 

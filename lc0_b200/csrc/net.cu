@@ -198,13 +198,21 @@ struct NetBase {
   std::atomic<long long> launches{0};
   // Optional per-kernel-class timing with CUDA events on the evaluation stream.
   enum { K_GEMM_TC = 0, K_GEMM_FMA = 1, K_ATTENTION = 2, K_LAYERNORM = 3, K_OTHER = 4, K_CLASSES = 5 };
-  bool profiling = false;
-  struct Span { int cls; cudaEvent_t a, b; double work; };
+  std::atomic<bool> profiling{false};
+  // `tag` names the launch within its class (the products of an encoder layer: see b200_net_get_profile_tagged)
+  struct Span { int cls, tag; cudaEvent_t a, b; double work; };
+  std::mutex prof_mu;  // computations of several slots may record spans at the same time
   std::vector<Span> spans;
   std::vector<cudaEvent_t> event_pool;
   double prof_ms[K_CLASSES] = {0}, prof_work[K_CLASSES] = {0};
   long long prof_launches[K_CLASSES] = {0};
-  cudaEvent_t get_event() {
+  enum { K_TAGS = 16 };
+  // Tags: which product of an encoder layer (or which other part of the evaluation) a tensor-core launch belongs to.
+  enum { TAG_NONE = 0, TAG_QKV = 1, TAG_OUT_PROJ = 2, TAG_FFN1 = 3, TAG_FFN2 = 4, TAG_SMOLGEN_DENSE = 5,
+         TAG_SMOLGEN_BIAS = 6, TAG_ATTENTION = 7, TAG_EMBEDDING = 8, TAG_HEADS = 9 };
+  double tag_ms[K_TAGS] = {0}, tag_work[K_TAGS] = {0};
+  long long tag_launches[K_TAGS] = {0};
+  cudaEvent_t get_event() {  // prof_mu held
     if (!event_pool.empty()) {
       cudaEvent_t e = event_pool.back();
       event_pool.pop_back();
@@ -214,33 +222,37 @@ struct NetBase {
     cudaEventCreate(&e);
     return e;
   }
-  // Brackets one launch: begin() before, end() after (no-ops unless profiling is on).
-  void span_begin(cudaStream_t st, int cls, double work) {
-    if (!profiling) return;
-    Span sp{cls, get_event(), get_event(), work};
+  // Brackets one launch: begin() before, end(index begin() returned) after (no-ops unless profiling is on).
+  int span_begin(cudaStream_t st, int cls, double work, int tag = 0) {
+    if (!profiling) return -1;
+    std::lock_guard<std::mutex> l(prof_mu);
+    Span sp{cls, tag, get_event(), get_event(), work};
     cudaEventRecord(sp.a, st);
     spans.push_back(sp);
+    return (int)spans.size() - 1;
   }
-  void span_end(cudaStream_t st) {
-    if (!profiling) return;
-    cudaEventRecord(spans.back().b, st);
+  void span_end(cudaStream_t st, int idx) {
+    if (idx < 0) return;
+    std::lock_guard<std::mutex> l(prof_mu);
+    if (idx < (int)spans.size()) cudaEventRecord(spans[idx].b, st);
   }
   void collect_spans() {
-    // B200_PROFILE_DUMP=<file>: append one "class work milliseconds" line per launch (development aid).
-    FILE* dump = nullptr;
-    if (const char* path = getenv("B200_PROFILE_DUMP")) dump = fopen(path, "a");
+    std::lock_guard<std::mutex> l(prof_mu);
     for (auto& sp : spans) {
       float ms = 0.f;
       if (cudaEventSynchronize(sp.b) == cudaSuccess && cudaEventElapsedTime(&ms, sp.a, sp.b) == cudaSuccess) {
-        if (dump) fprintf(dump, "%d %.6g %.6f\n", sp.cls, sp.work, ms);
         prof_ms[sp.cls] += ms;
         prof_work[sp.cls] += sp.work;
         prof_launches[sp.cls]++;
+        if (sp.tag > 0 && sp.tag < K_TAGS) {
+          tag_ms[sp.tag] += ms;
+          tag_work[sp.tag] += sp.work;
+          tag_launches[sp.tag]++;
+        }
       }
       event_pool.push_back(sp.a);
       event_pool.push_back(sp.b);
     }
-    if (dump) fclose(dump);
     spans.clear();
   }
   virtual int eval_device(int slot, const void* d_masks, const void* d_values, int n, void* d_policy,
@@ -341,6 +353,8 @@ struct NetBase {
                           int enc_fill = 0, int n_boards = 0) = 0;
   virtual cudaStream_t stream(int slot) = 0;
   virtual int device_status() = 0;
+  virtual int sync_slot(int slot) = 0;
+  virtual void inject_status(int code) = 0;
   // slot pool
   std::mutex mu;
   std::condition_variable cv;
@@ -357,7 +371,27 @@ struct NetBase {
       std::lock_guard<std::mutex> l(mu);
       free_slots.push_back(s);
     }
-    cv.notify_one();
+    cv.notify_all();
+  }
+  // The device-pointer entry points (b200_net_eval_device / _enqueue_device) run on slot 0, whose stream
+  // b200_net_stream exposes.  They take that slot out of the pool like a computation does; the enqueue form keeps it
+  // until b200_net_sync, so that a computation of another thread never shares the workspace of work still in flight.
+  bool dev_holds_slot0 = false;  // guarded by mu
+  void hold_slot0() {
+    std::unique_lock<std::mutex> l(mu);
+    if (dev_holds_slot0) return;
+    cv.wait(l, [&] { return std::find(free_slots.begin(), free_slots.end(), 0) != free_slots.end(); });
+    free_slots.erase(std::find(free_slots.begin(), free_slots.end(), 0));
+    dev_holds_slot0 = true;
+  }
+  void unhold_slot0() {
+    {
+      std::lock_guard<std::mutex> l(mu);
+      if (!dev_holds_slot0) return;
+      dev_holds_slot0 = false;
+      free_slots.push_back(0);
+    }
+    cv.notify_all();
   }
 };
 
@@ -369,9 +403,11 @@ struct Net : NetBase {
   // LayerNorms of the encoder stack folded into the neighbouring tensor-core products (16-bit storage only).
   bool fold_ln = false;
   bool fold_emb_ln = false;  // the embedding block's last LayerNorm is folded into the first encoder layer
-  bool merge_compress = true;  // B200_MERGE_COMPRESS=0: smolgen compression as a launch of its own
+  bool merge_compress = true;  // false (B200_FLAG_NO_MERGED_COMPRESS): smolgen compression as a launch of its own
   bool fold_heads = false;  // the heads' first products fold the last LayerNorm too (else it is materialised)
-  int* d_status = nullptr;
+  int* d_status = nullptr;  // one status word per slot
+  // Status word of the evaluation being enqueued on this thread (the slot's), handed to every kernel with bounded waits.
+  static inline thread_local int* t_status = nullptr;
 
   // format
   int network = 0, policy_fmt = 0, value_fmt = 0, emb_fmt = 0;
@@ -406,6 +442,7 @@ struct Net : NetBase {
   struct Slot {
     cudaStream_t stream = nullptr;
     cudaEvent_t compute_done = nullptr;  // recorded after the last kernel of an evaluation, before its result copies
+    int* h_status = nullptr;             // pinned copy of the device status word, refreshed by every evaluation
     uint64_t* d_masks = nullptr;
     float *d_values = nullptr, *d_policy = nullptr, *d_qdm = nullptr;
     unsigned short* d_move_ids = nullptr;
@@ -435,6 +472,7 @@ struct Net : NetBase {
     for (auto& s : slots) {
       if (s.stream) cudaStreamDestroy(s.stream);
       if (s.compute_done) cudaEventDestroy(s.compute_done);
+      if (s.h_status) cudaFreeHost(s.h_status);
     }
     free_host_sets();
     walloc.release();
@@ -686,8 +724,8 @@ struct Net : NetBase {
                                              std::to_string(prop.major) + std::to_string(prop.minor)};
       CK(gemm_tc_init());
     }
-    if (const char* v = getenv("B200_MERGE_COMPRESS")) merge_compress = v[0] != '0';
-    fold_ln = use_tc && attn_body && !(getenv("B200_FOLD_LN") && getenv("B200_FOLD_LN")[0] == '0');
+    merge_compress = !(opt.flags & B200_FLAG_NO_MERGED_COMPRESS);
+    fold_ln = use_tc && attn_body && !(opt.flags & B200_FLAG_NO_LN_FOLD);
     // Folding needs every product that consumes or produces a folded LayerNorm to be eligible for the tensor-core
     // kernel's TMA epilogue: output widths that are multiples of 8.
     auto foldable = [](size_t width) { return width >= 8 && width % 8 == 0; };
@@ -703,8 +741,9 @@ struct Net : NetBase {
     fold_heads = fold_ln && foldable(size_of("value.ip_val_b")) &&
                  (!mlh || foldable(size_of("ip_mov_b"))) &&
                  (policy_fmt != POLICY_ATTENTION || foldable(size_of("policy.ip_pol_b")));
-    d_status = (int*)walloc.alloc(sizeof(int));
-    CK(cudaMemset(d_status, 0, sizeof(int)));
+    if (opt.slots > 64) throw Fail{B200_ERR_INVALID, "at most 64 slots"};
+    d_status = (int*)walloc.alloc(64 * sizeof(int));
+    CK(cudaMemset(d_status, 0, 64 * sizeof(int)));
 
     const Tables& tb = tables();
     d_attn_src = (short*)walloc.alloc(1858 * sizeof(short));
@@ -736,13 +775,18 @@ struct Net : NetBase {
       }
     }
     const int body_ch = attn_body ? (int)size_of("ip_emb_b") : C;
+    // The reference's CPU path for an attention body on top of a residual tower (network_blas.cc:603-659) feeds the
+    // embedding from a buffer that nothing filled for that topology, so there is no reference result to match;
+    // refused at load rather than at the first evaluation.
+    if (attn_body && res_blocks > 0)
+      throw Fail{B200_ERR_UNSUPPORTED, "attention body on top of a residual tower is not supported"};
 
     // ---- attention body ----
     if (attn_body) {
       E = (int)size_of("ip_emb_b");
       H = (int)geti("headcount");
       if (E <= 0 || H <= 0 || E % H) throw Fail{B200_ERR_INVALID, "weights: bad embedding size / head count"};
-      if (E % 8) throw Fail{B200_ERR_UNSUPPORTED, "embedding size must be a multiple of 8"};
+      if (E % 8 || E > 8192) throw Fail{B200_ERR_UNSUPPORTED, "embedding size must be a multiple of 8 and at most 8192"};
       int in_ch;
       if (res_blocks == 0) {
         if (emb_fmt == EMB_PE_DENSE) {
@@ -811,7 +855,12 @@ struct Net : NetBase {
         enc.push_back(load_encoder("encoder." + std::to_string(i), E, H, g, bt));
         max_dff = std::max(max_dff, enc.back().ffn1.out);
       }
-      if (sg_gen) smolgen_w = dense("smolgen_w", "", 4096, sg_gen / H);
+      if (sg_gen) {
+        // the LayerNorm kernels read rows in vectors of 8 elements and keep a row of at most 8192 in registers
+        if (sg_hid % 8 || sg_gen % 8 || sg_hid > 8192 || sg_gen > 8192)
+          throw Fail{B200_ERR_UNSUPPORTED, "smolgen widths must be multiples of 8 and at most 8192"};
+        smolgen_w = dense("smolgen_w", "", 4096, sg_gen / H);
+      }
     }
 
     // ---- policy head ----
@@ -888,6 +937,9 @@ struct Net : NetBase {
     }
 
     alloc_slots();
+    // The uploads above are copies from pageable memory and the slots' streams are non-blocking: everything must have
+    // landed before the first evaluation is enqueued.
+    CK(cudaDeviceSynchronize());
 
     info.input_format = (int)geti("input_format");
     info.output_format = (int)geti("output_format");
@@ -918,6 +970,8 @@ struct Net : NetBase {
       Slot& s = slots[si];
       CK(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
       CK(cudaEventCreateWithFlags(&s.compute_done, cudaEventDisableTiming));
+      CK(cudaMallocHost(&s.h_status, sizeof(int)));
+      *s.h_status = 0;
       s.d_masks = (uint64_t*)salloc.alloc(nb * 112 * 8);
       s.d_values = (float*)salloc.alloc(nb * 112 * 4);
       s.d_policy = (float*)salloc.alloc(nb * 1858 * 4);
@@ -992,6 +1046,7 @@ struct Net : NetBase {
     p.A = A; p.lda = lda; p.W = d.w; p.ldw = d.in; p.bias = d.b;
     p.C = out_f32 ? cf32 : (void*)Cout; p.ldc = ldc; p.M = M; p.N = d.out; p.K = d.in; p.act = act;
     p.skip = skip; p.ldskip = ldskip; p.alpha = alpha_; p.out_f32 = out_f32;
+    p.whole_tiles = (opt.flags & B200_FLAG_NO_SPLIT_LAST_WAVE) != 0;
     run_gemm(st, p);
   }
   // A LayerNorm output that is either materialised (stats == nullptr) or kept as its un-normalised input `u`
@@ -1026,32 +1081,35 @@ struct Net : NetBase {
       if (zero_stats) CK(cudaMemsetAsync(out_stats, 0, (size_t)M * 2 * sizeof(float), st));
       p.out_stats = out_stats;
     }
+    p.whole_tiles = (opt.flags & B200_FLAG_NO_SPLIT_LAST_WAVE) != 0;
     run_gemm(st, p);
   }
+  // Tag of the launches that follow on this thread (which product of the layer they are), for the tagged profile.
+  static inline thread_local int t_tag = 0;
   void run_gemm(cudaStream_t st, const GemmParams& p) {
     launches++;
     const double flops = 2.0 * p.M * (double)p.N * p.K * p.batch;
     if constexpr (sizeof(T) == 2) {
       if (use_tc && p.M >= 64 && gemm_tc_supported(p)) {
-        span_begin(st, K_GEMM_TC, flops);
-        CK(launch_gemm_tc<T>(p, d_status, sm_count, st));
-        span_end(st);
+        const int sp_ = span_begin(st, K_GEMM_TC, flops, t_tag);
+        CK(launch_gemm_tc<T>(p, t_status, sm_count, st));
+        span_end(st, sp_);
         return;
       }
     }
     if (p.a_stats || p.res || p.out_stats)
       throw Fail{B200_ERR_UNSUPPORTED, "internal: folded LayerNorm product outside the tensor-core kernel"};
-    span_begin(st, K_GEMM_FMA, flops);
+    const int sp_ = span_begin(st, K_GEMM_FMA, flops);
     CK(launch_gemm_simt<T>(p, st));
-    span_end(st);
+    span_end(st, sp_);
   }
   // Any other kernel: counted, and timed under the class "other" (work = algorithmic bytes).
   template <typename F>
   void other(cudaStream_t st, double bytes, F&& launch) {
     launches++;
-    span_begin(st, K_OTHER, bytes);
+    const int sp_ = span_begin(st, K_OTHER, bytes);
     CK(launch());
-    span_end(st);
+    span_end(st, sp_);
   }
   // 3x3 convolution: tensor-core kernel (TMA board tiles with zero-filled halo) for 16-bit storage, FMA otherwise.
   void conv3(cudaStream_t st, const T* x, const ConvW<T>& c, const float* bias, T* y, int n, int act) {
@@ -1061,24 +1119,24 @@ struct Net : NetBase {
       p.act = act; p.conv_cin = c.cin; p.lda = c.cin; p.ldw = c.cin;
       if (use_tc && (c.cout % 8) == 0 && gemm_tc_supported(p)) {
         launches++;
-        span_begin(st, K_GEMM_TC, 2.0 * p.M * (double)p.N * p.K);
-        CK(launch_gemm_tc<T>(p, d_status, sm_count, st));
-        span_end(st);
+        const int sp_ = span_begin(st, K_GEMM_TC, 2.0 * p.M * (double)p.N * p.K);
+        CK(launch_gemm_tc<T>(p, t_status, sm_count, st));
+        span_end(st, sp_);
         return;
       }
     }
     launches++;
-    span_begin(st, K_GEMM_FMA, 2.0 * n * 64 * (double)c.cout * 9 * c.cin);
+    const int sp_ = span_begin(st, K_GEMM_FMA, 2.0 * n * 64 * (double)c.cout * 9 * c.cin);
     CK(launch_conv3x3<T>(x, c.cin, c.w, bias, y, c.cout, n, act, st));
-    span_end(st);
+    span_end(st, sp_);
   }
   void ln(cudaStream_t st, T* out, const T* x, const T* skip, const float* g, const float* b, int rows, int Cc,
           float a, float eps, const float* gm = nullptr, const float* ga = nullptr) {
     launches++;
     // algorithmic bytes: read x (+ skip), write out
-    span_begin(st, K_LAYERNORM, (double)rows * Cc * sizeof(T) * (skip ? 3 : 2));
+    const int sp_ = span_begin(st, K_LAYERNORM, (double)rows * Cc * sizeof(T) * (skip ? 3 : 2));
     CK(launch_layer_norm<T>(out, x, skip, g, b, gm, ga, rows, Cc, a, eps, st));
-    span_end(st);
+    span_end(st, sp_);
   }
 
   // `in` describes the layer input: buffer x, materialised for the first layer, afterwards the un-normalised
@@ -1107,6 +1165,7 @@ struct Net : NetBase {
       probe.M = R; probe.N = e.qkvc_out; probe.K = E; probe.C2 = s.sg_c; probe.ldc2 = sg_hc; probe.n_split = 3 * E;
       merged = gemm_tc_split_supported(probe, sm_count);
     }
+    t_tag = TAG_QKV;
     if (merged) {
       Dense<T> both = e.qkv;
       both.out = e.qkvc_out;
@@ -1115,49 +1174,54 @@ struct Net : NetBase {
       gemm_ln(st, in, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE);  // :341-350, :408-412
     }
     if (e.smolgen) {  // network_blas.cc:300-339
+      t_tag = TAG_SMOLGEN_DENSE;
       if (!merged) gemm_ln(st, in, E, e.sg_compress, s.sg_c, sg_hc, R, ACT_NONE);
       gemm(st, s.sg_c, 64 * sg_hc, e.sg_d1, s.sg_h1, sg_hid, n, act_smolgen);
       ln(st, s.sg_h1, s.sg_h1, nullptr, e.sg_ln1g, e.sg_ln1b, n, sg_hid, 1.f, 1e-3f);
       gemm(st, s.sg_h1, sg_hid, e.sg_d2, s.sg_h2, sg_gen, n, act_smolgen);
       ln(st, s.sg_h2, s.sg_h2, nullptr, e.sg_ln2g, e.sg_ln2b, n, sg_gen, 1.f, 1e-3f);
+      t_tag = TAG_SMOLGEN_BIAS;
       gemm(st, s.sg_h2, sg_gen / H, smolgen_w, s.sg_bias, 4096, n * H, ACT_NONE);
       bias = s.sg_bias;
     }
     launches++;
     // algorithmic bytes: read Q, K, V (+ bias), write the head outputs
-    span_begin(st, K_ATTENTION, (double)R * E * sizeof(T) * 4 + (bias ? (double)n * H * 4096 * sizeof(T) : 0.0));
+    const int sp_ = span_begin(st, K_ATTENTION, (double)R * E * sizeof(T) * 4 + (bias ? (double)n * H * 4096 * sizeof(T) : 0.0), TAG_ATTENTION);
     bool done = false;
     if constexpr (sizeof(T) == 2) {
       if (use_tc && attention_tc_supported(3 * E, E, depth, s.qkv, s.qkv + E, s.qkv + 2 * E, bias, s.att)) {
-        // :352-439.  The persistent TMA kernel unless B200_ATTN_TMA=0 asks for the cp.async one (kept for comparison).
-        static const bool tma = !(getenv("B200_ATTN_TMA") && getenv("B200_ATTN_TMA")[0] == '0');
-        if (tma)
-          CK(launch_attention_tma<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
-                                     1.0f / sqrtf((float)depth), d_status, sm_count, st));
-        else
-          CK(launch_attention_tc<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
-                                    1.0f / sqrtf((float)depth), st));
+        // :352-439
+        CK(launch_attention_tma<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
+                                   1.0f / sqrtf((float)depth), t_status, sm_count, st));
         done = true;
       }
     }
     if (!done)
       CK(launch_attention<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
                              1.0f / sqrtf((float)depth), st));
-    span_end(st);
+    span_end(st, sp_);
     if (fold_ln) {
       LNState att{s.att, nullptr, nullptr, nullptr}, ffn{s.ffn, nullptr, nullptr, nullptr};
+      t_tag = TAG_OUT_PROJ;
       gemm_ln(st, att, E, e.proj, x1, E, R, ACT_NONE, &in, alpha, s.stats1, nullptr, 0, 0, false);  // u1 = alpha * proj + x
       LNState mid{x1, s.stats1, e.ln1g, e.ln1b};
+      t_tag = TAG_FFN1;
       gemm_ln(st, mid, E, e.ffn1, s.ffn, e.ffn1.out, R, act_ffn);                  // relu2(LN1(u1) W1 + b1)
+      t_tag = TAG_FFN2;
       gemm_ln(st, ffn, e.ffn1.out, e.ffn2, x, E, R, ACT_NONE, &mid, alpha, stats2, nullptr, 0, 0, false);  // u2 = alpha * ffn + LN1(u1)
+      t_tag = TAG_NONE;
       in = LNState{x, stats2, e.ln2g, e.ln2b};
       return;
     }
+    t_tag = TAG_OUT_PROJ;
     gemm(st, s.att, E, e.proj, s.y, E, R, ACT_NONE);           // :441-445
     ln(st, x1, s.y, x, e.ln1g, e.ln1b, R, E, alpha, ln_eps);   // :447-452
+    t_tag = TAG_FFN1;
     gemm(st, x1, E, e.ffn1, s.ffn, e.ffn1.out, R, act_ffn);    // :454-458
+    t_tag = TAG_FFN2;
     gemm(st, s.ffn, e.ffn1.out, e.ffn2, s.y, E, R, ACT_NONE);  // :460-463
     ln(st, x, s.y, x1, e.ln2g, e.ln2b, R, E, alpha, ln_eps);   // :465-470
+    t_tag = TAG_NONE;
     in = LNState{x, nullptr, nullptr, nullptr};
   }
 
@@ -1168,6 +1232,7 @@ struct Net : NetBase {
     int body_ch = 0;
     LNState body_in;    // attention bodies: how the heads must read `flow` (folded LayerNorm or materialised)
     s.stats_parity = 0;
+    t_status = d_status + (&s - slots.data());
     CK(cudaMemsetAsync(d_qdm, 0, (size_t)n * 3 * sizeof(float), st));
     if (!res.empty() || !attn_body) {  // network_blas.cc:564-601
       other(st, (double)R * 112 * sizeof(T), [&] {
@@ -1187,7 +1252,6 @@ struct Net : NetBase {
       }
       flow = cur;
       body_ch = C;
-      if (attn_body) throw Fail{B200_ERR_UNSUPPORTED, "attention body on top of a residual tower is not supported"};
     }
     if (attn_body) {  // network_blas.cc:603-721
       if (emb_fmt == EMB_PE_DENSE) {
@@ -1202,6 +1266,7 @@ struct Net : NetBase {
         });
       }
       T *x = s.x, *x1 = s.x1;
+      t_tag = TAG_EMBEDDING;
       gemm(st, s.tokens, cin, emb, x, E, R, act_default);
       if (emb_fmt == EMB_PE_DENSE) {
         ln(st, x, x, nullptr, emb_lng, emb_lnb, R, E, 1.f, 1e-3f, gate_mult, gate_add);
@@ -1224,6 +1289,7 @@ struct Net : NetBase {
           other(st, 2.0 * R * E * sizeof(T), [&] { return launch_gate<T>(x, gate_mult, gate_add, R, E, st); });
         body_in = LNState{x, nullptr, nullptr, nullptr};
       }
+      t_tag = TAG_NONE;
       for (const auto& e : enc) encoder_layer(s, e, n, x, x1, body_in);
       if (body_in.stats && !fold_heads) {  // materialise the last LayerNorm for heads that cannot fold it
         ln(st, x1, x, nullptr, body_in.gamma, body_in.beta, R, E, 1.f, ln_eps);
@@ -1236,6 +1302,7 @@ struct Net : NetBase {
 
     // ---- value head (network_blas.cc:725-772) ----
     LNState head_in = attn_body ? body_in : LNState{flow, nullptr, nullptr, nullptr};
+    t_tag = TAG_HEADS;
     gemm_ln(st, head_in, body_ch, val_emb, s.vtok, val_emb.out, R, act_default);
     gemm(st, s.vtok, 64 * val_emb.out, val_fc1, s.vhid, val_fc1.out, n, act_default);
     other(st, (double)n * val_fc1.out * sizeof(T), [&] {
@@ -1258,9 +1325,9 @@ struct Net : NetBase {
       if constexpr (sizeof(T) == 2) {
         if (use_tc && policy_attn_tc_supported(pol_dm, s.pq, s.pk)) {
           launches++;
-          span_begin(st, K_OTHER, 2.0 * R * pol_dm * sizeof(T) + (double)n * 1858 * 4);
+          const int sp_ = span_begin(st, K_OTHER, 2.0 * R * pol_dm * sizeof(T) + (double)n * 1858 * 4);
           CK(launch_policy_attn_tc<T>(s.pq, s.pk, pol_w4, pol_dm, d_attn_src, n, d_policy, st));
-          span_end(st);
+          span_end(st, sp_);
           done = true;
         }
       }
@@ -1286,6 +1353,7 @@ struct Net : NetBase {
       gemm(st, flow, C, pol_c1x1, s.praw, pol_planes, R, act_default);
       gemm(st, s.praw, 64 * pol_planes, pol_fc, nullptr, 1858, n, ACT_NONE, nullptr, 0, 1.f, true, d_policy);
     }
+    t_tag = TAG_NONE;
   }
 
   // ---- CUDA graphs: the launch sequence of one evaluation is captured per (batch size, buffers) the second
@@ -1342,6 +1410,23 @@ struct Net : NetBase {
     if (policy_mode != 2)
       CK(cudaMemcpyAsync(hs.policy, s.d_policy, (size_t)n * 1858 * 4, cudaMemcpyDeviceToHost, s.stream));
     CK(cudaMemcpyAsync(hs.qdm, s.d_qdm, (size_t)n * 3 * 4, cudaMemcpyDeviceToHost, s.stream));
+    copy_status(s);
+  }
+  // The slot's status word follows the results to the host (inside a captured graph too), so that an evaluation
+  // whose kernels gave up on a bounded wait is reported by the call that ran it.
+  void copy_status(Slot& s) {
+    CK(cudaMemcpyAsync(s.h_status, d_status + (&s - slots.data()), sizeof(int), cudaMemcpyDeviceToHost, s.stream));
+  }
+  // After the stream has been synchronised: B200_ERR_TIMEOUT if a kernel of this slot gave up; the word is cleared so
+  // that the next evaluation starts clean.
+  void check_status(Slot& s) {
+    const int code = *s.h_status;
+    if (!code) return;
+    *s.h_status = 0;
+    CK(cudaMemsetAsync(d_status + (&s - slots.data()), 0, sizeof(int), s.stream));
+    CK(cudaStreamSynchronize(s.stream));
+    throw Fail{B200_ERR_TIMEOUT, "a bounded device-side wait gave up (kernel status " + std::to_string(code) +
+                                     "); the results of this evaluation are not valid"};
   }
 
   template <typename F>
@@ -1404,8 +1489,12 @@ struct Net : NetBase {
     Slot& s = slots[slot];
     run_or_replay(slot, GraphKey{n, 0, d_masks, d_values, d_policy, d_qdm}, [&] {
       forward(s, (const uint64_t*)d_masks, (const float*)d_values, n, (float*)d_policy, (float*)d_qdm);
+      copy_status(s);
     });
-    if (sync) CK(cudaStreamSynchronize(s.stream));
+    if (sync) {
+      CK(cudaStreamSynchronize(s.stream));
+      check_status(s);
+    }
     return B200_OK;
   }
   int eval_staged(int slot, HostSet& hs, int n, int policy_mode, float inv_t, int enc_format, int enc_fill,
@@ -1426,13 +1515,27 @@ struct Net : NetBase {
                            (const void*)(uintptr_t)tbits},
                   [&] { enqueue_staged(s, hs, n, policy_mode, inv_t, enc_format, enc_fill); });
     CK(cudaStreamSynchronize(s.stream));
+    check_status(s);
     return B200_OK;
   }
   cudaStream_t stream(int slot) override { return slots[slot].stream; }
   int device_status() override {
-    int v = 0;
-    cudaMemcpy(&v, d_status, sizeof(int), cudaMemcpyDeviceToHost);
-    return v;
+    int v[64] = {0};
+    cudaMemcpy(v, d_status, sizeof(v), cudaMemcpyDeviceToHost);
+    for (int i = 0; i < 64; ++i)
+      if (v[i]) return v[i];
+    return 0;
+  }
+  int sync_slot(int slot) override {
+    Slot& s = slots[slot];
+    CK(cudaStreamSynchronize(s.stream));
+    check_status(s);
+    return B200_OK;
+  }
+  void inject_status(int code) override {
+    int v[64];
+    for (int i = 0; i < 64; ++i) v[i] = code;
+    CK(cudaMemcpy(d_status, v, sizeof(v), cudaMemcpyHostToDevice));
   }
 };
 
@@ -1590,8 +1693,10 @@ int b200_comp_compute(b200_comp* c) {
   if (!c) return B200_ERR_INVALID;
   return guarded([&] {
     NetBase* nb = c->net.get();
-    c->computed = true;
-    if (c->n == 0) return (int)B200_OK;
+    if (c->n == 0) {
+      c->computed = true;
+      return (int)B200_OK;
+    }
     CK(cudaSetDevice(nb->opt.gpu));
     const int slot = nb->acquire();
     int rc;
@@ -1608,6 +1713,7 @@ int b200_comp_compute(b200_comp* c) {
       throw;
     }
     nb->release(slot);
+    c->computed = rc == B200_OK;
     return rc;
   });
 }
@@ -1776,7 +1882,17 @@ static int eval_dev(b200_net* net, const void* d_masks, const void* d_values, in
       throw Fail{B200_ERR_INVALID, "batch " + std::to_string(n) + " exceeds max_batch=" + std::to_string(nb->opt.max_batch)};
     if (n == 0) return (int)B200_OK;
     CK(cudaSetDevice(nb->opt.gpu));
-    return nb->eval_device(0, d_masks, d_values, n, d_policy, d_qdm, sync);
+    nb->hold_slot0();
+    if (!sync) return nb->eval_device(0, d_masks, d_values, n, d_policy, d_qdm, false);
+    int rc;
+    try {
+      rc = nb->eval_device(0, d_masks, d_values, n, d_policy, d_qdm, true);
+    } catch (...) {
+      nb->unhold_slot0();
+      throw;
+    }
+    nb->unhold_slot0();
+    return rc;
   });
 }
 int b200_net_eval_device(b200_net* net, const void* d_masks, const void* d_values, int n, void* d_policy,
@@ -1790,14 +1906,30 @@ int b200_net_enqueue_device(b200_net* net, const void* d_masks, const void* d_va
 int b200_net_sync(b200_net* net) {
   if (!net) return B200_ERR_INVALID;
   return guarded([&] {
-    CK(cudaSetDevice(net->impl->opt.gpu));
-    CK(cudaStreamSynchronize(net->impl->stream(0)));
-    return B200_OK;
+    NetBase* nb = net->impl.get();
+    CK(cudaSetDevice(nb->opt.gpu));
+    int rc;
+    try {
+      rc = nb->sync_slot(0);
+    } catch (...) {
+      nb->unhold_slot0();
+      throw;
+    }
+    nb->unhold_slot0();
+    return rc;
   });
 }
 void* b200_net_stream(b200_net* net) { return net ? (void*)net->impl->stream(0) : nullptr; }
 long long b200_net_launch_count(const b200_net* net) { return net ? net->impl->launches.load() : 0; }
 int b200_net_device_status(b200_net* net) { return net ? net->impl->device_status() : 0; }
+int b200_net_inject_device_status(b200_net* net, int code) {
+  if (!net) return B200_ERR_INVALID;
+  return guarded([&] {
+    CK(cudaSetDevice(net->impl->opt.gpu));
+    net->impl->inject_status(code);
+    return (int)B200_OK;
+  });
+}
 
 int b200_net_set_profiling(b200_net* net, int enabled) {
   if (!net) return B200_ERR_INVALID;
@@ -1818,6 +1950,25 @@ int b200_net_get_profile(b200_net* net, double* ms, double* work, long long* lau
       nb->prof_ms[i] = 0;
       nb->prof_work[i] = 0;
       nb->prof_launches[i] = 0;
+    }
+  }
+  return B200_OK;
+}
+
+int b200_net_get_profile_tagged(b200_net* net, double* ms, double* work, long long* launches, int reset) {
+  if (!net || !ms || !work || !launches) return B200_ERR_INVALID;
+  NetBase* nb = net->impl.get();
+  cudaSetDevice(nb->opt.gpu);
+  nb->collect_spans();
+  std::lock_guard<std::mutex> l(nb->prof_mu);
+  for (int i = 0; i < NetBase::K_TAGS; ++i) {
+    ms[i] = nb->tag_ms[i];
+    work[i] = nb->tag_work[i];
+    launches[i] = nb->tag_launches[i];
+    if (reset) {
+      nb->tag_ms[i] = 0;
+      nb->tag_work[i] = 0;
+      nb->tag_launches[i] = 0;
     }
   }
   return B200_OK;
@@ -1874,6 +2025,59 @@ int b200_op_gemm(const void* A, const void* W, const float* bias, void* C, int M
   };
   return by_precision(precision, [&] { return run(float()); }, [&] { return run(__half()); },
                       [&] { return run(__nv_bfloat16()); });
+}
+
+int b200_op_gemm_ex(const b200_gemm_desc* d, void* stream) {
+  if (!d || !d->A || !d->W || !d->C || d->M < 0 || d->N <= 0 || d->K <= 0) {
+    set_error("b200_op_gemm_ex: bad argument");
+    return B200_ERR_INVALID;
+  }
+  if (d->precision != B200_PREC_FP16 && d->precision != B200_PREC_BF16) {
+    set_error("b200_op_gemm_ex: the tensor-core kernel takes fp16 or bf16");
+    return B200_ERR_UNSUPPORTED;
+  }
+  GemmParams p;
+  p.A = d->A; p.lda = d->lda ? d->lda : d->K; p.W = d->W; p.ldw = d->ldw ? d->ldw : d->K; p.bias = d->bias;
+  p.C = d->C; p.ldc = d->ldc ? d->ldc : (d->n_split > 0 ? d->n_split : d->N);
+  p.M = d->M; p.N = d->N; p.K = d->K; p.act = d->activation;
+  p.scale = d->scale; p.alpha = d->alpha;
+  p.a_stats = d->a_stats; p.colsum = d->colsum; p.a_inv_c = d->a_inv_c; p.a_eps = d->a_eps;
+  p.res = d->res; p.ldres = d->ldres ? d->ldres : d->N;
+  p.res_stats = d->res_stats; p.res_gamma = d->res_gamma; p.res_beta = d->res_beta;
+  p.res_inv_c = d->res_inv_c; p.res_eps = d->res_eps;
+  p.out_stats = d->out_stats;
+  p.C2 = d->C2; p.ldc2 = d->ldc2; p.n_split = d->n_split;
+  p.whole_tiles = d->whole_tiles != 0;
+  if ((p.a_stats && !p.colsum) || (p.res_stats && (!p.res || !p.res_gamma || !p.res_beta)) || !gemm_tc_supported(p)) {
+    set_error("b200_op_gemm_ex: inconsistent description or shape not supported by the tensor-core kernel");
+    return B200_ERR_UNSUPPORTED;
+  }
+  B200_CUDA(gemm_tc_init());
+  int dev = 0, sms = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  B200_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (p.n_split > 0 && !gemm_tc_split_supported(p, sms)) {
+    set_error("b200_op_gemm_ex: the second output needs a product large enough for the CTA-pair kernel, n_split a "
+              "multiple of 256 and at most 256 columns beyond it");
+    return B200_ERR_UNSUPPORTED;
+  }
+  int* status = nullptr;
+  B200_CUDA(cudaMalloc(&status, sizeof(int)));
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t err = cudaMemsetAsync(status, 0, sizeof(int), st);
+  if (err == cudaSuccess)
+    err = d->precision == B200_PREC_FP16 ? launch_gemm_tc<__half>(p, status, sms, st)
+                                         : launch_gemm_tc<__nv_bfloat16>(p, status, sms, st);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(st);
+  int code = 0;
+  if (err == cudaSuccess) err = cudaMemcpy(&code, status, sizeof(int), cudaMemcpyDeviceToHost);
+  cudaFree(status);
+  B200_CUDA(err);
+  if (code) {
+    set_error("tensor-core GEMM: a bounded device-side wait gave up, status " + std::to_string(code));
+    return B200_ERR_TIMEOUT;
+  }
+  return B200_OK;
 }
 
 int b200_op_gemm_timed(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int activation,
@@ -1968,6 +2172,7 @@ int b200_op_policy_attention(const void* q, const void* k, const float* w4, int 
     if (!d_src[dev & 63]) {
       B200_CUDA(cudaMalloc(&d_src[dev & 63], 1858 * sizeof(short)));
       B200_CUDA(cudaMemcpy(d_src[dev & 63], attn_policy_src_table(), 1858 * sizeof(short), cudaMemcpyHostToDevice));
+      B200_CUDA(cudaDeviceSynchronize());  // the caller's stream may be non-blocking: the table must have landed
     }
   }
   const short* src = d_src[dev & 63];
@@ -2000,7 +2205,7 @@ int b200_op_layer_norm(void* out, const void* x, const void* skip, const float* 
 
 int b200_op_attention(const void* q, const void* k, const void* v, long long ld, const void* bias, void* out,
                       long long ldo, int n, int heads, int depth, int precision, int variant, void* stream) {
-  if (n < 0 || heads < 1 || depth < 1 || (n > 0 && (!q || !k || !v || !out)) || variant < 0 || variant > 2) {
+  if (n < 0 || heads < 1 || depth < 1 || (n > 0 && (!q || !k || !v || !out)) || variant < 0 || variant > 1) {
     set_error("b200_op_attention: bad argument");
     return B200_ERR_INVALID;
   }
@@ -2017,11 +2222,6 @@ int b200_op_attention(const void* q, const void* k, const void* v, long long ld,
       if (!attention_tc_supported(ld, ldo, depth, q, k, v, bias, out)) {
         set_error("b200_op_attention: layout not supported by the tensor-core kernels");
         return B200_ERR_UNSUPPORTED;
-      }
-      if (variant == 1) {
-        B200_CUDA(launch_attention_tc<T>((const T*)q, (const T*)k, (const T*)v, ld, (const T*)bias, (T*)out, ldo, n,
-                                         heads, depth, scale, st));
-        return B200_OK;
       }
       B200_CUDA(gemm_tc_init());
       int dev = 0, sms = 0;

@@ -39,6 +39,9 @@ int setup_device(int dev, DeviceSetup** out) {
     B200_CUDA(cudaGetSymbolAddress(&p, g_gather_table));
     s.table = static_cast<short*>(p);
     B200_CUDA(cudaMemcpy(s.table, b200::attn_policy_src_table(), 1858 * sizeof(short), cudaMemcpyHostToDevice));
+    // A copy from pageable memory may return before the data has landed, and a non-blocking caller stream is not
+    // ordered behind it: wait once here so that the first launch on any stream reads the finished table.
+    B200_CUDA(cudaDeviceSynchronize());
     s.ready = true;
   }
   *out = &s;

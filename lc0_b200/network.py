@@ -15,7 +15,7 @@ import numpy as np
 from . import _lib, netproto, weights as _weights
 
 _KNOWN_OPTIONS = {"gpu", "max_batch", "precision", "slots", "mlh", "policy_head", "value_head",
-                  "tensor_cores", "graph_capture"}
+                  "tensor_cores", "graph_capture", "fold_ln", "merge_compress", "split_last_wave", "fused_smolgen"}
 
 
 def parse_options(opts):
@@ -39,6 +39,17 @@ def parse_options(opts):
 
 def _as_bool(v):
     return str(v).lower() not in ("0", "false", "no", "off")
+
+
+def option_flags(opts):
+    """b200_net_options.flags from the boolean options (all default to on)."""
+    flags = 0
+    for key, bit in (("tensor_cores", _lib.FLAG_NO_TENSOR_CORES), ("graph_capture", _lib.FLAG_NO_GRAPHS),
+                     ("fold_ln", _lib.FLAG_NO_LN_FOLD), ("merge_compress", _lib.FLAG_NO_MERGED_COMPRESS),
+                     ("split_last_wave", _lib.FLAG_NO_SPLIT_LAST_WAVE), ("fused_smolgen", _lib.FLAG_NO_FUSED_SMOLGEN)):
+        if not _as_bool(opts.get(key, True)):
+            flags |= bit
+    return flags
 
 
 class NetworkComputation:
@@ -200,8 +211,7 @@ class Network:
             o = _lib.NetOptions(gpu=int(opts.get("gpu", 0)), max_batch=int(opts.get("max_batch", 1024)),
                                 precision=_lib.PRECISIONS[prec], slots=int(opts.get("slots", 1)),
                                 mlh=1 if _as_bool(opts.get("mlh", True)) else 0,
-                                flags=(0 if _as_bool(opts.get("tensor_cores", True)) else _lib.FLAG_NO_TENSOR_CORES) |
-                                      (0 if _as_bool(opts.get("graph_capture", True)) else _lib.FLAG_NO_GRAPHS))
+                                flags=option_flags(opts))
             h = ctypes.c_void_p()
             _lib.check(lib.b200_net_create(b, ctypes.byref(o), ctypes.byref(h)))
             self._handle = h
@@ -263,6 +273,10 @@ class Network:
     def device_status(self):
         return self._lib.b200_net_device_status(self._handle)
 
+    def inject_device_status(self, code):
+        """Test hook: make the next evaluation of every slot fail the way a kernel that gave up would."""
+        _lib.check(self._lib.b200_net_inject_device_status(self._handle, int(code)))
+
     PROFILE_CLASSES = ("gemm_tc", "gemm_fma", "attention", "layer_norm", "other")
 
     def set_profiling(self, enabled):
@@ -276,6 +290,18 @@ class Network:
                                                   cnt.ctypes.data, 1 if reset else 0))
         return {c: dict(ms=float(ms[i]), work=float(work[i]), launches=int(cnt[i]))
                 for i, c in enumerate(self.PROFILE_CLASSES)}
+
+    PROFILE_TAGS = ("untagged", "qkv", "out_proj", "ffn1", "ffn2", "smolgen_dense", "smolgen_bias", "attention",
+                    "embedding", "heads")
+
+    def get_profile_tagged(self, reset=True):
+        """{tag: dict(ms, work, launches)} of the launches that carry a tag: which product of the encoder layer."""
+        k = 16
+        ms, work, cnt = np.zeros(k), np.zeros(k), np.zeros(k, np.int64)
+        _lib.check(self._lib.b200_net_get_profile_tagged(self._handle, ms.ctypes.data, work.ctypes.data,
+                                                         cnt.ctypes.data, 1 if reset else 0))
+        return {c: dict(ms=float(ms[i]), work=float(work[i]), launches=int(cnt[i]))
+                for i, c in enumerate(self.PROFILE_TAGS) if i > 0}
 
     def close(self):
         if self._handle:
@@ -364,8 +390,7 @@ class MultiGpuNetwork:
                 _lib.check(lib.b200_builder_add_tensor(b, name.encode(), a.ctypes.data, a.size))
             o = _lib.NetOptions(gpu=0, max_batch=int(opts.get("max_batch", 1024)), precision=_lib.PRECISIONS[prec],
                                 slots=int(opts.get("slots", 1)), mlh=1 if _as_bool(opts.get("mlh", True)) else 0,
-                                flags=(0 if _as_bool(opts.get("tensor_cores", True)) else _lib.FLAG_NO_TENSOR_CORES) |
-                                      (0 if _as_bool(opts.get("graph_capture", True)) else _lib.FLAG_NO_GRAPHS))
+                                flags=option_flags(opts))
             ids = (ctypes.c_int * len(gpus))(*gpus)
             h = ctypes.c_void_p()
             _lib.check(lib.b200_multi_create(b, ctypes.byref(o), ids, len(gpus), ctypes.byref(h)))

@@ -135,13 +135,13 @@ def _attention_reference(qkv, bias, n, heads, depth):
     return torch.matmul(p, v).permute(0, 2, 1, 3).reshape(n * 64, e)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("variant", [0, 1])
 @pytest.mark.parametrize("prec", [1, 2])
 @pytest.mark.parametrize("n,heads,depth,with_bias", [(1, 4, 32, True), (7, 32, 32, True), (3, 8, 64, False),
                                                      (150, 8, 32, True), (40, 6, 64, True), (2, 1, 32, False)])
 def test_attention_op(lib, variant, prec, n, heads, depth, with_bias):
-    """The three attention kernels against an fp32 reference on the fused Q|K|V layout the network uses; the
-    persistent TMA kernel (variant 2) walks several items per CTA at the larger sizes."""
+    """Both attention kernels against an fp32 reference on the fused Q|K|V layout the network uses; the
+    persistent TMA kernel (variant 1) walks several items per CTA at the larger sizes."""
     torch.manual_seed(n * heads + depth)
     e = heads * depth
     qkv = torch.randn(n * 64, 3 * e, device="cuda").to(DT[prec])
@@ -158,21 +158,21 @@ def test_attention_op(lib, variant, prec, n, heads, depth, with_bias):
 
 
 def test_attention_op_variants_agree(lib):
-    """The persistent TMA kernel and the cp.async kernel differ only in how exp is evaluated."""
+    """The FMA kernel and the persistent TMA kernel on the same 16-bit inputs."""
     torch.manual_seed(5)
     n, heads, depth = 64, 32, 32
     e = heads * depth
     qkv = torch.randn(n * 64, 3 * e, device="cuda").half()
     bias = torch.randn(n, heads, 64, 64, device="cuda").half()
     outs = []
-    for variant in (1, 2):
+    for variant in (0, 1):
         out = torch.zeros(n * 64, e, device="cuda", dtype=torch.float16)
         _lib.check(lib.b200_op_attention(qkv.data_ptr(), qkv.data_ptr() + e * 2, qkv.data_ptr() + 4 * e, 3 * e,
                                          bias.data_ptr(), out.data_ptr(), e, n, heads, depth, 1, variant, None))
         outs.append(out.float())
     torch.cuda.synchronize()
-    assert (outs[0] - outs[1]).abs().max().item() <= 2e-3
+    assert (outs[0] - outs[1]).abs().max().item() <= 4e-3
 
 
 def test_attention_op_rejects_fp32_tensor_core_variants(lib):
-    assert lib.b200_op_attention(None, None, None, 96, None, None, 32, 0, 1, 32, 0, 2, None) == _lib.ERR_UNSUPPORTED
+    assert lib.b200_op_attention(None, None, None, 96, None, None, 32, 0, 1, 32, 0, 1, None) == _lib.ERR_UNSUPPORTED

@@ -211,7 +211,7 @@ def test_concurrent_computations_on_two_slots():
     nw.close()
 
 
-def test_merged_qkv_and_smolgen_compression_launch_matches_separate_launches(monkeypatch):
+def test_merged_qkv_and_smolgen_compression_launch_matches_separate_launches():
     """Q, K, V and the smolgen compression computed by one launch of the CTA-pair kernel (second output, narrow last
     tile) against the same network with the compression as a product of its own."""
     net = mknet.make_net("cfg4_2layer")
@@ -222,8 +222,7 @@ def test_merged_qkv_and_smolgen_compression_launch_matches_separate_launches(mon
     values = np.ones((n, 112), np.float32)
     outs = []
     for flag in ("1", "0"):
-        monkeypatch.setenv("B200_MERGE_COMPRESS", flag)
-        nw = network.Network(net, "precision=fp16,max_batch=%d" % n)
+        nw = network.Network(net, "precision=fp16,max_batch=%d,merge_compress=%s" % (n, flag))
         outs.append(nw.evaluate(masks, values))
         assert nw.device_status() == 0
         nw.close()
@@ -232,7 +231,7 @@ def test_merged_qkv_and_smolgen_compression_launch_matches_separate_launches(mon
     assert np.abs(outs[0]["q"] - outs[1]["q"]).max() <= 2e-3
 
 
-def test_split_last_wave_matches_whole_tiles(monkeypatch):
+def test_split_last_wave_matches_whole_tiles():
     """Products whose last wave of 256x256 tiles fills at most half of the CTA pairs compute that wave as half-width
     tiles (out-projection and FFN2 here, both with residual input and row statistics): same results as whole tiles."""
     net = mknet.make_net("cfg4_2layer")
@@ -243,8 +242,7 @@ def test_split_last_wave_matches_whole_tiles(monkeypatch):
     values = np.ones((n, 112), np.float32)
     outs = []
     for flag in ("1", "0"):
-        monkeypatch.setenv("B200_SPLIT_LAST_WAVE", flag)
-        nw = network.Network(net, "precision=fp16,max_batch=%d" % n)
+        nw = network.Network(net, "precision=fp16,max_batch=%d,split_last_wave=%s" % (n, flag))
         outs.append(nw.evaluate(masks, values))
         assert nw.device_status() == 0
         nw.close()
