@@ -60,6 +60,15 @@ CONFIGS["cfg4_mini"] = dict(CONFIGS["cfg4"], layers=2, emb=128, heads=4, dff=192
 # BT4-class shapes (E=1024, 32 heads, dff 1536, smolgen 32/256/256) but only two layers: the
 # tensor-core kernels see their production tile shapes while the CPU oracle still runs fast.
 CONFIGS["cfg4_2layer"] = dict(CONFIGS["cfg4"], layers=2, seed=1024)
+# Classical value head (one tanh output, VALUE_CLASSICAL / OUTPUT_CLASSICAL) on a residual and an attention body:
+# the branch of the value head that WDL networks never take (network_blas.cc:764-771).
+CONFIGS["cfg1_mini_tanh"] = dict(CONFIGS["cfg1_mini"], wdl=False, seed=1031)
+CONFIGS["cfg3_mini_tanh"] = dict(CONFIGS["cfg3_mini"], wdl=False, mlh=False, seed=1033)
+# Trained networks carry a few residual-stream channels that are orders of magnitude larger than the rest and rows
+# whose mean is far from zero; random initialisation never produces either.  This variant plants both (LayerNorm
+# gains / offsets of a few channels at 40..200, a common offset on the sub-layer biases), for the LayerNorm
+# arithmetic of the 16-bit path.
+CONFIGS["cfg4_mini_outlier"] = dict(CONFIGS["cfg4_mini"], outlier=True, seed=1044)
 
 
 class _Gen:
@@ -104,8 +113,9 @@ def _make_resnet(c, g):
     w["value"] = _conv(g, V, C, 1)
     w["ip1_val_w"] = _fc(g, VH, V * 64)
     w["ip1_val_b"] = g.normal(VH, 0.01)
-    w["ip2_val_w"] = _fc(g, 3, VH)
-    w["ip2_val_b"] = g.normal(3, 0.01)
+    outs = 3 if c.get("wdl", True) else 1
+    w["ip2_val_w"] = _fc(g, outs, VH)
+    w["ip2_val_b"] = g.normal(outs, 0.01)
     if c["mlh"]:
         M, MH = c["mlh_planes"], c["mlh_hidden"]
         w["moves_left"] = _conv(g, M, C, 1)
@@ -113,9 +123,10 @@ def _make_resnet(c, g):
         w["ip1_mov_b"] = g.normal(MH, 0.01)
         w["ip2_mov_w"] = _fc(g, 1, MH)
         w["ip2_mov_b"] = g.normal(1, 0.01, 1.0)
-    nf = {"input": c["input"], "output": NF.OUTPUT_WDL, "network": NF.NETWORK_SE_WITH_HEADFORMAT,
+    nf = {"input": c["input"], "output": NF.OUTPUT_WDL if c.get("wdl", True) else NF.OUTPUT_CLASSICAL,
+          "network": NF.NETWORK_SE_WITH_HEADFORMAT,
           "policy": NF.POLICY_CLASSICAL if c["policy"] == "classical" else NF.POLICY_CONVOLUTION,
-          "value": NF.VALUE_WDL,
+          "value": NF.VALUE_WDL if c.get("wdl", True) else NF.VALUE_CLASSICAL,
           "moves_left": NF.MOVES_LEFT_V1 if c["mlh"] else NF.MOVES_LEFT_NONE,
           "default_activation": NF.DEFAULT_ACTIVATION_RELU}
     return w, nf
@@ -175,7 +186,8 @@ def _make_attn(c, g):
     V, VH = c["value_planes"], c["value_hidden"]
     val = {"ip_val_w": g.normal(V * E, S), "ip_val_b": g.normal(V, S),
            "ip1_val_w": g.normal(VH * V * 64, S), "ip1_val_b": g.normal(VH, S),
-           "ip2_val_w": g.normal(3 * VH, S), "ip2_val_b": g.normal(3, S)}
+           "ip2_val_w": g.normal((3 if c.get("wdl", True) else 1) * VH, S),
+           "ip2_val_b": g.normal(3 if c.get("wdl", True) else 1, S)}
     if c["multihead"]:
         w["policy_heads"] = {"ip_pol_w": g.normal(PE * E, S), "ip_pol_b": g.normal(PE, S),
                              "vanilla": pol}
@@ -193,17 +205,38 @@ def _make_attn(c, g):
         w["ip1_mov_b"] = g.normal(MH, S)
         w["ip2_mov_w"] = g.normal(MH, S)
         w["ip2_mov_b"] = g.normal(1, S, 0.5)
-    nf = {"input": c["input"], "output": NF.OUTPUT_WDL,
+    nf = {"input": c["input"], "output": NF.OUTPUT_WDL if c.get("wdl", True) else NF.OUTPUT_CLASSICAL,
           "network": NF.NETWORK_ATTENTIONBODY_WITH_MULTIHEADFORMAT if c["multihead"]
           else NF.NETWORK_ATTENTIONBODY_WITH_HEADFORMAT,
-          "policy": NF.POLICY_ATTENTION, "value": NF.VALUE_WDL,
+          "policy": NF.POLICY_ATTENTION, "value": NF.VALUE_WDL if c.get("wdl", True) else NF.VALUE_CLASSICAL,
           "moves_left": NF.MOVES_LEFT_V1 if c["mlh"] else NF.MOVES_LEFT_NONE,
           "default_activation": c["default_act"], "ffn_activation": c["ffn_act"],
           "input_embedding": NF.INPUT_EMBEDDING_PE_DENSE if c["pe_dense"]
           else NF.INPUT_EMBEDDING_PE_MAP}
     if sg:
         nf["smolgen_activation"] = sg["act"]
+    if c.get("outlier"):
+        _plant_outliers(w, g.encoding)
     return w, nf
+
+
+def _plant_outliers(w, encoding):
+    """Large LayerNorm gains / offsets on a few channels and a common offset on the sub-layer output biases of every
+    encoder layer (see CONFIGS["cfg4_mini_outlier"])."""
+    def edit(holder, key, fn):
+        a = netproto.layer_to_array(holder[key]).copy()
+        fn(a)
+        holder[key] = array_to_layer(a, encoding)
+
+    for i, enc in enumerate(w["encoder"]):
+        def bump(a, ch, v):
+            a[ch % a.size] = v
+        edit(enc, "ln1_gammas", lambda a: bump(a, 3 + 7 * i, 12.0))
+        edit(enc, "ln1_betas", lambda a: bump(a, 3 + 7 * i, 20.0))
+        edit(enc, "ln2_gammas", lambda a: bump(a, 11 + 5 * i, 16.0))
+        edit(enc, "ln2_betas", lambda a: bump(a, 11 + 5 * i, -24.0))
+        edit(enc["mha"], "dense_b", lambda a: a.__iadd__(np.float32(5.0)))
+        edit(enc["ffn"], "dense2_b", lambda a: a.__isub__(np.float32(7.0)))
 
 
 def make_net(name, encoding=netproto.FLOAT32, **overrides):

@@ -38,6 +38,16 @@ GOLDENS = {  # net -> (position set, count)
     "cfg3": ("positions_fmt2_uniform", 16),
     "cfg4_2layer": ("positions_fmt2_uniform", 16),
     "cfg4": ("positions_fmt2_uniform", 8),
+    "cfg1_mini_tanh": ("positions_fmt1_uniform", 32),
+    "cfg3_mini_tanh": ("positions_fmt2_uniform", 32),
+    "cfg4_mini_outlier": ("positions_fmt2_uniform", 64),
+}
+# Large batches, recorded in compact form (the logits of the legal moves only, padded to 256 per position, instead of
+# all 1858): name -> (net, position set, count).  The batch sizes of the headline measurement.
+COMPACT = {
+    "cfg4_2layer_b1024": ("cfg4_2layer", "positions_fmt2_uniform", 1024),
+    "cfg4_b128": ("cfg4", "positions_fmt2_uniform", 128),
+    "cfg5_b128": ("cfg4", "positions_fmt2_split", 128),
 }
 
 
@@ -101,6 +111,26 @@ def main():
                                 count=np.int32(count), backend=np.array("blas"), **out)
             os.remove(npath)
             print("golden", net, out["policy"].shape, "q", out["q"][:3], "m", out["m"][:3])
+        for name, (net, pset, count) in COMPACT.items():
+            if only and name not in only:
+                continue
+            npath = os.path.join(tmp, net + ".pb.gz")
+            mknet.write_net(net, npath)
+            ppath = os.path.join(tmp, name + ".pos")
+            write_pos(ppath, sets[pset], count)
+            opath = os.path.join(tmp, name + ".out")
+            subprocess.check_call([os.path.join(REF, "ref_eval"), "blas", npath, ppath, opath, "threads=8"],
+                                  stderr=subprocess.DEVNULL)
+            out = read_out(opath)
+            legal = sets[pset]["legal"][:count].astype(np.int64)
+            n_legal = sets[pset]["n_legal"][:count]
+            logits = np.take_along_axis(out["policy"], np.clip(legal, 0, 1857), axis=1).astype(np.float32)
+            logits[np.arange(256)[None, :] >= n_legal[:, None]] = 0
+            np.savez_compressed(os.path.join(HERE, "golden_%s.npz" % name), net=np.array(net), positions=np.array(pset),
+                                count=np.int32(count), backend=np.array("blas"), legal_logits=logits, q=out["q"],
+                                d=out["d"], m=out["m"], legal_probs=out["legal_probs"])
+            os.remove(npath)
+            print("golden", name, logits.shape, "q", out["q"][:3], "m", out["m"][:3])
 
 
 if __name__ == "__main__":

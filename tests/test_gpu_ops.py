@@ -176,3 +176,145 @@ def test_attention_op_variants_agree(lib):
 
 def test_attention_op_rejects_fp32_tensor_core_variants(lib):
     assert lib.b200_op_attention(None, None, None, 96, None, None, 32, 0, 1, 32, 0, 1, None) == _lib.ERR_UNSUPPORTED
+
+
+# ---- folded-LayerNorm epilogues of the tensor-core product (b200_op_gemm_ex) -------------------------------------
+def _desc(**kw):
+    d = _lib.GemmDesc()
+    d.scale, d.alpha = 1.0, 1.0
+    for k, v in kw.items():
+        setattr(d, k, v.data_ptr() if hasattr(v, "data_ptr") else v)
+    return d
+
+
+def _planted_rows(M):
+    """Row classes of the epilogue tests: rows whose mean is 100 standard deviations away from zero, rows with one
+    channel at 3e3 or 1e4, and ordinary rows."""
+    r = np.arange(M)
+    return {"shifted": r[r % 7 == 3], "outlier3e3": r[r % 11 == 5], "outlier1e4": r[r % 13 == 8]}
+
+
+def _fold(W, b, gamma, beta, dt):
+    """What the loader does for a product that consumes a folded LayerNorm: W * gamma rounded to the storage type,
+    its row sums, and beta . W^T + b."""
+    Wg = (W * gamma[None, :]).to(dt)
+    colsum = Wg.float().sum(dim=1).contiguous()
+    bias = (b.double() + (W.double() * beta.double()[None, :]).sum(dim=1)).float().contiguous()
+    return Wg.contiguous(), colsum, bias
+
+
+@pytest.mark.parametrize("prec,M", [(1, 65536), (2, 8192 + 77)])
+def test_folded_layer_norm_epilogues_against_oracle(lib, prec, M):
+    """The three epilogue forms an encoder layer uses, chained as in the layer, at the row count of batch 1024:
+      1. u  = alpha * (A0 W0^T + b0) + R            with per-row (sum, sum of squares) of u accumulated by atomics
+      2. h  = relu2(LN(u) W1^T + b1)                LayerNorm folded: row scale and rank-1 correction from the statistics
+      3. u2 = alpha * (h W2^T + b2) + LN(u)         the residual normalised on the fly, statistics of u2 again
+    against oracle.fc / oracle.layer_norm (fully_connected_layer.cc:50-106, backends/blas/encoder.h:29-78) on a
+    sample of rows that contains every planted row class."""
+    dt = DT[prec]
+    E, F = 1024, 1536
+    alpha, eps_ln = 0.43, 1e-3
+    g = torch.Generator(device="cuda").manual_seed(M + prec)
+    rnd = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    A0 = (rnd(M, E) * 0.5).to(dt)
+    W0 = (rnd(E, E) * E ** -0.5).to(dt)
+    b0 = rnd(E) * 0.1
+    R = rnd(M, E)
+    rows = _planted_rows(M)
+    R[torch.from_numpy(rows["shifted"]).cuda()] += 100.0
+    R[torch.from_numpy(rows["outlier3e3"]).cuda(), 5] = 3000.0
+    R[torch.from_numpy(rows["outlier1e4"]).cuda(), 700] = -10000.0
+    R = R.to(dt)
+    gamma = 1 + rnd(E) * 0.1
+    beta = rnd(E) * 0.1
+    W1 = rnd(F, E) * E ** -0.5
+    b1 = rnd(F) * 0.1
+    W2 = (rnd(E, F) * F ** -0.5).to(dt)
+    b2 = rnd(E) * 0.1
+    W1g, cs1, b1f = _fold(W1, b1, gamma, beta, dt)
+
+    u = torch.zeros(M, E, dtype=dt, device="cuda")
+    st1 = torch.zeros(M, 2, device="cuda")
+    _lib.check(lib.b200_op_gemm_ex(_desc(A=A0, W=W0, bias=b0, C=u, M=M, N=E, K=E, precision=prec, alpha=alpha,
+                                         res=R, out_stats=st1), None))
+    h = torch.zeros(M, F, dtype=dt, device="cuda")
+    _lib.check(lib.b200_op_gemm_ex(_desc(A=u, W=W1g, bias=b1f, C=h, M=M, N=F, K=E, precision=prec,
+                                         activation=oracle.ACT_RELU_2, a_stats=st1, colsum=cs1, a_inv_c=1.0 / E,
+                                         a_eps=eps_ln), None))
+    u2 = torch.zeros(M, E, dtype=dt, device="cuda")
+    st2 = torch.zeros(M, 2, device="cuda")
+    _lib.check(lib.b200_op_gemm_ex(_desc(A=h, W=W2, bias=b2, C=u2, M=M, N=E, K=F, precision=prec, alpha=alpha,
+                                         res=u, res_stats=st1, res_gamma=gamma, res_beta=beta, res_inv_c=1.0 / E,
+                                         res_eps=eps_ln, out_stats=st2), None))
+    torch.cuda.synchronize()
+
+    rng = np.random.default_rng(7)
+    sample = np.unique(np.concatenate([rows["shifted"][:96], rows["outlier3e3"][:64], rows["outlier1e4"][:64],
+                                       rng.integers(0, M, 256), [0, M - 1]]))
+    sel = torch.from_numpy(sample).cuda()
+    f = lambda t: t.float().cpu().numpy()
+    rt = 2.0 ** -10 if prec == 1 else 2.0 ** -7  # output rounding of the storage type
+    # 1: product + plain residual + statistics
+    u_ref = alpha * oracle.fc(f(A0[sel]), f(W0).reshape(-1), f(b0), oracle.ACT_NONE, E) + f(R[sel])
+    assert np.all(np.abs(f(u[sel]) - u_ref) <= rt * np.abs(u_ref) + 2e-3)
+    s_ref = np.stack([u_ref.sum(-1, dtype=np.float64), (u_ref.astype(np.float64) ** 2).sum(-1)], 1)
+    mag = np.stack([np.abs(u_ref).sum(-1, dtype=np.float64), s_ref[:, 1]], 1)  # what the fp32 partial sums add up
+    assert np.all(np.abs(f(st1[sel]) - s_ref) <= 2e-5 * mag + 1e-3)
+    # 2: folded LayerNorm of the stored (rounded) u, two-pass in the oracle
+    un = f(u[sel])
+    x = oracle.layer_norm(un, 1.0, None, np.ones(E, np.float32), np.zeros(E, np.float32), eps_ln)
+    h_ref = oracle.fc(x, f(W1g).reshape(-1), f(b1f), oracle.ACT_RELU_2, F)
+    err = np.abs(f(h[sel]) - h_ref) - (rt * np.abs(h_ref) + 3e-3)
+    assert err.max() <= 0, "folded LayerNorm product: worst excess %.3g in sampled row %d" % (
+        err.max(), sample[err.max(-1).argmax()])
+    # 3: residual normalised on the fly
+    ln_u = oracle.layer_norm(un, 1.0, None, f(gamma), f(beta), eps_ln)
+    u2_ref = alpha * oracle.fc(f(h[sel]), f(W2).reshape(-1), f(b2), oracle.ACT_NONE, E) + ln_u
+    err = np.abs(f(u2[sel]) - u2_ref) - (rt * np.abs(u2_ref) + 3e-3)
+    assert err.max() <= 0, "normalised residual: worst excess %.3g in sampled row %d" % (
+        err.max(), sample[err.max(-1).argmax()])
+    s2_ref = np.stack([u2_ref.sum(-1, dtype=np.float64), (u2_ref.astype(np.float64) ** 2).sum(-1)], 1)
+    mag2 = np.stack([np.abs(u2_ref).sum(-1, dtype=np.float64), s2_ref[:, 1]], 1)
+    # u2_ref is built from the rounded h and u, the kernel's sums from its own unrounded values: the storage
+    # type's rounding, not the summation, bounds the difference
+    assert np.all(np.abs(f(st2[sel]) - s2_ref) <= 4 * rt * mag2 + 1e-2)
+
+
+@pytest.mark.parametrize("whole_tiles", [0, 1])
+def test_second_output_of_the_pair_kernel_with_folded_input(lib, whole_tiles):
+    """Q, K, V and the smolgen compression from one launch (columns from n_split on go to a second matrix through a
+    narrow last tile), with the LayerNorm of the input folded in, at the row count of batch 1024."""
+    M, E, N, hc = 65536, 1024, 3072, 32
+    g = torch.Generator(device="cuda").manual_seed(11)
+    rnd = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    u = (rnd(M, E) * 2 + 0.5).half()
+    gamma, beta = 1 + rnd(E) * 0.1, rnd(E) * 0.1
+    W = rnd(N + hc, E) * E ** -0.5
+    b = torch.cat([rnd(N) * 0.1, torch.zeros(hc, device="cuda")])
+    Wg, cs, bf = _fold(W, b, gamma, beta, torch.float16)
+    uf = u.float()
+    stats = torch.stack([uf.sum(1), (uf * uf).sum(1)], 1).contiguous()
+    C = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+    C2 = torch.zeros(M, hc, dtype=torch.float16, device="cuda")
+    _lib.check(lib.b200_op_gemm_ex(_desc(A=u, W=Wg, bias=bf, C=C, M=M, N=N + hc, K=E, precision=1, a_stats=stats,
+                                         colsum=cs, a_inv_c=1.0 / E, a_eps=1e-3, C2=C2, ldc2=hc, n_split=N,
+                                         whole_tiles=whole_tiles), None))
+    torch.cuda.synchronize()
+    sample = np.unique(np.concatenate([np.random.default_rng(3).integers(0, M, 300), [0, 127, 128, M - 129, M - 1]]))
+    sel = torch.from_numpy(sample).cuda()
+    f = lambda t: t.float().cpu().numpy()
+    x = oracle.layer_norm(f(u[sel]), 1.0, None, np.ones(E, np.float32), np.zeros(E, np.float32), 1e-3)
+    ref = oracle.fc(x, f(Wg).reshape(-1), f(bf), oracle.ACT_NONE, N + hc)
+    got = np.concatenate([f(C[sel]), f(C2[sel])], 1)
+    assert np.all(np.abs(got - ref) <= 2.0 ** -10 * np.abs(ref) + 3e-3)
+
+
+def test_gemm_ex_rejects_inconsistent_descriptions(lib):
+    a = torch.zeros(256, 64, dtype=torch.float16, device="cuda")
+    st = torch.zeros(256, 2, device="cuda")
+    assert lib.b200_op_gemm_ex(_desc(A=a, W=a, C=a, M=256, N=64, K=64, precision=0), None) == _lib.ERR_UNSUPPORTED
+    assert lib.b200_op_gemm_ex(_desc(A=a, W=a, C=a, M=256, N=64, K=64, precision=1, a_stats=st), None) == \
+        _lib.ERR_UNSUPPORTED  # statistics without column sums
+    assert lib.b200_op_gemm_ex(_desc(A=a, W=a, C=a, M=256, N=64, K=64, precision=1, C2=a, ldc2=64, n_split=32),
+                               None) == _lib.ERR_UNSUPPORTED  # too small for the kernel that has a second output
+    assert lib.b200_op_gemm_ex(None, None) == _lib.ERR_INVALID

@@ -2,15 +2,32 @@
 import numpy as np
 import pytest
 
-from conftest import load_case
+from conftest import legal_logits, load_case, load_compact
 from lc0_b200 import _lib, mknet, network, weights
 from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
-ALL = ["cfg1_mini", "cfg2_mini", "cfg3_mini", "cfg4_mini", "cfg1", "cfg2", "cfg3", "cfg4_2layer"]
-# fp32 verification mode: error relative to the largest logit of the batch (north star: <= 1e-5).
+ALL = ["cfg1_mini", "cfg2_mini", "cfg3_mini", "cfg4_mini", "cfg1", "cfg2", "cfg3", "cfg4_2layer", "cfg1_mini_tanh",
+       "cfg3_mini_tanh"]
+# fp32 verification mode, per logit: |got - want| <= 1e-5 * max(|want|, rms of the position's logits) + 1e-6.  The
+# relative term is anchored at the position's typical logit because two fp32 implementations of the same network that
+# only differ in summation order (the reference's OpenBLAS path and the numpy restatement) already differ by a few
+# 1e-6 on logits of order one, whatever the size of the individual logit.
 FP32_REL = 1e-5
+FP32_FLOOR = 1e-6
+
+
+def _assert_fp32_logits(got, want):
+    rms = np.sqrt(np.mean(np.square(want), axis=-1, keepdims=True))
+    bound = FP32_REL * np.maximum(np.abs(want), rms) + FP32_FLOOR
+    excess = np.abs(got - want) - bound
+    assert excess.max() <= 0, "worst logit exceeds its bound by %.3g" % excess.max()
+
+
+def _assert_fp32_scalar(got, want):
+    assert np.all(np.abs(got - want) <= FP32_REL * np.maximum(1.0, np.abs(want)) + FP32_FLOOR)
+
 # fp16 storage with fp32 accumulation (north star: policy softmax and WDL/Q/M max-abs <= 2e-3).
 HALF_ATOL = 2e-3
 
@@ -35,10 +52,9 @@ def test_fp32_mode_matches_reference(name):
     nw = network.Network(net, "precision=fp32,max_batch=%d" % n)
     out = nw.evaluate(pos["masks"][:n], pos["values"][:n])
     nw.close()
-    scale = float(np.abs(g["policy"]).max())
-    assert np.abs(out["policy"] - g["policy"]).max() <= FP32_REL * scale
+    _assert_fp32_logits(out["policy"], g["policy"])
     for k in ("q", "d", "m"):
-        assert np.abs(out[k] - g[k]).max() <= FP32_REL * max(1.0, float(np.abs(g[k]).max()))
+        _assert_fp32_scalar(out[k], g[k])
     worst, agree, decided = _softmax_err_and_argmax(out["policy"], g["policy"], pos, n)
     assert agree == decided
 
@@ -59,16 +75,23 @@ def test_fp16_mode_within_tolerance(name, tc):
     assert np.all(np.abs(out["m"] - g["m"]) <= HALF_ATOL * np.maximum(1.0, np.abs(g["m"])))
 
 
+# bf16 storage keeps 8 significant bits in the residual stream (fp16: 11).  The policy softmax stays within the 2e-3 of
+# the 16-bit contract on these networks; q, d and m do not (measured up to 5e-3) and are held to 1e-2.
+BF16_VALUE_ATOL = 1e-2
+
+
 @pytest.mark.parametrize("name", ["cfg3_mini", "cfg4_mini", "cfg4_2layer", "cfg2_mini"])
 def test_bf16_mode_runs_close(name):
-    """bf16 keeps 8 mantissa bits in the residual stream: looser bound, reported for completeness."""
     net, pos, n, g = load_case(name)
     nw = network.Network(net, "precision=bf16,max_batch=%d" % n)
     out = nw.evaluate(pos["masks"][:n], pos["values"][:n])
+    assert nw.device_status() == 0
     nw.close()
     worst, agree, decided = _softmax_err_and_argmax(out["policy"], g["policy"], pos, n)
     assert worst <= HALF_ATOL
-    assert np.abs(out["q"] - g["q"]).max() <= 1e-2
+    assert np.abs(out["q"] - g["q"]).max() <= BF16_VALUE_ATOL
+    assert np.abs(out["d"] - g["d"]).max() <= BF16_VALUE_ATOL
+    assert np.all(np.abs(out["m"] - g["m"]) <= BF16_VALUE_ATOL * np.maximum(1.0, np.abs(g["m"])))
 
 
 def test_full_bt4_class_net_fp16_against_reference():
@@ -83,6 +106,138 @@ def test_full_bt4_class_net_fp16_against_reference():
     assert np.abs(out["q"] - g["q"]).max() <= HALF_ATOL
     assert np.abs(out["d"] - g["d"]).max() <= HALF_ATOL
     assert np.all(np.abs(out["m"] - g["m"]) <= HALF_ATOL * np.maximum(1.0, np.abs(g["m"])))
+
+
+def _compact_errors(out, g, pos, idx):
+    """(worst legal-softmax error, argmax agreements, decided positions) against a compact golden; `idx` maps the
+    evaluated rows to the golden's positions."""
+    worst, agree, decided = 0.0, 0, 0
+    got = legal_logits(out["policy"], {"legal": pos["legal"][idx], "n_legal": pos["n_legal"][idx]}, len(idx))
+    for r, i in enumerate(idx):
+        k = int(pos["n_legal"][i])
+        if k == 0:
+            continue
+        a = oracle.legal_softmax(got[r][:k], np.arange(k))
+        b = oracle.legal_softmax(g["legal_logits"][i][:k], np.arange(k))
+        worst = max(worst, float(np.abs(a - b).max()))
+        top = np.sort(b)[::-1]
+        if len(top) < 2 or top[0] - top[1] > 2 * HALF_ATOL:
+            decided += 1
+            agree += int(a.argmax() == b.argmax())
+    return worst, agree, decided
+
+
+def _assert_half_against_compact(out, g, pos, idx):
+    worst, agree, decided = _compact_errors(out, g, pos, idx)
+    assert worst <= HALF_ATOL and agree == decided, (worst, agree, decided)
+    assert np.abs(out["q"] - g["q"][idx]).max() <= HALF_ATOL
+    assert np.abs(out["d"] - g["d"][idx]).max() <= HALF_ATOL
+    assert np.all(np.abs(out["m"] - g["m"][idx]) <= HALF_ATOL * np.maximum(1.0, np.abs(g["m"][idx])))
+
+
+@pytest.mark.parametrize("batch", [64, 256, 1024, 4096])
+def test_fp16_at_the_measured_batch_sizes_against_reference(batch):
+    """The BT4-class layer shapes (two layers) at the batch sizes the throughput is quoted on, against outputs of
+    the reference's CPU backend for the same 1024 positions: the multi-wave tile schedule of the large products, the
+    split last wave, the folded LayerNorm epilogues with their atomically accumulated row statistics and the merged
+    QKV + smolgen-compression launch only exist at these sizes.  4096 = the 1024 positions four times in one batch."""
+    net, pos, n, g = load_compact("cfg4_2layer_b1024")
+    idx = np.arange(batch) % n
+    nw = network.Network(net, "precision=fp16,max_batch=%d" % batch)
+    for rep in range(3):  # plain launches, then the captured graph
+        out = nw.evaluate(pos["masks"][idx], pos["values"][idx])
+        assert nw.device_status() == 0
+        _assert_half_against_compact(out, g, pos, idx)
+    nw.close()
+
+
+@pytest.mark.parametrize("batch", [64, 1024])
+def test_fp32_at_the_measured_batch_sizes_against_reference(batch):
+    net, pos, n, g = load_compact("cfg4_2layer_b1024")
+    idx = np.arange(batch)
+    nw = network.Network(net, "precision=fp32,max_batch=%d" % batch)
+    out = nw.evaluate(pos["masks"][idx], pos["values"][idx])
+    nw.close()
+    got = legal_logits(out["policy"], pos, batch)
+    want = g["legal_logits"][:batch]
+    rms = np.sqrt((want ** 2).sum(-1, keepdims=True) / np.maximum(1, pos["n_legal"][:batch])[:, None])
+    assert np.all(np.abs(got - want) <= FP32_REL * np.maximum(np.abs(want), rms) + FP32_FLOOR)
+    for k in ("q", "d", "m"):
+        _assert_fp32_scalar(out[k], g[k][:batch])
+
+
+@pytest.mark.parametrize("name", ["cfg4_b128", "cfg5_b128"])
+def test_full_bt4_class_net_fp16_at_batch_128(name):
+    """All 15 layers on 128 recorded positions: the uniform playout set and the opening / middlegame mix."""
+    net, pos, n, g = load_compact(name)
+    idx = np.arange(n)
+    nw = network.Network(net, "precision=fp16,max_batch=%d" % n)
+    out = nw.evaluate(pos["masks"][:n], pos["values"][:n])
+    assert nw.device_status() == 0
+    nw.close()
+    _assert_half_against_compact(out, g, pos, idx)
+
+
+@pytest.mark.parametrize("fold", [1, 0])
+def test_outlier_channels_and_shifted_rows_fp16(fold):
+    """A network with planted outlier channels (LayerNorm gains / offsets 12..24 on single channels) and a common
+    offset on the sub-layer biases, so that residual-stream rows have a mean far from zero: the folded LayerNorm
+    (one-pass row statistics accumulated by the producing product) against the reference, and the explicit LayerNorm
+    kernels beside it."""
+    net, pos, n, g = load_case("cfg4_mini_outlier")
+    nw = network.Network(net, "precision=fp16,max_batch=%d,fold_ln=%d" % (n, fold))
+    out = nw.evaluate(pos["masks"][:n], pos["values"][:n])
+    assert nw.device_status() == 0
+    nw.close()
+    worst, agree, decided = _softmax_err_and_argmax(out["policy"], g["policy"], pos, n)
+    assert worst <= HALF_ATOL and agree == decided, (worst, agree, decided)
+    assert np.abs(out["q"] - g["q"]).max() <= HALF_ATOL
+    assert np.abs(out["d"] - g["d"]).max() <= HALF_ATOL
+    assert np.all(np.abs(out["m"] - g["m"]) <= HALF_ATOL * np.maximum(1.0, np.abs(g["m"])))
+
+
+def test_kernel_timeout_is_reported_by_the_evaluation_call():
+    """A status word set the way a kernel whose bounded wait gave up sets it makes the evaluation that finds it fail
+    with B200_ERR_TIMEOUT (nothing on the GPU is disturbed: the word is written from the host), the word is cleared,
+    and the next evaluation succeeds."""
+    net, pos, n, g = load_case("cfg4_mini")
+    nw = network.Network(net, "precision=fp16,max_batch=32,slots=2")
+    want = nw.evaluate(pos["masks"][:n], pos["values"][:n])
+    for attempt in range(2):  # plain launches first, the captured graph the second time
+        nw.inject_device_status(103)
+        failures = 0
+        for slot in range(2):  # one failure per slot, whichever slot a call draws
+            c = nw.new_computation()
+            c.add_inputs(pos["masks"][:n], pos["values"][:n])
+            try:
+                c.compute_blocking()
+            except _lib.B200Error as e:
+                assert e.code == _lib.ERR_TIMEOUT and "103" in str(e)
+                failures += 1
+            c.close()
+        assert failures >= 1
+        nw.inject_device_status(0)
+        got = nw.evaluate(pos["masks"][:n], pos["values"][:n])
+        np.testing.assert_array_equal(got["policy"], want["policy"])
+    assert nw.device_status() == 0
+    nw.close()
+
+
+def test_unsupported_topologies_are_refused_at_load():
+    """An attention body on top of a residual tower and smolgen widths the LayerNorm kernels cannot take fail in the
+    factory, not at the first evaluation."""
+    from lc0_b200 import netproto
+    tower = netproto.parse_net(netproto.encode("Net", mknet.make_net("cfg1_mini")))
+    body = netproto.parse_net(netproto.encode("Net", mknet.make_net("cfg3_mini")))
+    mixed = dict(body)
+    mixed["weights"] = dict(body["weights"], input=tower["weights"]["input"], residual=tower["weights"]["residual"])
+    with pytest.raises(_lib.B200Error, match="residual tower") as e:
+        network.Network(mixed, "precision=fp16,max_batch=8")
+    assert e.value.code == _lib.ERR_UNSUPPORTED
+    odd = mknet.make_net("cfg4_mini", smolgen=dict(hc=8, hidden=36, gen=32, act=mknet.NF.ACTIVATION_SWISH))
+    with pytest.raises(_lib.B200Error, match="smolgen widths") as e:
+        network.Network(netproto.parse_net(netproto.encode("Net", odd)), "precision=fp16,max_batch=8")
+    assert e.value.code == _lib.ERR_UNSUPPORTED
 
 
 def test_computation_api_and_batch_shapes():

@@ -6,7 +6,7 @@ reference's network_blas.cc compiled from its sources, on seeded networks and po
 import numpy as np
 import pytest
 
-from conftest import load_case
+from conftest import legal_logits, load_case, load_compact
 from lc0_b200 import weights
 from oracle import oracle
 
@@ -16,7 +16,7 @@ VALUE_ATOL = 5e-6
 
 
 @pytest.mark.parametrize("name", ["cfg1_mini", "cfg2_mini", "cfg3_mini", "cfg4_mini", "cfg1", "cfg2", "cfg3",
-                                  "cfg4_2layer"])
+                                  "cfg4_2layer", "cfg1_mini_tanh", "cfg3_mini_tanh", "cfg4_mini_outlier"])
 def test_oracle_matches_reference_blas(name):
     net, pos, n, g = load_case(name)
     meta, t = weights.flatten(net)
@@ -28,6 +28,29 @@ def test_oracle_matches_reference_blas(name):
     np.testing.assert_allclose(out["m"], g["m"], rtol=0, atol=VALUE_ATOL)
     # the outputs must actually depend on the position
     assert np.abs(g["policy"] - g["policy"][0]).max() > 1e-4
+
+
+def test_classical_value_goldens_use_the_tanh_branch():
+    """VALUE_CLASSICAL networks: q = tanh(value), d = 0 (network_blas.cc:764-771)."""
+    for name in ("cfg1_mini_tanh", "cfg3_mini_tanh"):
+        net, pos, n, g = load_case(name)
+        meta, t = weights.flatten(net)
+        assert meta["value"] == 1  # VALUE_CLASSICAL
+        assert np.all(g["d"] == 0) and np.all(np.abs(g["q"]) < 1) and np.abs(g["q"]).max() > 1e-3
+
+
+def test_compact_large_batch_golden_matches_oracle_on_a_sample():
+    """The 1024-position golden of the two-layer BT4-class net: the oracle on 24 positions spread over the set."""
+    net, pos, n, g = load_compact("cfg4_2layer_b1024")
+    assert n == 1024 and g["legal_logits"].shape == (1024, 256)
+    meta, t = weights.flatten(net)
+    idx = np.arange(0, 1024, 43)
+    out = oracle.forward(meta, t, pos["masks"][idx], pos["values"][idx])
+    sub = {k: pos[k][idx] for k in ("legal", "n_legal")}
+    np.testing.assert_allclose(legal_logits(out["policy"], sub, len(idx)), g["legal_logits"][idx], rtol=0,
+                               atol=POLICY_ATOL)
+    np.testing.assert_allclose(out["q"], g["q"][idx], rtol=0, atol=VALUE_ATOL)
+    np.testing.assert_allclose(out["m"], g["m"][idx], rtol=0, atol=VALUE_ATOL)
 
 
 def test_oracle_empty_batch():
