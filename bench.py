@@ -28,6 +28,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+NOMINAL_DENSE_TFLOPS = 2250.0  # B200 dense fp16 / bf16 tensor throughput as specified (not measured)
 METRIC = "nn_evals_per_sec"
 UNIT = "evals/s"
 NET = "cfg4"
@@ -161,40 +162,61 @@ def cpu_reference(sample_positions, repeats, threads=None):
                        % (sample_positions, repeats, NET))
 
 
-def run_reference_cuda(args, rank):
-    """--impl reference-cuda (extra, not part of the driver contract): the reference's own CUDA backend
-    (`cuda-fp16`: cuBLAS GEMMs + its SIMT kernels, built for sm_100 by `oracle/build_ref.py --cuda`) on the same
-    GPU, same network, same batch, through lc0's NetworkComputation API with host buffers."""
-    if rank != 0:
-        return
+def reference_cuda_eval(net_name, runs, pos_fmt, backend, opts=""):
+    """The reference's own CUDA backend (oracle/_ref/ref_eval_cuda: cuBLAS GEMMs + lc0's SIMT kernels, built for sm_100
+    from the reference sources by `oracle/build_ref.py --cuda`) on this GPU through lc0's NetworkComputation API with
+    host buffers.  `runs` is a list of (batch, repeats); returns one dict(value, p50_ms, p99_ms) or
+    dict(unavailable=why) per run."""
     from lc0_b200 import mknet, netproto
     exe = os.path.join(ROOT, "oracle", "_ref", "ref_eval_cuda")
     if not os.path.exists(exe):
-        print(json.dumps({"impl": "reference-cuda", "unavailable": "oracle/_ref/ref_eval_cuda is not built"}))
+        return [{"unavailable": "oracle/_ref/ref_eval_cuda is not built"} for _ in runs]
+    out = []
+    with tempfile.TemporaryDirectory() as tmp:
+        npath, ppath = os.path.join(tmp, "net.pb"), os.path.join(tmp, "p.pos")
+        netproto.write_net(npath, mknet.make_net(net_name), compress=False)
+        for batch, repeats in runs:
+            masks, values = load_positions(0, batch, pos_fmt)
+            with open(ppath, "wb") as f:
+                f.write(b"LC0POS1\0")
+                f.write(np.array([batch, pos_fmt], "<i4").tobytes())
+                f.write(masks.astype("<u8").tobytes())
+                f.write(values.astype("<f4").tobytes())
+                f.write(np.zeros(2 * batch, "<i4").tobytes())
+                f.write(np.full((batch, 256), -1, "<i2").tobytes())
+            try:
+                r = subprocess.run([exe, backend, npath, ppath, "-",
+                                    "max_batch=%d%s" % (batch, "," + opts if opts else ""), str(max(1, repeats))],
+                                   capture_output=True, text=True, timeout=600)
+            except subprocess.TimeoutExpired:
+                out.append({"unavailable": "ref_eval_cuda did not finish within 600 s"})
+                continue
+            if r.returncode != 0 or "evals_per_s=" not in r.stdout:
+                out.append({"unavailable": (r.stderr or r.stdout).strip()[-300:]})
+                continue
+            field = lambda k: float(r.stdout.split(k + "=")[1].split()[0]) if k + "=" in r.stdout else None
+            out.append({"value": field("evals_per_s"), "p50_ms": field("p50_ms"), "p99_ms": field("p99_ms"),
+                        "batch": batch, "backend": backend, "repeats": repeats})
+    return out
+
+
+def run_reference_cuda(args, rank):
+    """--impl reference-cuda (extra, not part of the driver contract): the reference's own CUDA backend on the same
+    GPU, same network, same batch."""
+    if rank != 0:
         return
     net_name, cfg_batch, pos_fmt, cfg_prec, cfg_desc = CONFIGS[args.config]
     B = args.batch or cfg_batch
     backend = "cuda" if (args.precision or cfg_prec) == "fp32" else "cuda-fp16"
-    masks, values = load_positions(0, B, pos_fmt)
-    with tempfile.TemporaryDirectory() as tmp:
-        npath, ppath = os.path.join(tmp, "net.pb"), os.path.join(tmp, "p.pos")
-        netproto.write_net(npath, mknet.make_net(net_name), compress=False)
-        with open(ppath, "wb") as f:
-            f.write(b"LC0POS1\0")
-            f.write(np.array([B, 2], "<i4").tobytes())
-            f.write(masks.astype("<u8").tobytes())
-            f.write(values.astype("<f4").tobytes())
-            f.write(np.zeros(2 * B, "<i4").tobytes())
-            f.write(np.full((B, 256), -1, "<i2").tobytes())
-        r = subprocess.run([exe, backend, npath, ppath, "-", "max_batch=%d" % B, str(max(1, args.steps))],
-                           capture_output=True, text=True, timeout=900)
-    if r.returncode != 0 or "evals_per_s=" not in r.stdout:
-        print(json.dumps({"impl": "reference-cuda", "unavailable": (r.stderr or r.stdout)[-300:]}))
+    res = reference_cuda_eval(net_name, [(B, args.steps)], pos_fmt, backend, args.ref_opts)[0]
+    if "unavailable" in res:
+        print(json.dumps({"impl": "reference-cuda", "unavailable": res["unavailable"]}))
         return
-    v = float(r.stdout.split("evals_per_s=")[1].split()[0])
+    v = res["value"]
     print(json.dumps({"impl": "reference-cuda", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": 1,
                       "steps": args.steps, "ms_per_step": 1000.0 * B / v, "dtype": "fp16" if backend == "cuda-fp16" else "fp32",
                       "config": {"workload": "%s: %s; batch %d; reference backend %s" % (args.config, cfg_desc, B, backend)},
+                      "latency": {"batch": B, "p50_ms": res["p50_ms"], "p99_ms": res["p99_ms"]},
                       "e2e": {"value": v, "unit": UNIT}}), flush=True)
 
 
@@ -230,6 +252,9 @@ def main():
     ap.add_argument("--precision", default="", help="fp16 | bf16 | fp32 (default: the configuration's)")
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-cuda", action="store_true",
+                    help="skip the reference's CUDA backend on the same GPU (reported as `reference_cuda`)")
+    ap.add_argument("--ref-opts", default="", help="extra backend options for --impl reference-cuda")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -256,6 +281,16 @@ def main():
         args.precision = cfg_prec
     if not args.batch:
         args.batch = cfg_batch // world if args.config == "cfg5" else cfg_batch
+    # The reference's own GPU backend on this GPU, before anything of ours is resident: the same network at the
+    # benchmark's batch and at batch 256 (throughput and per-evaluation latency through lc0's API, host buffers).
+    ref_cuda = None
+    if world == 1 and rank == 0 and not args.no_reference_cuda and args.precision != "fp32":
+        ref_cuda = {"what": "the reference's cuda-fp16 backend (cuBLAS + lc0's own kernels, compiled for sm_100 from "
+                            "the reference sources) on the same GPU, NetworkComputation API with host buffers"}
+        sizes = sorted({args.batch, min(256, args.batch)}, reverse=True)
+        for b_ref, res in zip(sizes, reference_cuda_eval(net_name, [(b, 10 if b >= 1024 else 40) for b in sizes],
+                                                         pos_fmt, "cuda-fp16")):
+            ref_cuda["batch_%d" % b_ref] = res
     net = mknet.make_net(net_name)
     # two workspace slots, as the lc0 plug-in creates the network: a second computation can stage its inputs and have
     # its graph queued while the first one's kernels run (the phases with two computations in flight need it)
@@ -306,6 +341,7 @@ def main():
     # kernel by kernel; the timed pass above replays the captured graph of the same launches).
     nw.set_profiling(True)
     nw.get_profile(reset=True)
+    nw.get_profile_tagged(reset=True)
     ep0, ep1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ep0.record(stream)
     for _ in range(args.steps):
@@ -313,6 +349,7 @@ def main():
     ep1.record(stream)
     nw.sync()
     prof = nw.get_profile(reset=True)
+    tagged = nw.get_profile_tagged(reset=True)
     prof_ms = ep0.elapsed_time(ep1)
     nw.set_profiling(False)
     ms = sharding.gather_max(ms, dist if world > 1 else None)
@@ -453,6 +490,9 @@ def main():
         roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05 GEMM, all launches of the timed region)",
                     "achieved": achieved, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
                     "frac": achieved / peaks["tflops_sustained"], "peak_source": peaks["source"] + " sustained bf16",
+                    "frac_of_burst_peak": achieved / peaks["tflops_burst"],
+                    # the nominal dense fp16 / bf16 figure of the part, for context
+                    "frac_nominal": achieved / NOMINAL_DENSE_TFLOPS, "nominal_peak": NOMINAL_DENSE_TFLOPS,
                     "launches": g["launches"], "share_of_step": g["ms"] / total_ms if total_ms else None,
                     # DRAM bytes of the largest launch of the class (QKV + smolgen compression, M = 64 * batch): read
                     # A once and W once, write C once.  An ncu capture of the same kernel at M = 8192 measured DRAM
@@ -472,6 +512,26 @@ def main():
         for k in ("gemm_tc", "gemm_fma", "other"):
             other.setdefault(k, {})["ms_per_step"] = prof[k]["ms"] / args.steps
             other[k]["launches"] = prof[k]["launches"]
+        # the tensor-core products of the encoder layers one by one, timed in place (same pass)
+        by_shape = {}
+        for k in ("qkv", "out_proj", "ffn1", "ffn2", "smolgen_dense", "smolgen_bias", "embedding", "heads"):
+            v = tagged.get(k)
+            if v and v["launches"]:
+                tf = v["work"] / (v["ms"] * 1e-3) / 1e12
+                by_shape[k] = {"us_per_launch": 1000.0 * v["ms"] / v["launches"], "launches": v["launches"],
+                               "TFLOPs": tf, "frac_sustained": tf / peaks["tflops_sustained"],
+                               "frac_nominal": tf / NOMINAL_DENSE_TFLOPS, "ms_per_step": v["ms"] / args.steps}
+        other["gemm_tc"]["by_shape"] = by_shape
+        enc = [tagged[k] for k in ("qkv", "out_proj", "ffn1", "ffn2") if tagged.get(k) and tagged[k]["launches"]]
+        if enc:
+            tf = sum(v["work"] for v in enc) / (sum(v["ms"] for v in enc) * 1e-3) / 1e12
+            other["gemm_tc"]["encoder_gemms"] = {"TFLOPs": tf, "frac_sustained": tf / peaks["tflops_sustained"],
+                                                 "frac_burst": tf / peaks["tflops_burst"],
+                                                 "frac_nominal": tf / NOMINAL_DENSE_TFLOPS,
+                                                 "what": "QKV, output projection, FFN dense 1 and 2 of all layers"}
+        if tagged.get("attention") and tagged["attention"]["launches"]:
+            other.setdefault("attention", {})["us_per_launch"] = \
+                1000.0 * tagged["attention"]["ms"] / tagged["attention"]["launches"]
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
@@ -500,6 +560,7 @@ def main():
             "roofline": roofline,
             "kernel_classes": other,
             "latency": lat,
+            "reference_cuda": ref_cuda,
             "flops_per_eval": info.flops_per_position,
             "model_tflops": value / world * info.flops_per_position / 1e12,
         }

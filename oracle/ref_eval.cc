@@ -7,7 +7,8 @@
 //
 // usage: ref_eval <backend> <net.pb[.gz]> <in.pos> <out.bin|-> [opts-string] [repeat] [limit]
 //   repeat > 0: time <repeat> evaluations after one warm-up and print
-//               "evals_per_s=<v> n=<n> repeat=<r> seconds=<s>" on stdout.
+//               "evals_per_s=<v> n=<n> repeat=<r> seconds=<s> p50_ms=<..> p99_ms=<..>" on stdout
+//               (per-evaluation wall time: AddInput x n, ComputeBlocking, result reads).
 #include <chrono>
 #include <cstdlib>
 #include <algorithm>
@@ -91,12 +92,21 @@ int main(int argc, char** argv) {
       fclose(f);
     }
     if (repeat > 0) {
+      std::vector<double> each;
       const auto t0 = std::chrono::steady_clock::now();
-      for (int r = 0; r < repeat; ++r) Run(net.get(), pf, n);
-      const double sec =
-          std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+      auto prev = t0;
+      for (int r = 0; r < repeat; ++r) {
+        Run(net.get(), pf, n);
+        const auto now = std::chrono::steady_clock::now();
+        each.push_back(std::chrono::duration<double, std::milli>(now - prev).count());
+        prev = now;
+      }
+      const double sec = std::chrono::duration<double>(prev - t0).count();
+      std::sort(each.begin(), each.end());
+      const double p50 = each[each.size() / 2];
+      const double p99 = each[std::min(each.size() - 1, size_t(each.size() * 0.99))];
       std::cout << "evals_per_s=" << double(n) * repeat / sec << " n=" << n
-                << " repeat=" << repeat << " seconds=" << sec << std::endl;
+                << " repeat=" << repeat << " seconds=" << sec << " p50_ms=" << p50 << " p99_ms=" << p99 << std::endl;
     }
   } catch (const std::exception& e) {
     std::cerr << "ref_eval error: " << e.what() << std::endl;
