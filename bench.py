@@ -186,7 +186,11 @@ def reference_cuda_eval(net_name, runs, pos_fmt, backend, opts=""):
                 f.write(np.full((batch, 256), -1, "<i2").tobytes())
             try:
                 r = subprocess.run([exe, backend, npath, ppath, "-",
-                                    "max_batch=%d%s" % (batch, "," + opts if opts else ""), str(max(1, repeats))],
+                                    # the reference captures CUDA graphs for every batch size up to its mini-batch
+                                    # size (2 x SM count = 296, network_cuda.cc:633-648,1041-1044) and fails with
+                                    # "invalid argument" when max_batch is smaller than that
+                                    "max_batch=%d%s" % (max(batch, 512), "," + opts if opts else ""),
+                                    str(max(1, repeats))],
                                    capture_output=True, text=True, timeout=600)
             except subprocess.TimeoutExpired:
                 out.append({"unavailable": "ref_eval_cuda did not finish within 600 s"})
@@ -255,6 +259,7 @@ def main():
     ap.add_argument("--no-reference-cuda", action="store_true",
                     help="skip the reference's CUDA backend on the same GPU (reported as `reference_cuda`)")
     ap.add_argument("--ref-opts", default="", help="extra backend options for --impl reference-cuda")
+    ap.add_argument("--net-options", default="", help="extra options for the network, e.g. fused_se=0,fold_ln=0")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -294,7 +299,8 @@ def main():
     net = mknet.make_net(net_name)
     # two workspace slots, as the lc0 plug-in creates the network: a second computation can stage its inputs and have
     # its graph queued while the first one's kernels run (the phases with two computations in flight need it)
-    nw = network.Network(net, dict(gpu=local_rank, max_batch=args.batch, precision=args.precision, slots=2))
+    nw = network.Network(net, dict(network.parse_options(args.net_options), gpu=local_rank, max_batch=args.batch,
+                                   precision=args.precision, slots=2))
     del net
     info = nw.info
     B = args.batch

@@ -81,7 +81,7 @@ enum {
   B200_FLAG_NO_LN_FOLD = 4,          /* run the encoder LayerNorms as kernels instead of folding them into the products */
   B200_FLAG_NO_MERGED_COMPRESS = 8,  /* smolgen compression as a product of its own instead of riding on the QKV launch */
   B200_FLAG_NO_SPLIT_LAST_WAVE = 16, /* whole 256x256 tiles in the last wave of the CTA-pair kernel */
-  B200_FLAG_NO_FUSED_SMOLGEN = 32    /* smolgen bias written by a product of its own and read back by the attention kernel */
+  B200_FLAG_NO_FUSED_SE = 32         /* squeeze-excitation as a kernel of its own instead of the convolution's epilogue */
 };
 
 typedef struct b200_net_info {
@@ -280,13 +280,13 @@ int b200_op_gemm(const void* A, const void* W, const float* bias, void* C, int M
                  int activation, int precision, int use_tc, void* stream);
 /* b200_op_gemm_ex: the tensor-core product with every epilogue the network's schedule uses, for tests of those
  *   epilogues on their own.  out = alpha * act(rstd_a * (scale * A . W^T - mean_a * colsum) + bias) + residual, where
- *   - a_stats [M][2] (per-row sum and sum of squares of A's rows over K columns, with a_inv_c = 1/K and a_eps) and
+ *   - a_stats [M][2] (double; per-row sum and sum of squares of A's rows over K columns, with a_inv_c = 1/K and a_eps) and
  *     colsum [N] describe a LayerNorm of A folded into the product (W then holds W * gamma, bias holds
  *     beta . W^T + b): LayerNorm2DWithSkipConnection followed by Forward1D (backends/blas/encoder.h:29-78,
  *     fully_connected_layer.cc:50-106) in one launch; NULL: plain product;
  *   - res [M][N] is added after the activation, normalised on the fly with res_stats / res_gamma / res_beta
  *     (res_inv_c = 1/N, res_eps) when those are given;
- *   - out_stats [M][2] accumulates the per-row sum and sum of squares of the outputs (the caller zeroes it);
+ *   - out_stats [M][2] (double) accumulates the per-row sum and sum of squares of the outputs (the caller zeroes it);
  *   - columns [n_split, N) go to C2 (leading dimension ldc2) instead of C when n_split > 0.
  *   Leading dimensions of 0 mean dense.  fp16 / bf16 only; synchronises the stream before returning. */
 typedef struct b200_gemm_desc {
@@ -295,10 +295,10 @@ typedef struct b200_gemm_desc {
   long long lda, ldw, ldc;
   int activation, precision;
   float scale, alpha;
-  const float* a_stats; const float* colsum; float a_inv_c, a_eps;
+  const double* a_stats; const float* colsum; float a_inv_c, a_eps;
   const void* res; long long ldres;
-  const float* res_stats; const float* res_gamma; const float* res_beta; float res_inv_c, res_eps;
-  float* out_stats;
+  const double* res_stats; const float* res_gamma; const float* res_beta; float res_inv_c, res_eps;
+  double* out_stats;
   void* C2; long long ldc2; int n_split;
   int whole_tiles;
 } b200_gemm_desc;

@@ -19,7 +19,7 @@ FLAG_NO_GRAPHS = 2
 FLAG_NO_LN_FOLD = 4
 FLAG_NO_MERGED_COMPRESS = 8
 FLAG_NO_SPLIT_LAST_WAVE = 16
-FLAG_NO_FUSED_SMOLGEN = 32
+FLAG_NO_FUSED_SE = 32
 POLICY_SIZE = 1858
 INPUT_PLANES = 112
 

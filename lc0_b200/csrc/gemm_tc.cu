@@ -271,30 +271,36 @@ struct TcParams {
   int split_from, tiles_v;
   int conv_cblocks;  // > 0: 3x3 convolution, number of 64-channel blocks of the input (k_blocks = 9 * conv_cblocks)
   // folded LayerNorm (see GemmParams)
-  const float* a_stats; const float* colsum; float a_inv_c, a_eps;
+  const double* a_stats; const float* colsum; float a_inv_c, a_eps;
   int res_mode;  // 0 none, 1 add the residual tile, 2 add the normalised residual tile
-  const float* res_stats; const float* res_gamma; const float* res_beta; float res_inv_c, res_eps;
-  float* out_stats;
+  const double* res_stats; const float* res_gamma; const float* res_beta; float res_inv_c, res_eps;
+  double* out_stats;
   int n_split;  // > 0: columns from here on are stored through the second output map
+  // Squeeze-excitation unit fused into the epilogue of a convolution whose tile holds two whole boards and every
+  // output channel (se_k > 0; see GemmParams).
+  const float* se_w1; const float* se_b1; const float* se_w2; const float* se_b2; const float* se_bias; int se_k;
 };
 
 // Per-thread (= per output row) state of the folded-LayerNorm epilogue.
+// The sums are kept in double: a row whose mean is a hundred standard deviations from zero loses the variance's
+// leading digits in fp32 (sum of squares minus squared mean), which the two-pass reference does not.
 struct RowCtx {
-  float mean_a = 0.f, rstd_a = 1.f, mean_r = 0.f, rstd_r = 1.f, sum = 0.f, sumsq = 0.f;
+  float mean_a = 0.f, rstd_a = 1.f, mean_r = 0.f, rstd_r = 1.f;
+  double sum = 0.0, sumsq = 0.0;
 };
+__device__ __forceinline__ void mean_rstd(const double* stats, long long m, float inv_c, float eps, float& mean,
+                                          float& rstd) {
+  const double2 st = *reinterpret_cast<const double2*>(stats + 2 * m);
+  const double mu = st.x * (double)inv_c;
+  const double var = fmax(st.y * (double)inv_c - mu * mu, 0.0);
+  mean = (float)mu;
+  rstd = rsqrtf((float)var + eps);
+}
 __device__ __forceinline__ void load_row_ctx(const TcParams& p, int m, RowCtx& rc) {
-  rc.sum = 0.f;
-  rc.sumsq = 0.f;
-  if (p.a_stats && m < p.M) {
-    const float2 st = *reinterpret_cast<const float2*>(p.a_stats + 2 * (long long)m);
-    rc.mean_a = st.x * p.a_inv_c;
-    rc.rstd_a = rsqrtf(fmaxf(st.y * p.a_inv_c - rc.mean_a * rc.mean_a, 0.f) + p.a_eps);
-  }
-  if (p.res_mode == 2 && m < p.M) {
-    const float2 st = *reinterpret_cast<const float2*>(p.res_stats + 2 * (long long)m);
-    rc.mean_r = st.x * p.res_inv_c;
-    rc.rstd_r = rsqrtf(fmaxf(st.y * p.res_inv_c - rc.mean_r * rc.mean_r, 0.f) + p.res_eps);
-  }
+  rc.sum = 0.0;
+  rc.sumsq = 0.0;
+  if (p.a_stats && m < p.M) mean_rstd(p.a_stats, m, p.a_inv_c, p.a_eps, rc.mean_a, rc.rstd_a);
+  if (p.res_mode == 2 && m < p.M) mean_rstd(p.res_stats, m, p.res_inv_c, p.res_eps, rc.mean_r, rc.rstd_r);
 }
 __device__ __forceinline__ void flush_row_ctx(const TcParams& p, int m, const RowCtx& rc) {
   if (p.out_stats && m < p.M) {
@@ -337,11 +343,14 @@ __device__ __forceinline__ void load_col_regs(const TcParams& p, int nb, int lan
   }
 }
 
-template <typename T>
+template <typename T, bool kSe = false>
 __device__ __forceinline__ void epilogue_slab(const TcParams& p, uint8_t* buf, uint32_t res_bar, uint32_t free_bar,
                                               uint32_t full_bar, uint32_t use, bool leader, uint32_t taddr, int row,
                                               int lane, int nb, int next_nb, ColRegs& cr, float* wvec, RowCtx& rc,
-                                              volatile int* abort_flag) {
+                                              volatile int* abort_flag, const float* se_arg = nullptr) {
+  const float* se = kSe ? se_arg : nullptr;  // compiled out of the kernels that never fuse squeeze-excitation
+  // se != nullptr: gate (se[0..63]) and shift (se[256..319]) of this row's sample for the slab's 64 columns; the
+  // activation then follows the residual: act(gate * v + shift + residual)   (se_unit.cc:54-61)
   __syncwarp();  // the previous slab's reads of wvec are done
   if (p.bias) { wvec[lane] = cr.bias0; wvec[32 + lane] = cr.bias1; }
   if (p.a_stats) { wvec[64 + lane] = cr.cs0; wvec[96 + lane] = cr.cs1; }
@@ -377,14 +386,24 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, uint8_t* buf, u
         v[j + 3] = rc.rstd_a * (v[j + 3] - rc.mean_a * cs.w);
       }
     }
-    if (p.bias) {
+    if (se) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
-        const float4 b = *reinterpret_cast<const float4*>(wvec + 32 * h + j);
-        v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
+        const float4 g = *reinterpret_cast<const float4*>(se + 32 * h + j);
+        const float4 b = *reinterpret_cast<const float4*>(se + 256 + 32 * h + j);
+        v[j] = fmaf(g.x, v[j], b.x); v[j + 1] = fmaf(g.y, v[j + 1], b.y);
+        v[j + 2] = fmaf(g.z, v[j + 2], b.z); v[j + 3] = fmaf(g.w, v[j + 3], b.w);
       }
+    } else {
+      if (p.bias) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 b = *reinterpret_cast<const float4*>(wvec + 32 * h + j);
+          v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
+        }
+      }
+      apply_activation(v, p.act);
     }
-    apply_activation(v, p.act);
     if (h == 0) {
       // Every thread does its own bounded wait (after a failed wait the result is meaningless and the status word
       // says so): for the residual tile, which the store warp fetched into `buf` once the buffer was free, or
@@ -416,6 +435,7 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, uint8_t* buf, u
         for (int i = 0; i < 8; ++i) v[c * 8 + i] = fmaf(p.alpha, v[c * 8 + i], s[i]);
       }
     }
+    if (se) apply_activation(v, p.act);
     if (p.out_stats) {
       float a = 0.f, q = 0.f;
       const int nh = nb + 32 * h;
@@ -427,8 +447,8 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, uint8_t* buf, u
         for (int j = 0; j < 32; ++j)
           if (nh + j < p.N) { a += v[j]; q = fmaf(v[j], v[j], q); }
       }
-      rc.sum += a;
-      rc.sumsq += q;
+      rc.sum += (double)a;  // 32-column partial sums in fp32, their total in double
+      rc.sumsq += (double)q;
     }
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
@@ -444,6 +464,108 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, uint8_t* buf, u
   fence_async_smem();  // this thread's writes are visible to the TMA store the store warp will issue
   __syncwarp();
   if (lane == 0) mbar_arrive(full_bar);
+}
+
+// Sum over the warp's 32 lanes of each of 32 per-lane values: afterwards v[0] of lane j is the sum of column j.
+// Halving exchange (16 + 8 + 4 + 2 + 1 shuffles) instead of 32 full reductions.
+__device__ __forceinline__ void warp_column_sums(float (&v)[32], int lane) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    const bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < off; ++i) {
+      const float send = upper ? v[i] : v[i + off];
+      const float keep = upper ? v[i + off] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+  }
+}
+
+// Barrier among the 256 epilogue threads of a CTA on an mbarrier, with the bounded wait of every other wait here.
+__device__ __forceinline__ void epilogue_barrier(uint32_t bar, uint32_t& phase, volatile int* abort_flag) {
+  mbar_arrive(bar);
+  mbar_wait(bar, phase & 1, abort_flag, 8);
+  ++phase;
+}
+
+// Squeeze-excitation vectors of the two boards of a convolution tile (ApplySEUnit, backends/blas/se_unit.cc:31-63):
+// pool = mean over the 64 squares of the accumulator + conv bias, hid = act(W1 pool + b1), z = W2 hid + b2,
+// gate = sigmoid(z[:C]), shift = z[C:] + gate * conv bias.  Runs on the eight epilogue warps while the accumulator
+// stays in tensor memory; `gb` receives [2 boards][gate 256 | shift 256].  `tmp` is the per-warp scratch area of the
+// slabs (2048 floats), free between two tiles.
+template <int BN>
+__device__ __forceinline__ void se_prepare(const TcParams& p, uint32_t trow, int quarter, int group, int lane, int eid,
+                                           float* tmp, float* gb, uint32_t bar, uint32_t& phase,
+                                           volatile int* abort_flag) {
+  float* part = tmp;          // [4 quarters][256] column sums over 32 rows
+  float* pool = tmp + 1024;   // [2][256]
+  float* hid = tmp + 1536;    // [2][64]
+  const int C = p.N;
+  epilogue_barrier(bar, phase, abort_flag);  // nobody still reads the previous tile's per-warp vectors in `tmp`
+#pragma unroll 1
+  for (int c0 = group * 64; c0 < BN; c0 += 128) {
+#pragma unroll 1
+    for (int h = 0; h < 2; ++h) {
+      uint32_t r[32];
+      tmem_ld32(trow + c0 + 32 * h, r);
+      tmem_ld_wait();
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      warp_column_sums(v, lane);
+      part[quarter * 256 + c0 + 32 * h + lane] = v[0];
+    }
+  }
+  epilogue_barrier(bar, phase, abort_flag);
+  {
+    const int c = eid;  // 256 threads, one channel each
+    const float b = c < C ? __ldg(p.se_bias + c) : 0.f;
+    pool[c] = (part[c] + part[256 + c]) * (1.0f / 64.0f) + b;
+    pool[256 + c] = (part[512 + c] + part[768 + c]) * (1.0f / 64.0f) + b;
+  }
+  epilogue_barrier(bar, phase, abort_flag);
+  // hid[s][k]: four threads per output, a quarter of the channels each (C is a multiple of 16 and se_k of 4, so the
+  // quads of a warp run the same trip count).  The weights come from L2: 16-byte loads, several in flight, so that
+  // the whole dot product costs about one round trip.
+  for (int o = eid >> 2; o < 2 * p.se_k; o += 64) {
+    const int sidx = o / p.se_k, k = o - sidx * p.se_k;
+    const int cq = (eid & 3) * (C >> 2);
+    const float4* w = reinterpret_cast<const float4*>(p.se_w1 + (long long)k * C + cq);
+    const float4* x = reinterpret_cast<const float4*>(pool + sidx * 256 + cq);
+    float a = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < (C >> 4); ++i) {
+      const float4 wv = __ldg(w + i), xv = x[i];
+      a = fmaf(wv.x, xv.x, fmaf(wv.y, xv.y, fmaf(wv.z, xv.z, fmaf(wv.w, xv.w, a))));
+    }
+    a += __shfl_xor_sync(0xffffffffu, a, 1);
+    a += __shfl_xor_sync(0xffffffffu, a, 2);
+    if ((eid & 3) == 0) hid[sidx * 64 + k] = activate<false>(a + __ldg(p.se_b1 + k), p.act);
+  }
+  epilogue_barrier(bar, phase, abort_flag);
+  if (eid < C) {
+    const int c = eid;
+    float z0a = __ldg(p.se_b2 + c), z1a = __ldg(p.se_b2 + C + c), z0b = z0a, z1b = z1a;
+    const float4* w0 = reinterpret_cast<const float4*>(p.se_w2 + (long long)c * p.se_k);
+    const float4* w1 = reinterpret_cast<const float4*>(p.se_w2 + (long long)(C + c) * p.se_k);
+    const float4* ha = reinterpret_cast<const float4*>(hid);
+    const float4* hb = reinterpret_cast<const float4*>(hid + 64);
+#pragma unroll 8
+    for (int k = 0; k < (p.se_k >> 2); ++k) {
+      const float4 a = __ldg(w0 + k), b = __ldg(w1 + k), xa = ha[k], xb = hb[k];
+      z0a = fmaf(a.x, xa.x, fmaf(a.y, xa.y, fmaf(a.z, xa.z, fmaf(a.w, xa.w, z0a))));
+      z1a = fmaf(b.x, xa.x, fmaf(b.y, xa.y, fmaf(b.z, xa.z, fmaf(b.w, xa.w, z1a))));
+      z0b = fmaf(a.x, xb.x, fmaf(a.y, xb.y, fmaf(a.z, xb.z, fmaf(a.w, xb.w, z0b))));
+      z1b = fmaf(b.x, xb.x, fmaf(b.y, xb.y, fmaf(b.z, xb.z, fmaf(b.w, xb.w, z1b))));
+    }
+    const float cb = __ldg(p.se_bias + c);
+    const float ga = 1.0f / (1.0f + expf(-z0a)), gbb = 1.0f / (1.0f + expf(-z0b));
+    gb[c] = ga; gb[256 + c] = z1a + ga * cb;
+    gb[512 + c] = gbb; gb[768 + c] = z1b + gbb * cb;
+  } else {
+    gb[eid] = 0.f; gb[256 + eid] = 0.f; gb[512 + eid] = 0.f; gb[768 + eid] = 0.f;
+  }
+  epilogue_barrier(bar, phase, abort_flag);
 }
 
 // A store thread's side of the fast path: for every slab of this CTA's tiles that belongs to the epilogue groups
@@ -549,7 +671,7 @@ template <int BN> struct TileCfg {
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int kEpiBytes = 4 * BM * 128;  // 2 groups x 2 staging buffers of 128 rows x 128 bytes
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 512 /*barriers*/ +
-                                    8192 /*per-warp column vectors*/;
+                                    8192 /*per-warp column vectors*/ + 4096 /*squeeze-excitation gate and shift*/;
 };
 
 
@@ -573,7 +695,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint64_t* res_bar = reinterpret_cast<uint64_t*>(bar_mem + 192);   // [2 groups][2 buffers] residual tile landed
   uint64_t* stg_full = reinterpret_cast<uint64_t*>(bar_mem + 256);  // [2 groups][2 buffers] slab staged (4 warps)
   uint64_t* stg_free = stg_full + 4;                                // [2 groups][2 buffers] store has read the buffer
-  float* wvec = reinterpret_cast<float*>(bar_mem + 512) + ((threadIdx.x >> 5) & 7) * 256;  // per-warp scratch
+  float* wvec_all = reinterpret_cast<float*>(bar_mem + 512);                                // 8 warps x 256 floats
+  float* wvec = wvec_all + ((threadIdx.x >> 5) & 7) * 256;                                  // per-warp scratch
+  uint64_t* se_bar = reinterpret_cast<uint64_t*>(bar_mem + 384);    // barrier of the 256 epilogue threads
+  float* se_gb = reinterpret_cast<float*>(bar_mem + 512 + 8192);    // [2 boards][gate 256 | shift 256]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
@@ -600,6 +725,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       mbar_init(smem_u32(&stg_full[i]), 4);
       mbar_init(smem_u32(&stg_free[i]), 1);
     }
+    mbar_init(smem_u32(se_bar), 256);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -680,7 +806,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int group = (warp - 2) >> 2;
     const bool leader = ((warp - 2) & 3) == 0 && lane == 0;
     uint8_t* gbuf = epi_mem + group * (2 * BM * 128);
-    uint32_t tile_it = 0, slab_it = 0;
+    uint32_t tile_it = 0, slab_it = 0, se_phase = 0;
     ColRegs cr;
     int cr_nb = -1;  // first column of the slab whose vectors `cr` holds
     if ((int)blockIdx.x < tiles && ((int)blockIdx.x % n_tiles) * BN + group * 64 < p.N) {
@@ -700,6 +826,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // Fast path: 64-column slabs -> registers -> swizzled shared memory -> TMA store (clips the M/N tails).
         RowCtx rc;
         load_row_ctx(p, m, rc);
+        const float* se_row = nullptr;
+        if constexpr (BN == 256) {
+          if (p.se_k > 0) {  // one tile = two boards x all channels: the squeeze-excitation vectors of both boards
+            se_prepare<BN>(p, trow, quarter, group, lane, (int)threadIdx.x - 64, wvec_all, se_gb, smem_u32(se_bar),
+                           se_phase, abort_flag);
+            se_row = se_gb + (quarter >> 1) * 512;
+          }
+        }
 #pragma unroll 1
         for (int c0 = group * 64; c0 < BN; c0 += 128) {
           if (n0 + c0 >= p.N) break;  // uniform over the group
@@ -714,9 +848,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (nn < p.N) next_nb = nn;
           }
           cr_nb = next_nb;
-          epilogue_slab<T>(p, gbuf + (slab_it & 1) * (BM * 128), smem_u32(&res_bar[idx]), smem_u32(&stg_free[idx]),
+          epilogue_slab<T, BN == 256>(p, gbuf + (slab_it & 1) * (BM * 128), smem_u32(&res_bar[idx]), smem_u32(&stg_free[idx]),
                            smem_u32(&stg_full[idx]), slab_it >> 1, leader, trow + c0, quarter * 32 + lane, lane,
-                           n0 + c0, next_nb, cr, wvec, rc, abort_flag);
+                           n0 + c0, next_nb, cr, wvec, rc, abort_flag, se_row ? se_row + c0 : nullptr);
           ++slab_it;
         }
         flush_row_ctx(p, m, rc);
@@ -1084,6 +1218,8 @@ void fill_folded(TcParams& p, const GemmParams& g) {
   p.res_inv_c = g.res_inv_c; p.res_eps = g.res_eps;
   p.out_stats = g.out_stats;
   p.n_split = 0;
+  p.se_w1 = g.se_w1; p.se_b1 = g.se_b1; p.se_w2 = g.se_w2; p.se_b2 = g.se_b2; p.se_bias = g.se_bias;
+  p.se_k = g.se_k;
 }
 
 // 4D map over a token-major activation [positions][8][8][channels]; box = 64 channels x 8 x 8 x 2 boards
@@ -1139,8 +1275,9 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
     e = get_map(g.C, g.ldc, g.M, g.N, BM, prec, &mc);
     if (e != cudaSuccess) return e;
   }
-  const bool folded = g.a_stats || g.res || g.out_stats;
+  const bool folded = g.a_stats || g.res || g.out_stats || g.se_k > 0;
   if (folded && !tma_store) return cudaErrorInvalidValue;  // the folded-LayerNorm modes live in the TMA-store epilogue
+  if (g.se_k > 0 && (BN != 256 || !gemm_tc_se_supported(g))) return cudaErrorInvalidValue;
   CUtensorMap mr = mc;
   if (g.res) {
     if ((g.ldres % 8) != 0 || (reinterpret_cast<uintptr_t>(g.res) & 15) != 0) return cudaErrorInvalidValue;
@@ -1267,11 +1404,20 @@ bool gemm_tc_supported(const GemmParams& p) {
          (p.ldw % 8) == 0 && al16(p.A) && al16(p.W);
 }
 
+// Squeeze-excitation in the convolution's epilogue: a 128-row tile is two boards, so all output channels must fit one
+// 256-column tile; the residual arrives through `res`, the hidden width must suit the quad-wise reduction.
+bool gemm_tc_se_supported(const GemmParams& p) {
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  return p.conv_cin > 0 && p.N <= 256 && (p.N % 16) == 0 && al16(p.se_w1) && al16(p.se_w2) && p.se_k >= 4 && p.se_k <= 64 && (p.se_k % 4) == 0 &&
+         p.res && !p.res_stats && !p.a_stats && !p.out_stats && !p.bias && p.n_split == 0 && !p.out_f32 &&
+         p.se_w1 && p.se_b1 && p.se_w2 && p.se_b2 && p.se_bias && p.alpha == 1.0f && p.scale == 1.0f;
+}
+
 namespace {
 // Large problems with 16-bit output go to the CTA-pair kernel (256x256 tiles).
 bool pair_eligible(const GemmParams& p, int sm_count) {
   const bool tma_store_ok = !p.out_f32 && (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
-  return tma_store_ok && p.conv_cin == 0 && p.M >= 512 && p.N > 128 &&
+  return tma_store_ok && p.conv_cin == 0 && p.se_k == 0 && p.M >= 512 && p.N > 128 &&
          (long long)ceil_div(p.M, 2 * BM) * ceil_div(p.N, 256) >= sm_count / 4;
 }
 }  // namespace
@@ -1294,6 +1440,7 @@ cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaS
     const bool four = p.K <= 8 * BK;
     return four ? launch_pair<T, 4>(p, status, sm_count, s) : launch_pair<T, 2>(p, status, sm_count, s);
   }
+  if (p.se_k > 0) return launch_bn<T, 256>(p, status, sm_count, s);  // the tile must hold every channel of two boards
   // Wide tiles amortise the A-tile loads; narrow problems take the smallest tile that covers N, and skinny
   // problems (few rows) the widest tile that still yields at least half an SM count of CTAs.
   auto tiles = [&](int bn) { return (long long)ceil_div(p.M, BM) * ceil_div(p.N, bn); };

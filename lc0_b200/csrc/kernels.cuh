@@ -25,26 +25,34 @@ struct GemmParams {
   // The rows of A are LayerNorm *inputs* u whose normalisation x = (u - mean) * rstd * gamma + beta was folded
   // into this product: W holds W * gamma, `colsum[n]` = sum_k (W * gamma)[n][k], `bias` holds beta . W^T + b and
   // `a_stats` the per-row (sum, sum of squares) of u.  Then x . W^T + b = rstd * (u . (W gamma)^T - mean * colsum) + bias.
-  const float* a_stats = nullptr;
+  const double* a_stats = nullptr;
   const float* colsum = nullptr;
   float a_inv_c = 0.f, a_eps = 0.f;
   // Residual input added after the activation: out = alpha * act(...) + s, where s is read from `res`
   // ([M][N], leading dimension ldres) and, when res_stats is set, normalised on the fly:
   // s = (res - mean) * rstd * res_gamma[n] + res_beta[n].
   const void* res = nullptr; long long ldres = 0;
-  const float* res_stats = nullptr;
+  const double* res_stats = nullptr;
   const float* res_gamma = nullptr;
   const float* res_beta = nullptr;
   float res_inv_c = 0.f, res_eps = 0.f;
-  // Per-row (sum, sum of squares) of the outputs, accumulated with atomic adds into out_stats[M][2]
+  // Per-row (sum, sum of squares) of the outputs, accumulated in double with atomic adds into out_stats[M][2]
   // (the caller zeroes it), so that the next product can fold the LayerNorm of this output.
-  float* out_stats = nullptr;
+  double* out_stats = nullptr;
   // Second output of the CTA-pair kernel: columns [n_split, N) go to C2 (leading dimension ldc2, column n - n_split)
   // instead of C.  n_split must be a multiple of 256 and the remainder at most 256 columns wide; the last tile is then
   // computed with a narrower MMA.  Lets a narrow product share the operand traffic of a wide one (same A, same folded
   // LayerNorm); no residual / statistics in this mode.
   void* C2 = nullptr; long long ldc2 = 0;
   int n_split = 0;
+  // Squeeze-excitation unit fused into a convolution (tensor-core kernel, convolution mode, at most 256 output
+  // channels): out = act(gate * conv + shift + res) with gate / shift from the board's pooled conv output
+  // (ApplySEUnit, backends/blas/se_unit.cc:31-91).  se_w1 [se_k][N], se_b1 [se_k], se_w2 [2N][se_k], se_b2 [2N],
+  // se_bias [N] = the convolution's own bias (it enters through the pooled mean and the shift); `bias` stays null and
+  // `act` is applied after the residual.  See gemm_tc_se_supported.
+  const float* se_w1 = nullptr; const float* se_b1 = nullptr; const float* se_w2 = nullptr;
+  const float* se_b2 = nullptr; const float* se_bias = nullptr;
+  int se_k = 0;
   // CTA-pair kernel: compute a sparsely filled last wave as whole 256x256 tiles instead of half-width ones
   // (verification switch; the split is on by default).
   bool whole_tiles = false;
@@ -55,6 +63,7 @@ template <typename T> cudaError_t launch_gemm_simt(const GemmParams& p, cudaStre
 // `status` is a device int the kernel sets non-zero when a bounded wait gives up.
 template <typename T> cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaStream_t s);
 bool gemm_tc_supported(const GemmParams& p);
+bool gemm_tc_se_supported(const GemmParams& p);
 // Whether launch_gemm_tc would run `p` (with C2 / n_split set) on the CTA-pair kernel, the only one that splits.
 bool gemm_tc_split_supported(const GemmParams& p, int sm_count);
 cudaError_t gemm_tc_init();  // resolves the driver entry point used to encode TMA descriptors

@@ -454,9 +454,9 @@ struct Net : NetBase {
     T *tokens = nullptr, *pre = nullptr, *pe = nullptr;
     T *x = nullptr, *x1 = nullptr, *y = nullptr, *qkv = nullptr, *att = nullptr, *ffn = nullptr;
     T *sg_c = nullptr, *sg_h1 = nullptr, *sg_h2 = nullptr, *sg_bias = nullptr;
-    // per-row (sum, sum of squares) of the folded LayerNorm inputs, laid out [stats2[0] | stats1 | stats2[1]] so that
+    // per-row (sum, sum of squares; double) of the folded LayerNorm inputs, laid out [stats2[0] | stats1 | stats2[1]] so that
     // one memset at the start of a layer clears stats1 and the stats2 buffer that layer writes (layers alternate)
-    float *stats1 = nullptr, *stats2[2] = {nullptr, nullptr};
+    double *stats1 = nullptr, *stats2[2] = {nullptr, nullptr};
     int stats_parity = 0;
     size_t stats_stride = 0;  // floats between consecutive buffers of that block
     T *pemb = nullptr, *pq = nullptr, *pk = nullptr, *praw = nullptr;
@@ -1002,7 +1002,7 @@ struct Net : NetBase {
         }
         s.qkv = A(R * 3 * E);
         if (fold_ln) {
-          float* blk = (float*)salloc.alloc(3 * R * 2 * sizeof(float));
+          double* blk = (double*)salloc.alloc(3 * R * 2 * sizeof(double));
           s.stats2[0] = blk;
           s.stats1 = blk + R * 2;
           s.stats2[1] = blk + 2 * R * 2;
@@ -1053,14 +1053,14 @@ struct Net : NetBase {
   // with per-row statistics and the LayerNorm's parameters.
   struct LNState {
     const T* u = nullptr;
-    const float* stats = nullptr;
+    const double* stats = nullptr;
     const float* gamma = nullptr;
     const float* beta = nullptr;
   };
   // Product whose A operand is `in` (folded when in.stats is set); optional residual `res` added as
   // alpha * act(...) + LN(res) and optional accumulation of output row statistics.
   void gemm_ln(cudaStream_t st, const LNState& in, long long lda, const Dense<T>& d, T* Cout, long long ldc, int M,
-               int act, const LNState* res = nullptr, float alpha_ = 1.f, float* out_stats = nullptr,
+               int act, const LNState* res = nullptr, float alpha_ = 1.f, double* out_stats = nullptr,
                T* C2 = nullptr, long long ldc2 = 0, int n_split = 0, bool zero_stats = true) {
     GemmParams p;
     p.C2 = C2; p.ldc2 = ldc2; p.n_split = n_split;
@@ -1078,7 +1078,7 @@ struct Net : NetBase {
       }
     }
     if (out_stats) {
-      if (zero_stats) CK(cudaMemsetAsync(out_stats, 0, (size_t)M * 2 * sizeof(float), st));
+      if (zero_stats) CK(cudaMemsetAsync(out_stats, 0, (size_t)M * 2 * sizeof(double), st));
       p.out_stats = out_stats;
     }
     p.whole_tiles = (opt.flags & B200_FLAG_NO_SPLIT_LAST_WAVE) != 0;
@@ -1130,6 +1130,26 @@ struct Net : NetBase {
     CK(launch_conv3x3<T>(x, c.cin, c.w, bias, y, c.cout, n, act, st));
     span_end(st, sp_);
   }
+  // Second convolution of a residual block with its squeeze-excitation unit, the skip connection and the activation
+  // in the tensor-core kernel's epilogue (network_blas.cc:584-597); false when the shape does not qualify.
+  bool conv3_se(cudaStream_t st, const T* x, const ResidualW<T>& r, const T* skip, T* y, int n) {
+    if constexpr (sizeof(T) == 2) {
+      if (!use_tc || (opt.flags & B200_FLAG_NO_FUSED_SE)) return false;
+      const ConvW<T>& c = r.c2;
+      GemmParams p;
+      p.A = x; p.W = c.w; p.C = y; p.ldc = c.cout; p.M = n * 64; p.N = c.cout; p.K = 9 * c.cin;
+      p.act = act_default; p.conv_cin = c.cin; p.lda = c.cin; p.ldw = c.cin;
+      p.res = skip; p.ldres = c.cout;
+      p.se_w1 = r.se_w1; p.se_b1 = r.se_b1; p.se_w2 = r.se_w2; p.se_b2 = r.se_b2; p.se_bias = c.b; p.se_k = r.se_k;
+      if (!gemm_tc_supported(p) || !gemm_tc_se_supported(p)) return false;
+      launches++;
+      const int sp_ = span_begin(st, K_GEMM_TC, 2.0 * p.M * (double)p.N * p.K);
+      CK(launch_gemm_tc<T>(p, t_status, sm_count, st));
+      span_end(st, sp_);
+      return true;
+    }
+    return false;
+  }
   void ln(cudaStream_t st, T* out, const T* x, const T* skip, const float* g, const float* b, int rows, int Cc,
           float a, float eps, const float* gm = nullptr, const float* ga = nullptr) {
     launches++;
@@ -1150,12 +1170,12 @@ struct Net : NetBase {
     const T* bias = nullptr;
     // The statistics this layer accumulates are cleared here, in one memset ahead of all its launches, so that no
     // memset sits between two products.  The layer input may refer to the other stats2 buffer.
-    float* stats2 = nullptr;
+    double* stats2 = nullptr;
     if (fold_ln) {
       const int par = s.stats_parity;
       s.stats_parity ^= 1;
       stats2 = s.stats2[par];
-      CK(cudaMemsetAsync(par == 0 ? s.stats2[0] : s.stats1, 0, (s.stats_stride + (size_t)R * 2) * sizeof(float), st));
+      CK(cudaMemsetAsync(par == 0 ? s.stats2[0] : s.stats1, 0, (s.stats_stride + (size_t)R * 2) * sizeof(double), st));
     }
     // One launch for Q, K, V and the smolgen compression when the CTA-pair kernel takes the product.
     bool merged = false;
@@ -1242,6 +1262,10 @@ struct Net : NetBase {
       T *cur = s.x, *tmp = s.x1, *tmp2 = s.y;
       for (const auto& r : res) {
         conv3(st, cur, r.c1, r.c1.b, tmp, n, act_default);
+        if (r.se && conv3_se(st, tmp, r, cur, tmp2, n)) {  // second convolution, SE, skip and activation in one launch
+          std::swap(cur, tmp2);
+          continue;
+        }
         conv3(st, tmp, r.c2, nullptr, tmp2, n, ACT_NONE);
         other(st, 3.0 * R * C * sizeof(T), [&] {
           return r.se ? launch_se<T>(tmp2, r.c2.b, cur, r.se_w1, r.se_b1, r.se_w2, r.se_b2, tmp, C, r.se_k, n,
@@ -1343,7 +1367,7 @@ struct Net : NetBase {
         });
       }
     } else if (policy_fmt == POLICY_CONVOLUTION) {
-      T* t1 = s.y;  // free: the tower ping-pongs between x and x1
+      T* t1 = flow == s.y ? s.x : s.y;  // any tower buffer that does not hold the tower's output
       conv3(st, flow, pol_conv1, pol_conv1.b, t1, n, act_default);
       conv3(st, t1, pol_conv2, pol_conv2.b, s.praw, n, ACT_NONE);
       other(st, (double)n * 1858 * (4 + sizeof(T)), [&] {

@@ -235,7 +235,7 @@ def test_folded_layer_norm_epilogues_against_oracle(lib, prec, M, shift):
     W1g, cs1, b1f = _fold(W1, b1, gamma, beta, dt)
 
     u = torch.zeros(M, E, dtype=dt, device="cuda")
-    st1 = torch.zeros(M, 2, device="cuda")
+    st1 = torch.zeros(M, 2, device="cuda", dtype=torch.float64)
     _lib.check(lib.b200_op_gemm_ex(_desc(A=A0, W=W0, bias=b0, C=u, M=M, N=E, K=E, precision=prec, alpha=alpha,
                                          res=R, out_stats=st1), None))
     h = torch.zeros(M, F, dtype=dt, device="cuda")
@@ -243,7 +243,7 @@ def test_folded_layer_norm_epilogues_against_oracle(lib, prec, M, shift):
                                          activation=oracle.ACT_RELU_2, a_stats=st1, colsum=cs1, a_inv_c=1.0 / E,
                                          a_eps=eps_ln), None))
     u2 = torch.zeros(M, E, dtype=dt, device="cuda")
-    st2 = torch.zeros(M, 2, device="cuda")
+    st2 = torch.zeros(M, 2, device="cuda", dtype=torch.float64)
     _lib.check(lib.b200_op_gemm_ex(_desc(A=h, W=W2, bias=b2, C=u2, M=M, N=E, K=F, precision=prec, alpha=alpha,
                                          res=u, res_stats=st1, res_gamma=gamma, res_beta=beta, res_inv_c=1.0 / E,
                                          res_eps=eps_ln, out_stats=st2), None))
@@ -253,7 +253,7 @@ def test_folded_layer_norm_epilogues_against_oracle(lib, prec, M, shift):
     sample = np.unique(np.concatenate([rows["shifted"][:96], rows["outlier3e3"][:64], rows["outlier1e4"][:64],
                                        rng.integers(0, M, 256), [0, M - 1]]))
     sel = torch.from_numpy(sample).cuda()
-    f = lambda t: t.float().cpu().numpy()
+    f = lambda t: (t if t.dtype == torch.float64 else t.float()).cpu().numpy()
     rt = 2.0 ** -10 if prec == 1 else 2.0 ** -7  # output rounding of the storage type
     # 1: product + plain residual + statistics
     u_ref = alpha * oracle.fc(f(A0[sel]), f(W0).reshape(-1), f(b0), oracle.ACT_NONE, E) + f(R[sel])
@@ -265,15 +265,28 @@ def test_folded_layer_norm_epilogues_against_oracle(lib, prec, M, shift):
     un = f(u[sel])
     x = oracle.layer_norm(un, 1.0, None, np.ones(E, np.float32), np.zeros(E, np.float32), eps_ln)
     h_ref = oracle.fc(x, f(W1g).reshape(-1), f(b1f), oracle.ACT_RELU_2, F)
-    err = np.abs(f(h[sel]) - h_ref) - (rt * np.abs(h_ref) + 3e-3)
-    assert err.max() <= 0, "folded LayerNorm product: worst excess %.3g in sampled row %d" % (
-        err.max(), sample[err.max(-1).argmax()])
+    # Rows shifted by `shift` standard deviations: the folded form computes LN(u) W^T as rstd * (u W'^T - mean * colsum),
+    # two terms of size |mean| * |colsum| that cancel; the tensor core accumulates the first one at that size, so the
+    # pre-activation loses about 1e-4 * shift (fp16; more in bf16, whose statistics are also sums of the unrounded
+    # values while the product reads the rounded ones), and relu^2 turns it into 2 * sqrt(h) times that.
+    is_shifted = np.isin(sample, rows["shifted"])[:, None]
+    per_shift = 2e-4 if prec == 1 else 1e-3
+
+    def worst(got, ref, floor):
+        extra = np.where(is_shifted, per_shift * shift * (1 + 2 * np.sqrt(np.abs(ref))), 0.0)
+        err = np.abs(got - ref) - (rt * np.abs(ref) + floor + extra)
+        r, c = np.unravel_index(err.argmax(), err.shape)
+        cls = [k for k, v in rows.items() if sample[r] in v] or ["ordinary"]
+        return err.max(), "excess %.3g at row %d (%s) column %d: got %.6g, reference %.6g" % (
+            err.max(), sample[r], "+".join(cls), c, got[r, c], ref[r, c])
+
+    e, msg = worst(f(h[sel]), h_ref, 3e-3)
+    assert e <= 0, "folded LayerNorm product: " + msg
     # 3: residual normalised on the fly
     ln_u = oracle.layer_norm(un, 1.0, None, f(gamma), f(beta), eps_ln)
     u2_ref = alpha * oracle.fc(f(h[sel]), f(W2).reshape(-1), f(b2), oracle.ACT_NONE, E) + ln_u
-    err = np.abs(f(u2[sel]) - u2_ref) - (rt * np.abs(u2_ref) + 3e-3)
-    assert err.max() <= 0, "normalised residual: worst excess %.3g in sampled row %d" % (
-        err.max(), sample[err.max(-1).argmax()])
+    e, msg = worst(f(u2[sel]), u2_ref, 3e-3)
+    assert e <= 0, "normalised residual: " + msg
     s2_ref = np.stack([u2_ref.sum(-1, dtype=np.float64), (u2_ref.astype(np.float64) ** 2).sum(-1)], 1)
     mag2 = np.stack([np.abs(u2_ref).sum(-1, dtype=np.float64), s2_ref[:, 1]], 1)
     # u2_ref is built from the rounded h and u, the kernel's sums from its own unrounded values: the storage
@@ -293,7 +306,7 @@ def test_second_output_of_the_pair_kernel_with_folded_input(lib, whole_tiles):
     W = rnd(N + hc, E) * E ** -0.5
     b = torch.cat([rnd(N) * 0.1, torch.zeros(hc, device="cuda")])
     Wg, cs, bf = _fold(W, b, gamma, beta, torch.float16)
-    uf = u.float()
+    uf = u.double()
     stats = torch.stack([uf.sum(1), (uf * uf).sum(1)], 1).contiguous()
     C = torch.zeros(M, N, dtype=torch.float16, device="cuda")
     C2 = torch.zeros(M, hc, dtype=torch.float16, device="cuda")
@@ -312,7 +325,7 @@ def test_second_output_of_the_pair_kernel_with_folded_input(lib, whole_tiles):
 
 def test_gemm_ex_rejects_inconsistent_descriptions(lib):
     a = torch.zeros(256, 64, dtype=torch.float16, device="cuda")
-    st = torch.zeros(256, 2, device="cuda")
+    st = torch.zeros(256, 2, device="cuda", dtype=torch.float64)
     assert lib.b200_op_gemm_ex(_desc(A=a, W=a, C=a, M=256, N=64, K=64, precision=0), None) == _lib.ERR_UNSUPPORTED
     assert lib.b200_op_gemm_ex(_desc(A=a, W=a, C=a, M=256, N=64, K=64, precision=1, a_stats=st), None) == \
         _lib.ERR_UNSUPPORTED  # statistics without column sums

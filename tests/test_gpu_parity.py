@@ -196,6 +196,29 @@ def test_outlier_channels_and_shifted_rows_fp16(fold):
     assert np.all(np.abs(out["m"] - g["m"]) <= HALF_ATOL * np.maximum(1.0, np.abs(g["m"])))
 
 
+@pytest.mark.parametrize("name,count", [("cfg2", 16), ("cfg2", 5), ("cfg1_mini", 31), ("cfg1", 16)])
+def test_squeeze_excitation_in_the_convolution_epilogue(name, count):
+    """The second convolution of a residual block with SE, skip and activation in its epilogue (one tile = two whole
+    boards x all channels) against the reference, and the separate SE kernel beside it; an odd board count leaves the
+    last tile half empty."""
+    net, pos, n, g = load_case(name)
+    outs = []
+    for fused in (1, 0):
+        nw = network.Network(net, "precision=fp16,max_batch=%d,fused_se=%d" % (count, fused))
+        out = nw.evaluate(pos["masks"][:count], pos["values"][:count])
+        assert nw.device_status() == 0
+        if fused:
+            launches = nw.launch_count()
+        else:
+            assert nw.launch_count() > launches  # the fused schedule really has fewer launches
+        nw.close()
+        worst, agree, decided = _softmax_err_and_argmax(out["policy"], g["policy"], pos, count)
+        assert worst <= HALF_ATOL and agree == decided, (fused, worst)
+        assert np.abs(out["q"] - g["q"][:count]).max() <= HALF_ATOL
+        outs.append(out)
+    assert np.abs(outs[0]["policy"] - outs[1]["policy"]).max() <= 2e-2 * max(1.0, np.abs(outs[1]["policy"]).max())
+
+
 def test_kernel_timeout_is_reported_by_the_evaluation_call():
     """A status word set the way a kernel whose bounded wait gave up sets it makes the evaluation that finds it fail
     with B200_ERR_TIMEOUT (nothing on the GPU is disturbed: the word is written from the host), the word is cleared,
