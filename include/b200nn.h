@@ -81,7 +81,11 @@ enum {
   B200_FLAG_NO_LN_FOLD = 4,          /* run the encoder LayerNorms as kernels instead of folding them into the products */
   B200_FLAG_NO_MERGED_COMPRESS = 8,  /* smolgen compression as a product of its own instead of riding on the QKV launch */
   B200_FLAG_NO_SPLIT_LAST_WAVE = 16, /* whole 256x256 tiles in the last wave of the CTA-pair kernel */
-  B200_FLAG_NO_FUSED_SE = 32         /* squeeze-excitation as a kernel of its own instead of the convolution's epilogue */
+  B200_FLAG_NO_FUSED_SE = 32,        /* squeeze-excitation as a kernel of its own instead of the convolution's epilogue */
+  /* Residual networks in fp16 / bf16: 3x3 convolutions as Winograd F(4x4, 3x3) (transform kernels around 36 stacked
+   * tensor-core products, the reference GPU backend's decomposition) instead of the direct tensor-core convolution.
+   * Off by default: a quarter of the multiplications, but about ten times the rounding error in 16-bit storage. */
+  B200_FLAG_WINOGRAD = 64
 };
 
 typedef struct b200_net_info {

@@ -279,6 +279,7 @@ struct TcParams {
   // Squeeze-excitation unit fused into the epilogue of a convolution whose tile holds two whole boards and every
   // output channel (se_k > 0; see GemmParams).
   const float* se_w1; const float* se_b1; const float* se_w2; const float* se_b2; const float* se_bias; int se_k;
+  int batch_rows;  // > 0: stacked products, rows [b * batch_rows, (b + 1) * batch_rows) use W rows [b * N, (b + 1) * N)
 };
 
 // Per-thread (= per output row) state of the folded-LayerNorm epilogue.
@@ -761,7 +762,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tma_load_2d(sa + BM * BK * 2, &tmap_w, cb * BK, tap * p.N + n0, fb);
           } else {
             tma_load_2d(sa, &tmap_a, kb * BK, m0, fb);
-            tma_load_2d(sa + BM * BK * 2, &tmap_w, kb * BK, n0, fb);
+            tma_load_2d(sa + BM * BK * 2, &tmap_w, kb * BK, n0 + (p.batch_rows > 0 ? (m0 / p.batch_rows) * p.N : 0), fb);
           }
         }
       }
@@ -1035,7 +1036,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       for (int t = pair; t < tiles && ok; t += pairs) {
         const int m0 = (tile_of(t) / n_tiles) * (2 * BM) + (int)rank * BM;
         // a narrower tile is computed with a narrower MMA, of which each CTA supplies half the W rows
-        const int n0 = col_of(t) + (int)rank * (mma_n_of(t) / 2);
+        const int n0 = col_of(t) + (int)rank * (mma_n_of(t) / 2) + (p.batch_rows > 0 ? (m0 / p.batch_rows) * p.N : 0);
         const bool half = t >= split_from;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % S;
@@ -1220,6 +1221,7 @@ void fill_folded(TcParams& p, const GemmParams& g) {
   p.n_split = 0;
   p.se_w1 = g.se_w1; p.se_b1 = g.se_b1; p.se_w2 = g.se_w2; p.se_b2 = g.se_b2; p.se_bias = g.se_bias;
   p.se_k = g.se_k;
+  p.batch_rows = g.batch_rows;
 }
 
 // 4D map over a token-major activation [positions][8][8][channels]; box = 64 channels x 8 x 8 x 2 boards
@@ -1266,7 +1268,7 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
   } else {
     e = get_map(g.A, g.lda, g.M, g.K, BM, prec, &ma);
     if (e != cudaSuccess) return e;
-    e = get_map(g.W, g.ldw, g.N, g.K, BN, prec, &mw);
+    e = get_map(g.W, g.ldw, g.batch_rows > 0 ? g.N * (g.M / g.batch_rows) : g.N, g.K, BN, prec, &mw);
   }
   if (e != cudaSuccess) return e;
   const bool tma_store = !g.out_f32 && (g.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(g.C) & 15) == 0;
@@ -1316,7 +1318,8 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   const int prec = TypeTag<T>::prec;
   cudaError_t e = get_map(g.A, g.lda, g.M, g.K, BM, prec, &ma);
   if (e != cudaSuccess) return e;
-  e = get_map(g.W, g.ldw, g.N, g.K, Cfg::BN / 2, prec, &mw);
+  const int w_rows = g.batch_rows > 0 ? g.N * (g.M / g.batch_rows) : g.N;
+  e = get_map(g.W, g.ldw, w_rows, g.K, Cfg::BN / 2, prec, &mw);
   if (e != cudaSuccess) return e;
   e = get_map(g.C, g.ldc, g.M, g.n_split > 0 ? g.n_split : g.N, BM, prec, &mc);
   if (e != cudaSuccess) return e;
@@ -1354,7 +1357,7 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   }
   CUtensorMap mwh = mw;  // W in boxes of 64 rows, for the half-width tiles
   if (p.split_from < p.tiles_v) {
-    e = get_map(g.W, g.ldw, g.N, g.K, Cfg::BN / 4, prec, &mwh);
+    e = get_map(g.W, g.ldw, w_rows, g.K, Cfg::BN / 4, prec, &mwh);
     if (e != cudaSuccess) return e;
   }
   gemm_tc_pair_kernel<T, kGroups><<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, mc2, mwh, p);
@@ -1400,6 +1403,9 @@ bool gemm_tc_supported(const GemmParams& p) {
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   if (p.conv_cin > 0)
     return p.batch == 1 && p.M >= 64 && (p.M % 64) == 0 && p.N >= 8 && (p.conv_cin % 8) == 0 && al16(p.A) && al16(p.W);
+  if (p.batch_rows > 0 && ((p.batch_rows % 256) != 0 || (p.M % p.batch_rows) != 0 || p.res || p.a_stats || p.out_stats ||
+                           p.n_split > 0 || p.bias))
+    return false;
   return p.batch == 1 && p.M >= 1 && p.N >= 8 && p.K >= 8 && (p.K % 8) == 0 && (p.lda % 8) == 0 &&
          (p.ldw % 8) == 0 && al16(p.A) && al16(p.W);
 }

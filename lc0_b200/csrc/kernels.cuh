@@ -53,6 +53,10 @@ struct GemmParams {
   const float* se_w1 = nullptr; const float* se_b1 = nullptr; const float* se_w2 = nullptr;
   const float* se_b2 = nullptr; const float* se_bias = nullptr;
   int se_k = 0;
+  // Stacked products in one launch (tensor-core kernel): A and C are [batches * batch_rows][..], W is [batches * N][K];
+  // rows of batch b meet the W rows of batch b.  batch_rows must be a multiple of 256 (a tile never spans two
+  // batches); M = batches * batch_rows.  No bias, residual or statistics.  The 36 products of a Winograd convolution.
+  int batch_rows = 0;
   // CTA-pair kernel: compute a sparsely filled last wave as whole 256x256 tiles instead of half-width ones
   // (verification switch; the split is on by default).
   bool whole_tiles = false;
@@ -150,6 +154,18 @@ cudaError_t launch_se(const T* x, const float* conv_bias, const T* skip, const f
 template <typename T>
 cudaError_t launch_bias_skip_act(const T* x, const float* bias, const T* skip, T* y, int C, int rows, int act,
                                  cudaStream_t s);
+
+// Winograd F(4x4, 3x3) convolution pieces (winograd.cu): input transform x [boards*64][C] -> v [36][rows_padded][C]
+// (row = board * 4 + patch), output transform m [36][rows_padded][C] -> y [boards*64][C] with bias, optional
+// squeeze-excitation (se_k > 0), optional skip and the activation, and the host-side filter transform
+// w [Cout][Cin][3][3] -> u [36][Cout][Cin].
+template <typename T>
+cudaError_t launch_wino_input(const T* x, T* v, int C, int boards, long long rows_padded, cudaStream_t s);
+template <typename T>
+cudaError_t launch_wino_output(const T* m, const float* bias, const T* skip, const float* se_w1, const float* se_b1,
+                               const float* se_w2, const float* se_b2, int se_k, T* y, int C, int boards,
+                               long long rows_padded, int act, cudaStream_t s);
+void wino_transform_filters(const float* w, int cout, int cin, float* u);
 
 // Position encoding on the device (encoder.cu): game histories -> 112 packed planes per position, the work of the
 // reference's host-side EncodePositionForNN (src/neural/encoder.cc:134-328).  boards/offsets/from_start as in

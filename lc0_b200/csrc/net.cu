@@ -180,6 +180,7 @@ template <typename T> struct EncoderW {
 
 template <typename T> struct ConvW {
   T* w = nullptr;  // [9][Cout][Cin]
+  T* u = nullptr;  // [36][Cout][Cin]: Winograd-transformed filters (only with the winograd option)
   float* b = nullptr;
   int cout = 0, cin = 0;
 };
@@ -405,9 +406,11 @@ struct Net : NetBase {
   bool fold_emb_ln = false;  // the embedding block's last LayerNorm is folded into the first encoder layer
   bool merge_compress = true;  // false (B200_FLAG_NO_MERGED_COMPRESS): smolgen compression as a launch of its own
   bool fold_heads = false;  // the heads' first products fold the last LayerNorm too (else it is materialised)
+  bool winograd = false;    // 3x3 convolutions as Winograd F(4x4, 3x3) transforms around 36 stacked products
   int* d_status = nullptr;  // one status word per slot
   // Status word of the evaluation being enqueued on this thread (the slot's), handed to every kernel with bounded waits.
   static inline thread_local int* t_status = nullptr;
+  static inline thread_local void* t_slot_ptr = nullptr;  // the slot of that evaluation
 
   // format
   int network = 0, policy_fmt = 0, value_fmt = 0, emb_fmt = 0;
@@ -454,6 +457,7 @@ struct Net : NetBase {
     T *tokens = nullptr, *pre = nullptr, *pe = nullptr;
     T *x = nullptr, *x1 = nullptr, *y = nullptr, *qkv = nullptr, *att = nullptr, *ffn = nullptr;
     T *sg_c = nullptr, *sg_h1 = nullptr, *sg_h2 = nullptr, *sg_bias = nullptr;
+    T *wino_v = nullptr, *wino_m = nullptr;  // [36][rows_padded][channels]: transformed input / product output
     // per-row (sum, sum of squares; double) of the folded LayerNorm inputs, laid out [stats2[0] | stats1 | stats2[1]] so that
     // one memset at the start of a layer clears stats1 and the stats2 buffer that layer writes (layers alternate)
     double *stats1 = nullptr, *stats2[2] = {nullptr, nullptr};
@@ -577,6 +581,11 @@ struct Net : NetBase {
     cw.cout = cout;
     cw.cin = cin_;
     cw.w = up_T(p);
+    if (winograd) {
+      std::vector<float> u((size_t)36 * cout * cin_);
+      wino_transform_filters(w.data(), cout, cin_, u.data());
+      cw.u = up_T(u);
+    }
     cw.b = up_f32(prefix + ".biases", cout);
     return cw;
   }
@@ -725,6 +734,7 @@ struct Net : NetBase {
       CK(gemm_tc_init());
     }
     merge_compress = !(opt.flags & B200_FLAG_NO_MERGED_COMPRESS);
+    winograd = use_tc && !attn_body && (opt.flags & B200_FLAG_WINOGRAD);
     fold_ln = use_tc && attn_body && !(opt.flags & B200_FLAG_NO_LN_FOLD);
     // Folding needs every product that consumes or produces a folded LayerNorm to be eligible for the tensor-core
     // kernel's TMA epilogue: output widths that are multiples of 8.
@@ -988,6 +998,12 @@ struct Net : NetBase {
         s.x = A(R * C);
         s.x1 = A(R * C);
         s.y = A(R * C);
+        if (winograd) {
+          const size_t rows = (nb * 4 + 255) / 256 * 256;
+          const size_t ch = (size_t)std::max(std::max(C, 112), pol_planes);
+          s.wino_v = A(36 * rows * ch);
+          s.wino_m = A(36 * rows * ch);
+        }
       }
       if (attn_body) {
         if (res.empty()) s.tokens = A(R * cin);
@@ -1112,7 +1128,35 @@ struct Net : NetBase {
     span_end(st, sp_);
   }
   // 3x3 convolution: tensor-core kernel (TMA board tiles with zero-filled halo) for 16-bit storage, FMA otherwise.
+  // Winograd form of the same convolution (winograd.cu): transform, 36 stacked products, transform back with bias,
+  // optional squeeze-excitation (r != nullptr), optional skip and the activation.
+  bool conv3_wino(cudaStream_t st, const T* x, const ConvW<T>& c, const float* bias, T* y, int n, int act,
+                  const T* skip = nullptr, const ResidualW<T>* r = nullptr) {
+    if constexpr (sizeof(T) == 2) {
+      if (!winograd || !c.u || (c.cin % 8) || (c.cout % 8)) return false;
+      Slot& s = *static_cast<Slot*>(t_slot_ptr);
+      const long long rows = ((long long)n * 4 + 255) / 256 * 256;
+      GemmParams p;
+      p.A = s.wino_v; p.lda = c.cin; p.W = c.u; p.ldw = c.cin; p.C = s.wino_m; p.ldc = c.cout;
+      p.M = (int)(36 * rows); p.N = c.cout; p.K = c.cin; p.batch_rows = (int)rows;
+      if (!gemm_tc_supported(p)) return false;
+      other(st, (double)n * 64 * c.cin * sizeof(T) * (1.0 + 36.0 / 16.0),
+            [&] { return launch_wino_input<T>(x, s.wino_v, c.cin, n, rows, st); });
+      launches++;
+      const int sp_ = span_begin(st, K_GEMM_TC, 2.0 * 36 * n * 4 * (double)c.cin * c.cout);  // Winograd-domain FLOPs
+      CK(launch_gemm_tc<T>(p, t_status, sm_count, st));
+      span_end(st, sp_);
+      other(st, (double)n * 64 * c.cout * sizeof(T) * (1.0 + 36.0 / 16.0 + (skip ? 1.0 : 0.0)), [&] {
+        return launch_wino_output<T>(s.wino_m, bias, skip, r ? r->se_w1 : nullptr, r ? r->se_b1 : nullptr,
+                                     r ? r->se_w2 : nullptr, r ? r->se_b2 : nullptr, r ? r->se_k : 0, y, c.cout, n, rows,
+                                     act, st);
+      });
+      return true;
+    }
+    return false;
+  }
   void conv3(cudaStream_t st, const T* x, const ConvW<T>& c, const float* bias, T* y, int n, int act) {
+    if (conv3_wino(st, x, c, bias, y, n, act)) return;
     if constexpr (sizeof(T) == 2) {
       GemmParams p;
       p.A = x; p.W = c.w; p.bias = bias; p.C = y; p.ldc = c.cout; p.M = n * 64; p.N = c.cout; p.K = 9 * c.cin;
@@ -1253,6 +1297,7 @@ struct Net : NetBase {
     LNState body_in;    // attention bodies: how the heads must read `flow` (folded LayerNorm or materialised)
     s.stats_parity = 0;
     t_status = d_status + (&s - slots.data());
+    t_slot_ptr = &s;
     CK(cudaMemsetAsync(d_qdm, 0, (size_t)n * 3 * sizeof(float), st));
     if (!res.empty() || !attn_body) {  // network_blas.cc:564-601
       other(st, (double)R * 112 * sizeof(T), [&] {
@@ -1262,6 +1307,10 @@ struct Net : NetBase {
       T *cur = s.x, *tmp = s.x1, *tmp2 = s.y;
       for (const auto& r : res) {
         conv3(st, cur, r.c1, r.c1.b, tmp, n, act_default);
+        if (winograd && conv3_wino(st, tmp, r.c2, r.c2.b, tmp2, n, act_default, cur, r.se ? &r : nullptr)) {
+          std::swap(cur, tmp2);  // output transform with SE / skip / activation
+          continue;
+        }
         if (r.se && conv3_se(st, tmp, r, cur, tmp2, n)) {  // second convolution, SE, skip and activation in one launch
           std::swap(cur, tmp2);
           continue;

@@ -15,7 +15,7 @@ import numpy as np
 from . import _lib, netproto, weights as _weights
 
 _KNOWN_OPTIONS = {"gpu", "max_batch", "precision", "slots", "mlh", "policy_head", "value_head",
-                  "tensor_cores", "graph_capture", "fold_ln", "merge_compress", "split_last_wave", "fused_se"}
+                  "tensor_cores", "graph_capture", "fold_ln", "merge_compress", "split_last_wave", "fused_se", "winograd"}
 
 
 def parse_options(opts):
@@ -49,6 +49,8 @@ def option_flags(opts):
                      ("split_last_wave", _lib.FLAG_NO_SPLIT_LAST_WAVE), ("fused_se", _lib.FLAG_NO_FUSED_SE)):
         if not _as_bool(opts.get(key, True)):
             flags |= bit
+    if _as_bool(opts.get("winograd", False)):
+        flags |= _lib.FLAG_WINOGRAD
     return flags
 
 
