@@ -319,6 +319,12 @@ int b200_op_attention(const void* q, const void* k, const void* v, long long ld,
  *   drops out, which is what a launch costs inside a replayed graph (profiling surface only). */
 int b200_op_gemm_timed(const void* A, const void* W, const float* bias, void* C, int M, int N, int K,
                        int activation, int precision, int launches, float* ms_per_launch, void* stream);
+/* b200_op_scratch_residency_probe (profiling surface): every SM's CTA writes a private scratch slice of slice_kb, streams
+ *   stream_kb of a 2 GiB buffer and reads the slice back, `iters` times; *ms_out = best of three timed launches.  mode
+ *   bit 0: L2 evict_last policy on the scratch accesses, bit 1: evict_first on the stream loads, bit 2: discard the
+ *   slice after reading, bit 3: stream only.  Under ncu the DRAM byte counters of this launch show whether a scratch
+ *   tensor of that footprint stays in L2 (the question behind keeping the smolgen bias a materialised tensor). */
+int b200_op_scratch_residency_probe(int slice_kb, int stream_kb, int iters, int mode, float* ms_out);
 /* b200_op_policy_attention: tail of the attention policy head for n positions: logits = Q K^T / sqrt(dm)
  *   per position (64x64), promotion offsets from the rank-8 keys and `w4` ([4][dm], fp32), and the gather of
  *   the 1858 move logits (network_blas.cc:850-914).  q, k: [n*64][dm] in `precision`; scratch_logits: n*4096

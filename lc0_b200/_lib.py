@@ -121,6 +121,7 @@ SIGNATURES = {
     "b200_op_encode_positions": (_I, [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P]),
     "b200_op_planes_from_training_data": (_I, [_P, _I, ctypes.c_longlong, _I, _P, _P, _P, _P]),
     "b200_op_gemm": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "b200_op_scratch_residency_probe": (_I, [_I, _I, _I, _I, ctypes.POINTER(ctypes.c_float)]),
     "b200_op_gemm_ex": (_I, [ctypes.POINTER(GemmDesc), _P]),
     "b200_op_attention": (_I, [_P, _P, _P, ctypes.c_longlong, _P, _P, ctypes.c_longlong, _I, _I, _I, _I, _I, _P]),
     "b200_op_gemm_timed": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.POINTER(ctypes.c_float), _P]),

@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libb200nn.so")
-SOURCES = ["kernels.cu", "gemm_tc.cu", "attention_tc.cu", "winograd.cu", "net.cu", "no_alloc.cu", "encoder.cu", "mux.cu", "multi.cu"]
+SOURCES = ["kernels.cu", "gemm_tc.cu", "attention_tc.cu", "winograd.cu", "net.cu", "no_alloc.cu", "probe.cu", "encoder.cu", "mux.cu", "multi.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

@@ -1133,7 +1133,7 @@ struct Net : NetBase {
   bool conv3_wino(cudaStream_t st, const T* x, const ConvW<T>& c, const float* bias, T* y, int n, int act,
                   const T* skip = nullptr, const ResidualW<T>* r = nullptr) {
     if constexpr (sizeof(T) == 2) {
-      if (!winograd || !c.u || (c.cin % 8) || (c.cout % 8)) return false;
+      if (!winograd || !c.u || (c.cin % 8) || (c.cout % 8) || c.cout > 256) return false;
       Slot& s = *static_cast<Slot*>(t_slot_ptr);
       const long long rows = ((long long)n * 4 + 255) / 256 * 256;
       GemmParams p;

@@ -4,6 +4,8 @@ stand-alone operator entry points, on the matrix shapes of the BT4-class network
     python -m lc0_b200.opbench gemm [--batch 1024] [--precision fp16] [--reps 5] [--only NAME]
     python -m lc0_b200.opbench encode [--batch 65536] [--reps 5]     (device-side position encoder)
     python -m lc0_b200.opbench mux [--threads 64] [--request 16] [--config cfg4]   (batch aggregation across threads)
+    python -m lc0_b200.opbench multi [--gpus 8] [--batch 1024] [--reps 5]          (one batch over several GPUs)
+    python -m lc0_b200.opbench l2scratch [--slice-kb 1024] [--stream-kb 2048] [--iters 40] [--mode 3]
 
 Prints one line per shape with the CUDA-event time and achieved TFLOP/s.  Small enough to run under
 `ncu -k regex:gemm_tc --set full` (use --batch 64..256 and --reps 1 for a capture).
@@ -101,9 +103,57 @@ def mux_bench(args):
     return 0
 
 
+def multi_bench(args):
+    """b200_multi_eval_host: --batch positions per GPU in one call, host buffers, replicated weights."""
+    import time
+    from . import mknet, network
+    net = mknet.make_net(args.config)
+    gpus = list(range(args.gpus))
+    mg = network.MultiGpuNetwork(net, dict(max_batch=args.batch, precision=args.precision, slots=1), gpus=gpus)
+    n = args.batch * len(gpus)
+    rng = np.random.default_rng(0)
+    masks = rng.integers(0, 2 ** 62, size=(n, 112), dtype=np.int64).astype(np.uint64)
+    values = np.ones((n, 112), np.float32)
+    for _ in range(3):
+        mg.evaluate(masks, values)
+    t0 = time.time()
+    for _ in range(args.reps):
+        mg.evaluate(masks, values)
+    dt = (time.time() - t0) / args.reps
+    print("multi: %d GPUs x %d positions per call: %.1f ms per call, %.0f evals/s (host buffers, one process)"
+          % (len(gpus), args.batch, dt * 1e3, n / dt), flush=True)
+    mg.close()
+    return 0
+
+
+def l2scratch_bench(lib, args):
+    """b200_op_scratch_residency_probe: does a per-CTA scratch slice survive in L2 next to streaming traffic?"""
+    from . import _lib
+    ms = ctypes.c_float(0)
+    _lib.check(lib.b200_op_scratch_residency_probe(args.slice_kb, args.stream_kb, args.iters, args.mode, ctypes.byref(ms)))
+    sms = 148
+    try:
+        import torch
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+    except Exception:
+        pass
+    stream = sms * args.stream_kb * 1024.0 * args.iters
+    scratch = 0.0 if args.mode & 8 else sms * args.slice_kb * 1024.0 * args.iters
+    print("l2scratch slice_kb=%d stream_kb=%d iters=%d mode=%d: %.3f ms, footprint %.0f MB, moved %.0f GB/s through the "
+          "SMs (stream %.1f GB + scratch written and read %.1f GB each)"
+          % (args.slice_kb, args.stream_kb, args.iters, args.mode, ms.value, sms * args.slice_kb / 1024.0,
+             (stream + 2 * scratch) / ms.value / 1e6, stream / 1e9, scratch / 1e9), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "encode", "mux"])
+    ap.add_argument("what", choices=["gemm", "encode", "mux", "multi", "l2scratch"])
+    ap.add_argument("--gpus", type=int, default=2)
+    ap.add_argument("--slice-kb", type=int, default=1024)
+    ap.add_argument("--stream-kb", type=int, default=2048)
+    ap.add_argument("--iters", type=int, default=40)
+    ap.add_argument("--mode", type=int, default=3)
     ap.add_argument("--threads", type=int, default=64)
     ap.add_argument("--request", type=int, default=16, help="positions per request (mux)")
     ap.add_argument("--config", default="cfg4")
@@ -125,6 +175,10 @@ def main():
         return encode_bench(lib, args)
     if args.what == "mux":
         return mux_bench(args)
+    if args.what == "multi":
+        return multi_bench(args)
+    if args.what == "l2scratch":
+        return l2scratch_bench(lib, args)
     for name, M, N, K in gemm_shapes(args.batch):
         if args.only and args.only != name:
             continue

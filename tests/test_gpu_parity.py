@@ -219,6 +219,24 @@ def test_squeeze_excitation_in_the_convolution_epilogue(name, count):
     assert np.abs(outs[0]["policy"] - outs[1]["policy"]).max() <= 2e-2 * max(1.0, np.abs(outs[1]["policy"]).max())
 
 
+@pytest.mark.parametrize("name,count", [("cfg2", 16), ("cfg2_mini", 7), ("cfg1", 16), ("cfg1_mini", 32)])
+def test_winograd_path_within_tolerance(name, count):
+    """The optional Winograd F(4x4, 3x3) form of the residual tower (input transform, 36 stacked tensor-core products,
+    output transform with SE / skip / activation) against the reference in fp16: about twice the error of the direct
+    convolution, still inside the 16-bit contract on these networks."""
+    net, pos, n, g = load_case(name)
+    nw = network.Network(net, "precision=fp16,max_batch=%d,winograd=1" % count)
+    for rep in range(3):  # plain launches, then the captured graph
+        out = nw.evaluate(pos["masks"][:count], pos["values"][:count])
+    assert nw.device_status() == 0
+    nw.close()
+    worst, agree, decided = _softmax_err_and_argmax(out["policy"], g["policy"], pos, count)
+    assert worst <= HALF_ATOL and agree == decided, (worst, agree, decided)
+    assert np.abs(out["q"] - g["q"][:count]).max() <= HALF_ATOL
+    assert np.abs(out["d"] - g["d"][:count]).max() <= HALF_ATOL
+    assert np.all(np.abs(out["m"] - g["m"][:count]) <= HALF_ATOL * np.maximum(1.0, np.abs(g["m"][:count])))
+
+
 def test_kernel_timeout_is_reported_by_the_evaluation_call():
     """A status word set the way a kernel whose bounded wait gave up sets it makes the evaluation that finds it fail
     with B200_ERR_TIMEOUT (nothing on the GPU is disturbed: the word is written from the host), the word is cleared,
