@@ -433,6 +433,8 @@ struct Net : NetBase {
 
   // heads
   Dense<T> pol_emb, pol_q, pol_k, pol_fc;  // attention policy (emb, wq, wk) / classical FC
+  std::vector<EncoderW<T>> pol_enc;        // encoder layers of the attention policy head
+  int pol_heads = 0;
   float* pol_w4 = nullptr;
   int pol_dm = 0;
   ConvW<T> pol_conv1, pol_conv2;
@@ -464,6 +466,7 @@ struct Net : NetBase {
     int stats_parity = 0;
     size_t stats_stride = 0;  // floats between consecutive buffers of that block
     T *pemb = nullptr, *pq = nullptr, *pk = nullptr, *praw = nullptr;
+    T *p_qkv = nullptr, *p_att = nullptr, *p_ffn = nullptr, *p_x1 = nullptr, *p_y = nullptr;  // policy-head encoders
     float* logits = nullptr;
     T *vtok = nullptr, *vhid = nullptr, *mtok = nullptr, *mhid = nullptr;
   };
@@ -612,8 +615,10 @@ struct Net : NetBase {
 
   // in_gamma / in_beta: parameters of the LayerNorm whose output feeds this layer when that LayerNorm is folded
   // into the consuming products (nullptr: the layer input is a materialised activation).
+  // body = false: a policy-head encoder layer (no folding, no smolgen, not counted among the encoder products)
   EncoderW<T> load_encoder(const std::string& p, int emb, int heads, const std::vector<float>* in_gamma,
-                           const std::vector<float>* in_beta) {
+                           const std::vector<float>* in_beta, bool body = true) {
+    const bool fold_ffn1 = fold_ln && body;
     EncoderW<T> e;
     const int dm = (int)size_of(p + ".mha.q_b");
     if (dm <= 0 || dm % heads) throw Fail{B200_ERR_INVALID, "weights: bad attention width in " + p};
@@ -648,7 +653,7 @@ struct Net : NetBase {
     if (merge) e.qkvc_out = qkv_rows;
     e.proj = dense(p + ".mha.dense_w", p + ".mha.dense_b", emb, dm);
     const int dff = (int)size_of(p + ".ffn.dense1_b");
-    if (fold_ln)
+    if (fold_ffn1)
       e.ffn1 = dense_folded(need(p + ".ffn.dense1_w", (size_t)dff * emb), &need(p + ".ffn.dense1_b", dff), dff, emb,
                             need(p + ".ln1_gammas", emb), need(p + ".ln1_betas", emb));
     else
@@ -658,11 +663,13 @@ struct Net : NetBase {
     e.ln1b = up_f32(p + ".ln1_betas", emb);
     e.ln2g = up_f32(p + ".ln2_gammas", emb);
     e.ln2b = up_f32(p + ".ln2_betas", emb);
-    add_flops(64, e.qkv, true);
-    add_flops(64, e.proj, true);
-    add_flops(64, e.ffn1, true);
-    add_flops(64, e.ffn2, true);
+    add_flops(64, e.qkv, body);
+    add_flops(64, e.proj, body);
+    add_flops(64, e.ffn1, body);
+    add_flops(64, e.ffn2, body);
     info.flops_per_position += 2.0 * 2.0 * heads * 64 * 64 * (dm / heads);
+    if (!body && size_of(p + ".mha.smolgen.compress"))
+      throw Fail{B200_ERR_UNSUPPORTED, "smolgen in policy-head encoder layers is not supported"};
     if (size_of(p + ".mha.smolgen.compress")) {
       e.smolgen = true;
       const int hc = (int)size_of(p + ".mha.smolgen.compress") / emb;
@@ -718,9 +725,6 @@ struct Net : NetBase {
     attn_body = network == NET_ATTN_HF || network == NET_ATTN_MHF;
     wdl = value_fmt == VALUE_WDL;
     mlh = geti("moves_left") == 1 && opt.mlh != 0;
-    for (auto& kv : b->tensors)
-      if (kv.first.find("pol_encoder") != std::string::npos)
-        throw Fail{B200_ERR_UNSUPPORTED, "policy-head encoder layers are not supported by the b200 backend"};
 
     CK(cudaSetDevice(opt.gpu));
     cudaDeviceProp prop;
@@ -878,6 +882,18 @@ struct Net : NetBase {
       const int pe = (int)size_of("policy.ip_pol_b");
       pol_dm = (int)size_of("policy.ip2_pol_b");
       pol_emb = dense_maybe_folded("policy.ip_pol_w", "policy.ip_pol_b", pe, body_ch, head_gamma(), head_beta());
+      // encoder layers of the policy head (network_blas.cc:832-838): alpha 1, epsilon 1e-6, explicit LayerNorms
+      int n_pol = 0;
+      while (size_of("policy.pol_encoder." + std::to_string(n_pol) + ".mha.q_w")) ++n_pol;
+      if (n_pol > 0) {
+        pol_heads = (int)geti("pol_headcount");
+        if (pol_heads <= 0 || pe % pol_heads || pe % 8)
+          throw Fail{B200_ERR_INVALID, "weights: bad policy-head encoder width / head count"};
+        for (int i = 0; i < n_pol; ++i) {
+          pol_enc.push_back(load_encoder("policy.pol_encoder." + std::to_string(i), pe, pol_heads, nullptr, nullptr, false));
+          max_dff = std::max(max_dff, pol_enc.back().ffn1.out);
+        }
+      }
       pol_q = dense("policy.ip2_pol_w", "policy.ip2_pol_b", pol_dm, pe);
       pol_k = dense("policy.ip3_pol_w", "policy.ip3_pol_b", pol_dm, pe);
       pol_w4 = up_f32("policy.ip4_pol_w", (size_t)4 * pol_dm);
@@ -1035,6 +1051,15 @@ struct Net : NetBase {
       }
       if (policy_fmt == POLICY_ATTENTION) {
         s.pemb = A(R * pol_emb.out);
+        if (!pol_enc.empty()) {
+          int pdff = 8;
+          for (const auto& e : pol_enc) pdff = std::max(pdff, e.ffn1.out);
+          s.p_qkv = A(R * 3 * pol_emb.out);
+          s.p_att = A(R * pol_emb.out);
+          s.p_x1 = A(R * pol_emb.out);
+          s.p_y = A(R * pol_emb.out);
+          s.p_ffn = A(R * pdff);
+        }
         s.pq = A(R * pol_dm);
         s.pk = A(R * pol_dm);
         s.logits = (float*)salloc.alloc(nb * 4096 * 4);
@@ -1203,6 +1228,39 @@ struct Net : NetBase {
     span_end(st, sp_);
   }
 
+  // softmax(Q K^T / sqrt(depth) + bias) V for every (position, head); q, k, v are consecutive column blocks of `qkv`
+  void run_attention(cudaStream_t st, const T* qkv, int ld, const T* bias, T* out, int width, int n, int heads) {
+    const int depth = width / heads;
+    const float scale = 1.0f / sqrtf((float)depth);
+    launches++;
+    // algorithmic bytes: read Q, K, V (+ bias), write the head outputs
+    const int sp_ = span_begin(st, K_ATTENTION, (double)n * 64 * width * sizeof(T) * 4 +
+                                                    (bias ? (double)n * heads * 4096 * sizeof(T) : 0.0), TAG_ATTENTION);
+    bool done = false;
+    if constexpr (sizeof(T) == 2) {
+      if (use_tc && attention_tc_supported(ld, width, depth, qkv, qkv + width, qkv + 2 * width, bias, out)) {
+        CK(launch_attention_tma<T>(qkv, qkv + width, qkv + 2 * width, ld, bias, out, width, n, heads, depth, scale,
+                                   t_status, sm_count, st));
+        done = true;
+      }
+    }
+    if (!done) CK(launch_attention<T>(qkv, qkv + width, qkv + 2 * width, ld, bias, out, width, n, heads, depth, scale, st));
+    span_end(st, sp_);
+  }
+  // One encoder layer of the attention policy head (network_blas.cc:832-838: ForwardEncoderLayer with alpha 1 and
+  // epsilon 1e-6 on the policy embedding), LayerNorms as kernels; x [n*64][pe] is the layer's input and output.
+  void policy_encoder_layer(Slot& s, const EncoderW<T>& e, int n, T* x) {
+    cudaStream_t st = s.stream;
+    const int R = n * 64, pe = pol_emb.out;
+    const int act = attn_body ? act_ffn : ACT_SELU;
+    gemm(st, x, pe, e.qkv, s.p_qkv, 3 * pe, R, ACT_NONE);
+    run_attention(st, s.p_qkv, 3 * pe, nullptr, s.p_att, pe, n, pol_heads);
+    gemm(st, s.p_att, pe, e.proj, s.p_y, pe, R, ACT_NONE);
+    ln(st, s.p_x1, s.p_y, x, e.ln1g, e.ln1b, R, pe, 1.f, 1e-6f);
+    gemm(st, s.p_x1, pe, e.ffn1, s.p_ffn, e.ffn1.out, R, act);
+    gemm(st, s.p_ffn, e.ffn1.out, e.ffn2, s.p_y, pe, R, ACT_NONE);
+    ln(st, x, s.p_y, s.p_x1, e.ln2g, e.ln2b, R, pe, 1.f, 1e-6f);
+  }
   // `in` describes the layer input: buffer x, materialised for the first layer, afterwards the un-normalised
   // sum of the previous layer with its statistics.  With folding the two LayerNorms of the layer never run as
   // kernels: out-proj and FFN2 add the (normalised-on-the-fly) residual and accumulate row statistics, QKV,
@@ -1248,22 +1306,7 @@ struct Net : NetBase {
       gemm(st, s.sg_h2, sg_gen / H, smolgen_w, s.sg_bias, 4096, n * H, ACT_NONE);
       bias = s.sg_bias;
     }
-    launches++;
-    // algorithmic bytes: read Q, K, V (+ bias), write the head outputs
-    const int sp_ = span_begin(st, K_ATTENTION, (double)R * E * sizeof(T) * 4 + (bias ? (double)n * H * 4096 * sizeof(T) : 0.0), TAG_ATTENTION);
-    bool done = false;
-    if constexpr (sizeof(T) == 2) {
-      if (use_tc && attention_tc_supported(3 * E, E, depth, s.qkv, s.qkv + E, s.qkv + 2 * E, bias, s.att)) {
-        // :352-439
-        CK(launch_attention_tma<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
-                                   1.0f / sqrtf((float)depth), t_status, sm_count, st));
-        done = true;
-      }
-    }
-    if (!done)
-      CK(launch_attention<T>(s.qkv, s.qkv + E, s.qkv + 2 * E, 3 * E, bias, s.att, E, n, H, depth,
-                             1.0f / sqrtf((float)depth), st));
-    span_end(st, sp_);
+    run_attention(st, s.qkv, 3 * E, bias, s.att, E, n, H);  // :352-439
     if (fold_ln) {
       LNState att{s.att, nullptr, nullptr, nullptr}, ffn{s.ffn, nullptr, nullptr, nullptr};
       t_tag = TAG_OUT_PROJ;
@@ -1392,6 +1435,7 @@ struct Net : NetBase {
     // ---- policy head (:806-968) ----
     if (policy_fmt == POLICY_ATTENTION) {
       gemm_ln(st, head_in, body_ch, pol_emb, s.pemb, pol_emb.out, R, attn_body ? act_default : ACT_SELU);
+      for (const auto& e : pol_enc) policy_encoder_layer(s, e, n, s.pemb);
       gemm(st, s.pemb, pol_emb.out, pol_q, s.pq, pol_dm, R, ACT_NONE);
       gemm(st, s.pemb, pol_emb.out, pol_k, s.pk, pol_dm, R, ACT_NONE);
       bool done = false;

@@ -69,6 +69,8 @@ CONFIGS["cfg3_mini_tanh"] = dict(CONFIGS["cfg3_mini"], wdl=False, mlh=False, see
 # gains / offsets of a few channels at 40..200, a common offset on the sub-layer biases), for the LayerNorm
 # arithmetic of the 16-bit path.
 CONFIGS["cfg4_mini_outlier"] = dict(CONFIGS["cfg4_mini"], outlier=True, seed=1044)
+# Encoder layers inside the attention policy head (network_blas.cc:832-838), which no benchmark configuration has.
+CONFIGS["cfg3_mini_polenc"] = dict(CONFIGS["cfg3_mini"], pol_layers=2, pol_heads=2, pol_dff=80, seed=1053)
 
 
 class _Gen:
@@ -183,6 +185,17 @@ def _make_attn(c, g):
     pol = {"ip2_pol_w": g.normal(PD * PE, S), "ip2_pol_b": g.normal(PD, S),
            "ip3_pol_w": g.normal(PD * PE, S), "ip3_pol_b": g.normal(PD, S),
            "ip4_pol_w": g.normal(4 * PD, S)}
+    if c.get("pol_layers"):
+        PF = c["pol_dff"]
+        pol["pol_headcount"] = c["pol_heads"]
+        pol["pol_encoder"] = [{
+            "mha": {"q_w": g.normal(PE * PE, S), "q_b": g.normal(PE, S), "k_w": g.normal(PE * PE, S),
+                    "k_b": g.normal(PE, S), "v_w": g.normal(PE * PE, S), "v_b": g.normal(PE, S),
+                    "dense_w": g.normal(PE * PE, S), "dense_b": g.normal(PE, S)},
+            "ln1_gammas": g.normal(PE, S, 1.0), "ln1_betas": g.normal(PE, S),
+            "ffn": {"dense1_w": g.normal(PF * PE, S), "dense1_b": g.normal(PF, S),
+                    "dense2_w": g.normal(PE * PF, S), "dense2_b": g.normal(PE, S)},
+            "ln2_gammas": g.normal(PE, S, 1.0), "ln2_betas": g.normal(PE, S)} for _ in range(c["pol_layers"])]
     V, VH = c["value_planes"], c["value_hidden"]
     val = {"ip_val_w": g.normal(V * E, S), "ip_val_b": g.normal(V, S),
            "ip1_val_w": g.normal(VH * V * 64, S), "ip1_val_b": g.normal(VH, S),

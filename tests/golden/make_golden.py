@@ -41,6 +41,7 @@ GOLDENS = {  # net -> (position set, count)
     "cfg1_mini_tanh": ("positions_fmt1_uniform", 32),
     "cfg3_mini_tanh": ("positions_fmt2_uniform", 32),
     "cfg4_mini_outlier": ("positions_fmt2_uniform", 64),
+    "cfg3_mini_polenc": ("positions_fmt2_uniform", 32),
 }
 # Large batches, recorded in compact form (the logits of the legal moves only, padded to 256 per position, instead of
 # all 1858): name -> (net, position set, count).  The batch sizes of the headline measurement.

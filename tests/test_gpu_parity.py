@@ -9,7 +9,7 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 ALL = ["cfg1_mini", "cfg2_mini", "cfg3_mini", "cfg4_mini", "cfg1", "cfg2", "cfg3", "cfg4_2layer", "cfg1_mini_tanh",
-       "cfg3_mini_tanh"]
+       "cfg3_mini_tanh", "cfg3_mini_polenc"]
 # fp32 verification mode, per logit: |got - want| <= 1e-5 * max(|want|, rms of the position's logits) + 1e-6.  The
 # relative term is anchored at the position's typical logit because two fp32 implementations of the same network that
 # only differ in summation order (the reference's OpenBLAS path and the numpy restatement) already differ by a few

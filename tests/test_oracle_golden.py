@@ -16,7 +16,8 @@ VALUE_ATOL = 5e-6
 
 
 @pytest.mark.parametrize("name", ["cfg1_mini", "cfg2_mini", "cfg3_mini", "cfg4_mini", "cfg1", "cfg2", "cfg3",
-                                  "cfg4_2layer", "cfg1_mini_tanh", "cfg3_mini_tanh", "cfg4_mini_outlier"])
+                                  "cfg4_2layer", "cfg1_mini_tanh", "cfg3_mini_tanh", "cfg4_mini_outlier",
+                                  "cfg3_mini_polenc"])
 def test_oracle_matches_reference_blas(name):
     net, pos, n, g = load_case(name)
     meta, t = weights.flatten(net)
