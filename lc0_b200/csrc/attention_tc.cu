@@ -212,7 +212,8 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
     }
-    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores complete before the CTA exits
+    // the staging slabs must outlive the stores' reads of them; the grid's end completes the writes
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   }
   __syncthreads();
   if (*abort_flag) {

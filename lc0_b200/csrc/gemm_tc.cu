@@ -123,7 +123,6 @@ __device__ __forceinline__ void tma_store_wait_read1() {
 __device__ __forceinline__ void tma_store_wait_read0() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -186,6 +185,13 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                                 uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
       : "memory");
 }
 __device__ __forceinline__ void tcgen05_commit_pair(uint32_t cluster_bar) {
@@ -662,7 +668,9 @@ __device__ __forceinline__ void store_warp_loop(const TcParams& p, const CUtenso
       }
     }
   }
-  tma_store_wait_all();  // stores must complete before the CTA exits
+  // The CTA's shared memory must outlive the stores' reads of it; the writes themselves are complete, and visible to
+  // the next kernel of the stream, when the grid has finished.
+  tma_store_wait_read0();
 }
 
 template <int BN> struct TileCfg {
@@ -947,7 +955,8 @@ template <int kGroupsT> struct PairCfg {
   static constexpr int kBufs = 4 / kGroupsT;
   static constexpr int kThreads = 128 + 128 * kGroupsT;
   static constexpr int kEpiBytes = 4 * BM * 128;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 512 + 16 * 1024 /*column vectors*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 512 + 16 * 1024 /*column vectors*/ +
+                                    4096 /*squeeze-excitation gate and shift*/;
 };
 
 template <typename T, int kGroups>
@@ -973,7 +982,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint64_t* res_bar = reinterpret_cast<uint64_t*>(bar_mem + 192);   // [kGroups][kBufs]
   uint64_t* stg_full = reinterpret_cast<uint64_t*>(bar_mem + 256);  // [kGroups][kBufs]
   uint64_t* stg_free = stg_full + 4;                                // [kGroups][kBufs]
-  float* wvec = reinterpret_cast<float*>(bar_mem + 512) + ((threadIdx.x >> 5) & 15) * 256;  // per-warp scratch
+  float* wvec_all = reinterpret_cast<float*>(bar_mem + 512);                                 // 16 warps x 256 floats
+  float* wvec = wvec_all + ((threadIdx.x >> 5) & 15) * 256;                                  // per-warp scratch
+  uint64_t* se_bar = reinterpret_cast<uint64_t*>(bar_mem + 384);        // barrier of this CTA's epilogue threads
+  float* se_gb = reinterpret_cast<float*>(bar_mem + 512 + 16 * 1024);   // [2 boards][gate 256 | shift 256]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -989,7 +1001,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   auto width_of = [&](int t) { return t < split_from ? BN : BN / 2; };
   // N of the MMA that computes virtual tile t: the tile's width, or what is left of N rounded up to 32
   auto mma_n_of = [&](int t) { return pair_mma_n(p.N - col_of(t), width_of(t)); };
-  const int k_blocks = (p.K + BK - 1) / BK;
+  const int k_blocks = p.conv_cblocks > 0 ? 9 * p.conv_cblocks : (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 64) {
     tma_prefetch_map(&tmap_a);
@@ -1008,6 +1020,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       mbar_init(smem_u32(&tfull_bar[i]), 1);
       mbar_init(smem_u32(&tempty_bar[i]), 8 * kGroups);
     }
+    mbar_init(smem_u32(se_bar), 128 * kGroups);
     for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&res_bar[i]), 1);
       mbar_init(smem_u32(&stg_full[i]), 4);
@@ -1047,8 +1060,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (rank == 0) mbar_expect_tx(fb_local, half ? 2 * (BM + BN / 4) * BK * 2 : 2 * Cfg::kStageBytes);
           const uint32_t fb = mapa(fb_local, 0);
           const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
-          tma_load_2d_pair(sa, &tmap_a, kb * BK, m0, fb);
-          tma_load_2d_pair(sa + BM * BK * 2, half ? &tmap_wh : &tmap_w, kb * BK, n0, fb);
+          if (p.conv_cblocks > 0) {
+            // k-block = (filter tap, 64-channel block): this CTA's two boards shifted by the tap (the halo is zero
+            // filled by TMA) and its half of the tap's filter rows
+            const int tap = kb / p.conv_cblocks, cb = kb - tap * p.conv_cblocks;
+            tma_load_4d_pair(sa, &tmap_a, cb * BK, tap % 3 - 1, tap / 3 - 1, m0 >> 6, fb);
+            tma_load_2d_pair(sa + BM * BK * 2, &tmap_w, cb * BK, tap * p.N + n0, fb);
+          } else {
+            tma_load_2d_pair(sa, &tmap_a, kb * BK, m0, fb);
+            tma_load_2d_pair(sa + BM * BK * 2, half ? &tmap_wh : &tmap_w, kb * BK, n0, fb);
+          }
         }
       }
     }
@@ -1099,7 +1120,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int quarter = warp & 3;
     const int group = (warp - 4) >> 2;
     const bool leader = ((warp - 4) & 3) == 0 && lane == 0;
-    uint32_t tile_it = 0, slab_it = 0;
+    uint32_t tile_it = 0, slab_it = 0, se_phase = 0;
     ColRegs cr;
     int cr_nb = -1;
     if (pair < tiles && group * 64 < width_of(pair) && col_of(pair) + group * 64 < p.N) {
@@ -1115,6 +1136,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int m = m0 + quarter * 32 + lane;
       RowCtx rc;
       load_row_ctx(p, m, rc);
+      const float* se_row = nullptr;
+      if constexpr (kGroups == 2) {
+        if (p.se_k > 0) {  // this CTA's 128 rows are two boards with all their channels
+          se_prepare<BN>(p, trow, quarter, group, lane, (int)threadIdx.x - 128, wvec_all, se_gb, smem_u32(se_bar),
+                         se_phase, abort_flag);
+          se_row = se_gb + (quarter >> 1) * 512;
+        }
+      }
 #pragma unroll 1
       for (int c0 = group * 64; c0 < width; c0 += 64 * kGroups) {
         if (n0 + c0 >= p.N) break;  // uniform over the group
@@ -1129,9 +1158,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (nn < p.N) next_nb = nn;
         }
         cr_nb = next_nb;
-        epilogue_slab<T>(p, epi_mem + idx * (BM * 128), smem_u32(&res_bar[idx]), smem_u32(&stg_free[idx]),
-                         smem_u32(&stg_full[idx]), slab_it / kBufs, leader, trow + c0, quarter * 32 + lane, lane,
-                         n0 + c0, next_nb, cr, wvec, rc, abort_flag);
+        epilogue_slab<T, kGroups == 2>(p, epi_mem + idx * (BM * 128), smem_u32(&res_bar[idx]), smem_u32(&stg_free[idx]),
+                                       smem_u32(&stg_full[idx]), slab_it / kBufs, leader, trow + c0, quarter * 32 + lane,
+                                       lane, n0 + c0, next_nb, cr, wvec, rc, abort_flag,
+                                       se_row ? se_row + c0 : nullptr);
         ++slab_it;
       }
       flush_row_ctx(p, m, rc);
@@ -1316,11 +1346,13 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   }
   CUtensorMap ma, mw, mc;
   const int prec = TypeTag<T>::prec;
-  cudaError_t e = get_map(g.A, g.lda, g.M, g.K, BM, prec, &ma);
+  const bool conv = g.conv_cin > 0;
+  cudaError_t e = conv ? make_board_map(g.A, g.conv_cin, g.M / 64, prec, &ma) : get_map(g.A, g.lda, g.M, g.K, BM, prec, &ma);
   if (e != cudaSuccess) return e;
-  const int w_rows = g.batch_rows > 0 ? g.N * (g.M / g.batch_rows) : g.N;
-  e = get_map(g.W, g.ldw, w_rows, g.K, Cfg::BN / 2, prec, &mw);
+  const int w_rows = conv ? 9 * g.N : (g.batch_rows > 0 ? g.N * (g.M / g.batch_rows) : g.N);
+  e = get_map(g.W, conv ? g.conv_cin : g.ldw, w_rows, conv ? g.conv_cin : g.K, Cfg::BN / 2, prec, &mw);
   if (e != cudaSuccess) return e;
+  if (g.se_k > 0 && (kGroups != 2 || !gemm_tc_se_supported(g))) return cudaErrorInvalidValue;
   e = get_map(g.C, g.ldc, g.M, g.n_split > 0 ? g.n_split : g.N, BM, prec, &mc);
   if (e != cudaSuccess) return e;
   CUtensorMap mr = mc, mc2 = mc;
@@ -1340,7 +1372,7 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   p.bias = g.bias; p.C = g.C; p.ldc = g.ldc;
   p.M = g.M; p.N = g.N; p.K = g.K; p.act = g.act; p.scale = g.scale; p.alpha = g.alpha;
   p.out_f32 = 0; p.status = status;
-  p.conv_cblocks = 0;
+  p.conv_cblocks = conv ? ceil_div(g.conv_cin, BK) : 0;
   const int tiles = ceil_div(g.M, 2 * BM) * ceil_div(g.N, Cfg::BN);
   const int max_pairs = sm_count / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
@@ -1351,7 +1383,7 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
   const int rem = tiles % pairs;
   p.split_from = 0x7fffffff;
   p.tiles_v = tiles;
-  if (split_enabled && g.n_split == 0 && (g.N % Cfg::BN) == 0 && tiles > pairs && rem > 0 && 2 * rem <= pairs) {
+  if (split_enabled && !conv && g.n_split == 0 && (g.N % Cfg::BN) == 0 && tiles > pairs && rem > 0 && 2 * rem <= pairs) {
     p.split_from = tiles - rem;
     p.tiles_v = tiles + rem;
   }
@@ -1423,7 +1455,10 @@ namespace {
 // Large problems with 16-bit output go to the CTA-pair kernel (256x256 tiles).
 bool pair_eligible(const GemmParams& p, int sm_count) {
   const bool tma_store_ok = !p.out_f32 && (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
-  return tma_store_ok && p.conv_cin == 0 && p.se_k == 0 && p.M >= 512 && p.N > 128 &&
+  // a convolution qualifies when one 256-wide tile holds all its output channels (each CTA of a pair then loads half
+  // of every tap's filter rows instead of all of them)
+  if (p.conv_cin > 0 && (p.N > 256 || p.n_split > 0)) return false;
+  return tma_store_ok && p.M >= 512 && p.N > 128 &&
          (long long)ceil_div(p.M, 2 * BM) * ceil_div(p.N, 256) >= sm_count / 4;
 }
 }  // namespace
@@ -1443,7 +1478,7 @@ cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaS
   {
     // Four epilogue groups when a tile has few k-blocks (the epilogue then sets the pace), two otherwise (fewer
     // warps compete with the MMA issuer and the producer).
-    const bool four = p.K <= 8 * BK;
+    const bool four = p.K <= 8 * BK && p.conv_cin == 0 && p.se_k == 0;
     return four ? launch_pair<T, 4>(p, status, sm_count, s) : launch_pair<T, 2>(p, status, sm_count, s);
   }
   if (p.se_k > 0) return launch_bn<T, 256>(p, status, sm_count, s);  // the tile must hold every channel of two boards
