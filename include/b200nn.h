@@ -141,7 +141,10 @@ int b200_comp_legal_policy(const b200_comp* c, int sample, const float** probs, 
  *   (masks [n][112] u64, values [n][112] f32, policy [n][1858] f32, qdm [n][3] f32 as q,d,m);
  *   enqueues on the slot's stream and synchronises before returning.
  * b200_net_enqueue_device / b200_net_sync: the same without the final synchronisation, so a
- *   caller can time many evaluations with events on b200_net_stream(). */
+ *   caller can time many evaluations with events on b200_net_stream().  These entry points run on workspace slot 0
+ *   and take it out of the pool the computations draw from: the enqueue form holds it until b200_net_sync (which also
+ *   reports a kernel time-out of the enqueued evaluations), so every b200_net_enqueue_device must be followed by a
+ *   b200_net_sync before a network with a single slot can serve a computation again. */
 int b200_net_eval_host(b200_net* net, const uint64_t* masks, const float* values, int n,
                        float* policy, float* q, float* d, float* m);
 int b200_net_eval_device(b200_net* net, const void* d_masks, const void* d_values, int n,
