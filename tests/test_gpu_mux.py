@@ -63,3 +63,39 @@ def test_limits_and_errors():
     assert mux.evaluate(masks[:0], values[:0])["q"].size == 0
     mux.close()
     nw.close()
+
+
+def test_destroy_with_blocked_callers():
+    """Destroying the aggregator while callers are inside it: every caller returns (with its result or with the
+    'destroyed' error) and nothing touches freed memory: b200_mux_destroy waits until the last caller has left."""
+    net, pos, n, g = load_case("cfg3_mini")
+    masks, values = np.array(pos["masks"]), np.array(pos["values"])
+    nw = network.Network(net, "precision=fp32,max_batch=64")
+    for attempt in range(5):
+        mux = nw.new_mux(max_batch=64, wait_us=200000)  # workers wait 0.2 s for more requests: callers stay blocked
+        outcomes = []
+        entering = [threading.Event() for _ in range(8)]
+
+        def caller(k):
+            try:
+                entering[k].set()
+                out = mux.evaluate(masks[k:k + 3], values[k:k + 3])
+                outcomes.append(("ok", float(np.abs(out["q"] - g["q"][k:k + 3]).max())))
+            except _lib.B200Error as e:
+                outcomes.append(("error", str(e)))
+
+        threads = [threading.Thread(target=caller, args=(k,)) for k in range(8)]
+        for t in threads:
+            t.start()
+        import time
+        for e in entering:
+            e.wait()
+        time.sleep(0.05 + 0.03 * attempt)  # every caller is inside b200_mux_eval by now, blocked on its request
+        mux.close()
+        for t in threads:
+            t.join(timeout=30)
+            assert not t.is_alive()
+        assert len(outcomes) == 8
+        for kind, val in outcomes:
+            assert (kind == "ok" and val <= 1e-5) or (kind == "error" and "destroy" in val), (kind, val)
+    nw.close()
