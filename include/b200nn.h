@@ -85,7 +85,8 @@ enum {
   /* Residual networks in fp16 / bf16: 3x3 convolutions as Winograd F(4x4, 3x3) (transform kernels around 36 stacked
    * tensor-core products, the reference GPU backend's decomposition) instead of the direct tensor-core convolution.
    * Off by default: a quarter of the multiplications, but about ten times the rounding error in 16-bit storage. */
-  B200_FLAG_WINOGRAD = 64
+  B200_FLAG_WINOGRAD = 64,
+  B200_FLAG_NO_SIDE_STREAM = 128     /* smolgen's small dense layers in line instead of on a second stream beside the QKV product */
 };
 
 typedef struct b200_net_info {

@@ -411,6 +411,14 @@ struct Net : NetBase {
   // Status word of the evaluation being enqueued on this thread (the slot's), handed to every kernel with bounded waits.
   static inline thread_local int* t_status = nullptr;
   static inline thread_local void* t_slot_ptr = nullptr;  // the slot of that evaluation
+  // > 0: the tensor-core launches that follow on this thread use at most this many SMs (persistent grids are sized
+  // from it), so that two launches on different streams can share the GPU
+  static inline thread_local int t_sm_limit = 0;
+  // smolgen's two small dense layers and their LayerNorms run on a second stream on kSideSms SMs while the QKV product
+  // has the rest of the GPU: they are launch- and latency-bound (a quarter of a layer's time at batch 256), not
+  // throughput-bound
+  bool side_stream = false;
+  static constexpr int kSideSms = 8;
 
   // format
   int network = 0, policy_fmt = 0, value_fmt = 0, emb_fmt = 0;
@@ -446,6 +454,8 @@ struct Net : NetBase {
 
   struct Slot {
     cudaStream_t stream = nullptr;
+    cudaStream_t stream2 = nullptr;      // side stream of the smolgen dense layers
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     cudaEvent_t compute_done = nullptr;  // recorded after the last kernel of an evaluation, before its result copies
     int* h_status = nullptr;             // pinned copy of the device status word, refreshed by every evaluation
     uint64_t* d_masks = nullptr;
@@ -478,6 +488,9 @@ struct Net : NetBase {
         if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     for (auto& s : slots) {
       if (s.stream) cudaStreamDestroy(s.stream);
+      if (s.stream2) cudaStreamDestroy(s.stream2);
+      if (s.ev_fork) cudaEventDestroy(s.ev_fork);
+      if (s.ev_join) cudaEventDestroy(s.ev_join);
       if (s.compute_done) cudaEventDestroy(s.compute_done);
       if (s.h_status) cudaFreeHost(s.h_status);
     }
@@ -739,6 +752,7 @@ struct Net : NetBase {
     }
     merge_compress = !(opt.flags & B200_FLAG_NO_MERGED_COMPRESS);
     winograd = use_tc && !attn_body && (opt.flags & B200_FLAG_WINOGRAD);
+    side_stream = use_tc && attn_body && !(opt.flags & B200_FLAG_NO_SIDE_STREAM) && sm_count >= 4 * kSideSms;
     fold_ln = use_tc && attn_body && !(opt.flags & B200_FLAG_NO_LN_FOLD);
     // Folding needs every product that consumes or produces a folded LayerNorm to be eligible for the tensor-core
     // kernel's TMA epilogue: output widths that are multiples of 8.
@@ -994,7 +1008,12 @@ struct Net : NetBase {
     auto A = [&](size_t elems) { return (T*)salloc.alloc(elems * sizeof(T)); };
     for (int si = 0; si < opt.slots; ++si) {
       Slot& s = slots[si];
-      CK(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+      int prio_low = 0, prio_high = 0;
+      CK(cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high));
+      CK(cudaStreamCreateWithPriority(&s.stream, cudaStreamNonBlocking, prio_high));
+      CK(cudaStreamCreateWithPriority(&s.stream2, cudaStreamNonBlocking, prio_low));
+      CK(cudaEventCreateWithFlags(&s.ev_fork, cudaEventDisableTiming));
+      CK(cudaEventCreateWithFlags(&s.ev_join, cudaEventDisableTiming));
       CK(cudaEventCreateWithFlags(&s.compute_done, cudaEventDisableTiming));
       CK(cudaMallocHost(&s.h_status, sizeof(int)));
       *s.h_status = 0;
@@ -1133,7 +1152,7 @@ struct Net : NetBase {
     if constexpr (sizeof(T) == 2) {
       if (use_tc && p.M >= 64 && gemm_tc_supported(p)) {
         const int sp_ = span_begin(st, K_GEMM_TC, flops, t_tag);
-        CK(launch_gemm_tc<T>(p, t_status, sm_count, st));
+        CK(launch_gemm_tc<T>(p, t_status, t_sm_limit > 0 ? t_sm_limit : sm_count, st));
         span_end(st, sp_);
         return;
       }
@@ -1279,6 +1298,35 @@ struct Net : NetBase {
       stats2 = s.stats2[par];
       CK(cudaMemsetAsync(par == 0 ? s.stats2[0] : s.stats1, 0, (s.stats_stride + (size_t)R * 2) * sizeof(double), st));
     }
+    if (side_stream && e.smolgen && R >= 2048) {
+      // compression first (it reads the whole layer input: memory-bound, all SMs), then the two small dense layers
+      // with their LayerNorms on the side stream while Q, K, V are computed on the other SMs
+      cudaStream_t st2 = s.stream2;
+      t_tag = TAG_SMOLGEN_DENSE;
+      gemm_ln(st, in, E, e.sg_compress, s.sg_c, sg_hc, R, ACT_NONE);
+      CK(cudaEventRecord(s.ev_fork, st));
+      // Q, K, V first and on the higher-priority stream: its CTA pairs take whole TPCs, the side stream's CTAs then
+      // land on the SMs it leaves free
+      t_sm_limit = (sm_count - kSideSms) & ~1;
+      t_tag = TAG_QKV;
+      gemm_ln(st, in, E, e.qkv, s.qkv, 3 * E, R, ACT_NONE);
+      CK(cudaStreamWaitEvent(st2, s.ev_fork, 0));
+      t_sm_limit = kSideSms;
+      t_tag = TAG_SMOLGEN_DENSE;
+      gemm(st2, s.sg_c, 64 * sg_hc, e.sg_d1, s.sg_h1, sg_hid, n, act_smolgen);
+      ln(st2, s.sg_h1, s.sg_h1, nullptr, e.sg_ln1g, e.sg_ln1b, n, sg_hid, 1.f, 1e-3f);
+      gemm(st2, s.sg_h1, sg_hid, e.sg_d2, s.sg_h2, sg_gen, n, act_smolgen);
+      ln(st2, s.sg_h2, s.sg_h2, nullptr, e.sg_ln2g, e.sg_ln2b, n, sg_gen, 1.f, 1e-3f);
+      CK(cudaEventRecord(s.ev_join, st2));
+      t_sm_limit = 0;
+      CK(cudaStreamWaitEvent(st, s.ev_join, 0));
+      t_tag = TAG_SMOLGEN_BIAS;
+      gemm(st, s.sg_h2, sg_gen / H, smolgen_w, s.sg_bias, 4096, n * H, ACT_NONE);
+      bias = s.sg_bias;
+      run_attention(st, s.qkv, 3 * E, bias, s.att, E, n, H);
+      finish_layer(s, e, R, x, x1, in, stats2);
+      return;
+    }
     // One launch for Q, K, V and the smolgen compression when the CTA-pair kernel takes the product.
     bool merged = false;
     if (e.smolgen && e.qkvc_out && merge_compress) {
@@ -1307,6 +1355,11 @@ struct Net : NetBase {
       bias = s.sg_bias;
     }
     run_attention(st, s.qkv, 3 * E, bias, s.att, E, n, H);  // :352-439
+    finish_layer(s, e, R, x, x1, in, stats2);
+  }
+  // Output projection, first LayerNorm, FFN, second LayerNorm of an encoder layer (network_blas.cc:441-470).
+  void finish_layer(Slot& s, const EncoderW<T>& e, int R, T*& x, T*& x1, LNState& in, double* stats2) {
+    cudaStream_t st = s.stream;
     if (fold_ln) {
       LNState att{s.att, nullptr, nullptr, nullptr}, ffn{s.ffn, nullptr, nullptr, nullptr};
       t_tag = TAG_OUT_PROJ;

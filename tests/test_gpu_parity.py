@@ -423,13 +423,33 @@ def test_merged_qkv_and_smolgen_compression_launch_matches_separate_launches():
     values = np.ones((n, 112), np.float32)
     outs = []
     for flag in ("1", "0"):
-        nw = network.Network(net, "precision=fp16,max_batch=%d,merge_compress=%s" % (n, flag))
+        nw = network.Network(net, "precision=fp16,max_batch=%d,merge_compress=%s,side_stream=0" % (n, flag))
         outs.append(nw.evaluate(masks, values))
         assert nw.device_status() == 0
         nw.close()
     scale = np.abs(outs[1]["policy"]).max()
     assert np.abs(outs[0]["policy"] - outs[1]["policy"]).max() <= 2e-3 * scale
     assert np.abs(outs[0]["q"] - outs[1]["q"]).max() <= 2e-3
+
+
+@pytest.mark.parametrize("batch", [40, 256, 1024])
+def test_side_stream_schedule_matches_in_line_schedule(batch):
+    """smolgen's small dense layers on a second stream beside the QKV product (confined to fewer SMs) against the same
+    launches in line on one stream, and against the reference; three evaluations each so that the captured graph, with
+    its fork and join, is replayed too."""
+    net, pos, n, g = load_compact("cfg4_2layer_b1024")
+    idx = np.arange(batch)
+    outs = []
+    for side in (1, 0):
+        nw = network.Network(net, "precision=fp16,max_batch=%d,side_stream=%d" % (batch, side))
+        for rep in range(3):
+            out = nw.evaluate(pos["masks"][idx], pos["values"][idx])
+            assert nw.device_status() == 0
+        nw.close()
+        _assert_half_against_compact(out, g, pos, idx)
+        outs.append(out)
+    assert np.abs(outs[0]["policy"] - outs[1]["policy"]).max() <= 2e-3 * max(1.0, np.abs(outs[1]["policy"]).max())
+    assert np.abs(outs[0]["q"] - outs[1]["q"]).max() <= 1e-3
 
 
 def test_split_last_wave_matches_whole_tiles():
