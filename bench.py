@@ -344,7 +344,8 @@ def main():
     launches = nw.launch_count() - l0
     clocks = sampler.stop(t0, t1)
     # Per-kernel-class pass: the same K steps again with CUDA-event pairs around every launch (this pass launches
-    # kernel by kernel; the timed pass above replays the captured graph of the same launches).
+    # kernel by kernel; the timed pass above replays the captured graph of the same launches).  In this pass smolgen's
+    # small dense layers run in line rather than on the side stream, so that every span times one kernel alone.
     nw.set_profiling(True)
     nw.get_profile(reset=True)
     nw.get_profile_tagged(reset=True)

@@ -22,6 +22,7 @@ FLAG_NO_SPLIT_LAST_WAVE = 16
 FLAG_NO_FUSED_SE = 32
 FLAG_WINOGRAD = 64
 FLAG_NO_SIDE_STREAM = 128
+FLAG_NO_DEPENDENT_LAUNCH = 256
 POLICY_SIZE = 1858
 INPUT_PLANES = 112
 

@@ -227,7 +227,8 @@ b200_net_options MakeNetOptions(const OptionsDict& options, int precision) {
               (options.GetOrDefault<bool>("split_last_wave", true) ? 0 : B200_FLAG_NO_SPLIT_LAST_WAVE) |
               (options.GetOrDefault<bool>("fused_se", true) ? 0 : B200_FLAG_NO_FUSED_SE) |
               (options.GetOrDefault<bool>("winograd", false) ? B200_FLAG_WINOGRAD : 0) |
-              (options.GetOrDefault<bool>("side_stream", true) ? 0 : B200_FLAG_NO_SIDE_STREAM);
+              (options.GetOrDefault<bool>("side_stream", true) ? 0 : B200_FLAG_NO_SIDE_STREAM) |
+              (options.GetOrDefault<bool>("dependent_launch", true) ? 0 : B200_FLAG_NO_DEPENDENT_LAUNCH);
   return opt;
 }
 

@@ -73,16 +73,20 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (tid == 128) {
+    tma_prefetch_map(&map_q);
+    tma_prefetch_map(&map_k);
+    tma_prefetch_map(&map_v);
+    tma_prefetch_map(&map_o);
+    if (has_bias) tma_prefetch_map(&map_b);
+  }
   __syncthreads();
+  grid_dependency_wait();
+  grid_launch_dependents();
 
   if (warp == 4) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      tma_prefetch_map(&map_q);
-      tma_prefetch_map(&map_k);
-      tma_prefetch_map(&map_v);
-      tma_prefetch_map(&map_o);
-      if (has_bias) tma_prefetch_map(&map_b);
       uint32_t it = 0;
       for (int item = blockIdx.x; item < items; item += gridDim.x, ++it) {
         const int s = it % NS;
@@ -360,9 +364,8 @@ static cudaError_t launch_attention_tma_cfg(const T* q, const T* k, const T* v, 
   const int items = n * heads;
   const int max_ctas = sm_count * ctas_per_sm;
   const int grid = items < max_ctas ? items : max_ctas;
-  attention_tma_kernel<T, D, NS><<<grid, L::kThreads, L::kBytes, s>>>(mq, mk, mv, mb, mo, items, heads, bias ? 1 : 0,
-                                                                      scale, status);
-  return cudaGetLastError();
+  return launch_dependent(attention_tma_kernel<T, D, NS>, dim3(grid), dim3(L::kThreads), L::kBytes, s, mq, mk, mv, mb, mo,
+                          items, heads, bias ? 1 : 0, scale, status);
 }
 
 template <typename T>

@@ -25,6 +25,36 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
     if (e__ != cudaSuccess) return ::b200::cuda_fail(e__, #call, __FILE__, __LINE__); \
   } while (0)
 
+// ---- programmatic dependent launch --------------------------------------------------------------------------
+// A kernel launched through launch_dependent() may be made resident, and run its prologue (barrier initialisation,
+// tensor-memory allocation, descriptor prefetch), while the kernel before it in the stream is still running.  Such a
+// kernel calls grid_dependency_wait() in every thread before its first access to global memory: the call returns
+// when the kernels before it have completed and their writes are visible.  grid_launch_dependents() lets the kernel
+// after it do the same in turn.  Both are no-ops in a kernel that was launched the ordinary way.
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
+// Whether launch_dependent() asks for the overlap (off: an ordinary launch).  Set by the host schedule per thread.
+extern thread_local bool t_dependent_launch;
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = t_dependent_launch ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename T> struct TypeTag;
 template <> struct TypeTag<float> { static constexpr int prec = 0; };
 template <> struct TypeTag<__half> { static constexpr int prec = 1; };

@@ -748,6 +748,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dependency_wait();  // everything above overlapped the kernel before this one
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -1040,6 +1042,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dependency_wait();  // everything above overlapped the kernel before this one
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
@@ -1326,8 +1330,7 @@ cudaError_t launch_bn(const GemmParams& g, int* status, int sm_count, cudaStream
   p.conv_cblocks = g.conv_cin > 0 ? ceil_div(g.conv_cin, BK) : 0;
   const int tiles = ceil_div(g.M, BM) * ceil_div(g.N, BN);
   const int grid = tiles < sm_count ? tiles : sm_count;
-  gemm_tc_kernel<T, BN><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, p);
-  return cudaGetLastError();
+  return launch_dependent(gemm_tc_kernel<T, BN>, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, s, ma, mw, mc, mr, p);
 }
 
 
@@ -1392,8 +1395,8 @@ cudaError_t launch_pair(const GemmParams& g, int* status, int sm_count, cudaStre
     e = get_map(g.W, g.ldw, w_rows, g.K, Cfg::BN / 4, prec, &mwh);
     if (e != cudaSuccess) return e;
   }
-  gemm_tc_pair_kernel<T, kGroups><<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, s>>>(ma, mw, mc, mr, mc2, mwh, p);
-  return cudaGetLastError();
+  return launch_dependent(gemm_tc_pair_kernel<T, kGroups>, dim3(2 * pairs), dim3(Cfg::kThreads), Cfg::kSmemBytes, s, ma,
+                          mw, mc, mr, mc2, mwh, p);
 }
 
 }  // namespace

@@ -4,6 +4,8 @@
 
 namespace b200 {
 
+thread_local bool t_dependent_launch = false;
+
 // ------------------------------------------------------------------------------------------------
 // Plane expansion (reference: BlasComputation::EncodePlanes, backends/blas/network_blas.cc:973-981;
 // GPU twin expandPlanes_kernel_NCHW, backends/cuda/common_kernels.cu:484-521).
@@ -238,6 +240,8 @@ layer_norm_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restr
                   const float* __restrict__ gate_mult, const float* __restrict__ gate_add, int C,
                   float alpha, float eps) {
   __shared__ float red[32];
+  grid_dependency_wait();
+  grid_launch_dependents();
   const long long row = blockIdx.x;
   const T* xr = x + row * C;
   const T* sr = skip ? skip + row * C : nullptr;
@@ -306,6 +310,8 @@ layer_norm_warp_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __
                        const float* __restrict__ gamma, const float* __restrict__ beta,
                        const float* __restrict__ gate_mult, const float* __restrict__ gate_add, int rows, int C,
                        float alpha, float eps) {
+  grid_dependency_wait();
+  grid_launch_dependents();
   const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -388,11 +394,12 @@ cudaError_t launch_layer_norm(T* out, const T* x, const T* skip, const float* ga
   if (rows <= 0) return cudaSuccess;
   if (C % 8 != 0 || C > 8192) return cudaErrorInvalidValue;
 #define LNW_LAUNCH(CH)                                                                                      \
-  layer_norm_warp_kernel<T, CH><<<ceil_div(rows, 4), 128, 0, s>>>(out, x, skip, gamma, beta, gate_mult,     \
-                                                                   gate_add, rows, C, alpha, eps)
-#define LN_LAUNCH(TH, ST)                                                                          \
-  layer_norm_kernel<T, TH, ST><<<rows, TH, 0, s>>>(out, x, skip, gamma, beta, gate_mult, gate_add, C, \
-                                                    alpha, eps)
+  le = launch_dependent(layer_norm_warp_kernel<T, CH>, dim3(ceil_div(rows, 4)), dim3(128), 0, s, out, x, skip, \
+                        gamma, beta, gate_mult, gate_add, rows, C, alpha, eps)
+#define LN_LAUNCH(TH, ST)                                                                                     \
+  le = launch_dependent(layer_norm_kernel<T, TH, ST>, dim3(rows), dim3(TH), 0, s, out, x, skip, gamma, beta, \
+                        gate_mult, gate_add, C, alpha, eps)
+  cudaError_t le = cudaSuccess;
   if (C <= 256) LNW_LAUNCH(1);
   else if (C <= 512) LNW_LAUNCH(2);
   else if (C <= 1024) LNW_LAUNCH(4);
@@ -401,7 +408,7 @@ cudaError_t launch_layer_norm(T* out, const T* x, const T* skip, const float* ga
   else LN_LAUNCH(256, 4);
 #undef LN_LAUNCH
 #undef LNW_LAUNCH
-  return cudaGetLastError();
+  return le;
 }
 
 // Input gating x * mult + add (reference: network_blas.cc:669-682; gates re-laid out [64][C] at load).

@@ -414,10 +414,16 @@ struct Net : NetBase {
   // > 0: the tensor-core launches that follow on this thread use at most this many SMs (persistent grids are sized
   // from it), so that two launches on different streams can share the GPU
   static inline thread_local int t_sm_limit = 0;
+  struct DependentLaunchScope {
+    bool prev;
+    explicit DependentLaunchScope(bool on) : prev(t_dependent_launch) { t_dependent_launch = on; }
+    ~DependentLaunchScope() { t_dependent_launch = prev; }
+  };
   // smolgen's two small dense layers and their LayerNorms run on a second stream on kSideSms SMs while the QKV product
   // has the rest of the GPU: they are launch- and latency-bound (a quarter of a layer's time at batch 256), not
   // throughput-bound
   bool side_stream = false;
+  bool dependent_launch = false;  // tensor-core products, attention and LayerNorms launched with launch_dependent()
   static constexpr int kSideSms = 8;
 
   // format
@@ -753,6 +759,7 @@ struct Net : NetBase {
     merge_compress = !(opt.flags & B200_FLAG_NO_MERGED_COMPRESS);
     winograd = use_tc && !attn_body && (opt.flags & B200_FLAG_WINOGRAD);
     side_stream = use_tc && attn_body && !(opt.flags & B200_FLAG_NO_SIDE_STREAM) && sm_count >= 4 * kSideSms;
+    dependent_launch = use_tc && !(opt.flags & B200_FLAG_NO_DEPENDENT_LAUNCH);
     fold_ln = use_tc && attn_body && !(opt.flags & B200_FLAG_NO_LN_FOLD);
     // Folding needs every product that consumes or produces a folded LayerNorm to be eligible for the tensor-core
     // kernel's TMA epilogue: output widths that are multiples of 8.
@@ -1298,7 +1305,9 @@ struct Net : NetBase {
       stats2 = s.stats2[par];
       CK(cudaMemsetAsync(par == 0 ? s.stats2[0] : s.stats1, 0, (s.stats_stride + (size_t)R * 2) * sizeof(double), st));
     }
-    if (side_stream && e.smolgen && R >= 2048) {
+    // With per-launch event pairs on (profiling) the layer runs in line: a span around a launch that shares the GPU
+    // with another stream measures the sharing, not the kernel.
+    if (side_stream && !profiling && e.smolgen && R >= 2048) {
       // compression first (it reads the whole layer input: memory-bound, all SMs), then the two small dense layers
       // with their LayerNorms on the side stream while Q, K, V are computed on the other SMs
       cudaStream_t st2 = s.stream2;
@@ -1313,7 +1322,10 @@ struct Net : NetBase {
       CK(cudaStreamWaitEvent(st2, s.ev_fork, 0));
       t_sm_limit = kSideSms;
       t_tag = TAG_SMOLGEN_DENSE;
-      gemm(st2, s.sg_c, 64 * sg_hc, e.sg_d1, s.sg_h1, sg_hid, n, act_smolgen);
+      {  // the first launch behind an event of the other stream is an ordinary one
+        DependentLaunchScope ordinary(false);
+        gemm(st2, s.sg_c, 64 * sg_hc, e.sg_d1, s.sg_h1, sg_hid, n, act_smolgen);
+      }
       ln(st2, s.sg_h1, s.sg_h1, nullptr, e.sg_ln1g, e.sg_ln1b, n, sg_hid, 1.f, 1e-3f);
       gemm(st2, s.sg_h1, sg_hid, e.sg_d2, s.sg_h2, sg_gen, n, act_smolgen);
       ln(st2, s.sg_h2, s.sg_h2, nullptr, e.sg_ln2g, e.sg_ln2b, n, sg_gen, 1.f, 1e-3f);
@@ -1321,7 +1333,10 @@ struct Net : NetBase {
       t_sm_limit = 0;
       CK(cudaStreamWaitEvent(st, s.ev_join, 0));
       t_tag = TAG_SMOLGEN_BIAS;
-      gemm(st, s.sg_h2, sg_gen / H, smolgen_w, s.sg_bias, 4096, n * H, ACT_NONE);
+      {
+        DependentLaunchScope ordinary(false);
+        gemm(st, s.sg_h2, sg_gen / H, smolgen_w, s.sg_bias, 4096, n * H, ACT_NONE);
+      }
       bias = s.sg_bias;
       run_attention(st, s.qkv, 3 * E, bias, s.att, E, n, H);
       finish_layer(s, e, R, x, x1, in, stats2);
@@ -1394,6 +1409,8 @@ struct Net : NetBase {
     s.stats_parity = 0;
     t_status = d_status + (&s - slots.data());
     t_slot_ptr = &s;
+    // not with per-launch event pairs: the spans would then time the overlap with the neighbours
+    DependentLaunchScope launch_scope(dependent_launch && !profiling);
     CK(cudaMemsetAsync(d_qdm, 0, (size_t)n * 3 * sizeof(float), st));
     if (!res.empty() || !attn_body) {  // network_blas.cc:564-601
       other(st, (double)R * 112 * sizeof(T), [&] {

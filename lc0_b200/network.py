@@ -16,7 +16,7 @@ from . import _lib, netproto, weights as _weights
 
 _KNOWN_OPTIONS = {"gpu", "max_batch", "precision", "slots", "mlh", "policy_head", "value_head",
                   "tensor_cores", "graph_capture", "fold_ln", "merge_compress", "split_last_wave", "fused_se", "winograd",
-                  "side_stream"}
+                  "side_stream", "dependent_launch"}
 
 
 def parse_options(opts):
@@ -47,7 +47,8 @@ def option_flags(opts):
     flags = 0
     for key, bit in (("tensor_cores", _lib.FLAG_NO_TENSOR_CORES), ("graph_capture", _lib.FLAG_NO_GRAPHS),
                      ("fold_ln", _lib.FLAG_NO_LN_FOLD), ("merge_compress", _lib.FLAG_NO_MERGED_COMPRESS),
-                     ("split_last_wave", _lib.FLAG_NO_SPLIT_LAST_WAVE), ("fused_se", _lib.FLAG_NO_FUSED_SE), ("side_stream", _lib.FLAG_NO_SIDE_STREAM)):
+                     ("split_last_wave", _lib.FLAG_NO_SPLIT_LAST_WAVE), ("fused_se", _lib.FLAG_NO_FUSED_SE), ("side_stream", _lib.FLAG_NO_SIDE_STREAM),
+                     ("dependent_launch", _lib.FLAG_NO_DEPENDENT_LAUNCH)):
         if not _as_bool(opts.get(key, True)):
             flags |= bit
     if _as_bool(opts.get("winograd", False)):

@@ -452,6 +452,29 @@ def test_side_stream_schedule_matches_in_line_schedule(batch):
     assert np.abs(outs[0]["q"] - outs[1]["q"]).max() <= 1e-3
 
 
+@pytest.mark.parametrize("name,batch", [("cfg4_2layer_b1024", 40), ("cfg4_2layer_b1024", 256), ("cfg2", 16),
+                                        ("cfg3_mini_polenc", 16)])
+def test_dependent_launches_match_ordinary_launches(name, batch):
+    """Products, attention and LayerNorms launched as programmatic dependents (prologue under the tail of the kernel
+    before, griddepcontrol.wait before the first global access) against ordinary launches of the same schedule; five
+    evaluations each, so that the replayed graph is covered, and two slots used in turn."""
+    net, pos, n, g = load_compact(name) if name.startswith("cfg4_2layer") else load_case(name)
+    batch = min(batch, n)
+    idx = np.arange(batch)
+    outs = []
+    for dep in (1, 0):
+        nw = network.Network(net, "precision=fp16,max_batch=%d,slots=2,dependent_launch=%d" % (batch, dep))
+        for rep in range(5):
+            out = nw.evaluate(pos["masks"][idx], pos["values"][idx])
+            assert nw.device_status() == 0
+        nw.close()
+        outs.append(out)
+    scale = max(1.0, np.abs(outs[1]["policy"]).max())
+    assert np.abs(outs[0]["policy"] - outs[1]["policy"]).max() <= 1e-3 * scale
+    assert np.abs(outs[0]["q"] - outs[1]["q"]).max() <= 1e-3
+    assert np.abs(outs[0]["m"] - outs[1]["m"]).max() <= 1e-3 * max(1.0, np.abs(outs[1]["m"]).max())
+
+
 def test_split_last_wave_matches_whole_tiles():
     """Products whose last wave of 256x256 tiles fills at most half of the CTA pairs compute that wave as half-width
     tiles (out-projection and FFN2 here, both with residual input and row statistics): same results as whole tiles."""
