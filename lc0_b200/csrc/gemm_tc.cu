@@ -947,16 +947,21 @@ __host__ __device__ __forceinline__ int pair_mma_n(int remaining, int bn) {
 template <int kGroupsT> struct PairCfg {
   static constexpr int BN = 256;
   static constexpr int kStageBytes = (BM + BN / 2) * BK * 2;  // 32 KB per CTA
-  static constexpr int kStages = 4;
   static constexpr int kTmemCols = 512;
   // warp 0 TMA, warp 1 MMA, warps 2 and 3 stores (half of the epilogue groups each), then kGroups epilogue groups of
-  // four warps.  The 64 KB of staging are four buffers of 128 rows x 128 bytes: two groups with two buffers each
-  // (138 registers per thread; best when the main loop dominates) or four groups with one buffer each (96
-  // registers; twice the epilogue throughput, for products with few k-blocks per tile).
+  // four warps, each with one staging buffer of 128 rows x 128 bytes: two groups (138 registers per thread; best when
+  // the main loop dominates) or four groups (96 registers; twice the epilogue throughput, for products with few
+  // k-blocks per tile).  The two-group form spends the 32 KB it saves on staging on a fifth pipeline stage: a stage
+  // is refilled only after the MMAs that read it have completed, so with four stages a load has three k-blocks of MMA
+  // time to arrive.  Measured against four stages and two buffers per group, in the network at batch 1024 / 256:
+  // FFN2 (24 k-blocks per tile) 1040 -> 1084 and 872 -> 923 TFLOP/s, out-projection 868 -> 853 and 688 -> 670 (the
+  // residual tile is prefetched one slab ahead instead of two), the whole evaluation +0.9 % and +1.0 %.  Run for
+  // seconds under the power cap the two forms are equal: the clock settles where the power does.
   static constexpr int kGroups = kGroupsT;
-  static constexpr int kBufs = 4 / kGroupsT;
+  static constexpr int kStages = kGroupsT == 2 ? 5 : 4;
+  static constexpr int kBufs = 1;
   static constexpr int kThreads = 128 + 128 * kGroupsT;
-  static constexpr int kEpiBytes = 4 * BM * 128;
+  static constexpr int kEpiBytes = kGroups * kBufs * BM * 128;
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 512 + 16 * 1024 /*column vectors*/ +
                                     4096 /*squeeze-excitation gate and shift*/;
 };
