@@ -1485,8 +1485,11 @@ cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaS
   if (pair_eligible(p, sm_count))
   {
     // Four epilogue groups when a tile has few k-blocks (the epilogue then sets the pace), two otherwise (fewer
-    // warps compete with the MMA issuer and the producer).
-    const bool four = p.K <= 8 * BK && p.conv_cin == 0 && p.se_k == 0;
+    // warps compete with the MMA issuer and the producer).  With a residual input or row statistics a slab costs a
+    // residual fetch, the epilogue and a store in a row, which two groups only hide behind more than 16 k-blocks: the
+    // out-projection (16 k-blocks) went from 838 to 873 TFLOP/s at batch 1024 and from 668 to 723 at batch 256 on four.
+    const bool heavy = p.res != nullptr || p.out_stats != nullptr;
+    const bool four = p.conv_cin == 0 && p.se_k == 0 && (p.K <= 8 * BK || (heavy && p.K <= 16 * BK));
     return four ? launch_pair<T, 4>(p, status, sm_count, s) : launch_pair<T, 2>(p, status, sm_count, s);
   }
   if (p.se_k > 0) return launch_bn<T, 256>(p, status, sm_count, s);  // the tile must hold every channel of two boards
