@@ -91,7 +91,12 @@ enum {
    * kernel and the LayerNorms are launched so that a kernel's prologue (barrier set-up, tensor-memory allocation,
    * descriptor prefetch) runs under the tail of the kernel before it; each waits for its predecessors' results
    * (griddepcontrol.wait) before its first global-memory access. */
-  B200_FLAG_NO_DEPENDENT_LAUNCH = 256
+  B200_FLAG_NO_DEPENDENT_LAUNCH = 256,
+  /* One launch per convolution instead of the tower kernel.  By default a residual tower of at most 128 filters whose
+   * blocks all carry a squeeze-excitation unit runs, in fp16 / bf16 and for batches up to a few hundred positions, as
+   * ONE launch: a CTA owns two boards and walks the input convolution and every block for them (a convolution and the
+   * squeeze-excitation unit only mix squares of one board), waiting only for its own stores between layers. */
+  B200_FLAG_NO_TOWER_KERNEL = 512
 };
 
 typedef struct b200_net_info {

@@ -23,6 +23,7 @@ FLAG_NO_FUSED_SE = 32
 FLAG_WINOGRAD = 64
 FLAG_NO_SIDE_STREAM = 128
 FLAG_NO_DEPENDENT_LAUNCH = 256
+FLAG_NO_TOWER_KERNEL = 512
 POLICY_SIZE = 1858
 INPUT_PLANES = 112
 

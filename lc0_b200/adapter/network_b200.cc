@@ -228,7 +228,8 @@ b200_net_options MakeNetOptions(const OptionsDict& options, int precision) {
               (options.GetOrDefault<bool>("fused_se", true) ? 0 : B200_FLAG_NO_FUSED_SE) |
               (options.GetOrDefault<bool>("winograd", false) ? B200_FLAG_WINOGRAD : 0) |
               (options.GetOrDefault<bool>("side_stream", true) ? 0 : B200_FLAG_NO_SIDE_STREAM) |
-              (options.GetOrDefault<bool>("dependent_launch", true) ? 0 : B200_FLAG_NO_DEPENDENT_LAUNCH);
+              (options.GetOrDefault<bool>("dependent_launch", true) ? 0 : B200_FLAG_NO_DEPENDENT_LAUNCH) |
+              (options.GetOrDefault<bool>("tower", true) ? 0 : B200_FLAG_NO_TOWER_KERNEL);
   return opt;
 }
 

@@ -19,6 +19,7 @@
 
 #include <atomic>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -123,6 +124,8 @@ __device__ __forceinline__ void tma_store_wait_read1() {
 __device__ __forceinline__ void tma_store_wait_read0() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+__device__ __forceinline__ void tma_store_wait_all0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -350,11 +353,15 @@ __device__ __forceinline__ void load_col_regs(const TcParams& p, int nb, int lan
   }
 }
 
-template <typename T, bool kSe = false>
+// kMixed (the tower kernel, whose tiles alternate between layers with and without a residual input): the store thread
+// arrives on `free_bar` after every store and the group always waits for it; a slab with a residual also waits for
+// `res_bar`, whose phase is counted by `res_use` (the number of residual tiles this staging buffer has received).
+template <typename T, bool kSe = false, bool kMixed = false>
 __device__ __forceinline__ void epilogue_slab(const TcParams& p, uint8_t* buf, uint32_t res_bar, uint32_t free_bar,
                                               uint32_t full_bar, uint32_t use, bool leader, uint32_t taddr, int row,
                                               int lane, int nb, int next_nb, ColRegs& cr, float* wvec, RowCtx& rc,
-                                              volatile int* abort_flag, const float* se_arg = nullptr) {
+                                              volatile int* abort_flag, const float* se_arg = nullptr,
+                                              uint32_t res_use = 0) {
   const float* se = kSe ? se_arg : nullptr;  // compiled out of the kernels that never fuse squeeze-excitation
   // se != nullptr: gate (se[0..63]) and shift (se[256..319]) of this row's sample for the slab's 64 columns; the
   // activation then follows the residual: act(gate * v + shift + residual)   (se_unit.cc:54-61)
@@ -415,8 +422,13 @@ __device__ __forceinline__ void epilogue_slab(const TcParams& p, uint8_t* buf, u
       // Every thread does its own bounded wait (after a failed wait the result is meaningless and the status word
       // says so): for the residual tile, which the store warp fetched into `buf` once the buffer was free, or
       // for the buffer itself.
-      if (p.res_mode) mbar_wait(res_bar, use & 1, abort_flag, 5);
-      else mbar_wait(free_bar, (use & 1) ^ 1, abort_flag, 6);
+      if (kMixed) {
+        mbar_wait(free_bar, (use & 1) ^ 1, abort_flag, 6);
+        if (p.res_mode) mbar_wait(res_bar, res_use & 1, abort_flag, 5);
+      } else {
+        if (p.res_mode) mbar_wait(res_bar, use & 1, abort_flag, 5);
+        else mbar_wait(free_bar, (use & 1) ^ 1, abort_flag, 6);
+      }
     }
     if (p.res_mode) {
 #pragma unroll
@@ -930,6 +942,318 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Tower kernel: every 3x3 convolution of a residual tower in ONE launch.  A CTA owns 128 rows = two whole boards and
+// walks the layers for them: a convolution only mixes squares of the same board, and the squeeze-excitation unit
+// only pools over a board, so a CTA never needs another CTA's output and the only dependency is its own: the A
+// operand of layer l (and its skip input) are rows this CTA stored for an earlier layer.  The store thread waits for
+// those stores to complete (cp.async.bulk.wait_group 0) and arrives on a shared-memory barrier that the producer
+// waits on before it loads the next layer's A tiles; nothing is waited for across CTAs.  What it removes is the fixed
+// cost of 2 x blocks + 1 launches (drain, dependency resolution, prologue, first loads: about 10 us each), which is
+// most of the evaluation of a small residual net at the batch sizes a search sends.
+//   layers: device array, one entry per convolution (tensor maps of A as boards, W as [9][N][Cin] with boxes of BN
+//           rows, C and the skip input; the epilogue parameters incl. the squeeze-excitation unit).
+// Roles and barriers are those of gemm_tc_kernel; the staging buffers follow the mixed protocol of epilogue_slab.
+// ------------------------------------------------------------------------------------------------
+struct alignas(64) TowerLayer {
+  CUtensorMap a, w, c, r;
+  TcParams p;
+};
+// Towers of at most 128 output channels: 128x128 tiles, one 64-column slab per epilogue group and tile, so one staging
+// buffer per group is enough (the next tile's epilogue is a whole main loop away) and the shared memory goes to the
+// pipeline: a CTA alone on its rows is bound by the bytes it has in flight.
+struct TowerCfg {
+  static constexpr int BN = 128;
+  static constexpr int kStageBytes = (BM + BN) * BK * 2;  // 32 KB
+  static constexpr int kStages = 4;  // five leave L1 too small for the squeeze-excitation prefetch (measured slower)
+  static constexpr int kBufs = 1;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kEpiBytes = 2 * kBufs * BM * 128;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 512 /*barriers*/ +
+                                    8192 /*per-warp column vectors*/ + 4096 /*squeeze-excitation gate and shift*/;
+};
+
+// The tiles of one CTA in the order it computes them.  With more row blocks than CTAs (gridDim.x * 2 <= row blocks
+// + 1) a CTA takes its blocks two at a time and, for such a pair, goes layer by layer, alternating between the two
+// blocks: a tile then depends on the tile before the previous one, so the wait for a block's stores and for the next
+// layer's first loads falls under the other block's main loop (9.3 us per tile against 13.8; measured on a tower of 128
+// filters).  With fewer blocks each CTA has one: all layers of a block take 21 x 13.8 us, of a pair 21 x 18.5 us.
+struct TowerWalk {
+  int n_layers, first, step, nb;  // nb: row blocks of this CTA
+  int i0 = 0, l = 0, j = 0;       // index of the pair's first block among the CTA's blocks, layer, block of the pair
+  __device__ TowerWalk(int n_layers_, int row_blocks) : n_layers(n_layers_), first(blockIdx.x), step(gridDim.x) {
+    nb = first < row_blocks ? (row_blocks - first + step - 1) / step : 0;
+  }
+  __device__ bool valid() const { return i0 < nb; }
+  __device__ int rb() const { return first + (i0 + j) * step; }
+  __device__ int cnt() const { return nb - i0 >= 2 ? 2 : 1; }  // a CTA with one block (grid = row blocks) never pairs
+  __device__ void next() {
+    if (++j >= cnt()) {
+      j = 0;
+      if (++l >= n_layers) { l = 0; i0 += 2; }
+    }
+  }
+};
+
+// Store thread: writes the slabs of this CTA's tiles out in order (two groups, kBufs staging buffers each), counts a
+// tile as complete when its stores have landed, and then fetches the skip input of the next tile's slabs into the
+// buffers those slabs will use (all are free at that point, and the rows it reads were completed two tiles ago).
+__device__ __forceinline__ void tower_store_loop(const TowerLayer* layers, int n_layers, int row_blocks, uint8_t* epi_mem,
+                                                 uint64_t* stg_full, uint64_t* stg_free, uint64_t* res_bar,
+                                                 uint64_t* done_bar, volatile int* abort_flag) {
+  constexpr int BN = TowerCfg::BN, kBufs = TowerCfg::kBufs;
+  uint32_t count[2] = {0, 0};  // slabs stored per group
+  auto fetch_tile = [&](int rb, int l) {  // skip input of tile (rb, l), slab by slab, into the buffers they will use
+    const TowerLayer& L = layers[l];
+    if (!L.p.res_mode) return;
+    uint32_t k[2] = {count[0], count[1]};
+    for (int c0 = 0; c0 < BN && c0 < L.p.N; c0 += 64) {
+      const int g = (c0 >> 6) & 1;
+      const int idx = g * kBufs + (int)(k[g]++ % kBufs);
+      const uint32_t bar = smem_u32(&res_bar[idx]);
+      mbar_expect_tx(bar, BM * 128);
+      tma_load_2d(smem_u32(epi_mem + idx * (BM * 128)), &L.r, c0, rb * BM, bar);
+    }
+  };
+  bool ok = true;
+  for (TowerWalk w(n_layers, row_blocks); w.valid() && ok; w.next()) {
+    const TowerLayer& L = layers[w.l];
+    const int rb = w.rb();
+    for (int c0 = 0; c0 < BN && c0 < L.p.N; c0 += 64) {
+      const int g = (c0 >> 6) & 1;
+      const uint32_t k = count[g]++;
+      const int idx = g * kBufs + (int)(k % kBufs);
+      if (!mbar_wait(smem_u32(&stg_full[idx]), (k / kBufs) & 1, abort_flag, 7)) { ok = false; break; }
+      tma_store_2d(&L.c, c0, rb * BM, smem_u32(epi_mem + idx * (BM * 128)));
+      tma_store_commit();
+      tma_store_wait_read0();
+      mbar_arrive(smem_u32(&stg_free[idx]));
+    }
+    if (!ok) break;
+    tma_store_wait_all0();    // the tile's rows are in memory
+    fence_proxy_async_all();  // ... before the loads of the block's next layer, which the producer issues after the arrival
+    mbar_arrive(smem_u32(&done_bar[w.j]));
+    TowerWalk nx = w;
+    nx.next();
+    if (nx.valid()) fetch_tile(nx.rb(), nx.l);  // its source is that block's output of two layers ago
+  }
+  tma_store_wait_read0();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_tower_kernel(const TowerLayer* __restrict__ layers, int n_layers, int row_blocks, int* status) {
+  using Cfg = TowerCfg;
+  constexpr int S = Cfg::kStages, BN = Cfg::BN, kBufs = Cfg::kBufs;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi_mem = smem + S * Cfg::kStageBytes;
+  uint8_t* bar_mem = epi_mem + Cfg::kEpiBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_mem);       // [S]
+  uint64_t* empty_bar = full_bar + S;                               // [S]
+  uint64_t* tfull_bar = empty_bar + S;                              // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;                             // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* res_bar = reinterpret_cast<uint64_t*>(bar_mem + 192);   // [2 groups][2 buffers] skip tile landed
+  uint64_t* stg_full = reinterpret_cast<uint64_t*>(bar_mem + 256);  // [2 groups][2 buffers] slab staged (4 warps)
+  uint64_t* stg_free = stg_full + 4;                                // [2 groups][2 buffers] store has read the buffer
+  uint64_t* se_bar = reinterpret_cast<uint64_t*>(bar_mem + 384);    // barrier of the 256 epilogue threads
+  uint64_t* done_bar = se_bar + 1;                                  // [2] the latest tile of block 0 / 1 of the pair is in memory
+  float* wvec_all = reinterpret_cast<float*>(bar_mem + 512);        // 8 warps x 256 floats
+  float* wvec = wvec_all + ((threadIdx.x >> 5) & 7) * 256;
+  float* se_gb = reinterpret_cast<float*>(bar_mem + 512 + 8192);    // [2 boards][gate 256 | shift 256]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 32) {
+    for (int l = 0; l < n_layers; ++l) {
+      tma_prefetch_map(&layers[l].a);
+      tma_prefetch_map(&layers[l].w);
+      tma_prefetch_map(&layers[l].c);
+      if (layers[l].p.res_mode) tma_prefetch_map(&layers[l].r);
+    }
+  }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(smem_u32(&full_bar[i]), 1);
+      mbar_init(smem_u32(&empty_bar[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&tfull_bar[i]), 1);
+      mbar_init(smem_u32(&tempty_bar[i]), 8);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(smem_u32(&res_bar[i]), 1);
+      mbar_init(smem_u32(&stg_full[i]), 4);
+      mbar_init(smem_u32(&stg_free[i]), 1);
+    }
+    mbar_init(smem_u32(se_bar), 256);
+    mbar_init(smem_u32(&done_bar[0]), 1);
+    mbar_init(smem_u32(&done_bar[1]), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)Cfg::kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  grid_dependency_wait();
+  grid_launch_dependents();
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t it = 0, nslot[2] = {0, 0};  // nslot: tiles issued per block of the pair
+      bool ok = true;
+      for (TowerWalk w(n_layers, row_blocks); w.valid() && ok; w.next()) {
+        const TowerLayer& L = layers[w.l];
+        const int rb = w.rb();
+        const int cblocks = L.p.conv_cblocks, k_blocks = 9 * cblocks, N = L.p.N;
+        // The filters do not depend on this CTA's earlier output: those of the first stages are requested before
+        // the wait for it.
+        const int early = k_blocks < S ? k_blocks : S;
+        for (int kb = 0; kb < early && ok; ++kb) {
+          const int s = (it + kb) % S;
+          const uint32_t ph = ((it + kb) / S) & 1;
+          if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, 1)) { ok = false; break; }
+          const uint32_t fb = smem_u32(&full_bar[s]);
+          mbar_expect_tx(fb, Cfg::kStageBytes);
+          const int tap = kb / cblocks, cb = kb - tap * cblocks;
+          tma_load_2d(smem_u32(smem + s * Cfg::kStageBytes) + BM * BK * 2, &L.w, cb * BK, tap * N, fb);
+        }
+        if (!ok) break;
+        const uint32_t nth = nslot[w.j]++;
+        if (w.l > 0) {  // the block's previous layer (the first layer reads what was complete before the launch)
+          if (!mbar_wait(smem_u32(&done_bar[w.j]), (nth - 1) & 1, abort_flag, 9)) break;
+          fence_proxy_async_all();
+        }
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t fb = smem_u32(&full_bar[s]);
+          const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
+          const int tap = kb / cblocks, cb = kb - tap * cblocks;
+          if (kb >= early) {
+            const uint32_t ph = (it / S) & 1;
+            if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag, 1)) { ok = false; break; }
+            mbar_expect_tx(fb, Cfg::kStageBytes);
+            tma_load_2d(sa + BM * BK * 2, &L.w, cb * BK, tap * N, fb);
+          }
+          tma_load_4d(sa, &L.a, cb * BK, tap % 3 - 1, tap / 3 - 1, rb * 2, fb);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc<T, BN>();
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (TowerWalk w(n_layers, row_blocks); w.valid() && ok; w.next(), ++tile_it) {
+        const int k_blocks = 9 * layers[w.l].p.conv_cblocks;
+        const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
+        if (!mbar_wait(smem_u32(&tempty_bar[acc]), aph ^ 1, abort_flag, 2)) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, 3)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
+          const uint64_t adesc = make_smem_desc(sa);
+          const uint64_t bdesc = make_smem_desc(sa + BM * BK * 2);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            tcgen05_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          tcgen05_commit(smem_u32(&empty_bar[s]));
+        }
+        if (ok) tcgen05_commit(smem_u32(&tfull_bar[acc]));
+      }
+    }
+  } else if (warp == 10) {
+    // ---------------- store warp ----------------
+    if (lane == 0)
+      tower_store_loop(layers, n_layers, row_blocks, epi_mem, stg_full, stg_free, res_bar, done_bar, abort_flag);
+  } else {
+    // ---------------- epilogue (warps 2..9: two groups of four warps, alternating 64-column slabs) ----------------
+    const int quarter = warp & 3;
+    const int group = (warp - 2) >> 2;
+    const bool leader = ((warp - 2) & 3) == 0 && lane == 0;
+    uint8_t* gbuf = epi_mem + group * (kBufs * BM * 128);
+    uint32_t tile_it = 0, slab_it = 0, se_phase = 0;
+    uint32_t res_use0 = 0, res_use1 = 0;  // skip tiles each of the group's two staging buffers has received
+    ColRegs cr;
+    {
+      for (TowerWalk w(n_layers, row_blocks); w.valid(); w.next(), ++tile_it) {
+        const TcParams& P = layers[w.l].p;
+        const int rb = w.rb();
+        const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
+        if (group * 64 < P.N) load_col_regs(P, group * 64, lane, cr);  // in flight while the tile is computed
+        if (P.se_k > 0) {
+          // the squeeze-excitation weights of this layer towards L1 while the tile is computed (one 128-byte line per
+          // thread and matrix); se_prepare then reads them with two dependent passes of short latency
+          const int eid = (int)threadIdx.x - 64;
+          const int l1 = P.se_k * P.N / 32, l2 = 2 * l1;  // lines of se_w1, se_w2
+          if (eid < l1) asm volatile("prefetch.global.L1 [%0];" ::"l"(P.se_w1 + eid * 32));
+          for (int i = eid; i < l2; i += 256) asm volatile("prefetch.global.L1 [%0];" ::"l"(P.se_w2 + i * 32));
+        }
+        if (!mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4)) break;
+        tcgen05_fence_after();
+        const int m = rb * BM + quarter * 32 + lane;
+        const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+        RowCtx rc;
+        load_row_ctx(P, m, rc);
+        const float* se_row = nullptr;
+        if (P.se_k > 0) {
+          se_prepare<BN>(P, trow, quarter, group, lane, (int)threadIdx.x - 64, wvec_all, se_gb, smem_u32(se_bar), se_phase,
+                         abort_flag);
+          se_row = se_gb + (quarter >> 1) * 512;
+        }
+#pragma unroll 1
+        for (int c0 = group * 64; c0 < BN; c0 += 128) {
+          if (c0 >= P.N) break;  // uniform over the group
+          const int b = (int)(slab_it % kBufs);
+          const int idx = group * kBufs + b;
+          const int next_nb = (c0 + 128 < BN && c0 + 128 < P.N) ? c0 + 128 : -1;
+          epilogue_slab<T, true, true>(P, gbuf + b * (BM * 128), smem_u32(&res_bar[idx]), smem_u32(&stg_free[idx]),
+                                       smem_u32(&stg_full[idx]), slab_it / kBufs, leader, trow + c0, quarter * 32 + lane, lane,
+                                       c0, next_nb, cr, wvec, rc, abort_flag, se_row ? se_row + c0 : nullptr,
+                                       b ? res_use1 : res_use0);
+          if (P.res_mode) {
+            if (b) ++res_use1; else ++res_use0;
+          }
+          ++slab_it;
+        }
+        flush_row_ctx(P, m, rc);
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+      }
+    }
+  }
+
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    if (threadIdx.x == 0 && status) atomicCAS(status, 0, 400 + *abort_flag);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)Cfg::kTmemCols)
+                 : "memory");
+  }
+}
 
 // ------------------------------------------------------------------------------------------------
 // CTA-pair variant: a cluster of two CTAs (one TPC) computes a 256x256 tile with
@@ -1476,6 +1800,85 @@ bool gemm_tc_split_supported(const GemmParams& p, int sm_count) {
          p.N > p.n_split && p.N - p.n_split <= 256 && p.C2 && (p.ldc2 % 8) == 0 &&
          (reinterpret_cast<uintptr_t>(p.C2) & 15) == 0 && !p.res && !p.out_stats && !p.skip;
 }
+
+// ---- tower kernel, host side ----
+size_t gemm_tc_tower_layer_bytes() { return sizeof(TowerLayer); }
+
+bool gemm_tc_tower_supported(const GemmParams* g, int n) {
+  if (n < 2) return false;
+  for (int i = 0; i < n; ++i) {
+    const GemmParams& p = g[i];
+    const bool tma_ok = !p.out_f32 && (p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
+    if (p.conv_cin <= 0 || !gemm_tc_supported(p) || !tma_ok || p.skip || p.n_split > 0 || p.batch_rows > 0 || p.a_stats ||
+        p.out_stats || p.res_stats)
+      return false;
+    if (p.M != g[0].M || p.N != g[0].N || p.N > TowerCfg::BN || (p.N % 64) != 0) return false;
+    if (p.se_k > 0 && !gemm_tc_se_supported(p)) return false;
+    if (p.res && ((p.ldres % 8) != 0 || (reinterpret_cast<uintptr_t>(p.res) & 15) != 0)) return false;
+    // a layer reads what an earlier layer of the same CTA wrote, or something complete before the launch; the skip
+    // input must be at least two layers old (it is fetched while the layer before is still being computed)
+    if (i > 0 && p.res && p.res == g[i - 1].C) return false;
+  }
+  return true;
+}
+
+// Fills `host_layers` (n entries of gemm_tc_tower_layer_bytes() each) for a later launch; the caller copies them to
+// the device.  The descriptors cover the buffers' full extent (M rows), so one table serves every batch size: a launch
+// only walks the row blocks it is given.
+template <typename T>
+cudaError_t gemm_tc_tower_build(const GemmParams* g, int n, int* status, void* host_layers) {
+  if (!gemm_tc_tower_supported(g, n)) return cudaErrorInvalidValue;
+  const int prec = TypeTag<T>::prec;
+  const int bn = TowerCfg::BN;
+  TowerLayer* out = static_cast<TowerLayer*>(host_layers);
+  for (int i = 0; i < n; ++i) {
+    const GemmParams& q = g[i];
+    TowerLayer& L = out[i];
+    memset(&L, 0, sizeof(L));
+    cudaError_t e = make_board_map(q.A, q.conv_cin, q.M / 64, prec, &L.a);
+    if (e != cudaSuccess) return e;
+    if ((e = get_map(q.W, q.conv_cin, 9 * q.N, q.conv_cin, bn, prec, &L.w)) != cudaSuccess) return e;
+    if ((e = get_map(q.C, q.ldc, q.M, q.N, BM, prec, &L.c)) != cudaSuccess) return e;
+    L.r = L.c;
+    if (q.res && (e = get_map(q.res, q.ldres, q.M, q.N, BM, prec, &L.r)) != cudaSuccess) return e;
+    TcParams& p = L.p;
+    fill_folded(p, q);
+    p.tma_store = 1;
+    p.split_from = 0x7fffffff; p.tiles_v = 0;
+    p.bias = q.bias; p.C = q.C; p.ldc = q.ldc;
+    p.M = q.M; p.N = q.N; p.K = q.K; p.act = q.act; p.scale = q.scale; p.alpha = q.alpha;
+    p.out_f32 = 0; p.status = status;
+    p.conv_cblocks = ceil_div(q.conv_cin, BK);
+  }
+  return cudaSuccess;
+}
+template cudaError_t gemm_tc_tower_build<__half>(const GemmParams*, int, int*, void*);
+template cudaError_t gemm_tc_tower_build<__nv_bfloat16>(const GemmParams*, int, int*, void*);
+
+// One launch for `n_layers` convolutions over the first `row_blocks` blocks of 128 rows (two boards).
+template <typename T>
+cudaError_t launch_gemm_tower(const void* d_layers, int n_layers, int channels, int row_blocks, int* status, int sm_count,
+                              cudaStream_t s) {
+  if (row_blocks <= 0) return cudaSuccess;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  // one row block per CTA while there are SMs for that, two at a time beyond (see TowerWalk)
+  const int want = row_blocks <= sm_count ? row_blocks : (row_blocks + 1) / 2;
+  const int grid = want < sm_count ? want : sm_count;
+  const TowerLayer* layers = static_cast<const TowerLayer*>(d_layers);
+  if (channels > TowerCfg::BN) return cudaErrorInvalidValue;
+  static std::atomic<unsigned long long> mask{0};
+  if (!(mask.load() >> (dev & 63) & 1ull)) {
+    e = cudaFuncSetAttribute(gemm_tc_tower_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, TowerCfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    mask.fetch_or(1ull << (dev & 63));
+  }
+  return launch_dependent(gemm_tc_tower_kernel<T>, dim3(grid), dim3(kThreads), TowerCfg::kSmemBytes, s, layers, n_layers,
+                          row_blocks, status);
+}
+template cudaError_t launch_gemm_tower<__half>(const void*, int, int, int, int*, int, cudaStream_t);
+template cudaError_t launch_gemm_tower<__nv_bfloat16>(const void*, int, int, int, int*, int, cudaStream_t);
 
 template <typename T>
 cudaError_t launch_gemm_tc(const GemmParams& p, int* status, int sm_count, cudaStream_t s) {

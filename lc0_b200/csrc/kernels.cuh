@@ -70,6 +70,16 @@ bool gemm_tc_supported(const GemmParams& p);
 bool gemm_tc_se_supported(const GemmParams& p);
 // Whether launch_gemm_tc would run `p` (with C2 / n_split set) on the CTA-pair kernel, the only one that splits.
 bool gemm_tc_split_supported(const GemmParams& p, int sm_count);
+// Tower kernel (gemm_tc.cu): the 3x3 convolutions of a residual tower (conv_cin > 0, optional fused squeeze-excitation
+// and skip input), all with the same rows and output channels (at most 256), in one launch.  gemm_tc_tower_build fills
+// a host table of n entries of gemm_tc_tower_layer_bytes() bytes, which the caller copies to the device once;
+// launch_gemm_tower runs the first `row_blocks` blocks of 128 rows (two boards) through all layers.
+bool gemm_tc_tower_supported(const GemmParams* g, int n);
+size_t gemm_tc_tower_layer_bytes();
+template <typename T> cudaError_t gemm_tc_tower_build(const GemmParams* g, int n, int* status, void* host_layers);
+template <typename T>
+cudaError_t launch_gemm_tower(const void* d_layers, int n_layers, int channels, int row_blocks, int* status, int sm_count,
+                              cudaStream_t s);
 cudaError_t gemm_tc_init();  // resolves the driver entry point used to encode TMA descriptors
 // TMA descriptor over a row-major 16-bit matrix [rows][cols] with leading dimension ld (elements), box
 // box_cols x box_rows, shared-memory swizzle of 64 or 128 bytes (= box_cols * 2); `out` is a CUtensorMap.

@@ -424,6 +424,8 @@ struct Net : NetBase {
   // throughput-bound
   bool side_stream = false;
   bool dependent_launch = false;  // tensor-core products, attention and LayerNorms launched with launch_dependent()
+  bool tower = false;             // residual towers: all 3x3 convolutions in one launch up to tower_max_batch positions
+  int tower_max_batch = 0;
   static constexpr int kSideSms = 8;
 
   // format
@@ -466,6 +468,8 @@ struct Net : NetBase {
     int* h_status = nullptr;             // pinned copy of the device status word, refreshed by every evaluation
     uint64_t* d_masks = nullptr;
     float *d_values = nullptr, *d_policy = nullptr, *d_qdm = nullptr;
+    void* tower_layers = nullptr;  // device table of the tower kernel (one entry per convolution), or null
+    int tower_n = 0;
     unsigned short* d_move_ids = nullptr;
     int* d_n_moves = nullptr;
     float* d_probs = nullptr;
@@ -760,6 +764,8 @@ struct Net : NetBase {
     winograd = use_tc && !attn_body && (opt.flags & B200_FLAG_WINOGRAD);
     side_stream = use_tc && attn_body && !(opt.flags & B200_FLAG_NO_SIDE_STREAM) && sm_count >= 4 * kSideSms;
     dependent_launch = use_tc && !(opt.flags & B200_FLAG_NO_DEPENDENT_LAUNCH);
+    tower = use_tc && !attn_body && !(opt.flags & B200_FLAG_NO_TOWER_KERNEL) && !(opt.flags & B200_FLAG_NO_FUSED_SE) &&
+            !(opt.flags & B200_FLAG_WINOGRAD);
     fold_ln = use_tc && attn_body && !(opt.flags & B200_FLAG_NO_LN_FOLD);
     // Folding needs every product that consumes or produces a folded LayerNorm to be eligible for the tensor-core
     // kernel's TMA epilogue: output widths that are multiples of 8.
@@ -984,6 +990,7 @@ struct Net : NetBase {
     }
 
     alloc_slots();
+    build_towers();
     // The uploads above are copies from pageable memory and the slots' streams are non-blocking: everything must have
     // landed before the first evaluation is enqueued.
     CK(cudaDeviceSynchronize());
@@ -1206,12 +1213,58 @@ struct Net : NetBase {
     }
     return false;
   }
+  static GemmParams conv_params(const T* x, const ConvW<T>& c, const float* bias, T* y, int n, int act) {
+    GemmParams p;
+    p.A = x; p.W = c.w; p.bias = bias; p.C = y; p.ldc = c.cout; p.M = n * 64; p.N = c.cout; p.K = 9 * c.cin;
+    p.act = act; p.conv_cin = c.cin; p.lda = c.cin; p.ldw = c.cin;
+    return p;
+  }
+  GemmParams conv_se_params(const T* x, const ResidualW<T>& r, const T* skip, T* y, int n) const {
+    const ConvW<T>& c = r.c2;
+    GemmParams p = conv_params(x, c, nullptr, y, n, act_default);
+    p.res = skip; p.ldres = c.cout;
+    p.se_w1 = r.se_w1; p.se_b1 = r.se_b1; p.se_w2 = r.se_w2; p.se_b2 = r.se_b2; p.se_bias = c.b; p.se_k = r.se_k;
+    return p;
+  }
+  // Residual towers whose blocks all carry a squeeze-excitation unit: the table of the tower kernel, once per slot
+  // (its descriptors cover the buffers' full extent, so it serves every batch size).  The buffers rotate exactly as in
+  // forward().
+  void build_towers() {
+    if constexpr (sizeof(T) == 2) {
+      // Measured (evaluations per second, tower / per-layer launches): 10 blocks of 128 filters 176 100 / 161 400 at
+      // batch 64 and 670 800 / 589 000 at batch 256; 20 blocks of 256 filters 57 100 / 55 300 at batch 64 and 210 100 /
+      // 212 300 at batch 256: the wide tower stays on one launch per convolution (CTA pairs from 150 positions on).
+      if (!tower || res.empty() || C > 128) { tower = false; return; }
+      for (const auto& r : res)
+        if (!r.se) { tower = false; return; }
+      const int nb = opt.max_batch;
+      for (size_t si = 0; si < slots.size(); ++si) {
+        Slot& s = slots[si];
+        std::vector<GemmParams> g;
+        g.push_back(conv_params(s.tokens, conv_in, conv_in.b, s.x, nb, act_default));
+        T *cur = s.x, *tmp = s.x1, *tmp2 = s.y;
+        for (const auto& r : res) {
+          g.push_back(conv_params(cur, r.c1, r.c1.b, tmp, nb, act_default));
+          g.push_back(conv_se_params(tmp, r, cur, tmp2, nb));
+          std::swap(cur, tmp2);
+        }
+        if (!gemm_tc_tower_supported(g.data(), (int)g.size())) { tower = false; return; }
+        std::vector<unsigned char> host(g.size() * gemm_tc_tower_layer_bytes());
+        CK(gemm_tc_tower_build<T>(g.data(), (int)g.size(), d_status + si, host.data()));
+        s.tower_layers = salloc.alloc(host.size());
+        CK(cudaMemcpy(s.tower_layers, host.data(), host.size(), cudaMemcpyHostToDevice));
+        s.tower_n = (int)g.size();
+      }
+      // one CTA per two boards walks all layers: worth it while the launches it replaces are latency-bound
+      tower_max_batch = 16 * sm_count;
+    } else {
+      tower = false;
+    }
+  }
   void conv3(cudaStream_t st, const T* x, const ConvW<T>& c, const float* bias, T* y, int n, int act) {
     if (conv3_wino(st, x, c, bias, y, n, act)) return;
     if constexpr (sizeof(T) == 2) {
-      GemmParams p;
-      p.A = x; p.W = c.w; p.bias = bias; p.C = y; p.ldc = c.cout; p.M = n * 64; p.N = c.cout; p.K = 9 * c.cin;
-      p.act = act; p.conv_cin = c.cin; p.lda = c.cin; p.ldw = c.cin;
+      GemmParams p = conv_params(x, c, bias, y, n, act);
       if (use_tc && (c.cout % 8) == 0 && gemm_tc_supported(p)) {
         launches++;
         const int sp_ = span_begin(st, K_GEMM_TC, 2.0 * p.M * (double)p.N * p.K);
@@ -1230,12 +1283,7 @@ struct Net : NetBase {
   bool conv3_se(cudaStream_t st, const T* x, const ResidualW<T>& r, const T* skip, T* y, int n) {
     if constexpr (sizeof(T) == 2) {
       if (!use_tc || (opt.flags & B200_FLAG_NO_FUSED_SE)) return false;
-      const ConvW<T>& c = r.c2;
-      GemmParams p;
-      p.A = x; p.W = c.w; p.C = y; p.ldc = c.cout; p.M = n * 64; p.N = c.cout; p.K = 9 * c.cin;
-      p.act = act_default; p.conv_cin = c.cin; p.lda = c.cin; p.ldw = c.cin;
-      p.res = skip; p.ldres = c.cout;
-      p.se_w1 = r.se_w1; p.se_b1 = r.se_b1; p.se_w2 = r.se_w2; p.se_b2 = r.se_b2; p.se_bias = c.b; p.se_k = r.se_k;
+      const GemmParams p = conv_se_params(x, r, skip, y, n);
       if (!gemm_tc_supported(p) || !gemm_tc_se_supported(p)) return false;
       launches++;
       const int sp_ = span_begin(st, K_GEMM_TC, 2.0 * p.M * (double)p.N * p.K);
@@ -1416,9 +1464,24 @@ struct Net : NetBase {
       other(st, (double)R * 112 * sizeof(T), [&] {
         return launch_expand_tokens<T>(d_masks, d_values, n, nullptr, (const T*)nullptr, 0, 112, s.tokens, st);
       });
-      conv3(st, s.tokens, conv_in, conv_in.b, s.x, n, act_default);
       T *cur = s.x, *tmp = s.x1, *tmp2 = s.y;
+      bool in_one = false;
+      if constexpr (sizeof(T) == 2) {
+        if (tower && s.tower_layers && n <= tower_max_batch) {
+          // input convolution and every block of the tower in one launch (gemm_tc.cu, tower kernel)
+          launches++;
+          double flops = 2.0 * R * (double)C * 9 * 112;
+          for (const auto& r : res) flops += 2.0 * R * (double)C * 9 * (r.c1.cin + r.c2.cin);
+          const int sp_ = span_begin(st, K_GEMM_TC, flops);
+          CK(launch_gemm_tower<T>(s.tower_layers, s.tower_n, C, (n + 1) / 2, t_status, sm_count, st));
+          span_end(st, sp_);
+          if (res.size() & 1) cur = s.y;  // the blocks' outputs alternate between y and x
+          in_one = true;
+        }
+      }
+      if (!in_one) conv3(st, s.tokens, conv_in, conv_in.b, s.x, n, act_default);
       for (const auto& r : res) {
+        if (in_one) break;
         conv3(st, cur, r.c1, r.c1.b, tmp, n, act_default);
         if (winograd && conv3_wino(st, tmp, r.c2, r.c2.b, tmp2, n, act_default, cur, r.se ? &r : nullptr)) {
           std::swap(cur, tmp2);  // output transform with SE / skip / activation

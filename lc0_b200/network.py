@@ -16,7 +16,7 @@ from . import _lib, netproto, weights as _weights
 
 _KNOWN_OPTIONS = {"gpu", "max_batch", "precision", "slots", "mlh", "policy_head", "value_head",
                   "tensor_cores", "graph_capture", "fold_ln", "merge_compress", "split_last_wave", "fused_se", "winograd",
-                  "side_stream", "dependent_launch"}
+                  "side_stream", "dependent_launch", "tower"}
 
 
 def parse_options(opts):
@@ -53,6 +53,8 @@ def option_flags(opts):
             flags |= bit
     if _as_bool(opts.get("winograd", False)):
         flags |= _lib.FLAG_WINOGRAD
+    if not _as_bool(opts.get("tower", True)):
+        flags |= _lib.FLAG_NO_TOWER_KERNEL
     return flags
 
 
