@@ -515,7 +515,16 @@ __device__ __forceinline__ void epilogue_barrier(uint32_t bar, uint32_t& phase, 
 template <int BN>
 __device__ __forceinline__ void se_prepare(const TcParams& p, uint32_t trow, int quarter, int group, int lane, int eid,
                                            float* tmp, float* gb, uint32_t bar, uint32_t& phase,
-                                           volatile int* abort_flag) {
+                                           volatile int* abort_flag, const float* w_smem = nullptr) {
+  // w_smem: se_w1 [se_k][C], se_w2 [2C][se_k], se_bias [C], se_b1 [se_k], se_b2 [2C] in shared memory, copied there
+  // while the tile was computed; otherwise they are read from global memory (a chain of five dependent round trips)
+  const float* g_w1 = w_smem ? w_smem : p.se_w1;
+  const float* g_w2 = w_smem ? g_w1 + p.se_k * p.N : p.se_w2;
+  const float* g_bias = w_smem ? g_w2 + 2 * p.N * p.se_k : p.se_bias;
+  const float* g_b1 = w_smem ? g_bias + p.N : p.se_b1;
+  const float* g_b2 = w_smem ? g_b1 + p.se_k : p.se_b2;
+  auto ld = [&](const float* q) { return w_smem ? *q : __ldg(q); };
+  auto ld4 = [&](const float4* q) { return w_smem ? *q : __ldg(q); };
   float* part = tmp;          // [4 quarters][256] column sums over 32 rows
   float* pool = tmp + 1024;   // [2][256]
   float* hid = tmp + 1536;    // [2][64]
@@ -538,7 +547,7 @@ __device__ __forceinline__ void se_prepare(const TcParams& p, uint32_t trow, int
   epilogue_barrier(bar, phase, abort_flag);
   {
     const int c = eid;  // 256 threads, one channel each
-    const float b = c < C ? __ldg(p.se_bias + c) : 0.f;
+    const float b = c < C ? ld(g_bias + c) : 0.f;
     pool[c] = (part[c] + part[256 + c]) * (1.0f / 64.0f) + b;
     pool[256 + c] = (part[512 + c] + part[768 + c]) * (1.0f / 64.0f) + b;
   }
@@ -549,35 +558,35 @@ __device__ __forceinline__ void se_prepare(const TcParams& p, uint32_t trow, int
   for (int o = eid >> 2; o < 2 * p.se_k; o += 64) {
     const int sidx = o / p.se_k, k = o - sidx * p.se_k;
     const int cq = (eid & 3) * (C >> 2);
-    const float4* w = reinterpret_cast<const float4*>(p.se_w1 + (long long)k * C + cq);
+    const float4* w = reinterpret_cast<const float4*>(g_w1 + (long long)k * C + cq);
     const float4* x = reinterpret_cast<const float4*>(pool + sidx * 256 + cq);
     float a = 0.f;
 #pragma unroll 8
     for (int i = 0; i < (C >> 4); ++i) {
-      const float4 wv = __ldg(w + i), xv = x[i];
+      const float4 wv = ld4(w + i), xv = x[i];
       a = fmaf(wv.x, xv.x, fmaf(wv.y, xv.y, fmaf(wv.z, xv.z, fmaf(wv.w, xv.w, a))));
     }
     a += __shfl_xor_sync(0xffffffffu, a, 1);
     a += __shfl_xor_sync(0xffffffffu, a, 2);
-    if ((eid & 3) == 0) hid[sidx * 64 + k] = activate<false>(a + __ldg(p.se_b1 + k), p.act);
+    if ((eid & 3) == 0) hid[sidx * 64 + k] = activate<false>(a + ld(g_b1 + k), p.act);
   }
   epilogue_barrier(bar, phase, abort_flag);
   if (eid < C) {
     const int c = eid;
-    float z0a = __ldg(p.se_b2 + c), z1a = __ldg(p.se_b2 + C + c), z0b = z0a, z1b = z1a;
-    const float4* w0 = reinterpret_cast<const float4*>(p.se_w2 + (long long)c * p.se_k);
-    const float4* w1 = reinterpret_cast<const float4*>(p.se_w2 + (long long)(C + c) * p.se_k);
+    float z0a = ld(g_b2 + c), z1a = ld(g_b2 + C + c), z0b = z0a, z1b = z1a;
+    const float4* w0 = reinterpret_cast<const float4*>(g_w2 + (long long)c * p.se_k);
+    const float4* w1 = reinterpret_cast<const float4*>(g_w2 + (long long)(C + c) * p.se_k);
     const float4* ha = reinterpret_cast<const float4*>(hid);
     const float4* hb = reinterpret_cast<const float4*>(hid + 64);
 #pragma unroll 8
     for (int k = 0; k < (p.se_k >> 2); ++k) {
-      const float4 a = __ldg(w0 + k), b = __ldg(w1 + k), xa = ha[k], xb = hb[k];
+      const float4 a = ld4(w0 + k), b = ld4(w1 + k), xa = ha[k], xb = hb[k];
       z0a = fmaf(a.x, xa.x, fmaf(a.y, xa.y, fmaf(a.z, xa.z, fmaf(a.w, xa.w, z0a))));
       z1a = fmaf(b.x, xa.x, fmaf(b.y, xa.y, fmaf(b.z, xa.z, fmaf(b.w, xa.w, z1a))));
       z0b = fmaf(a.x, xb.x, fmaf(a.y, xb.y, fmaf(a.z, xb.z, fmaf(a.w, xb.w, z0b))));
       z1b = fmaf(b.x, xb.x, fmaf(b.y, xb.y, fmaf(b.z, xb.z, fmaf(b.w, xb.w, z1b))));
     }
-    const float cb = __ldg(p.se_bias + c);
+    const float cb = ld(g_bias + c);
     const float ga = 1.0f / (1.0f + expf(-z0a)), gbb = 1.0f / (1.0f + expf(-z0b));
     gb[c] = ga; gb[256 + c] = z1a + ga * cb;
     gb[512 + c] = gbb; gb[768 + c] = z1b + gbb * cb;
@@ -966,12 +975,15 @@ struct alignas(64) TowerLayer {
 struct TowerCfg {
   static constexpr int BN = 128;
   static constexpr int kStageBytes = (BM + BN) * BK * 2;  // 32 KB
-  static constexpr int kStages = 4;  // five leave L1 too small for the squeeze-excitation prefetch (measured slower)
+  static constexpr int kStages = 4;  // a fifth did not pay, and its 32 KB hold the squeeze-excitation parameters
   static constexpr int kBufs = 1;
   static constexpr int kTmemCols = 2 * BN;
   static constexpr int kEpiBytes = 2 * kBufs * BM * 128;
+  // a layer's squeeze-excitation parameters: two matrices of 128 channels x 32 hidden units and three vectors (fp32)
+  static constexpr int kSeWBytes = 48 * 1024 + 2048;
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 512 /*barriers*/ +
-                                    8192 /*per-warp column vectors*/ + 4096 /*squeeze-excitation gate and shift*/;
+                                    8192 /*per-warp column vectors*/ + 4096 /*squeeze-excitation gate and shift*/ +
+                                    kSeWBytes;
 };
 
 // The tiles of one CTA in the order it computes them.  With more row blocks than CTAs (gridDim.x * 2 <= row blocks
@@ -1064,6 +1076,7 @@ gemm_tc_tower_kernel(const TowerLayer* __restrict__ layers, int n_layers, int ro
   float* wvec_all = reinterpret_cast<float*>(bar_mem + 512);        // 8 warps x 256 floats
   float* wvec = wvec_all + ((threadIdx.x >> 5) & 7) * 256;
   float* se_gb = reinterpret_cast<float*>(bar_mem + 512 + 8192);    // [2 boards][gate 256 | shift 256]
+  float* se_w = se_gb + 1024;                                       // the layer's squeeze-excitation parameters (kSeWBytes)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 32) {
@@ -1190,19 +1203,34 @@ gemm_tc_tower_kernel(const TowerLayer* __restrict__ layers, int n_layers, int ro
     uint32_t tile_it = 0, slab_it = 0, se_phase = 0;
     uint32_t res_use0 = 0, res_use1 = 0;  // skip tiles each of the group's two staging buffers has received
     ColRegs cr;
+    int se_layer = -1;  // layer whose squeeze-excitation parameters sit in shared memory
     {
       for (TowerWalk w(n_layers, row_blocks); w.valid(); w.next(), ++tile_it) {
         const TcParams& P = layers[w.l].p;
         const int rb = w.rb();
         const uint32_t acc = tile_it & 1, aph = (tile_it >> 1) & 1;
         if (group * 64 < P.N) load_col_regs(P, group * 64, lane, cr);  // in flight while the tile is computed
-        if (P.se_k > 0) {
-          // the squeeze-excitation weights of this layer towards L1 while the tile is computed (one 128-byte line per
-          // thread and matrix); se_prepare then reads them with two dependent passes of short latency
+        const bool se_in_smem = P.se_k > 0 && (12 * P.se_k * P.N + 4 * (3 * P.N + P.se_k)) <= Cfg::kSeWBytes;
+        if (se_in_smem && se_layer != w.l) {
+          // This layer's squeeze-excitation parameters into shared memory while the tile is computed: the epilogue
+          // warps are idle and all their loads are in flight at once.  se_prepare then reads shared memory where it
+          // otherwise walks a chain of dependent round trips to L2 (pooling bias, first matrix and bias, second matrix
+          // and bias: 6 us per layer at batch 64).  The previous user of the region finished behind the last barrier
+          // of its se_prepare; the first barrier of this one orders the stores below before the reads.
           const int eid = (int)threadIdx.x - 64;
-          const int l1 = P.se_k * P.N / 32, l2 = 2 * l1;  // lines of se_w1, se_w2
-          if (eid < l1) asm volatile("prefetch.global.L1 [%0];" ::"l"(P.se_w1 + eid * 32));
-          for (int i = eid; i < l2; i += 256) asm volatile("prefetch.global.L1 [%0];" ::"l"(P.se_w2 + i * 32));
+          const int n1 = P.se_k * P.N / 4, n2 = 2 * n1;  // float4 of se_w1, se_w2
+          const float4* g1 = reinterpret_cast<const float4*>(P.se_w1);
+          const float4* g2 = reinterpret_cast<const float4*>(P.se_w2);
+          float4* s1 = reinterpret_cast<float4*>(se_w);
+          float4* s2 = s1 + n1;
+          float* sv = se_w + 12 * n1;  // se_bias [N], se_b1 [se_k], se_b2 [2N]
+          for (int i = eid; i < n1; i += 256) s1[i] = __ldg(g1 + i);
+#pragma unroll 4
+          for (int i = eid; i < n2; i += 256) s2[i] = __ldg(g2 + i);
+          for (int i = eid; i < P.N; i += 256) sv[i] = __ldg(P.se_bias + i);
+          for (int i = eid; i < P.se_k; i += 256) sv[P.N + i] = __ldg(P.se_b1 + i);
+          for (int i = eid; i < 2 * P.N; i += 256) sv[P.N + P.se_k + i] = __ldg(P.se_b2 + i);
+          se_layer = w.l;
         }
         if (!mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag, 4)) break;
         tcgen05_fence_after();
@@ -1213,7 +1241,7 @@ gemm_tc_tower_kernel(const TowerLayer* __restrict__ layers, int n_layers, int ro
         const float* se_row = nullptr;
         if (P.se_k > 0) {
           se_prepare<BN>(P, trow, quarter, group, lane, (int)threadIdx.x - 64, wvec_all, se_gb, smem_u32(se_bar), se_phase,
-                         abort_flag);
+                         abort_flag, se_in_smem ? se_w : nullptr);
           se_row = se_gb + (quarter >> 1) * 512;
         }
 #pragma unroll 1
