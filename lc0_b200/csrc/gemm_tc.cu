@@ -557,12 +557,13 @@ __device__ __forceinline__ void se_prepare(const TcParams& p, uint32_t trow, int
   // the whole dot product costs about one round trip.
   for (int o = eid >> 2; o < 2 * p.se_k; o += 64) {
     const int sidx = o / p.se_k, k = o - sidx * p.se_k;
-    const int cq = (eid & 3) * (C >> 2);
-    const float4* w = reinterpret_cast<const float4*>(g_w1 + (long long)k * C + cq);
-    const float4* x = reinterpret_cast<const float4*>(pool + sidx * 256 + cq);
+    // the four threads of an output take every fourth 16-byte piece of the row: consecutive addresses (no bank
+    // conflicts in shared memory, whole lines per quad in global memory)
+    const float4* w = reinterpret_cast<const float4*>(g_w1 + (long long)k * C) + (eid & 3);
+    const float4* x = reinterpret_cast<const float4*>(pool + sidx * 256) + (eid & 3);
     float a = 0.f;
 #pragma unroll 8
-    for (int i = 0; i < (C >> 4); ++i) {
+    for (int i = 0; i < (C >> 2); i += 4) {
       const float4 wv = ld4(w + i), xv = x[i];
       a = fmaf(wv.x, xv.x, fmaf(wv.y, xv.y, fmaf(wv.z, xv.z, fmaf(wv.w, xv.w, a))));
     }
@@ -576,11 +577,14 @@ __device__ __forceinline__ void se_prepare(const TcParams& p, uint32_t trow, int
     float z0a = ld(g_b2 + c), z1a = ld(g_b2 + C + c), z0b = z0a, z1b = z1a;
     const float4* w0 = reinterpret_cast<const float4*>(g_w2 + (long long)c * p.se_k);
     const float4* w1 = reinterpret_cast<const float4*>(g_w2 + (long long)(C + c) * p.se_k);
+    // in shared memory the 16-byte pieces of row r sit at position k ^ (r & 7) (eight or more pieces per row): thread c
+    // reads row c, and without the swizzle every lane of a warp would hit the same banks
+    const int swz = (w_smem && p.se_k >= 32) ? (c & 7) : 0;  // (C + c) & 7 == c & 7: C is a multiple of 16
     const float4* ha = reinterpret_cast<const float4*>(hid);
     const float4* hb = reinterpret_cast<const float4*>(hid + 64);
 #pragma unroll 8
     for (int k = 0; k < (p.se_k >> 2); ++k) {
-      const float4 a = ld4(w0 + k), b = ld4(w1 + k), xa = ha[k], xb = hb[k];
+      const float4 a = ld4(w0 + (k ^ swz)), b = ld4(w1 + (k ^ swz)), xa = ha[k], xb = hb[k];
       z0a = fmaf(a.x, xa.x, fmaf(a.y, xa.y, fmaf(a.z, xa.z, fmaf(a.w, xa.w, z0a))));
       z1a = fmaf(b.x, xa.x, fmaf(b.y, xa.y, fmaf(b.z, xa.z, fmaf(b.w, xa.w, z1a))));
       z0b = fmaf(a.x, xb.x, fmaf(a.y, xb.y, fmaf(a.z, xb.z, fmaf(a.w, xb.w, z0b))));
@@ -1225,8 +1229,12 @@ gemm_tc_tower_kernel(const TowerLayer* __restrict__ layers, int n_layers, int ro
           float4* s2 = s1 + n1;
           float* sv = se_w + 12 * n1;  // se_bias [N], se_b1 [se_k], se_b2 [2N]
           for (int i = eid; i < n1; i += 256) s1[i] = __ldg(g1 + i);
+          const int L = P.se_k >> 2;  // 16-byte pieces per row of se_w2; swizzled within the row (see se_prepare)
 #pragma unroll 4
-          for (int i = eid; i < n2; i += 256) s2[i] = __ldg(g2 + i);
+          for (int i = eid; i < n2; i += 256) {
+            const int r = i / L, k = i - r * L;
+            s2[r * L + (P.se_k >= 32 ? (k ^ (r & 7)) : k)] = __ldg(g2 + i);
+          }
           for (int i = eid; i < P.N; i += 256) sv[i] = __ldg(P.se_bias + i);
           for (int i = eid; i < P.se_k; i += 256) sv[P.N + i] = __ldg(P.se_b1 + i);
           for (int i = eid; i < 2 * P.N; i += 256) sv[P.N + P.se_k + i] = __ldg(P.se_b2 + i);
