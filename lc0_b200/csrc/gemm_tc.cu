@@ -515,15 +515,17 @@ __device__ __forceinline__ void epilogue_barrier(uint32_t bar, uint32_t& phase, 
 template <int BN>
 __device__ __forceinline__ void se_prepare(const TcParams& p, uint32_t trow, int quarter, int group, int lane, int eid,
                                            float* tmp, float* gb, uint32_t bar, uint32_t& phase,
-                                           volatile int* abort_flag, const float* w_smem = nullptr) {
-  // w_smem: se_w1 [se_k][C], se_w2 [2C][se_k], se_bias [C], se_b1 [se_k], se_b2 [2C] in shared memory, copied there
-  // while the tile was computed; otherwise they are read from global memory (a chain of five dependent round trips)
+                                           volatile int* abort_flag, const float* w_smem = nullptr,
+                                           const float* v_smem = nullptr) {
+  // w_smem: se_w1 [se_k][C] and se_w2 [2C][se_k]; v_smem: se_bias [C], se_b1 [se_k], se_b2 [2C]: copies in shared
+  // memory, made while the tile was computed.  What is not there is read from global memory, and each of the five
+  // is then one more round trip in a chain of dependent ones.
   const float* g_w1 = w_smem ? w_smem : p.se_w1;
   const float* g_w2 = w_smem ? g_w1 + p.se_k * p.N : p.se_w2;
-  const float* g_bias = w_smem ? g_w2 + 2 * p.N * p.se_k : p.se_bias;
-  const float* g_b1 = w_smem ? g_bias + p.N : p.se_b1;
-  const float* g_b2 = w_smem ? g_b1 + p.se_k : p.se_b2;
-  auto ld = [&](const float* q) { return w_smem ? *q : __ldg(q); };
+  const float* g_bias = v_smem ? v_smem : p.se_bias;
+  const float* g_b1 = v_smem ? g_bias + p.N : p.se_b1;
+  const float* g_b2 = v_smem ? g_b1 + p.se_k : p.se_b2;
+  auto ld = [&](const float* q) { return v_smem ? *q : __ldg(q); };
   auto ld4 = [&](const float4* q) { return w_smem ? *q : __ldg(q); };
   float* part = tmp;          // [4 quarters][256] column sums over 32 rows
   float* pool = tmp + 1024;   // [2][256]
@@ -705,7 +707,8 @@ template <int BN> struct TileCfg {
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int kEpiBytes = 4 * BM * 128;  // 2 groups x 2 staging buffers of 128 rows x 128 bytes
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 512 /*barriers*/ +
-                                    8192 /*per-warp column vectors*/ + 4096 /*squeeze-excitation gate and shift*/;
+                                    8192 /*per-warp column vectors*/ + 4096 /*squeeze-excitation gate and shift*/ +
+                                    4096 /*squeeze-excitation bias vectors*/;
 };
 
 
@@ -733,6 +736,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   float* wvec = wvec_all + ((threadIdx.x >> 5) & 7) * 256;                                  // per-warp scratch
   uint64_t* se_bar = reinterpret_cast<uint64_t*>(bar_mem + 384);    // barrier of the 256 epilogue threads
   float* se_gb = reinterpret_cast<float*>(bar_mem + 512 + 8192);    // [2 boards][gate 256 | shift 256]
+  float* se_vec = se_gb + 1024;                                     // se_bias [N], se_b1 [se_k], se_b2 [2N]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
@@ -845,6 +849,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint32_t tile_it = 0, slab_it = 0, se_phase = 0;
     ColRegs cr;
     int cr_nb = -1;  // first column of the slab whose vectors `cr` holds
+    bool se_vec_ok = false;
+    if constexpr (BN == 256) {
+      if (p.se_k > 0 && 3 * p.N + p.se_k <= 1024) {
+        // the squeeze-excitation bias vectors into shared memory while the first tile is computed (the first
+        // barrier of se_prepare orders these stores before the reads)
+        const int eid = (int)threadIdx.x - 64;
+        for (int i = eid; i < p.N; i += 256) se_vec[i] = __ldg(p.se_bias + i);
+        for (int i = eid; i < p.se_k; i += 256) se_vec[p.N + i] = __ldg(p.se_b1 + i);
+        for (int i = eid; i < 2 * p.N; i += 256) se_vec[p.N + p.se_k + i] = __ldg(p.se_b2 + i);
+        se_vec_ok = true;
+      }
+    }
     if ((int)blockIdx.x < tiles && ((int)blockIdx.x % n_tiles) * BN + group * 64 < p.N) {
       cr_nb = ((int)blockIdx.x % n_tiles) * BN + group * 64;  // first slab: fetched while the first tile is computed
       load_col_regs(p, cr_nb, lane, cr);
@@ -866,7 +882,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if constexpr (BN == 256) {
           if (p.se_k > 0) {  // one tile = two boards x all channels: the squeeze-excitation vectors of both boards
             se_prepare<BN>(p, trow, quarter, group, lane, (int)threadIdx.x - 64, wvec_all, se_gb, smem_u32(se_bar),
-                           se_phase, abort_flag);
+                           se_phase, abort_flag, nullptr, se_vec_ok ? se_vec : nullptr);
             se_row = se_gb + (quarter >> 1) * 512;
           }
         }
@@ -1249,7 +1265,7 @@ gemm_tc_tower_kernel(const TowerLayer* __restrict__ layers, int n_layers, int ro
         const float* se_row = nullptr;
         if (P.se_k > 0) {
           se_prepare<BN>(P, trow, quarter, group, lane, (int)threadIdx.x - 64, wvec_all, se_gb, smem_u32(se_bar), se_phase,
-                         abort_flag, se_in_smem ? se_w : nullptr);
+                         abort_flag, se_in_smem ? se_w : nullptr, se_in_smem ? se_w + 3 * P.se_k * P.N : nullptr);
           se_row = se_gb + (quarter >> 1) * 512;
         }
 #pragma unroll 1
@@ -1323,7 +1339,7 @@ template <int kGroupsT> struct PairCfg {
   static constexpr int kThreads = 128 + 128 * kGroupsT;
   static constexpr int kEpiBytes = kGroups * kBufs * BM * 128;
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 512 + 16 * 1024 /*column vectors*/ +
-                                    4096 /*squeeze-excitation gate and shift*/;
+                                    4096 /*squeeze-excitation gate and shift*/ + 4096 /*... bias vectors*/;
 };
 
 template <typename T, int kGroups>
@@ -1353,6 +1369,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   float* wvec = wvec_all + ((threadIdx.x >> 5) & 15) * 256;                                  // per-warp scratch
   uint64_t* se_bar = reinterpret_cast<uint64_t*>(bar_mem + 384);        // barrier of this CTA's epilogue threads
   float* se_gb = reinterpret_cast<float*>(bar_mem + 512 + 16 * 1024);   // [2 boards][gate 256 | shift 256]
+  float* se_vec = se_gb + 1024;                                         // se_bias [N], se_b1 [se_k], se_b2 [2N]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -1492,6 +1509,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint32_t tile_it = 0, slab_it = 0, se_phase = 0;
     ColRegs cr;
     int cr_nb = -1;
+    bool se_vec_ok = false;
+    if constexpr (kGroups == 2) {
+      if (p.se_k > 0 && 3 * p.N + p.se_k <= 1024) {
+        // the squeeze-excitation bias vectors into shared memory while the first tile is computed
+        const int eid = (int)threadIdx.x - 128;
+        for (int i = eid; i < p.N; i += 256) se_vec[i] = __ldg(p.se_bias + i);
+        for (int i = eid; i < p.se_k; i += 256) se_vec[p.N + i] = __ldg(p.se_b1 + i);
+        for (int i = eid; i < 2 * p.N; i += 256) se_vec[p.N + p.se_k + i] = __ldg(p.se_b2 + i);
+        se_vec_ok = true;
+      }
+    }
     if (pair < tiles && group * 64 < width_of(pair) && col_of(pair) + group * 64 < p.N) {
       cr_nb = col_of(pair) + group * 64;  // first slab: fetched while the first tile is computed
       load_col_regs(p, cr_nb, lane, cr);
@@ -1509,7 +1537,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if constexpr (kGroups == 2) {
         if (p.se_k > 0) {  // this CTA's 128 rows are two boards with all their channels
           se_prepare<BN>(p, trow, quarter, group, lane, (int)threadIdx.x - 128, wvec_all, se_gb, smem_u32(se_bar),
-                         se_phase, abort_flag);
+                         se_phase, abort_flag, nullptr, se_vec_ok ? se_vec : nullptr);
           se_row = se_gb + (quarter >> 1) * 512;
         }
       }
