@@ -86,7 +86,8 @@ enum {
    * tensor-core products, the reference GPU backend's decomposition) instead of the direct tensor-core convolution.
    * Off by default: a quarter of the multiplications, but about ten times the rounding error in 16-bit storage. */
   B200_FLAG_WINOGRAD = 64,
-  B200_FLAG_NO_SIDE_STREAM = 128,    /* smolgen's small dense layers in line instead of on a second stream beside the QKV product */
+  B200_FLAG_NO_SIDE_STREAM = 128,    /* smolgen's small dense layers in line instead of on a second stream beside the QKV
+                                      * product; value and moves-left heads in line instead of beside the policy head */
   /* Ordinary launches instead of programmatic dependent launches: by default the tensor-core products, the attention
    * kernel and the LayerNorms are launched so that a kernel's prologue (barrier set-up, tensor-memory allocation,
    * descriptor prefetch) runs under the tail of the kernel before it; each waits for its predecessors' results
